@@ -1,0 +1,456 @@
+"""Paged KV cache on CUDA tensors.
+
+Host-side mirror of easymlx ``caching/paged/cache.py``: ``PageCacheView``
+(``:499-1306``), ``PageCacheConfig`` / ``PageCache`` (``:1309-1445``),
+``build_query_start_loc`` (``:1448-1465``) and ``PageMetadata`` (``:1468-1543``) keep
+their names, arguments and return values.  The index arithmetic and the scatter of
+``concatenate_to_cache`` run in two CUDA kernels (``emlx_build_metadata``,
+``emlx_kv_write``) instead of host loops and fancy-index assignments; nothing here
+synchronises with the device.
+
+Storage modes: ``float16`` / ``bfloat16`` / ``float32`` pools in the reference layout
+``[num_blocks, block_size, num_kv_heads, head_dim]``, and affine group-64 pools with 8 or
+4 bits (``cache_dtype="affine8" | "affine4"`` or ``cache_bits=8 | 4``), which the reference
+does not have.  Its ``fp8`` and ``turboquant`` modes are not provided.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+import typing as tp
+from collections import OrderedDict
+from dataclasses import dataclass, field
+
+import torch
+
+from ... import _native as nv
+
+_CHECK = os.environ.get("EASYMLX_B200_CHECK", "0") not in ("", "0")
+QUANT_GROUP = 64
+
+_TORCH_DTYPES = {
+    "float16": torch.float16, "half": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32,
+    "torch.float16": torch.float16, "torch.bfloat16": torch.bfloat16, "torch.float32": torch.float32,
+}
+
+
+def _resolve_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        return dtype
+    name = getattr(dtype, "__name__", None) or str(dtype)
+    return _TORCH_DTYPES.get(name.replace("numpy.", "").replace("<class '", "").replace("'>", ""), torch.float16)
+
+
+def _resolve_bits(cache_dtype: str | None, cache_bits: int | None) -> int:
+    """0 for a float pool, 8 or 4 for an affine pool."""
+    mode = str(cache_dtype or "auto").lower()
+    if mode in ("fp8",) or mode.startswith("turboquant"):
+        raise NotImplementedError(f"cache_dtype={cache_dtype!r} is not provided; use float16/bfloat16/float32 or affine8/affine4")
+    if mode in ("affine", "affine8", "int8", "q8"):
+        bits = 8 if mode != "affine" else int(cache_bits or 8)
+    elif mode in ("affine4", "int4", "q4"):
+        bits = 4
+    else:
+        return 0
+    if bits not in (4, 8):
+        raise ValueError("affine KV supports 8 or 4 bits")
+    return bits
+
+
+class _DeviceIntCache:
+    """Small LRU of host integer tuples already uploaded (the reference keeps an LRU of 64 start-location
+    arrays for the same reason, ``inference/esurge/runners/model_runner.py:559-570``)."""
+
+    def __init__(self, capacity: int = 64):
+        self.capacity = capacity
+        self.items: OrderedDict = OrderedDict()
+
+    def get(self, values: tuple[int, ...], device) -> torch.Tensor:
+        key = (values, str(device))
+        hit = self.items.get(key)
+        if hit is not None:
+            self.items.move_to_end(key)
+            return hit
+        t = torch.tensor(values, dtype=torch.int32).pin_memory().to(device, non_blocking=True) if values else \
+            torch.zeros(0, dtype=torch.int32, device=device)
+        self.items[key] = t
+        if len(self.items) > self.capacity:
+            self.items.popitem(last=False)
+        return t
+
+
+_uploaded = _DeviceIntCache()
+
+
+def build_query_start_loc(query_lens: tp.Iterable[int], device=None) -> torch.Tensor:
+    """``[0, q0, q0+q1, ...]`` as int32 (host prefix sum, like the reference; the packed-batch path
+    builds the same array on the GPU inside ``concatenate_to_cache``)."""
+    offsets = [0]
+    for n in query_lens:
+        offsets.append(offsets[-1] + int(n))
+    return torch.tensor(offsets, dtype=torch.int32, device=device)
+
+
+@dataclass
+class PageMetadata:
+    """Kernel-agnostic paged-attention metadata; same fields as the reference's dataclass."""
+
+    query_start_loc: tp.Any
+    block_tables: tp.Any | None = None
+    kv_lens: tp.Any | None = None
+    block_size: int | None = None
+    sliding_window: int | None = None
+    is_single_token_decode: bool = False
+    slot_ids: tuple[int, ...] | None = None
+    # filled by concatenate_to_cache: upper bound of query tokens per sequence known on the host (0 = unknown)
+    max_query_len: int = field(default=0, compare=False)
+
+    def with_cache_state(self, *, block_tables, kv_lens, block_size: int) -> "PageMetadata":
+        return PageMetadata(
+            query_start_loc=self.query_start_loc, block_tables=block_tables, kv_lens=kv_lens,
+            block_size=int(block_size), sliding_window=self.sliding_window,
+            is_single_token_decode=self.is_single_token_decode, slot_ids=self.slot_ids,
+            max_query_len=self.max_query_len,
+        )
+
+    def with_sliding_window(self, sliding_window: int | None) -> "PageMetadata":
+        return PageMetadata(
+            query_start_loc=self.query_start_loc, block_tables=self.block_tables, kv_lens=self.kv_lens,
+            block_size=self.block_size, sliding_window=sliding_window,
+            is_single_token_decode=self.is_single_token_decode, slot_ids=self.slot_ids,
+            max_query_len=self.max_query_len,
+        )
+
+
+class PageCacheView:
+    """Block-table based KV cache backed by CUDA tensors.
+
+    ``key_cache`` / ``value_cache``: ``[num_blocks, block_size, num_kv_heads, head_dim]`` for float pools.
+    Affine pools (``cache_bits`` 8 or 4) hold bytes instead: keys ``[NB, bs, Hkv, D*bits/8]``, values
+    ``[NB, Hkv, D, bs*bits/8]`` and fp16 ``k_scales/k_biases/v_scales/v_biases [NB, Hkv, bs, D/64]``.
+    ``block_tables [num_seqs, blocks_per_seq]`` and ``kv_lens [num_seqs]`` are int32; the runner writes
+    them directly, as it does in the reference (``inference/esurge/runners/model_runner.py:1127-1131``).
+    """
+
+    def __init__(self, *, key_cache, value_cache, block_tables, kv_lens, block_size: int, num_kv_heads: int,
+                 head_dim: int, page_key_cache=None, page_value_cache=None, page_vec_size: int | None = None,
+                 cache_dtype_is_fp8: bool = False, k_scales=None, v_scales=None, k_biases=None, v_biases=None,
+                 cache_bits: int = 0) -> None:
+        if cache_dtype_is_fp8:
+            raise NotImplementedError("fp8 KV pools are not provided")
+        if page_key_cache is not None or page_value_cache is not None:
+            raise NotImplementedError("the packed side caches of the PageAttention runtime are not provided")
+        self.key_cache, self.value_cache = key_cache, value_cache
+        self.block_tables, self.kv_lens = block_tables, kv_lens
+        self.block_size, self.num_kv_heads, self.head_dim = int(block_size), int(num_kv_heads), int(head_dim)
+        self.page_key_cache = self.page_value_cache = None
+        self.page_vec_size = 0
+        self.cache_dtype_is_fp8 = False
+        self.k_scales, self.v_scales, self.k_biases, self.v_biases = k_scales, v_scales, k_biases, v_biases
+        self.cache_bits = int(cache_bits)
+        self._status: torch.Tensor | None = None
+        self._validate_shape()
+
+    # ------------------------------------------------------------------ geometry
+    @property
+    def cache(self) -> "PageCacheView":
+        return self
+
+    @property
+    def blocks_per_seq(self) -> int:
+        return int(self.block_tables.shape[1])
+
+    @property
+    def num_seqs(self) -> int:
+        return int(self.block_tables.shape[0])
+
+    @property
+    def max_seq_len(self) -> int:
+        return self.blocks_per_seq * self.block_size
+
+    @property
+    def num_blocks(self) -> int:
+        return int(self.key_cache.shape[0])
+
+    @property
+    def is_affine(self) -> bool:
+        return self.cache_bits in (4, 8)
+
+    @property
+    def status(self) -> torch.Tensor:
+        """Device word the kernels OR their validation bits into (see ``check``)."""
+        if self._status is None:
+            self._status = torch.zeros(1, dtype=torch.int32, device=self.key_cache.device)
+        return self._status
+
+    def check(self) -> None:
+        """Synchronise and raise if any kernel that used this cache flagged a bad slot / page / overflow."""
+        nv.check(nv.lib().emlx_read_status(nv.ptr(self.status), nv.stream_ptr(self.key_cache.device)))
+
+    def _validate_shape(self) -> None:
+        if self.block_tables.ndim != 2:
+            raise ValueError("block_tables must be rank-2: [num_seqs, blocks_per_seq]")
+        if self.kv_lens.ndim != 1:
+            raise ValueError("kv_lens must be rank-1: [num_seqs]")
+        if self.key_cache.ndim != 4 or self.value_cache.ndim != 4:
+            raise ValueError("key_cache/value_cache must be rank-4.")
+        num_seqs, blocks_per_seq = self.block_tables.shape
+        if self.kv_lens.shape[0] != num_seqs:
+            raise ValueError("kv_lens length must match block_tables first dimension.")
+        nb, bs, hkv, d = self.key_cache.shape[0], self.block_size, self.num_kv_heads, self.head_dim
+        if self.is_affine:
+            bits = self.cache_bits
+            if d % QUANT_GROUP or bs % 8:
+                raise ValueError("affine KV needs head_dim % 64 == 0 and block_size % 8 == 0")
+            if tuple(self.key_cache.shape) != (nb, bs, hkv, d * bits // 8) or self.key_cache.dtype != torch.uint8:
+                raise ValueError("affine key_cache must be uint8 [num_blocks, block_size, num_kv_heads, head_dim*bits/8]")
+            if tuple(self.value_cache.shape) != (nb, hkv, d, bs * bits // 8) or self.value_cache.dtype != torch.uint8:
+                raise ValueError("affine value_cache must be uint8 [num_blocks, num_kv_heads, head_dim, block_size*bits/8]")
+            for t in (self.k_scales, self.k_biases, self.v_scales, self.v_biases):
+                if t is None or tuple(t.shape) != (nb, hkv, bs, d // QUANT_GROUP) or t.dtype != torch.float16:
+                    raise ValueError("affine scale/bias must be float16 [num_blocks, num_kv_heads, block_size, head_dim/64]")
+        else:
+            if self.key_cache.shape != self.value_cache.shape:
+                raise ValueError("key_cache and value_cache must have the same shape.")
+            if self.key_cache.shape[1] != bs:
+                raise ValueError("key_cache block size does not match block_size.")
+            if self.key_cache.shape[2] != hkv:
+                raise ValueError("key_cache num_kv_heads does not match configured value.")
+            if self.key_cache.shape[3] != d:
+                raise ValueError("key_cache head_dim does not match configured value.")
+
+    # ------------------------------------------------------------------ allocation
+    @classmethod
+    def init(cls, *, num_seqs: int, max_seq_len: int, num_kv_heads: int, head_dim: int, block_size: int = 16,
+             dtype=torch.float16, cache_dtype: str | None = None, cache_bits: int | None = None,
+             device=None, num_blocks: int | None = None) -> "PageCacheView":
+        """Zeroed pool with the reference's contiguous table: slot ``i`` owns pages
+        ``[i*blocks_per_seq, (i+1)*blocks_per_seq)`` (``caching/paged/cache.py:779-791``).  ``num_blocks``
+        overrides the pool size for callers that manage page ids themselves."""
+        if num_seqs <= 0:
+            raise ValueError("num_seqs must be positive")
+        if max_seq_len <= 0:
+            raise ValueError("max_seq_len must be positive")
+        if block_size <= 0:
+            raise ValueError("block_size must be positive")
+        device = torch.device(device if device is not None else "cuda")
+        bits = _resolve_bits(cache_dtype, cache_bits)
+        mode = str(cache_dtype or "auto").lower()
+        pool_dtype = _TORCH_DTYPES.get(mode, _resolve_dtype(dtype))
+        blocks_per_seq = math.ceil(max_seq_len / block_size)
+        nb = int(num_blocks) if num_blocks is not None else blocks_per_seq * num_seqs
+        tables = torch.arange(blocks_per_seq * num_seqs, dtype=torch.int32, device=device).reshape(num_seqs, blocks_per_seq)
+        kv_lens = torch.zeros(num_seqs, dtype=torch.int32, device=device)
+        extra: dict = {}
+        if bits:
+            kc = torch.zeros((nb, block_size, num_kv_heads, head_dim * bits // 8), dtype=torch.uint8, device=device)
+            vc = torch.zeros((nb, num_kv_heads, head_dim, block_size * bits // 8), dtype=torch.uint8, device=device)
+            sb = (nb, num_kv_heads, block_size, head_dim // QUANT_GROUP)
+            extra = dict(k_scales=torch.zeros(sb, dtype=torch.float16, device=device),
+                         k_biases=torch.zeros(sb, dtype=torch.float16, device=device),
+                         v_scales=torch.zeros(sb, dtype=torch.float16, device=device),
+                         v_biases=torch.zeros(sb, dtype=torch.float16, device=device), cache_bits=bits)
+        else:
+            kc = torch.zeros((nb, block_size, num_kv_heads, head_dim), dtype=pool_dtype, device=device)
+            vc = torch.zeros_like(kc)
+        return cls(key_cache=kc, value_cache=vc, block_tables=tables, kv_lens=kv_lens, block_size=block_size,
+                   num_kv_heads=num_kv_heads, head_dim=head_dim, **extra)
+
+    allocate = init
+
+    def can_append(self, seq_idx: int, num_new_tokens: int) -> bool:
+        if num_new_tokens < 0:
+            raise ValueError("num_new_tokens must be non-negative.")
+        if seq_idx < 0 or seq_idx >= self.num_seqs:
+            raise IndexError(f"Invalid seq_idx {seq_idx}")
+        return int(self.kv_lens[seq_idx].item()) + int(num_new_tokens) <= self.max_seq_len
+
+    # ------------------------------------------------------------------ native descriptors
+    def native_pool(self) -> nv.Pool:
+        p = nv.Pool()
+        p.key_cache, p.value_cache = self.key_cache.data_ptr(), self.value_cache.data_ptr()
+        if self.is_affine:
+            p.k_scale, p.k_bias = self.k_scales.data_ptr(), self.k_biases.data_ptr()
+            p.v_scale, p.v_bias = self.v_scales.data_ptr(), self.v_biases.data_ptr()
+            p.kv_format, p.kv_dtype = self.cache_bits, nv.F16
+        else:
+            p.kv_format, p.kv_dtype = nv.KV_FLOAT, nv.dtype_code(self.key_cache.dtype)
+        p.num_blocks, p.block_size = self.num_blocks, self.block_size
+        p.num_kv_heads, p.head_dim = self.num_kv_heads, self.head_dim
+        return p
+
+    # ------------------------------------------------------------------ writes
+    def _write_batch(self, keys: torch.Tensor, values: torch.Tensor, query_lens_dev: torch.Tensor,
+                     slots_dev: torch.Tensor, total_tokens: int):
+        """Metadata kernel + write kernel for one packed batch.  Returns ``(qsl, block_tables, kv_lens)``
+        of the scheduled rows; ``self.kv_lens`` is advanced in place."""
+        nv.require_cuda(keys, values, self.key_cache)
+        dev = self.key_cache.device
+        lib, stream = nv.lib(), nv.stream_ptr(dev)
+        s = int(slots_dev.shape[0])
+        qsl = torch.empty(s + 1, dtype=torch.int32, device=dev)
+        bt = torch.empty((s, self.blocks_per_seq), dtype=torch.int32, device=dev)
+        lens = torch.empty(s, dtype=torch.int32, device=dev)
+        slot_mapping = torch.empty(max(total_tokens, 1), dtype=torch.int64, device=dev)
+        if self.block_tables.dtype != torch.int32 or self.kv_lens.dtype != torch.int32:
+            raise ValueError("block_tables and kv_lens must be int32")
+        if not (self.block_tables.is_contiguous() and self.kv_lens.is_contiguous()):
+            raise ValueError("block_tables and kv_lens must be contiguous")
+        nv.check(lib.emlx_build_metadata(
+            nv.ptr(query_lens_dev), nv.ptr(slots_dev), s, total_tokens, nv.ptr(self.block_tables), self.num_seqs,
+            self.blocks_per_seq, nv.ptr(self.kv_lens), self.block_size, 1, nv.ptr(qsl), nv.ptr(bt), nv.ptr(lens),
+            nv.ptr(slot_mapping), self.num_blocks, nv.ptr(self.status), stream))
+        if total_tokens > 0:
+            if keys.shape != values.shape:
+                raise ValueError("key and value must have the same shape")
+            if keys.ndim != 3 or keys.shape[1] != self.num_kv_heads or keys.shape[2] != self.head_dim:
+                raise ValueError("key/value must be [num_tokens, num_kv_heads, head_dim] matching the cache")
+            if keys.dtype != values.dtype:
+                raise ValueError("key and value must have the same dtype")
+            keys, values = keys.contiguous(), values.contiguous()
+            pool = self.native_pool()
+            nv.check(lib.emlx_kv_write(nv.ptr(keys), nv.ptr(values), nv.dtype_code(keys.dtype), total_tokens,
+                                       nv.ptr(slot_mapping), pool, nv.ptr(self.status), stream))
+        if _CHECK:
+            self.check()
+        return qsl, bt, lens
+
+    def append(self, seq_idx: int, key: torch.Tensor, value: torch.Tensor) -> None:
+        """Append ``[num_tokens, num_kv_heads, head_dim]`` rows to one slot (``cache.py:834-872``)."""
+        if key.shape != value.shape:
+            raise ValueError("key and value must have the same shape")
+        if key.ndim != 3:
+            raise ValueError("key/value must be rank-3: [num_tokens, num_kv_heads, head_dim]")
+        if key.shape[1] != self.num_kv_heads or key.shape[2] != self.head_dim:
+            raise ValueError("key/value head dims do not match cache")
+        if seq_idx < 0 or seq_idx >= self.num_seqs:
+            raise IndexError(f"Invalid seq_idx {seq_idx}")
+        n = int(key.shape[0])
+        dev = self.key_cache.device
+        self._write_batch(key, value, _uploaded.get((n,), dev), _uploaded.get((int(seq_idx),), dev), n)
+
+    def reset(self, seq_idx: int) -> None:
+        """Zero a slot's length.  (The reference also zero-fills the slot's pages; stale rows beyond
+        ``kv_lens`` are never read by the kernels, so only the length is reset here.)"""
+        if seq_idx < 0 or seq_idx >= self.num_seqs:
+            raise IndexError(f"Invalid seq_idx {seq_idx}")
+        self.kv_lens[seq_idx] = 0
+
+    def reset_batch(self, seq_indices: tp.Sequence[int]) -> None:
+        for i in seq_indices:
+            self.reset(int(i))
+
+    def clear(self, seq_idx: int | None = None) -> None:
+        if seq_idx is None:
+            self.kv_lens.zero_()
+            return
+        self.reset(int(seq_idx))
+
+    def clear_many(self, seq_indices: tp.Iterable[int]) -> None:
+        for i in seq_indices:
+            self.reset(int(i))
+
+    def concatenate_to_cache(self, queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, *,
+                             cache_metadata: tp.Any, rope: tp.Any = None,
+                             slot_ids: tp.Sequence[int] | None = None,
+                             query_lens: tp.Sequence[int] | None = None):
+        """Append the batch's K/V to the pool and resolve the metadata (``cache.py:1088-1306``).
+
+        Returns ``(prepared_queries, key_cache, value_cache, resolved_metadata)``; the metadata carries the
+        scheduled slots' page-table rows and their lengths after the write.  ``slot_ids`` and
+        ``query_lens`` are host sequences, as in the reference; when ``query_lens`` is omitted the lengths
+        are derived on the device from ``cache_metadata.query_start_loc``.
+        """
+        if rope is not None:
+            raise NotImplementedError("RoPE inside the cache write is not provided yet; rotate q/k before the call")
+        if slot_ids is None:
+            slot_ids = getattr(cache_metadata, "slot_ids", None) or ()
+        slots = tuple(int(s) for s in slot_ids)
+        dev = self.key_cache.device
+        total = int(queries.shape[0])
+        max_q = 0
+        if query_lens is not None:
+            qlens = tuple(max(0, int(q)) for q in query_lens)
+            qlens_dev = _uploaded.get(qlens, dev)
+            max_q = max(qlens, default=0)
+            single = bool(qlens) and total == len(qlens) and max_q == 1 and min(qlens) == 1
+        else:
+            qsl_in = cache_metadata.query_start_loc
+            if not isinstance(qsl_in, torch.Tensor):
+                qsl_in = torch.as_tensor(list(qsl_in), dtype=torch.int32)
+                qlens = tuple(int(x) for x in (qsl_in[1:] - qsl_in[:-1]).tolist())[: len(slots)]
+                qlens_dev = _uploaded.get(tuple(max(0, q) for q in qlens), dev)
+                max_q = max(qlens, default=0)
+                single = bool(qlens) and total == len(qlens) and all(q == 1 for q in qlens)
+            else:
+                qlens_dev = (qsl_in[1:len(slots) + 1] - qsl_in[:len(slots)]).to(device=dev, dtype=torch.int32).contiguous()
+                single = bool(getattr(cache_metadata, "is_single_token_decode", False)) and total == len(slots)
+                max_q = 1 if single else 0
+        qsl, bt, lens = self._write_batch(keys, values, qlens_dev, _uploaded.get(slots, dev), total)
+        meta = PageMetadata(
+            query_start_loc=qsl, sliding_window=getattr(cache_metadata, "sliding_window", None),
+            is_single_token_decode=bool(getattr(cache_metadata, "is_single_token_decode", False)) or single,
+            slot_ids=getattr(cache_metadata, "slot_ids", None) or slots, max_query_len=max_q,
+        ).with_cache_state(block_tables=bt, kv_lens=lens, block_size=self.block_size)
+        return queries, self.key_cache, self.value_cache, meta
+
+
+class PageCacheConfig:
+    """Static configuration of a multi-layer paged cache (``cache.py:1309-1375``)."""
+
+    def __init__(self, *, num_hidden_layers: int, num_kv_heads: int, head_dim: int, page_size: int = 16,
+                 max_num_reqs: int = 4, max_model_length: int = 4096, memory_utilization: float = 0.85,
+                 dtype=torch.float16, cache_dtype: str | None = None, cache_bits: int | None = None,
+                 device=None) -> None:
+        self.num_hidden_layers, self.num_kv_heads, self.head_dim = int(num_hidden_layers), int(num_kv_heads), int(head_dim)
+        self.page_size, self.max_num_reqs, self.max_model_length = int(page_size), int(max_num_reqs), int(max_model_length)
+        self.memory_utilization = float(memory_utilization)
+        self.dtype, self.cache_dtype = dtype, cache_dtype
+        self.cache_bits = int(cache_bits) if cache_bits is not None else None
+        self.device = device
+
+    @property
+    def num_pages(self) -> int:
+        return math.ceil(self.max_model_length / self.page_size) * self.max_num_reqs
+
+    @classmethod
+    def create(cls, **kwargs) -> "PageCacheConfig":
+        return cls(**kwargs)
+
+
+class PageCache:
+    """One ``PageCacheView`` per layer (``cache.py:1378-1445``)."""
+
+    def __init__(self, views: list[PageCacheView], config: PageCacheConfig | None = None) -> None:
+        self.views, self.config = views, config
+
+    def __getitem__(self, index: int) -> PageCacheView:
+        return self.views[index]
+
+    def __setitem__(self, index: int, view: PageCacheView) -> None:
+        self.views[index] = view
+
+    def __len__(self) -> int:
+        return len(self.views)
+
+    def __iter__(self):
+        return iter(self.views)
+
+    @classmethod
+    def init_cache(cls, config: PageCacheConfig) -> "PageCache":
+        views = [
+            PageCacheView.init(num_seqs=config.max_num_reqs, max_seq_len=config.max_model_length,
+                               num_kv_heads=config.num_kv_heads, head_dim=config.head_dim,
+                               block_size=config.page_size, dtype=config.dtype, cache_dtype=config.cache_dtype,
+                               cache_bits=config.cache_bits, device=config.device)
+            for _ in range(config.num_hidden_layers)
+        ]
+        return cls(views=views, config=config)
+
+    def clear(self) -> None:
+        for view in self.views:
+            view.clear()
+
+
+__all__ = ("PageCache", "PageCacheConfig", "PageCacheView", "PageMetadata", "build_query_start_loc")

@@ -1,0 +1,150 @@
+// Reference-semantics ragged paged attention for any geometry: head_dim <= 256, any page size,
+// fp16/bf16/fp32 queries and pools, affine pools.  One warp per (packed token, q head) walks the
+// keys of its causal range with an fp32 online softmax.  This is the coverage kernel; the tiled
+// kernels in attn_tiled.cu are the fast path for page size 128 and head_dim 64/128.
+#include "common.cuh"
+
+namespace emlx {
+
+int validate_pool(const emlx_pool* pool);
+
+constexpr int kMaxHeadDim = 256;
+constexpr int kPerLane = kMaxHeadDim / 32;
+
+struct PoolView {
+    emlx_pool p;
+    __device__ __forceinline__ float key(int64_t page, int off, int h, int d) const {
+        const int D = p.head_dim, Hkv = p.num_kv_heads, bs = p.block_size;
+        if (p.kv_format == EMLX_KV_FLOAT) {
+            const int64_t i = ((page * bs + off) * Hkv + h) * D + d;
+            if (p.kv_dtype == EMLX_F16) return __half2float(((const __half*)p.key_cache)[i]);
+            if (p.kv_dtype == EMLX_BF16) return __bfloat162float(((const __nv_bfloat16*)p.key_cache)[i]);
+            return ((const float*)p.key_cache)[i];
+        }
+        const int bits = p.kv_format;
+        const uint8_t* row = (const uint8_t*)p.key_cache + ((page * bs + off) * Hkv + h) * (int64_t)(D * bits / 8);
+        const int code = bits == 8 ? row[d] : ((row[d >> 1] >> ((d & 1) * 4)) & 0xF);
+        const int64_t sb = ((page * Hkv + h) * bs + off) * (D / kQuantGroup) + d / kQuantGroup;
+        return __fadd_rn(__fmul_rn(__half2float(((const __half*)p.k_scale)[sb]), (float)code),
+                         __half2float(((const __half*)p.k_bias)[sb]));
+    }
+    __device__ __forceinline__ float value(int64_t page, int off, int h, int d) const {
+        const int D = p.head_dim, Hkv = p.num_kv_heads, bs = p.block_size;
+        if (p.kv_format == EMLX_KV_FLOAT) {
+            const int64_t i = ((page * bs + off) * Hkv + h) * D + d;
+            if (p.kv_dtype == EMLX_F16) return __half2float(((const __half*)p.value_cache)[i]);
+            if (p.kv_dtype == EMLX_BF16) return __bfloat162float(((const __nv_bfloat16*)p.value_cache)[i]);
+            return ((const float*)p.value_cache)[i];
+        }
+        const int bits = p.kv_format;
+        const uint8_t* col = (const uint8_t*)p.value_cache + ((page * Hkv + h) * D + d) * (int64_t)(bs * bits / 8);
+        const int code = bits == 8 ? col[off] : ((col[off >> 1] >> ((off & 1) * 4)) & 0xF);
+        const int64_t sb = ((page * Hkv + h) * bs + off) * (D / kQuantGroup) + d / kQuantGroup;
+        return __fadd_rn(__fmul_rn(__half2float(((const __half*)p.v_scale)[sb]), (float)code),
+                         __half2float(((const __half*)p.v_bias)[sb]));
+    }
+};
+
+template <typename TQ>
+__global__ void __launch_bounds__(128) attn_generic_kernel(emlx_attn_args a, PoolView pv) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int Hq = a.num_q_heads, D = pv.p.head_dim, Hkv = pv.p.num_kv_heads, bs = pv.p.block_size;
+    if (warp >= (int64_t)a.total_tokens * Hq) return;
+    const int token = (int)(warp / Hq), head = (int)(warp - (int64_t)token * Hq);
+    const int kvh = head / (Hq / Hkv);
+    TQ* out = (TQ*)a.out + ((int64_t)token * Hq + head) * D;
+
+    float acc[kPerLane], q[kPerLane];
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) acc[j] = 0.f;
+
+    const int s = find_sequence(a.query_start_loc, a.num_seqs, token);
+    int start_k = 0, max_k = -1;
+    if (s >= 0) {
+        const int q0 = a.query_start_loc[s], q_len = a.query_start_loc[s + 1] - q0, kv_len = a.kv_lens[s];
+        if (kv_len > 0) {
+            max_k = min(kv_len - 1, (kv_len - q_len) + (token - q0));
+            if (a.sliding_window > 0) start_k = max(0, max_k - a.sliding_window + 1);
+        }
+    }
+    const TQ* qrow = (const TQ*)a.queries + ((int64_t)token * Hq + head) * D;
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+        const int d = lane + 32 * j;
+        q[j] = d < D ? __fmul_rn(to_f32<TQ>(qrow[d]), a.softmax_scale) : 0.f;
+    }
+
+    float m = -INFINITY, l = 0.f;
+    const int32_t* table = a.block_tables + (int64_t)max(s, 0) * a.max_blocks_per_seq;
+    for (int k = start_k; k <= max_k; ++k) {
+        const int page_idx = k / bs, off = k - page_idx * bs;
+        const int64_t page = page_idx < a.max_blocks_per_seq ? table[page_idx] : -1;
+        const bool live = page >= 0 && page < pv.p.num_blocks;  // an unassigned page reads as zero rows
+        if (!live && lane == 0) flag_error(a.status, EMLX_DEV_BAD_PAGE);
+        float dot = 0.f;
+        if (live) {
+#pragma unroll
+            for (int j = 0; j < kPerLane; ++j) {
+                const int d = lane + 32 * j;
+                if (d < D) dot = fmaf(q[j], pv.key(page, off, kvh, d), dot);
+            }
+        }
+        dot = warp_sum(dot);
+        const float m_new = fmaxf(m, dot);
+        const float corr = expf(m - m_new), p = expf(dot - m_new);
+        l = fmaf(l, corr, p);
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j) {
+            const int d = lane + 32 * j;
+            const float v = (live && d < D) ? pv.value(page, off, kvh, d) : 0.f;
+            acc[j] = fmaf(acc[j], corr, p * v);
+        }
+        m = m_new;
+    }
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+#pragma unroll
+    for (int j = 0; j < kPerLane; ++j) {
+        const int d = lane + 32 * j;
+        if (d < D) out[d] = from_f32<TQ>(acc[j] * inv);
+    }
+}
+
+int validate_attn(const emlx_attn_args* a, const emlx_pool* pool, bool need_plan) {
+    if (!a) return fail(EMLX_ERR_INVALID, "attention args are NULL");
+    if (int rc = validate_pool(pool)) return rc;
+    if (a->total_tokens < 0 || a->num_seqs < 0) return fail(EMLX_ERR_INVALID, "total_tokens/num_seqs must be non-negative");
+    if (a->num_q_heads <= 0 || a->num_q_heads % pool->num_kv_heads)
+        return fail(EMLX_ERR_INVALID, "num_q_heads must be divisible by num_kv_heads (GQA)");
+    if (a->q_dtype < EMLX_F16 || a->q_dtype > EMLX_F32) return fail(EMLX_ERR_INVALID, "unknown q_dtype");
+    if (a->total_tokens > 0) {
+        if (!a->queries || !a->out) return fail(EMLX_ERR_INVALID, "queries/out is NULL");
+        if (!a->query_start_loc) return fail(EMLX_ERR_INVALID, "query_start_loc is NULL");
+        if (a->num_seqs > 0 && (!a->block_tables || !a->kv_lens || a->max_blocks_per_seq <= 0))
+            return fail(EMLX_ERR_INVALID, "block_tables/kv_lens missing");
+    }
+    if (need_plan && a->total_tokens > 0 && (!a->plan || !a->workspace))
+        return fail(EMLX_ERR_WORKSPACE, "plan and workspace are required");
+    return EMLX_OK;
+}
+
+}  // namespace emlx
+
+extern "C" int emlx_attn_generic(const emlx_attn_args* args, const emlx_pool* pool, void* stream) {
+    using namespace emlx;
+    if (int rc = validate_attn(args, pool, false)) return rc;
+    if (pool->head_dim > kMaxHeadDim) return fail(EMLX_ERR_UNSUPPORTED, "head_dim %d > %d", pool->head_dim, kMaxHeadDim);
+    if (args->total_tokens == 0) return EMLX_OK;
+    PoolView pv{*pool};
+    const int64_t warps = (int64_t)args->total_tokens * args->num_q_heads;
+    const int threads = 128;
+    const unsigned blocks = (unsigned)((warps * 32 + threads - 1) / threads);
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (args->q_dtype) {
+        case EMLX_F16: attn_generic_kernel<__half><<<blocks, threads, 0, s>>>(*args, pv); break;
+        case EMLX_BF16: attn_generic_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>(*args, pv); break;
+        default: attn_generic_kernel<float><<<blocks, threads, 0, s>>>(*args, pv); break;
+    }
+    EMLX_LAUNCHED();
+    return EMLX_OK;
+}

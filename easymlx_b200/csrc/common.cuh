@@ -1,0 +1,91 @@
+// Shared host/device helpers for the paged-attention kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "../../include/easymlx_b200.h"
+
+namespace emlx {
+
+// ---------------------------------------------------------------- host side: errors, accounting
+void set_error(const char* fmt, ...);
+int fail(int code, const char* fmt, ...);
+extern std::atomic<int64_t> g_launches;
+
+#define EMLX_CUDA_OK(expr)                                                                     \
+    do {                                                                                       \
+        cudaError_t _e = (expr);                                                               \
+        if (_e != cudaSuccess)                                                                 \
+            return ::emlx::fail(EMLX_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                 \
+                                cudaGetErrorString(_e), __FILE__, __LINE__);                   \
+    } while (0)
+
+#define EMLX_LAUNCHED()                                                                        \
+    do {                                                                                       \
+        ::emlx::g_launches.fetch_add(1, std::memory_order_relaxed);                            \
+        EMLX_CUDA_OK(cudaGetLastError());                                                      \
+    } while (0)
+
+inline int num_sms() {
+    static int cached = 0;
+    if (!cached) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
+    }
+    return cached;
+}
+
+constexpr int kQuantGroup = 64;
+
+// ---------------------------------------------------------------- device side
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+
+__device__ __forceinline__ void flag_error(int32_t* status, int bits) {
+    if (status) atomicOr(status, bits);
+}
+
+// Largest s in [0, n) with loc[s] <= token < loc[s+1] for a non-decreasing loc[0..n]; rows of
+// zero length are skipped.  Returns -1 when token is outside [loc[0], loc[n]).
+__device__ __forceinline__ int find_sequence(const int32_t* __restrict__ loc, int n, int token) {
+    if (n <= 0 || token < loc[0] || token >= loc[n]) return -1;
+    int lo = 0, hi = n;  // invariant: loc[lo] <= token < loc[hi]
+    while (hi - lo > 1) {
+        int mid = (lo + hi) >> 1;
+        if (loc[mid] <= token) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+__device__ __forceinline__ float warp_min(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+}  // namespace emlx

@@ -1,0 +1,158 @@
+// Paged KV write: scatter the new K/V rows of one packed batch into the page pool, either as
+// plain 16/32-bit rows or as affine group-64 codes (8 or 4 bits) with fp16 scale and bias.
+// One warp per (token, kv head); HBM-bound, a few MB per batch.
+#include "common.cuh"
+
+namespace emlx {
+
+struct WriteParams {
+    const void* keys;
+    const void* values;
+    const int64_t* slot_mapping;
+    emlx_pool pool;
+    int T;
+    int32_t* status;
+};
+
+template <typename TIn, typename TOut>
+__device__ __forceinline__ void copy_row(const TIn* __restrict__ src, TOut* __restrict__ dst, int D, int lane) {
+    for (int d = lane; d < D; d += 32) dst[d] = from_f32<TOut>(to_f32<TIn>(src[d]));
+}
+
+template <typename TIn>
+__device__ __forceinline__ void write_float_row(const TIn* src, void* cache, int kv_dtype, int64_t elem_off, int D,
+                                                int lane) {
+    if (kv_dtype == EMLX_F16) copy_row(src, (__half*)cache + elem_off, D, lane);
+    else if (kv_dtype == EMLX_BF16) copy_row(src, (__nv_bfloat16*)cache + elem_off, D, lane);
+    else copy_row(src, (float*)cache + elem_off, D, lane);
+}
+
+// Quantise one group of 64 elements held two per lane.  Arithmetic is spelled with the
+// round-to-nearest intrinsics so that no contraction or fast-math option can change the codes.
+template <int BITS>
+__device__ __forceinline__ void quantize_group(float x0, float x1, int& c0, int& c1, __half& scale_h, __half& bias_h) {
+    const float levels = (float)((1 << BITS) - 1);
+    float lo = warp_min(fminf(x0, x1));
+    float hi = warp_max(fmaxf(x0, x1));
+    scale_h = __float2half_rn(__fdiv_rn(__fsub_rn(hi, lo), levels));
+    if (__half2float(scale_h) == 0.0f) scale_h = __float2half_rn(1.0f);
+    bias_h = __float2half_rn(lo);
+    const float s = __half2float(scale_h), b = __half2float(bias_h);
+    float q0 = rintf(__fdiv_rn(__fsub_rn(x0, b), s));
+    float q1 = rintf(__fdiv_rn(__fsub_rn(x1, b), s));
+    c0 = (int)fminf(fmaxf(q0, 0.0f), levels);
+    c1 = (int)fminf(fmaxf(q1, 0.0f), levels);
+}
+
+template <typename TIn, int BITS>
+__device__ __forceinline__ void write_affine_rows(const TIn* krow, const TIn* vrow, const emlx_pool& p, int64_t page,
+                                                  int off, int h, int lane) {
+    const int D = p.head_dim, bs = p.block_size, Hkv = p.num_kv_heads, groups = D / kQuantGroup;
+    const int64_t sb_base = ((page * Hkv + h) * bs + off) * groups;
+    // keys: token-major codes [NB, bs, Hkv, D*BITS/8]
+    uint8_t* kdst = (uint8_t*)p.key_cache + ((page * bs + off) * Hkv + h) * (int64_t)(D * BITS / 8);
+    // values: [NB, Hkv, D, bs*BITS/8], the tokens of one element are contiguous
+    uint8_t* vdst = (uint8_t*)p.value_cache + (page * Hkv + h) * (int64_t)D * (bs * BITS / 8);
+    for (int g = 0; g < groups; ++g) {
+        const int d0 = g * kQuantGroup + 2 * lane;
+        int c0, c1;
+        __half s, b;
+        quantize_group<BITS>(to_f32<TIn>(krow[d0]), to_f32<TIn>(krow[d0 + 1]), c0, c1, s, b);
+        if (BITS == 8) *(uchar2*)(kdst + d0) = make_uchar2((unsigned char)c0, (unsigned char)c1);
+        else kdst[d0 >> 1] = (uint8_t)(c0 | (c1 << 4));
+        if (lane == 0) {
+            ((__half*)p.k_scale)[sb_base + g] = s;
+            ((__half*)p.k_bias)[sb_base + g] = b;
+        }
+        quantize_group<BITS>(to_f32<TIn>(vrow[d0]), to_f32<TIn>(vrow[d0 + 1]), c0, c1, s, b);
+        if (BITS == 8) {
+            vdst[(int64_t)d0 * bs + off] = (uint8_t)c0;
+            vdst[(int64_t)(d0 + 1) * bs + off] = (uint8_t)c1;
+        } else {
+            // two tokens share a byte; tokens of the same batch may land in the same 32-bit word, so the
+            // nibble is replaced with word atomics (each nibble has exactly one writer per batch)
+            const int shift = ((off >> 1) & 3) * 8 + (off & 1) * 4;
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                uint8_t* byte = vdst + (int64_t)(d0 + e) * (bs / 2) + (off >> 1);
+                unsigned int* word = (unsigned int*)((uintptr_t)byte & ~(uintptr_t)3);
+                atomicAnd(word, ~(0xFu << shift));
+                atomicOr(word, (unsigned int)(e ? c1 : c0) << shift);
+            }
+        }
+        if (lane == 0) {
+            ((__half*)p.v_scale)[sb_base + g] = s;
+            ((__half*)p.v_bias)[sb_base + g] = b;
+        }
+    }
+}
+
+template <typename TIn>
+__global__ void __launch_bounds__(256) kv_write_kernel(WriteParams w) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const emlx_pool& p = w.pool;
+    const int Hkv = p.num_kv_heads, D = p.head_dim;
+    if (warp >= (int64_t)w.T * Hkv) return;
+    const int t = (int)(warp / Hkv), h = (int)(warp - (int64_t)t * Hkv);
+    const int64_t slot = w.slot_mapping[t];
+    if (slot < 0) return;
+    if (slot >= p.num_blocks * p.block_size) {
+        if (lane == 0) flag_error(w.status, EMLX_DEV_BAD_PAGE);
+        return;
+    }
+    const TIn* krow = (const TIn*)w.keys + ((int64_t)t * Hkv + h) * D;
+    const TIn* vrow = (const TIn*)w.values + ((int64_t)t * Hkv + h) * D;
+    if (p.kv_format == EMLX_KV_FLOAT) {
+        const int64_t off = (slot * Hkv + h) * D;
+        write_float_row(krow, p.key_cache, p.kv_dtype, off, D, lane);
+        write_float_row(vrow, p.value_cache, p.kv_dtype, off, D, lane);
+    } else {
+        const int64_t page = slot / p.block_size;
+        const int in_page = (int)(slot - page * p.block_size);
+        if (p.kv_format == EMLX_KV_AFFINE8) write_affine_rows<TIn, 8>(krow, vrow, p, page, in_page, h, lane);
+        else write_affine_rows<TIn, 4>(krow, vrow, p, page, in_page, h, lane);
+    }
+}
+
+int validate_pool(const emlx_pool* pool) {
+    if (!pool) return fail(EMLX_ERR_INVALID, "pool is NULL");
+    if (!pool->key_cache || !pool->value_cache) return fail(EMLX_ERR_INVALID, "key_cache/value_cache is NULL");
+    if (pool->num_blocks <= 0 || pool->block_size <= 0 || pool->num_kv_heads <= 0 || pool->head_dim <= 0)
+        return fail(EMLX_ERR_INVALID, "pool geometry must be positive");
+    if (pool->kv_format == EMLX_KV_FLOAT) {
+        if (pool->kv_dtype < EMLX_F16 || pool->kv_dtype > EMLX_F32) return fail(EMLX_ERR_INVALID, "unknown kv_dtype");
+    } else if (pool->kv_format == EMLX_KV_AFFINE8 || pool->kv_format == EMLX_KV_AFFINE4) {
+        if (pool->head_dim % kQuantGroup) return fail(EMLX_ERR_INVALID, "affine KV needs head_dim %% 64 == 0");
+        if (pool->block_size % 8) return fail(EMLX_ERR_INVALID, "affine KV needs block_size %% 8 == 0");
+        if (!pool->k_scale || !pool->k_bias || !pool->v_scale || !pool->v_bias)
+            return fail(EMLX_ERR_INVALID, "affine KV needs k/v scale and bias arrays");
+    } else {
+        return fail(EMLX_ERR_INVALID, "unknown kv_format %d", pool->kv_format);
+    }
+    return EMLX_OK;
+}
+
+}  // namespace emlx
+
+extern "C" int emlx_kv_write(const void* keys, const void* values, int32_t in_dtype, int32_t total_tokens,
+                             const int64_t* slot_mapping, const emlx_pool* pool, int32_t* status, void* stream) {
+    using namespace emlx;
+    if (int rc = validate_pool(pool)) return rc;
+    if (total_tokens < 0) return fail(EMLX_ERR_INVALID, "total_tokens must be non-negative");
+    if (total_tokens == 0) return EMLX_OK;
+    if (!keys || !values || !slot_mapping) return fail(EMLX_ERR_INVALID, "kv_write: NULL input");
+    WriteParams w{keys, values, slot_mapping, *pool, total_tokens, status};
+    const int64_t warps = (int64_t)total_tokens * pool->num_kv_heads;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((warps * 32 + threads - 1) / threads);
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (in_dtype) {
+        case EMLX_F16: kv_write_kernel<__half><<<blocks, threads, 0, s>>>(w); break;
+        case EMLX_BF16: kv_write_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>(w); break;
+        case EMLX_F32: kv_write_kernel<float><<<blocks, threads, 0, s>>>(w); break;
+        default: return fail(EMLX_ERR_INVALID, "unknown in_dtype %d", in_dtype);
+    }
+    EMLX_LAUNCHED();
+    return EMLX_OK;
+}

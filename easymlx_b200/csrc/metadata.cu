@@ -1,0 +1,130 @@
+// Batch metadata on the GPU: prefix sum of query lengths, gather of the scheduled slots' page-table
+// rows and lengths, per-token slot mapping.  One CTA; the batch is a few thousand integers.
+#include "common.cuh"
+
+namespace emlx {
+
+constexpr int kMetaThreads = 1024;
+
+// Exclusive prefix sum over data[0..n) in place; returns the total to every thread.
+// Each thread owns a contiguous segment; segment totals are scanned through shared memory.
+__device__ int block_exclusive_scan(int32_t* data, int n, int32_t* smem /* [kMetaThreads/32 + 1] */) {
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int per = (n + kMetaThreads - 1) / kMetaThreads;
+    const int begin = min(n, tid * per), end = min(n, begin + per);
+    int local = 0;
+    for (int i = begin; i < end; ++i) local += data[i];
+    int incl = local;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) smem[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int w = smem[lane];
+        int wi = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            int v = __shfl_up_sync(0xffffffffu, wi, o);
+            if (lane >= o) wi += v;
+        }
+        smem[lane] = wi - w;  // exclusive offset of each warp
+        if (lane == 31) smem[32] = wi;
+    }
+    __syncthreads();
+    int running = smem[warp] + incl - local;
+    const int total = smem[32];
+    for (int i = begin; i < end; ++i) {
+        int v = data[i];
+        data[i] = running;
+        running += v;
+    }
+    __syncthreads();
+    return total;
+}
+
+__global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
+    const int32_t* __restrict__ query_lens, const int32_t* __restrict__ slot_ids, int S, int T,
+    const int32_t* __restrict__ bt_all, int num_slots, int MB, int32_t* kv_lens_all, int bs, int advance,
+    int32_t* __restrict__ qsl, int32_t* __restrict__ bt_out, int32_t* __restrict__ kv_out,
+    int64_t* __restrict__ slot_mapping, int64_t num_blocks, int32_t* status) {
+    __shared__ int32_t scan_smem[kMetaThreads / 32 + 1];
+    const int tid = threadIdx.x;
+
+    for (int i = tid; i < S; i += kMetaThreads) qsl[i] = max(query_lens[i], 0);
+    if (tid == 0) qsl[S] = 0;
+    __syncthreads();
+    const int total = block_exclusive_scan(qsl, S, scan_smem);
+    if (tid == 0) {
+        qsl[S] = total;
+        if (total != T) flag_error(status, EMLX_DEV_TOKEN_MISMATCH);
+    }
+
+    // lengths after the step, for the scheduled rows
+    for (int i = tid; i < S; i += kMetaThreads) {
+        int slot = slot_ids[i];
+        if (slot < 0 || slot >= num_slots) {
+            flag_error(status, EMLX_DEV_BAD_SLOT);
+            kv_out[i] = 0;
+            continue;
+        }
+        int q_len = max(query_lens[i], 0);
+        int after = kv_lens_all[slot] + q_len;
+        if (after > MB * bs) flag_error(status, EMLX_DEV_OVERFLOW);
+        kv_out[i] = after;
+        if (advance) kv_lens_all[slot] = after;
+    }
+    // gathered page-table rows
+    const int64_t cells = (int64_t)S * MB;
+    for (int64_t c = tid; c < cells; c += kMetaThreads) {
+        int row = (int)(c / MB), col = (int)(c - (int64_t)row * MB);
+        int slot = slot_ids[row];
+        bt_out[c] = (slot >= 0 && slot < num_slots) ? bt_all[(int64_t)slot * MB + col] : -1;
+    }
+    __syncthreads();  // qsl and kv_out of this CTA are now visible to all its threads
+
+    if (slot_mapping == nullptr) return;
+    const int n = min(T, total);
+    for (int t = tid; t < T; t += kMetaThreads) {
+        int64_t dst = -1;
+        if (t < n) {
+            int s = find_sequence(qsl, S, t);
+            int slot = s >= 0 ? slot_ids[s] : -1;
+            if (slot >= 0 && slot < num_slots) {
+                int q_len = qsl[s + 1] - qsl[s];
+                int pos = kv_out[s] - q_len + (t - qsl[s]);
+                int page_idx = pos / bs;
+                if (page_idx < MB) {
+                    int page = bt_all[(int64_t)slot * MB + page_idx];
+                    if (page >= 0 && page < num_blocks) dst = (int64_t)page * bs + (pos - page_idx * bs);
+                    else flag_error(status, EMLX_DEV_BAD_PAGE);
+                }
+            }
+        }
+        slot_mapping[t] = dst;
+    }
+}
+
+}  // namespace emlx
+
+extern "C" int emlx_build_metadata(const int32_t* query_lens, const int32_t* slot_ids, int32_t num_seqs,
+                                   int32_t total_tokens, const int32_t* block_tables_all, int32_t num_slots,
+                                   int32_t max_blocks_per_seq, int32_t* kv_lens_all, int32_t block_size,
+                                   int32_t advance_kv_lens, int32_t* query_start_loc, int32_t* block_tables,
+                                   int32_t* kv_lens, int64_t* slot_mapping, int64_t num_blocks, int32_t* status,
+                                   void* stream) {
+    using namespace emlx;
+    if (num_seqs < 0 || total_tokens < 0) return fail(EMLX_ERR_INVALID, "num_seqs/total_tokens must be non-negative");
+    if (block_size <= 0 || max_blocks_per_seq <= 0 || num_slots <= 0)
+        return fail(EMLX_ERR_INVALID, "block_size, max_blocks_per_seq and num_slots must be positive");
+    if (!query_start_loc || !kv_lens_all || !block_tables_all || (num_seqs > 0 && (!query_lens || !slot_ids)))
+        return fail(EMLX_ERR_INVALID, "build_metadata: NULL input");
+    if (num_seqs > 0 && (!block_tables || !kv_lens)) return fail(EMLX_ERR_INVALID, "build_metadata: NULL output");
+    build_metadata_kernel<<<1, kMetaThreads, 0, (cudaStream_t)stream>>>(
+        query_lens, slot_ids, num_seqs, total_tokens, block_tables_all, num_slots, max_blocks_per_seq, kv_lens_all,
+        block_size, advance_kv_lens, query_start_loc, block_tables, kv_lens, slot_mapping, num_blocks, status);
+    EMLX_LAUNCHED();
+    return EMLX_OK;
+}

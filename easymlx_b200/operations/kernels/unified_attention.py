@@ -1,0 +1,274 @@
+"""Unified ragged paged attention on B200.
+
+Host-side mirror of easymlx ``operations/kernels/unified_attention.py``:
+``paged_attention`` (``:1377-1512``), ``UnifiedAttnMetadata`` (``:44-66``),
+``UnifiedAttnConfig`` (``:69-82``) and the registered ``UnifiedAttention`` operation
+(``:1515-1684``) keep their names, arguments, defaults and error behaviour.  The work is
+done by the CUDA library behind ``include/easymlx_b200.h``; there is no CPU path, so
+where the reference would fall back to NumPy this module raises.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+import typing as tp
+from dataclasses import dataclass
+
+import torch
+
+from ... import _native as nv
+from .._attention_outputs import AttentionOutput
+from .._base_operation import BaseOperation, OperationRegistry
+from ..requirements import ExecutionMode, MetadataField, RequirementsBuilder
+
+_CHECK = os.environ.get("EASYMLX_B200_CHECK", "0") not in ("", "0")
+_TILED_HEAD_DIMS = (64, 128)
+_TILED_BLOCK_SIZE = 128
+
+
+@dataclass
+class UnifiedAttnMetadata:
+    block_tables: tp.Any
+    kv_lens: tp.Any
+    query_start_loc: tp.Any
+    block_size: int
+    sliding_window: int | None = None
+    is_single_token_decode: bool = False
+
+
+@dataclass
+class UnifiedAttnConfig:
+    """Kept for signature compatibility; the Metal-specific knobs have no effect here."""
+
+    use_metal_kernel: bool = True
+    allow_fallback: bool = True
+    threadgroup_size: int = 256
+
+
+def _validate_inputs(queries, key_cache, value_cache, block_tables, kv_lens, query_start_loc, affine: bool) -> None:
+    if queries.ndim != 3:
+        raise ValueError("queries must be rank-3: [total_tokens, num_q_heads, head_dim]")
+    if key_cache.ndim != 4 or value_cache.ndim != 4:
+        raise ValueError("key_cache/value_cache must be rank-4: [num_blocks, block_size, num_kv_heads, head_dim]")
+    if not affine:
+        if key_cache.shape != value_cache.shape:
+            raise ValueError("key_cache and value_cache must have the same shape")
+        if queries.shape[2] != key_cache.shape[3]:
+            raise ValueError("queries head_dim must match key/value cache head_dim")
+    if queries.shape[1] % key_cache.shape[2] != 0:
+        raise ValueError("num_q_heads must be divisible by num_kv_heads (GQA)")
+    if block_tables.ndim != 2:
+        raise ValueError("block_tables must be rank-2: [num_seqs, max_blocks_per_seq]")
+    if kv_lens.ndim != 1 or query_start_loc.ndim != 1:
+        raise ValueError("kv_lens/query_start_loc must be rank-1")
+    if query_start_loc.shape[0] != block_tables.shape[0] + 1:
+        raise ValueError("query_start_loc must have length num_seqs + 1")
+
+
+def _as_int32(value, device) -> torch.Tensor:
+    if isinstance(value, torch.Tensor):
+        if value.dtype != torch.int32 or value.device != device or not value.is_contiguous():
+            value = value.to(device=device, dtype=torch.int32).contiguous()
+        return value
+    return torch.as_tensor(value, dtype=torch.int32).to(device)
+
+
+class _Scratch:
+    """Per-device plan / workspace / status buffers, grown on demand and reused across calls.
+
+    The workspace must start zeroed (its counters reset themselves after every merge), so it is
+    zero-filled whenever it is (re)allocated.
+    """
+
+    def __init__(self):
+        self.buffers: dict = {}
+
+    def get(self, device, kind: str, nbytes: int, zero: bool) -> torch.Tensor:
+        key = (str(device), kind)
+        buf = self.buffers.get(key)
+        if buf is None or buf.numel() < nbytes:
+            size = max(256, int(nbytes))
+            buf = torch.zeros(size, dtype=torch.uint8, device=device) if zero else \
+                torch.empty(size, dtype=torch.uint8, device=device)
+            self.buffers[key] = buf
+        return buf
+
+
+_scratch = _Scratch()
+
+
+def _make_pool(key_cache, value_cache, head_dim, k_scale, v_scale, k_bias, v_bias) -> tuple[nv.Pool, bool]:
+    p = nv.Pool()
+    affine = key_cache.dtype == torch.uint8
+    p.key_cache, p.value_cache = key_cache.data_ptr(), value_cache.data_ptr()
+    p.num_blocks, p.block_size, p.num_kv_heads = int(key_cache.shape[0]), int(key_cache.shape[1]), int(key_cache.shape[2])
+    p.head_dim = int(head_dim)
+    if affine:
+        if k_scale is None or v_scale is None or k_bias is None or v_bias is None:
+            raise ValueError("a uint8 (affine) KV pool needs k_scale, v_scale, k_bias and v_bias")
+        width = int(key_cache.shape[3])
+        if width == head_dim:
+            bits = 8
+        elif width * 2 == head_dim:
+            bits = 4
+        else:
+            raise ValueError("affine key_cache last dimension must be head_dim (8-bit) or head_dim/2 (4-bit)")
+        expect_v = (p.num_blocks, p.num_kv_heads, head_dim, p.block_size * bits // 8)
+        if tuple(value_cache.shape) != expect_v:
+            raise ValueError(f"affine value_cache must be [num_blocks, num_kv_heads, head_dim, block_size*bits/8] = {expect_v}")
+        sb_shape = (p.num_blocks, p.num_kv_heads, p.block_size, head_dim // 64)
+        for t in (k_scale, k_bias, v_scale, v_bias):
+            if tuple(t.shape) != sb_shape or t.dtype != torch.float16 or not t.is_contiguous():
+                raise ValueError(f"affine scale/bias must be contiguous float16 {sb_shape}")
+        p.k_scale, p.k_bias, p.v_scale, p.v_bias = k_scale.data_ptr(), k_bias.data_ptr(), v_scale.data_ptr(), v_bias.data_ptr()
+        p.kv_format, p.kv_dtype = bits, nv.F16
+    else:
+        p.kv_format, p.kv_dtype = nv.KV_FLOAT, nv.dtype_code(key_cache.dtype)
+    return p, affine
+
+
+def paged_attention(
+    queries: torch.Tensor,
+    key_cache: torch.Tensor,
+    value_cache: torch.Tensor,
+    block_tables,
+    kv_lens,
+    query_start_loc,
+    *,
+    softmax_scale: float | None = None,
+    sliding_window: int | None = None,
+    use_metal: bool | None = None,
+    single_token_decode: bool | None = None,
+    threadgroup_size: int = 256,
+    allow_fallback: bool = True,
+    k_scale: torch.Tensor | None = None,
+    v_scale: torch.Tensor | None = None,
+    k_bias: torch.Tensor | None = None,
+    v_bias: torch.Tensor | None = None,
+    kernel: str | None = None,
+) -> torch.Tensor:
+    """Ragged causal attention of packed queries over a paged KV pool.
+
+    Same arguments as the reference.  ``kv_lens`` are the lengths after this step's write;
+    ``block_tables`` / ``kv_lens`` hold one row per scheduled sequence.  ``use_metal``,
+    ``threadgroup_size`` and ``allow_fallback`` are accepted and ignored.  For affine pools
+    ``k_scale``/``v_scale`` are per-group fp16 arrays and ``k_bias``/``v_bias`` join them.
+    ``kernel`` (``None`` = automatic, ``"generic"``, ``"tiled"``, ``"decode"``, ``"prefill"``) selects
+    an entry point explicitly; tests and benchmarks use it.
+    """
+    del use_metal, threadgroup_size, allow_fallback
+    nv.require_cuda(queries, key_cache, value_cache)
+    dev = queries.device
+    affine = key_cache.dtype == torch.uint8
+    block_tables = _as_int32(block_tables, dev)
+    kv_lens = _as_int32(kv_lens, dev)
+    query_start_loc = _as_int32(query_start_loc, dev)
+    _validate_inputs(queries, key_cache, value_cache, block_tables, kv_lens, query_start_loc, affine)
+
+    total, hq, d = int(queries.shape[0]), int(queries.shape[1]), int(queries.shape[2])
+    if softmax_scale is None:
+        softmax_scale = 1.0 / math.sqrt(d)
+    window = int(sliding_window or 0)
+    if total == 0:
+        return torch.zeros_like(queries)
+    if not (key_cache.is_contiguous() and value_cache.is_contiguous()):
+        raise ValueError("key_cache and value_cache must be contiguous")
+    queries = queries.contiguous()
+    pool, _ = _make_pool(key_cache, value_cache, d, k_scale, v_scale, k_bias, v_bias)
+    out = torch.empty_like(queries)
+    s = int(block_tables.shape[0])
+
+    tiled_ok = (
+        pool.block_size == _TILED_BLOCK_SIZE and d in _TILED_HEAD_DIMS
+        and queries.dtype in (torch.float16, torch.bfloat16)
+        and (affine or key_cache.dtype == queries.dtype)
+    )
+    if kernel is None:
+        kernel = "tiled" if tiled_ok else "generic"
+    if kernel != "generic" and not tiled_ok:
+        raise NotImplementedError(
+            "the tiled kernels need page size 128, head_dim 64 or 128, fp16/bf16 queries and a pool of the same "
+            "dtype (or an affine pool)")
+
+    lib, stream = nv.lib(), nv.stream_ptr(dev)
+    status = _scratch.get(dev, "status", 4, zero=True)
+    a = nv.AttnArgs()
+    a.queries, a.out = queries.data_ptr(), out.data_ptr()
+    a.block_tables, a.kv_lens, a.query_start_loc = block_tables.data_ptr(), kv_lens.data_ptr(), query_start_loc.data_ptr()
+    a.total_tokens, a.num_seqs, a.num_q_heads = total, s, hq
+    a.max_blocks_per_seq, a.q_dtype = int(block_tables.shape[1]), nv.dtype_code(queries.dtype)
+    a.sliding_window, a.softmax_scale = window, float(softmax_scale)
+    a.status = status.data_ptr()
+    if kernel == "generic":
+        nv.check(lib.emlx_attn_generic(a, pool, stream))
+    else:
+        hkv = pool.num_kv_heads
+        plan_bytes = int(lib.emlx_attn_plan_bytes(s, total, hq, hkv))
+        ws_bytes = int(lib.emlx_attn_workspace_bytes(s, total, hq, hkv, d))
+        plan = _scratch.get(dev, "plan", plan_bytes, zero=False)
+        ws = _scratch.get(dev, "workspace", ws_bytes, zero=True)
+        nv.check(lib.emlx_attn_plan(nv.ptr(query_start_loc), nv.ptr(kv_lens), s, total, hq, hkv, pool.block_size,
+                                    window, nv.ptr(plan), plan_bytes, stream))
+        a.plan, a.plan_bytes = plan.data_ptr(), plan_bytes
+        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+        entry = {"tiled": lib.emlx_attn_unified, "decode": lib.emlx_attn_decode, "prefill": lib.emlx_attn_prefill}[kernel]
+        nv.check(entry(a, pool, stream))
+    if _CHECK:
+        nv.check(lib.emlx_read_status(nv.ptr(status), stream))
+    return out
+
+
+@OperationRegistry.register
+class UnifiedAttention(BaseOperation):
+    """Paged (unified) attention operation for block-tabled KV caches.
+
+    Registered under the reference's names.  Every batch - decode rows, prefill chunks, one
+    multi-token sequence - goes to the same CUDA entry point; the reference's separate dense route
+    for a single multi-token sequence (``unified_attention.py:1658-1673``) differs from it only by
+    rounding the probabilities to the value dtype, which lies inside the op's tolerance.
+    """
+
+    def __init__(self, metadata: tp.Any | None = None, *, use_metal: bool = True):
+        super().__init__(metadata=metadata)
+        self.use_metal = bool(use_metal)
+
+    @classmethod
+    def get_impl_name(cls) -> str | tuple[str, ...]:
+        return ("unified_attention", "unified", "paged", "full_attention", "linear_attention")
+
+    @classmethod
+    def get_requirements(cls, mode: ExecutionMode = ExecutionMode.MIXED):
+        from ...caching.paged.cache import PageCacheView
+
+        return (
+            RequirementsBuilder("unified_attention")
+            .require_metadata(MetadataField.QUERY_START_LOC, MetadataField.BLOCK_TABLES, MetadataField.KV_LENS,
+                              MetadataField.BLOCK_SIZE)
+            .optional_metadata(MetadataField.SLIDING_WINDOW)
+            .require_cache(PageCacheView)
+            .build()
+        )
+
+    def forward_native(self, *, query, key, value, cache_metadata=None, cache_view=None, scale: float | None = None,
+                       use_metal: bool | None = None, threadgroup_size: int = 256, **_: tp.Any) -> AttentionOutput:
+        from ...caching.paged.cache import PageMetadata
+
+        if cache_metadata is None:
+            raise ValueError("UnifiedAttention requires cache_metadata.")
+        if isinstance(cache_metadata, PageMetadata):
+            if cache_metadata.block_tables is None or cache_metadata.kv_lens is None or cache_metadata.block_size is None:
+                raise ValueError("PageMetadata must be resolved before unified attention execution.")
+        extra: dict[str, tp.Any] = {}
+        if cache_view is not None and getattr(cache_view, "is_affine", False) and key.dtype == torch.uint8:
+            extra = dict(k_scale=cache_view.k_scales, v_scale=cache_view.v_scales,
+                         k_bias=cache_view.k_biases, v_bias=cache_view.v_biases)
+        outputs = paged_attention(
+            query, key, value, cache_metadata.block_tables, cache_metadata.kv_lens, cache_metadata.query_start_loc,
+            softmax_scale=scale, sliding_window=cache_metadata.sliding_window,
+            single_token_decode=cache_metadata.is_single_token_decode, **extra,
+        )
+        return AttentionOutput(attention_outputs=outputs, cache_view=cache_view)
+
+
+__all__ = ("UnifiedAttention", "UnifiedAttnConfig", "UnifiedAttnMetadata", "paged_attention")

@@ -1,0 +1,162 @@
+/*
+ * easymlx_b200 - C ABI of the B200 (sm_100a) ragged paged-attention path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as
+ * void*), launches asynchronously on that stream and returns an emlx_status.  Nothing
+ * here allocates or frees device memory unless its comment says so; the caller owns all
+ * buffers.  After a non-zero return emlx_last_error() describes the failure (per host
+ * thread).
+ *
+ * The comments cite the easymlx function each entry point replaces; paths are relative
+ * to lib/python/easymlx/ in that project.
+ */
+#ifndef EASYMLX_B200_H
+#define EASYMLX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+#if defined(__GNUC__)
+#pragma GCC visibility push(default)
+#endif
+
+typedef enum emlx_status {
+    EMLX_OK = 0,
+    EMLX_ERR_INVALID = 1,     /* bad rank/shape/geometry  -> ValueError in the Python mirror        */
+    EMLX_ERR_UNSUPPORTED = 2, /* geometry a kernel does not cover -> NotImplementedError            */
+    EMLX_ERR_CUDA = 3,        /* a CUDA runtime/driver call failed -> RuntimeError                   */
+    EMLX_ERR_WORKSPACE = 4,   /* plan/workspace buffer missing or too small -> RuntimeError          */
+    EMLX_ERR_DEVICE = 5       /* the device status word holds an error (see emlx_read_status)        */
+} emlx_status;
+
+/* Element types of queries / new rows / 16- and 32-bit pools. */
+typedef enum emlx_dtype { EMLX_F16 = 0, EMLX_BF16 = 1, EMLX_F32 = 2 } emlx_dtype;
+
+/* Storage format of the page pool.
+ *   FLOAT   : key_cache/value_cache[NB, bs, Hkv, D] in `kv_dtype` (the reference layout,
+ *             caching/paged/cache.py:779-791).
+ *   AFFINE8 / AFFINE4 : min-max affine codes over groups of 64 along head_dim.
+ *             key codes   uint8 [NB, bs, Hkv, D*bits/8]  (token-major, low nibble = even element)
+ *             value codes uint8 [NB, Hkv, D, bs*bits/8]  (transposed inside a page: the tokens of one
+ *                               head_dim element are contiguous; low nibble = even token)
+ *             scale, bias fp16  [NB, Hkv, bs, D/64] for keys and for values.
+ *             The reference has no such cache; its hook for a quantised cache is the k_scale/v_scale
+ *             pair of operations/kernels/unified_attention.py:1391-1392.
+ */
+typedef enum emlx_kv_format { EMLX_KV_FLOAT = 0, EMLX_KV_AFFINE8 = 8, EMLX_KV_AFFINE4 = 4 } emlx_kv_format;
+
+/* Bits of the device status word (int32, caller-allocated, zeroed by the caller). Kernels OR bits in. */
+enum {
+    EMLX_DEV_BAD_SLOT = 1,        /* slot id outside [0, num_slots)                                   */
+    EMLX_DEV_BAD_PAGE = 2,        /* page id outside [0, num_blocks) inside a sequence's live range   */
+    EMLX_DEV_OVERFLOW = 4,        /* a sequence would outgrow its page-table row                      */
+    EMLX_DEV_TOKEN_MISMATCH = 8,  /* sum(query_lens) != total_tokens                                  */
+    EMLX_DEV_WAIT_TIMEOUT = 16    /* an in-kernel barrier wait hit its iteration limit                */
+};
+
+/* The page pool, shared by the write and attention entry points. */
+typedef struct emlx_pool {
+    void* key_cache;      /* see emlx_kv_format                                      */
+    void* value_cache;
+    void* k_scale;        /* AFFINE only, else NULL                                  */
+    void* k_bias;
+    void* v_scale;
+    void* v_bias;
+    int64_t num_blocks;   /* NB                                                      */
+    int32_t block_size;   /* bs, tokens per page                                     */
+    int32_t num_kv_heads; /* Hkv                                                     */
+    int32_t head_dim;     /* D                                                       */
+    int32_t kv_format;    /* emlx_kv_format                                          */
+    int32_t kv_dtype;     /* emlx_dtype of a FLOAT pool                              */
+    int32_t reserved;
+} emlx_pool;
+
+/* One attention call: packed queries over already-gathered per-sequence rows.
+ * Mirrors the arguments of paged_attention(), operations/kernels/unified_attention.py:1377-1393. */
+typedef struct emlx_attn_args {
+    const void* queries;            /* [T, Hq, D] q_dtype                             */
+    void* out;                      /* [T, Hq, D] q_dtype, fully overwritten          */
+    const int32_t* block_tables;    /* [S, MB], -1 = unassigned                       */
+    const int32_t* kv_lens;         /* [S], lengths AFTER this step's write           */
+    const int32_t* query_start_loc; /* [S+1]                                          */
+    int32_t total_tokens;           /* T                                              */
+    int32_t num_seqs;               /* S                                              */
+    int32_t num_q_heads;            /* Hq, multiple of Hkv                            */
+    int32_t max_blocks_per_seq;     /* MB                                             */
+    int32_t q_dtype;                /* emlx_dtype                                     */
+    int32_t sliding_window;         /* 0 = off                                        */
+    float softmax_scale;
+    int32_t reserved;
+    void* plan;                     /* from emlx_attn_plan (not used by emlx_attn_generic)        */
+    size_t plan_bytes;
+    void* workspace;                /* split-KV partials and counters; zero it once after allocating */
+    size_t workspace_bytes;
+    int32_t* status;                /* device status word, may be NULL                */
+} emlx_attn_args;
+
+const char* emlx_last_error(void);
+int emlx_abi_version(void);
+
+/* Blocking read of a device status word (synchronises `stream`). Returns EMLX_OK when it is 0,
+ * EMLX_ERR_DEVICE otherwise with the bits spelled out in emlx_last_error(). */
+int emlx_read_status(const int32_t* status, void* stream);
+
+/* (2) Batch metadata on the GPU.  Replaces the host code of PageCacheView.concatenate_to_cache
+ * (caching/paged/cache.py:1123-1169,1214-1261,1300-1305), build_query_start_loc
+ * (caching/paged/cache.py:1448-1465) and the row gather of PageMetadata.with_cache_state
+ * (caching/paged/cache.py:1201-1205,1301-1305).
+ *   query_lens[S], slot_ids[S]             packed batch, in batch order (negative lengths count as 0)
+ *   block_tables_all[num_slots, MB]        the cache's page table
+ *   kv_lens_all[num_slots]                 in/out: advanced by query_lens when advance_kv_lens != 0
+ *   query_start_loc[S+1]                   out: exclusive prefix sum of query_lens
+ *   block_tables[S, MB], kv_lens[S]        out: rows of the scheduled slots, lengths after the step
+ *   slot_mapping[T]                        out: page*bs + offset of every new row, -1 = skip
+ * A slot id must not appear twice in one batch. */
+int emlx_build_metadata(const int32_t* query_lens, const int32_t* slot_ids, int32_t num_seqs, int32_t total_tokens,
+                        const int32_t* block_tables_all, int32_t num_slots, int32_t max_blocks_per_seq,
+                        int32_t* kv_lens_all, int32_t block_size, int32_t advance_kv_lens,
+                        int32_t* query_start_loc, int32_t* block_tables, int32_t* kv_lens, int64_t* slot_mapping,
+                        int64_t num_blocks, int32_t* status, void* stream);
+
+/* (1) Paged KV write.  Replaces the scatter of PageCacheView.concatenate_to_cache
+ * (caching/paged/cache.py:1186-1190,1278-1282) and, for AFFINE pools, the quantised-write hook
+ * (caching/paged/cache.py:1171-1184).  keys/values are [T, Hkv, D] in `in_dtype`, contiguous. */
+int emlx_kv_write(const void* keys, const void* values, int32_t in_dtype, int32_t total_tokens,
+                  const int64_t* slot_mapping, const emlx_pool* pool, int32_t* status, void* stream);
+
+/* Work list for the tiled attention kernels, built on the GPU from query_start_loc / kv_lens
+ * (replaces the host-side classification of _is_single_token_decode,
+ * operations/kernels/unified_attention.py:175-184, which forces a device->host sync). */
+size_t emlx_attn_plan_bytes(int32_t num_seqs, int32_t total_tokens, int32_t num_q_heads, int32_t num_kv_heads);
+size_t emlx_attn_workspace_bytes(int32_t num_seqs, int32_t total_tokens, int32_t num_q_heads, int32_t num_kv_heads,
+                                 int32_t head_dim);
+int emlx_attn_plan(const int32_t* query_start_loc, const int32_t* kv_lens, int32_t num_seqs, int32_t total_tokens,
+                   int32_t num_q_heads, int32_t num_kv_heads, int32_t block_size, int32_t sliding_window,
+                   void* plan, size_t plan_bytes, void* stream);
+
+/* (5) Unified ragged attention: decode rows and prefill chunks of one packed batch in one call.
+ * Replaces paged_attention() (operations/kernels/unified_attention.py:1377-1512) and the Metal
+ * kernels it launches (unified_attention.py:290-464, 467-608). */
+int emlx_attn_unified(const emlx_attn_args* args, const emlx_pool* pool, void* stream);
+/* (3) Split-KV flash-decode over the plan's short-row units only (rows with few query tokens). */
+int emlx_attn_decode(const emlx_attn_args* args, const emlx_pool* pool, void* stream);
+/* (4) Prefill-chunk attention over the plan's long-row units only. */
+int emlx_attn_prefill(const emlx_attn_args* args, const emlx_pool* pool, void* stream);
+/* Reference-semantics kernel for any geometry the tiled kernels do not cover (head_dim <= 256,
+ * any page size, fp16/bf16/fp32); same arithmetic as _paged_attention_reference
+ * (operations/kernels/unified_attention.py:187-281).  Needs neither plan nor workspace. */
+int emlx_attn_generic(const emlx_attn_args* args, const emlx_pool* pool, void* stream);
+
+/* Number of kernels this library has launched from the calling process (for launch accounting). */
+int64_t emlx_launch_count(void);
+
+#if defined(__GNUC__)
+#pragma GCC visibility pop
+#endif
+#ifdef __cplusplus
+}
+#endif
+#endif /* EASYMLX_B200_H */

@@ -18,10 +18,12 @@ arithmetic IEEE fp32 round-to-nearest-even unless a cast is named:
     code   = clamp( rint( (x - fp32(bias)) / fp32(scale) ), 0, 2**bits - 1 )
     x'     = fp32(scale) * code + fp32(bias)      (dequantised value, fp32)
 
-Storage: codes are bytes ``[NB, bs, Hkv, D*bits/8]``; with 4 bits element ``2i`` sits in
-the low nibble of byte ``i`` and element ``2i+1`` in the high nibble.  ``scale`` and
-``bias`` are fp16 ``[NB, Hkv, bs, D/64]`` (head-major inside a page so that the
-128 tokens of one (page, head) tile are contiguous).
+Storage.  Key codes are bytes ``[NB, bs, Hkv, D*bits/8]`` (token-major; with 4 bits element
+``2i`` sits in the low nibble of byte ``i``).  Value codes are bytes ``[NB, Hkv, D, bs*bits/8]``:
+transposed inside a page, so that the tokens of one head_dim element are contiguous (with 4
+bits token ``2i`` sits in the low nibble of byte ``i``).  ``scale`` and ``bias`` are fp16
+``[NB, Hkv, bs, D/64]`` for keys and for values (head-major inside a page, so the 128 tokens
+of one (page, head) tile are contiguous).
 """
 
 from __future__ import annotations
@@ -77,9 +79,18 @@ def dequantize_rows(codes, scale, bias):
     return x.reshape(codes.shape)
 
 
-def dequantize_pool(code_cache, scale, bias, bits):
-    """Stored pool ``[NB, bs, Hkv, D*bits/8]`` + ``scale/bias[NB, Hkv, bs, D/64]`` -> fp32 ``[NB, bs, Hkv, D]``."""
+def dequantize_key_pool(code_cache, scale, bias, bits):
+    """Key pool ``[NB, bs, Hkv, D*bits/8]`` + ``scale/bias[NB, Hkv, bs, D/64]`` -> fp32 ``[NB, bs, Hkv, D]``."""
     codes = unpack_codes(code_cache, bits)
+    s = np.transpose(scale, (0, 2, 1, 3))
+    b = np.transpose(bias, (0, 2, 1, 3))
+    return dequantize_rows(codes, s, b)
+
+
+def dequantize_value_pool(code_cache, scale, bias, bits):
+    """Value pool ``[NB, Hkv, D, bs*bits/8]`` + ``scale/bias[NB, Hkv, bs, D/64]`` -> fp32 ``[NB, bs, Hkv, D]``."""
+    codes = unpack_codes(code_cache, bits)               # [NB, Hkv, D, bs]
+    codes = np.ascontiguousarray(np.transpose(codes, (0, 3, 1, 2)))  # [NB, bs, Hkv, D]
     s = np.transpose(scale, (0, 2, 1, 3))
     b = np.transpose(bias, (0, 2, 1, 3))
     return dequantize_rows(codes, s, b)

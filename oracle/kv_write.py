@@ -10,7 +10,7 @@ Restates, with paths relative to ``lib/python/easymlx``:
 * ``write_rows``                     -> the scatter itself (``cache.py:1186-1190,1278-1282``),
   including the cast to the pool dtype (``cache.py:830-832``).
 * ``append``                         -> ``PageCacheView.append`` (``cache.py:834-872``).
-* ``write_rows_quantized``           -> this build's affine extension (see ``kv_quant.py``;
+* ``write_key_rows_quantized`` / ``write_value_rows_quantized`` -> this build's affine extension (see ``kv_quant.py``;
   PARITY UNPINNED), same placement rule.
 
 One deliberate difference from the reference, which applies to caller errors only: a
@@ -75,8 +75,8 @@ def write_rows(key_cache, value_cache, keys, values, slot_mapping):
     vc[slot_mapping[ok]] = np.asarray(values)[ok].astype(value_cache.dtype)
 
 
-def write_rows_quantized(code_cache, scale, bias, rows, slot_mapping, bits):
-    """Quantise ``rows[T, Hkv, D]`` and scatter codes / scale / bias (layouts in ``kv_quant``)."""
+def write_key_rows_quantized(code_cache, scale, bias, rows, slot_mapping, bits):
+    """Quantise ``rows[T, Hkv, D]`` and scatter into a key pool (layouts in ``kv_quant``)."""
     nb, bs, hkv, _ = code_cache.shape
     codes, s, b = kv_quant.quantize_rows(rows, bits)
     packed = kv_quant.pack_codes(codes, bits)
@@ -88,6 +88,25 @@ def write_rows_quantized(code_cache, scale, bias, rows, slot_mapping, bits):
     for h in range(hkv):
         scale[page, h, off] = s[ok][:, h]
         bias[page, h, off] = b[ok][:, h]
+
+
+def write_value_rows_quantized(code_cache, scale, bias, rows, slot_mapping, bits):
+    """Quantise ``rows[T, Hkv, D]`` and scatter into a value pool ``[NB, Hkv, D, bs*bits/8]``."""
+    nb, hkv, d, _ = code_cache.shape
+    bs = scale.shape[2]
+    codes, s, b = kv_quant.quantize_rows(rows, bits)      # [T, Hkv, D]
+    for t in np.nonzero(slot_mapping >= 0)[0]:
+        page, off = int(slot_mapping[t]) // bs, int(slot_mapping[t]) % bs
+        if bits == 8:
+            code_cache[page, :, :, off] = codes[t]
+        else:
+            col = code_cache[page, :, :, off // 2]
+            if off & 1:
+                code_cache[page, :, :, off // 2] = (col & 0x0F) | (codes[t] << 4)
+            else:
+                code_cache[page, :, :, off // 2] = (col & 0xF0) | codes[t]
+        scale[page, :, off] = s[t]
+        bias[page, :, off] = b[t]
 
 
 def append(key_cache, value_cache, block_tables_all, kv_lens_all, slot, keys, values, block_size):

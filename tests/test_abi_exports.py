@@ -1,0 +1,86 @@
+"""The C-ABI library builds, loads without a GPU and exports every symbol the header declares."""
+
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def built_lib():
+    from easymlx_b200 import build
+
+    return build.build()
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "easymlx_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(emlx_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(built_lib):
+    handle = ctypes.CDLL(built_lib)
+    names = _declared_symbols()
+    assert len(names) >= 12
+    for name in names:
+        assert hasattr(handle, name), f"{name} is declared in the header but not exported"
+
+
+def test_binding_covers_the_header(built_lib):
+    from easymlx_b200 import _native
+
+    assert sorted(_native.SIGNATURES) == _declared_symbols()
+    assert _native.lib().emlx_abi_version() >= 1
+
+
+def test_struct_layouts_match_the_header():
+    from easymlx_b200 import _native
+
+    # 6 pointers + int64 + 6 int32; 5 pointers + 6 int32 + float + int32 + 2x(pointer,size_t) + pointer
+    assert ctypes.sizeof(_native.Pool) == 6 * 8 + 8 + 6 * 4
+    assert ctypes.sizeof(_native.AttnArgs) == 5 * 8 + 8 * 4 + 4 * 8 + 8
+
+
+def test_host_side_validation_needs_no_gpu(built_lib):
+    from easymlx_b200 import _native
+
+    lib = _native.lib()
+    pool = _native.Pool()
+    rc = lib.emlx_kv_write(None, None, 0, 4, None, pool, None, None)
+    assert rc == _native.EMLX_ERR_INVALID
+    with pytest.raises(ValueError):
+        _native.check(rc)
+    assert b"key_cache" in lib.emlx_last_error()
+
+
+def test_registry_and_requirements():
+    import easymlx_b200 as emlx
+    from easymlx_b200.operations import MetadataField
+
+    for alias in ("unified_attention", "unified", "paged", "full_attention", "linear_attention"):
+        assert emlx.OperationRegistry.get(alias) is emlx.UnifiedAttention
+    req = emlx.UnifiedAttention.get_requirements()
+    assert req.required_metadata == (MetadataField.QUERY_START_LOC | MetadataField.BLOCK_TABLES
+                                     | MetadataField.KV_LENS | MetadataField.BLOCK_SIZE)
+    assert req.optional_metadata == MetadataField.SLIDING_WINDOW
+    assert req.requires_cache and req.cache_view_cls is emlx.PageCacheView
+    with pytest.raises(KeyError):
+        emlx.OperationRegistry.get("nope")
+    with pytest.raises(ValueError, match="requires cache_metadata"):
+        emlx.UnifiedAttention()(query=None, key=None, value=None)
+
+
+def test_cpu_tensors_are_refused():
+    import torch
+
+    import easymlx_b200 as emlx
+
+    q = torch.zeros((1, 2, 64), dtype=torch.float16)
+    kc = torch.zeros((1, 128, 1, 64), dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        emlx.paged_attention(q, kc, kc, torch.zeros((1, 1), dtype=torch.int32), torch.ones(1, dtype=torch.int32),
+                             torch.tensor([0, 1], dtype=torch.int32))
