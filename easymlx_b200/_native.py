@@ -36,7 +36,7 @@ class AttnArgs(C.Structure):
         ("query_start_loc", C.c_void_p),
         ("total_tokens", C.c_int32), ("num_seqs", C.c_int32), ("num_q_heads", C.c_int32),
         ("max_blocks_per_seq", C.c_int32), ("q_dtype", C.c_int32), ("sliding_window", C.c_int32),
-        ("softmax_scale", C.c_float), ("reserved", C.c_int32),
+        ("softmax_scale", C.c_float), ("max_query_len", C.c_int32),
         ("plan", C.c_void_p), ("plan_bytes", C.c_size_t), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p),
     ]

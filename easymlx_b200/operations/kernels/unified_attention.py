@@ -128,6 +128,92 @@ def _make_pool(key_cache, value_cache, head_dim, k_scale, v_scale, k_bias, v_bia
     return p, affine
 
 
+class AttentionCall:
+    """One validated attention call, split into ``plan()`` (work list built on the GPU) and ``launch()``
+    (the attention kernels) so that a caller can build the plan once per engine step and launch once per
+    layer, or time the kernels alone.  ``paged_attention`` is ``AttentionCall(...).plan().launch()``."""
+
+    def __init__(self, queries, key_cache, value_cache, block_tables, kv_lens, query_start_loc, *,
+                 softmax_scale: float | None = None, sliding_window: int | None = None,
+                 k_scale=None, v_scale=None, k_bias=None, v_bias=None, kernel: str | None = None,
+                 max_query_len: int = 0):
+        nv.require_cuda(queries, key_cache, value_cache)
+        dev = queries.device
+        affine = key_cache.dtype == torch.uint8
+        self.block_tables = _as_int32(block_tables, dev)
+        self.kv_lens = _as_int32(kv_lens, dev)
+        self.query_start_loc = _as_int32(query_start_loc, dev)
+        _validate_inputs(queries, key_cache, value_cache, self.block_tables, self.kv_lens, self.query_start_loc, affine)
+        self.total, self.hq, self.d = int(queries.shape[0]), int(queries.shape[1]), int(queries.shape[2])
+        self.scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(self.d)
+        self.window = int(sliding_window or 0)
+        self.device = dev
+        self.queries = queries.contiguous()
+        self.out = None
+        self.kernel = kernel
+        if self.total == 0:
+            return
+        if not (key_cache.is_contiguous() and value_cache.is_contiguous()):
+            raise ValueError("key_cache and value_cache must be contiguous")
+        self.key_cache, self.value_cache = key_cache, value_cache
+        self.scales = (k_scale, v_scale, k_bias, v_bias)
+        self.pool, _ = _make_pool(key_cache, value_cache, self.d, k_scale, v_scale, k_bias, v_bias)
+        tiled_ok = (
+            self.pool.block_size == _TILED_BLOCK_SIZE and self.d in _TILED_HEAD_DIMS
+            and queries.dtype in (torch.float16, torch.bfloat16)
+            and (affine or key_cache.dtype == queries.dtype)
+            and (not affine or queries.dtype == torch.float16)
+        )
+        if self.kernel is None:
+            self.kernel = "tiled" if tiled_ok else "generic"
+        if self.kernel != "generic" and not tiled_ok:
+            raise NotImplementedError(
+                "the tiled kernels need page size 128, head_dim 64 or 128, fp16/bf16 queries and a pool of the "
+                "same dtype (or fp16 queries with an affine pool)")
+        self.num_seqs = int(self.block_tables.shape[0])
+        self.status = _scratch.get(dev, "status", 4, zero=True)
+        a = nv.AttnArgs()
+        a.queries = self.queries.data_ptr()
+        a.block_tables, a.kv_lens = self.block_tables.data_ptr(), self.kv_lens.data_ptr()
+        a.query_start_loc = self.query_start_loc.data_ptr()
+        a.total_tokens, a.num_seqs, a.num_q_heads = self.total, self.num_seqs, self.hq
+        a.max_blocks_per_seq, a.q_dtype = int(self.block_tables.shape[1]), nv.dtype_code(queries.dtype)
+        a.sliding_window, a.softmax_scale = self.window, self.scale
+        a.max_query_len = max(0, int(max_query_len))
+        a.status = self.status.data_ptr()
+        self.args = a
+        if self.kernel != "generic":
+            lib = nv.lib()
+            hkv = self.pool.num_kv_heads
+            self.plan_bytes = int(lib.emlx_attn_plan_bytes(self.num_seqs, self.total, self.hq, hkv))
+            ws_bytes = int(lib.emlx_attn_workspace_bytes(self.num_seqs, self.total, self.hq, hkv, self.d))
+            self.plan_buf = _scratch.get(dev, "plan", self.plan_bytes, zero=False)
+            self.workspace = _scratch.get(dev, "workspace", ws_bytes, zero=True)
+            a.plan, a.plan_bytes = self.plan_buf.data_ptr(), self.plan_bytes
+            a.workspace, a.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
+
+    def plan(self) -> "AttentionCall":
+        if self.total and self.kernel != "generic":
+            nv.check(nv.lib().emlx_attn_plan(
+                nv.ptr(self.query_start_loc), nv.ptr(self.kv_lens), self.num_seqs, self.total, self.hq,
+                self.pool.num_kv_heads, self.pool.block_size, self.window, nv.ptr(self.plan_buf), self.plan_bytes,
+                nv.stream_ptr(self.device)))
+        return self
+
+    def launch(self) -> torch.Tensor:
+        if self.total == 0:
+            return torch.zeros_like(self.queries)
+        lib = nv.lib()
+        self.out = torch.empty_like(self.queries)
+        self.args.out = self.out.data_ptr()
+        entry = {"generic": lib.emlx_attn_generic, "tiled": lib.emlx_attn_unified, "decode": lib.emlx_attn_decode,
+                 "prefill": lib.emlx_attn_prefill}[self.kernel]
+        nv.check(entry(self.args, self.pool, nv.stream_ptr(self.device)))
+        if _CHECK:
+            nv.check(lib.emlx_read_status(nv.ptr(self.status), nv.stream_ptr(self.device)))
+        return self.out
+
+
 def paged_attention(
     queries: torch.Tensor,
     key_cache: torch.Tensor,
@@ -147,6 +233,7 @@ def paged_attention(
     k_bias: torch.Tensor | None = None,
     v_bias: torch.Tensor | None = None,
     kernel: str | None = None,
+    max_query_len: int = 0,
 ) -> torch.Tensor:
     """Ragged causal attention of packed queries over a paged KV pool.
 
@@ -154,69 +241,17 @@ def paged_attention(
     ``block_tables`` / ``kv_lens`` hold one row per scheduled sequence.  ``use_metal``,
     ``threadgroup_size`` and ``allow_fallback`` are accepted and ignored.  For affine pools
     ``k_scale``/``v_scale`` are per-group fp16 arrays and ``k_bias``/``v_bias`` join them.
-    ``kernel`` (``None`` = automatic, ``"generic"``, ``"tiled"``, ``"decode"``, ``"prefill"``) selects
+    ``single_token_decode`` / ``max_query_len`` are host-side hints (an upper bound on the query tokens of
+    any sequence); without them the kernels for every row class are launched and the empty ones return at
+    once.  ``kernel`` (``None`` = automatic, ``"generic"``, ``"tiled"``, ``"decode"``, ``"prefill"``) selects
     an entry point explicitly; tests and benchmarks use it.
     """
     del use_metal, threadgroup_size, allow_fallback
-    nv.require_cuda(queries, key_cache, value_cache)
-    dev = queries.device
-    affine = key_cache.dtype == torch.uint8
-    block_tables = _as_int32(block_tables, dev)
-    kv_lens = _as_int32(kv_lens, dev)
-    query_start_loc = _as_int32(query_start_loc, dev)
-    _validate_inputs(queries, key_cache, value_cache, block_tables, kv_lens, query_start_loc, affine)
-
-    total, hq, d = int(queries.shape[0]), int(queries.shape[1]), int(queries.shape[2])
-    if softmax_scale is None:
-        softmax_scale = 1.0 / math.sqrt(d)
-    window = int(sliding_window or 0)
-    if total == 0:
-        return torch.zeros_like(queries)
-    if not (key_cache.is_contiguous() and value_cache.is_contiguous()):
-        raise ValueError("key_cache and value_cache must be contiguous")
-    queries = queries.contiguous()
-    pool, _ = _make_pool(key_cache, value_cache, d, k_scale, v_scale, k_bias, v_bias)
-    out = torch.empty_like(queries)
-    s = int(block_tables.shape[0])
-
-    tiled_ok = (
-        pool.block_size == _TILED_BLOCK_SIZE and d in _TILED_HEAD_DIMS
-        and queries.dtype in (torch.float16, torch.bfloat16)
-        and (affine or key_cache.dtype == queries.dtype)
-    )
-    if kernel is None:
-        kernel = "tiled" if tiled_ok else "generic"
-    if kernel != "generic" and not tiled_ok:
-        raise NotImplementedError(
-            "the tiled kernels need page size 128, head_dim 64 or 128, fp16/bf16 queries and a pool of the same "
-            "dtype (or an affine pool)")
-
-    lib, stream = nv.lib(), nv.stream_ptr(dev)
-    status = _scratch.get(dev, "status", 4, zero=True)
-    a = nv.AttnArgs()
-    a.queries, a.out = queries.data_ptr(), out.data_ptr()
-    a.block_tables, a.kv_lens, a.query_start_loc = block_tables.data_ptr(), kv_lens.data_ptr(), query_start_loc.data_ptr()
-    a.total_tokens, a.num_seqs, a.num_q_heads = total, s, hq
-    a.max_blocks_per_seq, a.q_dtype = int(block_tables.shape[1]), nv.dtype_code(queries.dtype)
-    a.sliding_window, a.softmax_scale = window, float(softmax_scale)
-    a.status = status.data_ptr()
-    if kernel == "generic":
-        nv.check(lib.emlx_attn_generic(a, pool, stream))
-    else:
-        hkv = pool.num_kv_heads
-        plan_bytes = int(lib.emlx_attn_plan_bytes(s, total, hq, hkv))
-        ws_bytes = int(lib.emlx_attn_workspace_bytes(s, total, hq, hkv, d))
-        plan = _scratch.get(dev, "plan", plan_bytes, zero=False)
-        ws = _scratch.get(dev, "workspace", ws_bytes, zero=True)
-        nv.check(lib.emlx_attn_plan(nv.ptr(query_start_loc), nv.ptr(kv_lens), s, total, hq, hkv, pool.block_size,
-                                    window, nv.ptr(plan), plan_bytes, stream))
-        a.plan, a.plan_bytes = plan.data_ptr(), plan_bytes
-        a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
-        entry = {"tiled": lib.emlx_attn_unified, "decode": lib.emlx_attn_decode, "prefill": lib.emlx_attn_prefill}[kernel]
-        nv.check(entry(a, pool, stream))
-    if _CHECK:
-        nv.check(lib.emlx_read_status(nv.ptr(status), stream))
-    return out
+    if single_token_decode and not max_query_len:
+        max_query_len = 1
+    return AttentionCall(queries, key_cache, value_cache, block_tables, kv_lens, query_start_loc,
+                         softmax_scale=softmax_scale, sliding_window=sliding_window, k_scale=k_scale, v_scale=v_scale,
+                         k_bias=k_bias, v_bias=v_bias, kernel=kernel, max_query_len=max_query_len).plan().launch()
 
 
 @OperationRegistry.register
@@ -266,9 +301,10 @@ class UnifiedAttention(BaseOperation):
         outputs = paged_attention(
             query, key, value, cache_metadata.block_tables, cache_metadata.kv_lens, cache_metadata.query_start_loc,
             softmax_scale=scale, sliding_window=cache_metadata.sliding_window,
-            single_token_decode=cache_metadata.is_single_token_decode, **extra,
+            single_token_decode=cache_metadata.is_single_token_decode,
+            max_query_len=int(getattr(cache_metadata, "max_query_len", 0) or 0), **extra,
         )
         return AttentionOutput(attention_outputs=outputs, cache_view=cache_view)
 
 
-__all__ = ("UnifiedAttention", "UnifiedAttnConfig", "UnifiedAttnMetadata", "paged_attention")
+__all__ = ("AttentionCall", "UnifiedAttention", "UnifiedAttnConfig", "UnifiedAttnMetadata", "paged_attention")

@@ -1,0 +1,80 @@
+"""One attention-layer step (KV write + metadata + attention) as a replayable CUDA graph.
+
+The reference compiles its single-token decode closure per (slots, query lengths) key with
+``mx.compile`` (``inference/esurge/runners/model_runner.py:744-856``) to get rid of per-launch host
+overhead; here the same role is played by capturing the step's kernels once in a CUDA graph and
+replaying it.  Inputs live in static device tensors that the caller overwrites between replays.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _native as nv
+from .caching.paged.cache import PageCacheView, PageMetadata, build_query_start_loc
+from .layers.attention import AttentionPerformer
+
+
+class AttentionStep:
+    """``step()`` = restore the slots' lengths, write the new K/V rows, attend.
+
+    ``rewind=True`` puts ``kv_lens`` back to their values at construction before every step, so that the
+    same batch can be replayed any number of times (benchmarks); a serving loop passes ``rewind=False``.
+    """
+
+    def __init__(self, cache: PageCacheView, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, query_lens,
+                 slot_ids, *, scale: float | None = None, sliding_window: int | None = None, rewind: bool = True):
+        self.cache = cache
+        self.q, self.k, self.v = q, k, v
+        self.query_lens = tuple(int(x) for x in query_lens)
+        self.slot_ids = tuple(int(x) for x in slot_ids)
+        self.performer = AttentionPerformer(scale=scale if scale is not None else float(q.shape[-1]) ** -0.5)
+        self.rewind = rewind
+        self._base_lens = cache.kv_lens.clone()
+        single = len(self.query_lens) == q.shape[0] and all(x == 1 for x in self.query_lens)
+        self._meta = PageMetadata(query_start_loc=build_query_start_loc(self.query_lens), slot_ids=self.slot_ids,
+                                  sliding_window=sliding_window, is_single_token_decode=single)
+        self._meta_lens = None if single else self.query_lens
+        self.out: torch.Tensor | None = None
+        self.graph: torch.cuda.CUDAGraph | None = None
+        self.launches_per_step = 0
+
+    def _eager(self) -> torch.Tensor:
+        if self.rewind:
+            self.cache.kv_lens.copy_(self._base_lens)
+        if self._meta_lens is None:
+            return self.performer(self.q, self.k, self.v, cache_view=self.cache, cache_metadata=self._meta)
+        _, kc, vc, meta = self.cache.concatenate_to_cache(self.q, self.k, self.v, cache_metadata=self._meta,
+                                                          slot_ids=self.slot_ids, query_lens=self._meta_lens)
+        op = self.performer.executor.mixin_impl
+        return op(query=self.q, key=kc, value=vc, cache_metadata=meta, cache_view=self.cache,
+                  scale=self.performer.scale).attention_outputs
+
+    def capture(self, warmup: int = 3) -> "AttentionStep":
+        """Run the step eagerly a few times on a side stream, then record it into a CUDA graph."""
+        side = torch.cuda.Stream(device=self.q.device)
+        side.wait_stream(torch.cuda.current_stream(self.q.device))
+        with torch.cuda.stream(side):
+            for _ in range(max(1, warmup)):
+                self.out = self._eager()
+        torch.cuda.current_stream(self.q.device).wait_stream(side)
+        torch.cuda.synchronize(self.q.device)
+        graph = torch.cuda.CUDAGraph()
+        before = nv.launch_count()
+        with torch.cuda.graph(graph):
+            self.out = self._eager()
+        self.launches_per_step = nv.launch_count() - before
+        self.graph = graph
+        return self
+
+    def step(self) -> torch.Tensor:
+        if self.graph is not None:
+            self.graph.replay()
+            return self.out
+        before = nv.launch_count()
+        self.out = self._eager()
+        self.launches_per_step = nv.launch_count() - before
+        return self.out
+
+
+__all__ = ("AttentionStep",)

@@ -89,7 +89,7 @@ typedef struct emlx_attn_args {
     int32_t q_dtype;                /* emlx_dtype                                     */
     int32_t sliding_window;         /* 0 = off                                        */
     float softmax_scale;
-    int32_t reserved;
+    int32_t max_query_len;          /* host hint: upper bound of query tokens per sequence, 0 = unknown */
     void* plan;                     /* from emlx_attn_plan (not used by emlx_attn_generic)        */
     size_t plan_bytes;
     void* workspace;                /* split-KV partials and counters; zero it once after allocating */
