@@ -53,7 +53,7 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
         subprocess.run(cmd, check=True)
         rebuilt = True
     if rebuilt or not os.path.exists(LIB):
-        cmd = [_nvcc(), "-shared", "-o", LIB, *objects, "-lcuda"]
+        cmd = [_nvcc(), "-shared", "-o", LIB, *objects]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)

@@ -186,7 +186,10 @@ class PageCacheView:
 
     def check(self) -> None:
         """Synchronise and raise if any kernel that used this cache flagged a bad slot / page / overflow."""
-        nv.check(nv.lib().emlx_read_status(nv.ptr(self.status), nv.stream_ptr(self.key_cache.device)))
+        rc = nv.lib().emlx_read_status(nv.ptr(self.status), nv.stream_ptr(self.key_cache.device))
+        if rc != nv.EMLX_OK:
+            self.status.zero_()  # report once
+        nv.check(rc)
 
     def _validate_shape(self) -> None:
         if self.block_tables.ndim != 2:

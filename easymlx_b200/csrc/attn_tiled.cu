@@ -1,11 +1,916 @@
-// placeholder: tiled kernels arrive next; the unified entry routes to the coverage kernel
-#include "common.cuh"
-namespace emlx { int validate_attn(const emlx_attn_args* a, const emlx_pool* pool, bool need_plan); }
+// Tiled ragged paged attention for B200: split-KV flash-decode and short-row (spec-verify, prefill
+// chunk) attention over 128-token pages, fp16/bf16 pools and affine 8/4-bit pools with fused dequant.
+//
+// One persistent CTA per SM walks a contiguous slice of the flat (unit, kv head, tile) work list.
+// A producer warp stages K/V tiles into a shared-memory ring with TMA (tile mode, this GPU's own
+// memory, no multicast) and mbarriers; eight consumer warps run
+//     phase 1   S^T[128 tokens x rows] = K_tile . Q^T      (mma.sync m16n8k16; tokens on M, all GQA
+//                                                           rows of the KV head on N, 16 tokens per warp)
+//               online softmax (tile max through shared atomics), P^T to shared memory
+//     phase 2   O^T[D x rows] += V_tile^T . P^T            (each warp owns a 16-wide slice of D)
+// so that one page read serves every query row of its KV head.  A slice that ends inside a
+// (unit, head) writes an un-normalised partial; the CTA that delivers the last partial merges all of
+// them in CTA order (deterministic), so no CTA ever waits for another.
+#include "attn_tiled.cuh"
+#include "ptx.cuh"
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace emlx {
+
+int validate_attn(const emlx_attn_args* a, const emlx_pool* pool, bool need_plan);
+
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kPStride = kTile * 2 + 16;  // bytes per row of a P buffer (padding keeps ldmatrix conflict-free)
+constexpr int kSmemBudget = 227 * 1024 - 1024;  // dynamic shared memory minus alignment slack
+
+struct TiledParams {
+    const void* q;
+    void* out;
+    const int32_t* bt;
+    const int32_t* kv_lens;
+    const int32_t* qsl;
+    const int32_t* hdr;  // [0] = units, [1] = tiles per head (sum over units)
+    const int32_t* unit_seq;
+    const int32_t* unit_row0;
+    const int32_t* unit_tile_lo;
+    const int32_t* unit_cum;
+    int32_t* counters;
+    float* slots;
+    int32_t* status;
+    const __half* k_scale;
+    const __half* k_bias;
+    const __half* v_scale;
+    const __half* v_bias;
+    long long num_blocks;
+    int Hq, Hkv, G, MB, window;
+    float scale_log2e;
+};
+
+template <int D, int NT, int FMT>
+struct Cfg {
+    static constexpr int ROWS = 8 * NT;
+    static constexpr int KROW = FMT == 0 ? 128 : D * FMT / 8;           // bytes per smem row of the K tile
+    static constexpr int KBYTES = FMT == 0 ? kTile * D * 2 : kTile * KROW;
+    static constexpr int VROW = FMT == 0 ? 128 : kTile * FMT / 8;      // V: [tok][d] halves, or V^T: [d][tok bytes]
+    static constexpr int VBYTES = FMT == 0 ? kTile * D * 2 : D * VROW;
+    static constexpr int GROUPS = D / 64;
+    static constexpr int SB1 = kTile * GROUPS * 2;                       // one scale (or bias) tile
+    static constexpr int SBBYTES = FMT == 0 ? 0 : 4 * SB1;
+    static constexpr int STAGE = KBYTES + VBYTES + SBBYTES;
+    static constexpr int KSW = KROW == 128 ? 3 : (KROW == 64 ? 2 : 1);  // swizzle bits of the K tile
+    static constexpr int VSW = VROW == 128 ? 3 : (VROW == 64 ? 2 : 1);
+    static constexpr int DSL = D / 16;                                   // 16-wide slices of D
+    static constexpr int TS = kConsumerWarps / DSL;                      // warps sharing a slice split the tokens
+    static constexpr int NPBUF = FMT == 0 ? 1 : GROUPS;
+    static constexpr int PBYTES = NPBUF * ROWS * kPStride;
+    static constexpr int OREDBYTES = TS > 1 ? kConsumerWarps * 16 * ROWS * 4 : 0;
+    static constexpr int FIXED = PBYTES + OREDBYTES + 2 * 32 * 4 + 3 * kConsumerWarps * 32 * 4 + 64 + 2 * 8 * 8;
+    static constexpr int STAGES_RAW = (kSmemBudget - FIXED) / STAGE;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int SMEM = STAGES * STAGE + FIXED + 1024;
+    static_assert(STAGES >= 2, "shared memory holds fewer than two stages");
+};
+
+// ordered-int encoding so that atomicMax on ints orders floats
+__device__ __forceinline__ int f2ord(float f) {
+    int i = __float_as_int(f);
+    return i >= 0 ? i : i ^ 0x7fffffff;
+}
+__device__ __forceinline__ float ord2f(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7fffffff); }
+
+struct Walk {
+    int u, head, j, ntiles;
+    __device__ __forceinline__ void locate(long long f, const int32_t* cum, int num_units, int Hkv) {
+        int lo = 0, hi = num_units;  // cum[lo]*Hkv <= f < cum[hi]*Hkv
+        while (hi - lo > 1) {
+            int mid = (lo + hi) >> 1;
+            if ((long long)cum[mid] * Hkv <= f) lo = mid; else hi = mid;
+        }
+        u = lo;
+        ntiles = cum[u + 1] - cum[u];
+        long long rem = f - (long long)cum[u] * Hkv;
+        head = (int)(rem / ntiles);
+        j = (int)(rem - (long long)head * ntiles);
+    }
+    __device__ __forceinline__ void next_part(const int32_t* cum, int num_units, int Hkv) {
+        j = 0;
+        if (++head == Hkv) {
+            head = 0;
+            ++u;
+            if (u < num_units) ntiles = cum[u + 1] - cum[u];
+        }
+    }
+};
+
+// ------------------------------------------------------------------------------------------ producer
+template <int D, int NT, int FMT>
+__device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUtensorMap* vmap, const TiledParams& p,
+                                              uint8_t* stages, uint64_t* full, uint64_t* empty, volatile int* abort_word,
+                                              long long f_begin, long long f_end, int num_units) {
+    using C = Cfg<D, NT, FMT>;
+    const int lane = threadIdx.x & 31;
+    Walk w;
+    w.locate(f_begin, p.unit_cum, num_units, p.Hkv);
+    long long f = f_begin;
+    uint32_t it = 0;
+    while (f < f_end && !*abort_word) {
+        const int seq = p.unit_seq[w.u];
+        const int tile_lo = p.unit_tile_lo[w.u];
+        const int kv_len = p.kv_lens[seq];
+        const int run = (int)min((long long)(w.ntiles - w.j), f_end - f);
+        for (int base = 0; base < run; base += 32) {
+            const int idx = tile_lo + w.j + base + lane;
+            int page = -1;
+            if (base + lane < run && idx < p.MB) page = p.bt[(long long)seq * p.MB + idx];
+            const int cnt = min(32, run - base);
+            for (int i = 0; i < cnt; ++i) {
+                int pg = __shfl_sync(0xffffffffu, page, i);
+                const uint32_t stage = it % C::STAGES, use = it / C::STAGES;
+                if (use > 0) ptx::mbar_wait(&empty[stage], (use & 1) ^ 1, abort_word);
+                if (lane == 0 && !*abort_word) {
+                    const bool bad = pg < 0 || pg >= p.num_blocks;
+                    if (bad && (long long)(tile_lo + w.j + base + i) * kTile < kv_len) flag_error(p.status, EMLX_DEV_BAD_PAGE);
+                    uint8_t* st = stages + (size_t)stage * C::STAGE;
+                    ptx::mbar_arrive_expect_tx(&full[stage], C::STAGE);
+                    if constexpr (FMT == 0) {
+                        // a page id outside the pool gives out-of-range coordinates: the tile is zero-filled
+                        const int tok0 = bad ? -kTile : pg * kTile;
+#pragma unroll
+                        for (int h = 0; h < D / 64; ++h) {
+                            ptx::tma_load_3d(st + h * (kTile * 128), kmap, &full[stage], 64 * h, w.head, tok0);
+                            ptx::tma_load_3d(st + C::KBYTES + h * (kTile * 128), vmap, &full[stage], 64 * h, w.head, tok0);
+                        }
+                    } else {
+                        const long long pgc = bad ? 0 : pg;  // keep every address inside the pool; such tiles are masked
+                        ptx::tma_load_3d(st, kmap, &full[stage], 0, w.head, (int)(pgc * kTile));
+                        ptx::tma_load_2d(st + C::KBYTES, vmap, &full[stage], 0, (int)((pgc * p.Hkv + w.head) * D));
+                        const long long sb = (pgc * p.Hkv + w.head) * (long long)(kTile * C::GROUPS);
+                        uint8_t* sbs = st + C::KBYTES + C::VBYTES;
+                        ptx::bulk_load(sbs + 0 * C::SB1, p.k_scale + sb, C::SB1, &full[stage]);
+                        ptx::bulk_load(sbs + 1 * C::SB1, p.k_bias + sb, C::SB1, &full[stage]);
+                        ptx::bulk_load(sbs + 2 * C::SB1, p.v_scale + sb, C::SB1, &full[stage]);
+                        ptx::bulk_load(sbs + 3 * C::SB1, p.v_bias + sb, C::SB1, &full[stage]);
+                    }
+                }
+                __syncwarp();
+                ++it;
+            }
+        }
+        f += run;
+        w.next_part(p.unit_cum, num_units, p.Hkv);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ consumers
+template <bool BF16> __device__ __forceinline__ uint16_t to_bits16(float v) {
+    if constexpr (BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(v));
+    else return __half_as_ushort(__float2half_rn(v));
+}
+__device__ __forceinline__ float quad_column_max(float v) {  // over the 8 lanes that share lane%4
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+    return fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+}
+__device__ __forceinline__ float quad_column_sum(float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    return v + __shfl_xor_sync(0xffffffffu, v, 16);
+}
+__device__ __forceinline__ void consumer_sync() { ptx::named_barrier(1, kConsumerThreads); }
+
+// 8 nibbles of x -> four half2 registers holding (n0,n2) (n4,n6) (n1,n3) (n5,n7) as fp16 bit patterns 0x000c
+__device__ __forceinline__ void nibbles_to_h2(uint32_t x, uint32_t (&h)[4]) {
+    const uint32_t lo = x & 0x0F0F0F0Fu, hi = (x >> 4) & 0x0F0F0F0Fu;
+    h[0] = ptx::prmt(lo, 0u, 0x4140u);
+    h[1] = ptx::prmt(lo, 0u, 0x4342u);
+    h[2] = ptx::prmt(hi, 0u, 0x4140u);
+    h[3] = ptx::prmt(hi, 0u, 0x4342u);
+}
+
+constexpr float kTwo24 = 16777216.0f;  // codes enter the MMA as fp16 subnormals c * 2^-24
+
+template <int D, int NT, int FMT, bool BF16>
+__device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* stages, uint8_t* fixed, uint64_t* full,
+                                              uint64_t* empty, volatile int* abort_word, long long f_begin,
+                                              long long f_end, int num_units, long long total_flat, long long active) {
+    using C = Cfg<D, NT, FMT>;
+    constexpr int KS = D / 16, ROWS = C::ROWS, GROUPS = C::GROUPS;
+    constexpr int NG = FMT == 0 ? 1 : GROUPS;  // accumulator sets of phase 1
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int ds = warp % C::DSL, ts = warp / C::DSL;
+    const int jd = FMT == 0 ? 0 : (16 * ds) / 64;  // scale group of this warp's slice of D
+
+    uint8_t* Ps = fixed;
+    float* ored = (float*)(fixed + C::PBYTES);
+    int* tmax = (int*)(fixed + C::PBYTES + C::OREDBYTES);
+    float* wl = (float*)(tmax + 64);
+    float* wb = wl + kConsumerWarps * 32;  // [2][warps][32]
+    int* misc = (int*)(wb + 2 * kConsumerWarps * 32);
+    const int ORD_NEG_INF = f2ord(-INFINITY);
+
+    Walk w;
+    w.locate(f_begin, p.unit_cum, num_units, p.Hkv);
+    long long f = f_begin;
+    uint32_t it = 0;
+    const uint32_t ps_base = ptx::smem_u32(Ps);
+
+    while (f < f_end) {
+        // ------------------------------------------------------------------ begin a (unit, head) part
+        const int seq = p.unit_seq[w.u], row0 = p.unit_row0[w.u], tile_lo = p.unit_tile_lo[w.u];
+        const int qs = p.qsl[seq], q_len = p.qsl[seq + 1] - qs, kv_len = p.kv_lens[seq];
+        const int R = q_len * p.G, ctx = kv_len - q_len, head = w.head;
+        const int run = (int)min((long long)(w.ntiles - w.j), f_end - f);
+        const int rows_here = min(ROWS, R - row0);
+
+        int row_hi[NT][2], row_lo[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int rr = min(row0 + 8 * nt + 2 * t + e, R - 1);  // padding rows mirror the last real row
+                const int i = rr / p.G;
+                int hi = min(kv_len, ctx + i + 1);
+                int lo = p.window > 0 ? max(0, min(kv_len - 1, ctx + i) - p.window + 1) : 0;
+                if (hi <= 0) { hi = 0; lo = 0; }
+                row_hi[nt][e] = hi;
+                row_lo[nt][e] = lo;
+            }
+        const int i_first = row0 / p.G, i_last = (row0 + rows_here - 1) / p.G;
+        const int hi_min = min(kv_len, ctx + i_first + 1);
+        const int lo_max = p.window > 0 ? max(0, min(kv_len - 1, ctx + i_last) - p.window + 1) : 0;
+
+        // Q^T fragments (B operand): rows on N, head_dim on K in the order the K tile is read
+        uint32_t qf[KS][NT][2];
+        float qsum[NG][NT][2];
+        {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int r = row0 + 8 * nt + g;
+                const bool ok = r < R;
+                const int i = ok ? r / p.G : 0, hh = ok ? r - i * p.G : 0;
+                const uint16_t* qrow = (const uint16_t*)p.q + ((long long)(qs + i) * p.Hq + head * p.G + hh) * D;
+                if constexpr (FMT == 0) {
+#pragma unroll
+                    for (int ks = 0; ks < KS; ++ks) {
+                        qf[ks][nt][0] = ok ? *(const uint32_t*)(qrow + 16 * ks + 2 * t) : 0u;
+                        qf[ks][nt][1] = ok ? *(const uint32_t*)(qrow + 16 * ks + 2 * t + 8) : 0u;
+                    }
+                } else if constexpr (FMT == 8) {
+#pragma unroll
+                    for (int ks = 0; ks < KS; ++ks) {
+                        const int d0 = 64 * (ks >> 2) + 16 * t + 4 * (ks & 3);
+                        const uint2 v = ok ? *(const uint2*)(qrow + d0) : make_uint2(0u, 0u);
+                        qf[ks][nt][0] = v.x;
+                        qf[ks][nt][1] = v.y;
+                    }
+                } else {
+#pragma unroll
+                    for (int jx = 0; jx < KS / 2; ++jx) {  // (group j, word x) -> k-steps 2*jx, 2*jx+1
+                        const int db = 64 * (jx >> 1) + 16 * t + 8 * (jx & 1);
+                        const uint4 v = ok ? *(const uint4*)(qrow + db) : make_uint4(0u, 0u, 0u, 0u);
+                        qf[2 * jx][nt][0] = ptx::prmt(v.x, v.y, 0x5410u);      // (q0, q2)
+                        qf[2 * jx][nt][1] = ptx::prmt(v.z, v.w, 0x5410u);      // (q4, q6)
+                        qf[2 * jx + 1][nt][0] = ptx::prmt(v.x, v.y, 0x7632u);  // (q1, q3)
+                        qf[2 * jx + 1][nt][1] = ptx::prmt(v.z, v.w, 0x7632u);  // (q5, q7)
+                    }
+                }
+            }
+            if constexpr (FMT != 0) {
+                // column sums of Q per scale group through an all-ones A operand: c[e] = sum_d q[row 2t+e][d]
+                const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
+#pragma unroll
+                for (int j = 0; j < NG; ++j)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        float c[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                        for (int s = 0; s < 4; ++s) ptx::mma_16816<false>(c, ones, qf[4 * j + s][nt]);
+                        qsum[j][nt][0] = c[0];
+                        qsum[j][nt][1] = c[1];
+                    }
+            }
+        }
+
+        float m[NT][2], l[NT][2], o[NT][4], bsum[NG][NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            m[nt][0] = m[nt][1] = -INFINITY;
+            l[nt][0] = l[nt][1] = 0.f;
+            o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+#pragma unroll
+            for (int j = 0; j < NG; ++j) bsum[j][nt][0] = bsum[j][nt][1] = 0.f;
+        }
+
+        // ------------------------------------------------------------------ tiles of this part
+        for (int jj = 0; jj < run; ++jj, ++it) {
+            const uint32_t stage = it % C::STAGES, buf = it & 1;
+            uint8_t* st = stages + (size_t)stage * C::STAGE;
+            const uint32_t ks_base = ptx::smem_u32(st), vs_base = ks_base + C::KBYTES;
+            const __half* sbs = (const __half*)(st + C::KBYTES + C::VBYTES);  // [4][128][GROUPS]
+            const int t0 = (tile_lo + w.j + jj) * kTile;
+            const bool interior = (t0 + kTile <= hi_min) && (t0 >= lo_max);
+            ptx::mbar_wait(&full[stage], (it / C::STAGES) & 1, abort_word);
+
+            // ---- phase 1: S^T = K . Q^T for this warp's 16 tokens
+            float s[NT][4];
+            const int tokA = 16 * warp + g, tokB = tokA + 8;
+            if constexpr (FMT == 0) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks) {
+                    const uint32_t off = (uint32_t)((ks >> 2) * (kTile * 128) + (16 * warp + (lane & 15)) * 128 +
+                                                    ((ks & 3) * 2 + (lane >> 4)) * 16);
+                    uint32_t a[4];
+                    ptx::ldmatrix_x4(a, ks_base + ptx::swz<3>(off));
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) ptx::mma_16816<BF16>(s[nt], a, qf[ks][nt]);
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) s[nt][c] *= p.scale_log2e;
+            } else {
+                float acc[NG][NT][4];
+#pragma unroll
+                for (int j = 0; j < NG; ++j)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) acc[j][nt][0] = acc[j][nt][1] = acc[j][nt][2] = acc[j][nt][3] = 0.f;
+#pragma unroll
+                for (int j = 0; j < NG; ++j) {
+                    if constexpr (FMT == 8) {
+                        const uint32_t offA = (uint32_t)(tokA * C::KROW + 64 * j + 16 * t);
+                        const uint32_t offB = offA + 8 * C::KROW;
+                        const uint4 xa = *(const uint4*)(st + ptx::swz<C::KSW>(offA));
+                        const uint4 xb = *(const uint4*)(st + ptx::swz<C::KSW>(offB));
+                        const uint32_t wa[4] = {xa.x, xa.y, xa.z, xa.w}, wbv[4] = {xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                        for (int sidx = 0; sidx < 4; ++sidx) {
+                            uint32_t a[4];
+                            a[0] = ptx::prmt(wa[sidx], 0u, 0x4140u);
+                            a[1] = ptx::prmt(wbv[sidx], 0u, 0x4140u);
+                            a[2] = ptx::prmt(wa[sidx], 0u, 0x4342u);
+                            a[3] = ptx::prmt(wbv[sidx], 0u, 0x4342u);
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) ptx::mma_16816<false>(acc[j][nt], a, qf[4 * j + sidx][nt]);
+                        }
+                    } else {
+                        const uint32_t offA = (uint32_t)(tokA * C::KROW + 32 * j + 8 * t);
+                        const uint32_t offB = offA + 8 * C::KROW;
+                        const uint2 xa = *(const uint2*)(st + ptx::swz<C::KSW>(offA));
+                        const uint2 xb = *(const uint2*)(st + ptx::swz<C::KSW>(offB));
+                        const uint32_t wa[2] = {xa.x, xa.y}, wbv[2] = {xb.x, xb.y};
+#pragma unroll
+                        for (int x = 0; x < 2; ++x) {
+                            uint32_t ha[4], hb[4];
+                            nibbles_to_h2(wa[x], ha);
+                            nibbles_to_h2(wbv[x], hb);
+#pragma unroll
+                            for (int y = 0; y < 2; ++y) {
+                                const uint32_t a[4] = {ha[2 * y], hb[2 * y], ha[2 * y + 1], hb[2 * y + 1]};
+#pragma unroll
+                                for (int nt = 0; nt < NT; ++nt)
+                                    ptx::mma_16816<false>(acc[j][nt], a, qf[4 * j + 2 * x + y][nt]);
+                            }
+                        }
+                    }
+                }
+                // S = sum_j scale_j[tok] * (2^24 * acc_j) + bias_j[tok] * qsum_j
+                float ksA[NG], ksB[NG], kbA[NG], kbB[NG];
+#pragma unroll
+                for (int j = 0; j < NG; ++j) {
+                    ksA[j] = __half2float(sbs[0 * kTile * GROUPS + tokA * GROUPS + j]) * kTwo24;
+                    ksB[j] = __half2float(sbs[0 * kTile * GROUPS + tokB * GROUPS + j]) * kTwo24;
+                    kbA[j] = __half2float(sbs[1 * kTile * GROUPS + tokA * GROUPS + j]);
+                    kbB[j] = __half2float(sbs[1 * kTile * GROUPS + tokB * GROUPS + j]);
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        float v = 0.f;
+#pragma unroll
+                        for (int j = 0; j < NG; ++j)
+                            v += (c < 2 ? ksA[j] : ksB[j]) * acc[j][nt][c] + (c < 2 ? kbA[j] : kbB[j]) * qsum[j][nt][c & 1];
+                        s[nt][c] = v * p.scale_log2e;
+                    }
+            }
+            if (!interior) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int tok = t0 + (c < 2 ? tokA : tokB);
+                        if (tok < row_lo[nt][c & 1] || tok >= row_hi[nt][c & 1]) s[nt][c] = -INFINITY;
+                    }
+            }
+            // tile maximum per row: own 16 tokens, then all warps through shared atomics
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float mx = quad_column_max(fmaxf(s[nt][e], s[nt][2 + e]));
+                    if (g == 0) atomicMax(&tmax[buf * 32 + 8 * nt + 2 * t + e], f2ord(mx));
+                }
+            if constexpr (FMT == 0) {
+                // rows of V past the sequence end are stale memory: clear them so that 0 * garbage cannot be NaN
+                if (t0 + kTile > kv_len) {
+                    const int first = max(0, kv_len - t0);
+                    for (int c = lane; c < 16 * (D / 8); c += 32) {
+                        const int tok = 16 * warp + c / (D / 8), ch = c % (D / 8);
+                        if (tok >= first)
+                            *(uint4*)(st + C::KBYTES + (ch >> 3) * (kTile * 128) + tok * 128 + (ch & 7) * 16) =
+                                make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    ptx::fence_proxy_async();
+                }
+            }
+            consumer_sync();
+            if (warp == 0) tmax[(buf ^ 1) * 32 + lane] = ORD_NEG_INF;
+
+            float corr[NT][2];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const float m_new = fmaxf(m[nt][e], ord2f(tmax[buf * 32 + 8 * nt + 2 * t + e]));
+                    const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+                    corr[nt][e] = exp2f(m[nt][e] - m_safe);
+                    m[nt][e] = m_new;
+                    const float pA = exp2f(s[nt][e] - m_safe), pB = exp2f(s[nt][2 + e] - m_safe);
+                    l[nt][e] = l[nt][e] * corr[nt][e] + pA + pB;
+                    s[nt][e] = pA;
+                    s[nt][2 + e] = pB;
+                }
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) o[nt][c] *= corr[nt][c & 1];
+
+            // P^T to shared memory, rows x tokens
+            if constexpr (FMT == 0) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int row = 8 * nt + 2 * t + (c & 1), tok = c < 2 ? tokA : tokB;
+                        *(uint16_t*)(Ps + row * kPStride + tok * 2) = to_bits16<BF16>(s[nt][c]);
+                    }
+            } else {
+                float vsA[NG], vsB[NG], vbA[NG], vbB[NG];
+#pragma unroll
+                for (int j = 0; j < NG; ++j) {
+                    vsA[j] = __half2float(sbs[2 * kTile * GROUPS + tokA * GROUPS + j]);
+                    vsB[j] = __half2float(sbs[2 * kTile * GROUPS + tokB * GROUPS + j]);
+                    vbA[j] = __half2float(sbs[3 * kTile * GROUPS + tokA * GROUPS + j]);
+                    vbB[j] = __half2float(sbs[3 * kTile * GROUPS + tokB * GROUPS + j]);
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int e = c & 1, row = 8 * nt + 2 * t + e, tok = c < 2 ? tokA : tokB;
+                        const float pv = s[nt][c];
+                        // 4-bit values are read eight tokens per word as (0,2)(4,6)(1,3)(5,7): store P in that order
+                        const int pos = FMT == 8 ? tok : (tok & ~7) + ((tok & 1) ? 4 + ((tok & 7) >> 1) : ((tok & 7) >> 1));
+#pragma unroll
+                        for (int j = 0; j < NG; ++j) {
+                            // stale scale/bias bytes of unwritten slots may be NaN: select, do not multiply by zero
+                            const float sc = pv > 0.f ? pv * (c < 2 ? vsA[j] : vsB[j]) : 0.f;
+                            const float bi = pv > 0.f ? pv * (c < 2 ? vbA[j] : vbB[j]) : 0.f;
+                            *(uint16_t*)(Ps + (j * ROWS + row) * kPStride + pos * 2) = __half_as_ushort(__float2half_rn(sc));
+                            if (c < 2) bsum[j][nt][e] = bsum[j][nt][e] * corr[nt][e] + bi;
+                            else bsum[j][nt][e] += bi;
+                        }
+                    }
+            }
+            consumer_sync();
+
+            // ---- phase 2: O^T[16 x rows] += V^T[16 x tokens] . P^T[tokens x rows] for this warp's slice of D
+            if constexpr (FMT == 0) {
+                constexpr int STEPS = kTile / C::TS / 16;
+#pragma unroll
+                for (int kk = 0; kk < STEPS; ++kk) {
+                    const int tok0 = ts * (kTile / C::TS) + 16 * kk;
+                    const int tok = tok0 + (lane & 7) + 8 * (lane >> 4);
+                    const int ch = 2 * ds + ((lane >> 3) & 1);  // 16-byte chunk of the row (8 halves of D)
+                    const uint32_t off = (uint32_t)((ch >> 3) * (kTile * 128) + tok * 128 + (ch & 7) * 16);
+                    uint32_t a[4];
+                    ptx::ldmatrix_x4_trans(a, vs_base + ptx::swz<3>(off));
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        uint32_t b[2];
+                        ptx::ldmatrix_x2(b, ps_base + (8 * nt + (lane & 7)) * kPStride + (tok0 + 8 * ((lane >> 3) & 1)) * 2);
+                        ptx::mma_16816<BF16>(o[nt], a, b);
+                    }
+                }
+            } else {
+                const int dA = 16 * ds + g, dB = dA + 8;
+#pragma unroll
+                for (int Jx = 0; Jx < (kTile / 64) / C::TS; ++Jx) {
+                    const int J = C::TS > 1 ? ts : Jx;  // block of 64 tokens
+                    if constexpr (FMT == 8) {
+                        const uint4 xa = *(const uint4*)(st + C::KBYTES + ptx::swz<C::VSW>((uint32_t)(dA * C::VROW + 64 * J + 16 * t)));
+                        const uint4 xb = *(const uint4*)(st + C::KBYTES + ptx::swz<C::VSW>((uint32_t)(dB * C::VROW + 64 * J + 16 * t)));
+                        const uint32_t wa[4] = {xa.x, xa.y, xa.z, xa.w}, wbv[4] = {xb.x, xb.y, xb.z, xb.w};
+#pragma unroll
+                        for (int sidx = 0; sidx < 4; ++sidx) {
+                            uint32_t a[4];
+                            a[0] = ptx::prmt(wa[sidx], 0u, 0x4140u);
+                            a[1] = ptx::prmt(wbv[sidx], 0u, 0x4140u);
+                            a[2] = ptx::prmt(wa[sidx], 0u, 0x4342u);
+                            a[3] = ptx::prmt(wbv[sidx], 0u, 0x4342u);
+                            const int tok0 = 64 * J + 16 * t + 4 * sidx;
+#pragma unroll
+                            for (int nt = 0; nt < NT; ++nt) {
+                                const uint2 bv = *(const uint2*)(Ps + (jd * ROWS + 8 * nt + g) * kPStride + tok0 * 2);
+                                const uint32_t b[2] = {bv.x, bv.y};
+                                ptx::mma_16816<false>(o[nt], a, b);
+                            }
+                        }
+                    } else {
+                        const uint2 xa = *(const uint2*)(st + C::KBYTES + ptx::swz<C::VSW>((uint32_t)(dA * C::VROW + 32 * J + 8 * t)));
+                        const uint2 xb = *(const uint2*)(st + C::KBYTES + ptx::swz<C::VSW>((uint32_t)(dB * C::VROW + 32 * J + 8 * t)));
+                        const uint32_t wa[2] = {xa.x, xa.y}, wbv[2] = {xb.x, xb.y};
+#pragma unroll
+                        for (int x = 0; x < 2; ++x) {
+                            uint32_t ha[4], hb[4];
+                            nibbles_to_h2(wa[x], ha);
+                            nibbles_to_h2(wbv[x], hb);
+#pragma unroll
+                            for (int y = 0; y < 2; ++y) {
+                                const uint32_t a[4] = {ha[2 * y], hb[2 * y], ha[2 * y + 1], hb[2 * y + 1]};
+                                const int pos0 = 64 * J + 16 * t + 8 * x + 4 * y;
+#pragma unroll
+                                for (int nt = 0; nt < NT; ++nt) {
+                                    const uint2 bv = *(const uint2*)(Ps + (jd * ROWS + 8 * nt + g) * kPStride + pos0 * 2);
+                                    const uint32_t b[2] = {bv.x, bv.y};
+                                    ptx::mma_16816<false>(o[nt], a, b);
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&empty[stage]);
+        }
+
+        // ------------------------------------------------------------------ end of the part
+        // row sums (and the values' bias terms) across this warp's tokens, then across warps in a fixed order
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float v = quad_column_sum(l[nt][e]);
+                if (g == 0) wl[warp * 32 + 8 * nt + 2 * t + e] = v;
+                if constexpr (FMT != 0) {
+#pragma unroll
+                    for (int j = 0; j < NG; ++j) {
+                        const float bv = quad_column_sum(bsum[j][nt][e]);
+                        if (g == 0) wb[(j * kConsumerWarps + warp) * 32 + 8 * nt + 2 * t + e] = bv;
+                    }
+                }
+            }
+        if constexpr (C::TS > 1) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) ored[(warp * NT * 4 + nt * 4 + c) * 32 + lane] = o[nt][c];
+        }
+        consumer_sync();
+        float lsum[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float v = 0.f, bv = 0.f;
+#pragma unroll
+                for (int ww = 0; ww < kConsumerWarps; ++ww) {
+                    v += wl[ww * 32 + 8 * nt + 2 * t + e];
+                    if constexpr (FMT != 0) bv += wb[(jd * kConsumerWarps + ww) * 32 + 8 * nt + 2 * t + e];
+                }
+                lsum[nt][e] = v;
+                if constexpr (FMT != 0) {
+                    o[nt][e] = o[nt][e] * kTwo24 + bv;
+                    o[nt][2 + e] = o[nt][2 + e] * kTwo24 + bv;
+                }
+            }
+        if constexpr (C::TS > 1) {
+            if (ts == 0) {
+#pragma unroll
+                for (int k = 1; k < C::TS; ++k)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            float other = ored[((warp + k * C::DSL) * NT * 4 + nt * 4 + c) * 32 + lane];
+                            if constexpr (FMT != 0) other *= kTwo24;
+                            o[nt][c] += other;
+                        }
+            }
+        }
+
+        const long long a_flat = (long long)p.unit_cum[w.u] * p.Hkv + (long long)head * w.ntiles;
+        const long long b_flat = a_flat + w.ntiles;
+        const bool complete = (w.j == 0) && (run == w.ntiles);
+        const uint16_t* qbase = (const uint16_t*)p.q;
+        (void)qbase;
+        if (complete) {
+            // normalise, stage as [row][D] in the P buffer, store rows with 16-byte accesses
+            if (ts == 0) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int e = c & 1, row = 8 * nt + 2 * t + e, d = 16 * ds + g + 8 * (c >> 1);
+                        const float inv = lsum[nt][e] > 0.f ? 1.0f / lsum[nt][e] : 0.f;
+                        *(uint16_t*)(Ps + row * kPStride + d * 2) = to_bits16<BF16>(o[nt][c] * inv);
+                    }
+            }
+            consumer_sync();
+            constexpr int CH = D / 8;
+            for (int idx = tid; idx < ROWS * CH; idx += kConsumerThreads) {
+                const int row = idx / CH, ch = idx - row * CH, r = row0 + row;
+                if (r < R) {
+                    const int i = r / p.G, hh = r - i * p.G;
+                    uint16_t* dst = (uint16_t*)p.out + ((long long)(qs + i) * p.Hq + head * p.G + hh) * D + ch * 8;
+                    *(uint4*)dst = *(const uint4*)(Ps + row * kPStride + ch * 16);
+                }
+            }
+        } else {
+            // un-normalised partial into this CTA's slot; the CTA that delivers the last one merges
+            const long long P = active;  // CTAs that hold a slice
+            const int which = (max(a_flat, f_begin) != f_begin) ? 1 : 0;
+            float* slot = p.slots + ((size_t)blockIdx.x * 2 + which) * kSlotFloats;
+            if (ts == 0) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int row = 8 * nt + 2 * t + (c & 1), d = 16 * ds + g + 8 * (c >> 1);
+                        slot[row * D + d] = o[nt][c];
+                    }
+            }
+            if (warp == 0 && g == 0) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        slot[ROWS * D + 8 * nt + 2 * t + e] = m[nt][e];
+                        slot[ROWS * D + ROWS + 8 * nt + 2 * t + e] = lsum[nt][e];
+                    }
+            }
+            __threadfence();
+            consumer_sync();
+            const int c_first = (int)(((a_flat + 1) * P - 1) / total_flat);
+            const int c_last = (int)((b_flat * P - 1) / total_flat);
+            int* counter = p.counters + (size_t)w.u * p.Hkv + head;
+            if (tid == 0) misc[1] = atomicAdd(counter, 1);
+            consumer_sync();
+            if (misc[1] == c_last - c_first) {
+                __threadfence();
+                for (int idx = tid; idx < ROWS * D; idx += kConsumerThreads) {
+                    const int row = idx / D, d = idx - row * D, r = row0 + row;
+                    if (r >= R) continue;
+                    float M = -INFINITY;
+                    for (int c = c_first; c <= c_last; ++c) {
+                        const long long cb = total_flat * c / P;
+                        const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
+                        if (__ldcg(sl + ROWS * D + ROWS + row) > 0.f) M = fmaxf(M, __ldcg(sl + ROWS * D + row));
+                    }
+                    float acc = 0.f, den = 0.f;
+                    for (int c = c_first; c <= c_last; ++c) {
+                        const long long cb = total_flat * c / P;
+                        const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
+                        const float lp = __ldcg(sl + ROWS * D + ROWS + row);
+                        if (lp > 0.f) {
+                            const float wgt = exp2f(__ldcg(sl + ROWS * D + row) - M);
+                            acc += wgt * __ldcg(sl + row * D + d);
+                            den += wgt * lp;
+                        }
+                    }
+                    const int i = r / p.G, hh = r - i * p.G;
+                    ((uint16_t*)p.out)[((long long)(qs + i) * p.Hq + head * p.G + hh) * D + d] =
+                        to_bits16<BF16>(den > 0.f ? acc / den : 0.f);
+                }
+                if (tid == 0) *counter = 0;  // ready for the next launch
+            }
+        }
+        consumer_sync();  // the P buffer and the reduction scratch are reused by the next part
+        f += run;
+        w.next_part(p.unit_cum, num_units, p.Hkv);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ kernel
+template <int D, int NT, int FMT, bool BF16>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const TiledParams p) {
+    using C = Cfg<D, NT, FMT>;
+    extern __shared__ uint8_t smem_raw[];
+    const int num_units = p.hdr[0];
+    const long long total_flat = (long long)p.hdr[1] * p.Hkv;
+    // min(grid, tiles) CTAs take one contiguous, non-empty slice each; the others have nothing to do
+    const long long active = total_flat < (long long)gridDim.x ? total_flat : (long long)gridDim.x;
+    if ((long long)blockIdx.x >= active) return;  // uniform, before any barrier exists
+    const long long f_begin = total_flat * blockIdx.x / active;
+    const long long f_end = total_flat * (blockIdx.x + 1) / active;
+
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* fixed = smem + (size_t)C::STAGES * C::STAGE;
+    uint64_t* full = (uint64_t*)(fixed + C::FIXED - 2 * 8 * 8);
+    uint64_t* empty = full + 8;
+    int* tmax = (int*)(fixed + C::PBYTES + C::OREDBYTES);
+    volatile int* abort_word = (volatile int*)(tmax + 64 + 3 * kConsumerWarps * 32);  // misc[0]
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            ptx::mbar_init(&full[s], 1);
+            ptx::mbar_init(&empty[s], kConsumerWarps);
+        }
+        *abort_word = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&kmap);
+        ptx::prefetch_tensormap(&vmap);
+    }
+    if (threadIdx.x < 64) tmax[threadIdx.x] = f2ord(-INFINITY);
+    __syncthreads();
+
+    if (threadIdx.x >= kConsumerThreads) {
+        producer_loop<D, NT, FMT>(&kmap, &vmap, p, smem, full, empty, abort_word, f_begin, f_end, num_units);
+    } else {
+        consumer_loop<D, NT, FMT, BF16>(p, smem, fixed, full, empty, abort_word, f_begin, f_end, num_units, total_flat, active);
+    }
+    if (*abort_word && threadIdx.x == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
+}
+
+// ------------------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    });
+    return fn;
+}
+
+static CUtensorMapSwizzle swizzle_of(int row_bytes) {
+    return row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+}
+
+struct MapPair {
+    CUtensorMap k, v;
+};
+
+// Tensor maps depend only on the pool's address and geometry; they are encoded once and cached.
+static int get_maps(const emlx_pool& pool, MapPair** out) {
+    static std::mutex mu;
+    static std::map<std::tuple<void*, void*, long long, int, int, int, int>, MapPair> cache;
+    auto key = std::make_tuple(pool.key_cache, pool.value_cache, (long long)pool.num_blocks, pool.num_kv_heads,
+                               pool.head_dim, pool.kv_format, pool.kv_dtype);
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = &it->second;
+        return EMLX_OK;
+    }
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return fail(EMLX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    if (((uintptr_t)pool.key_cache | (uintptr_t)pool.value_cache) & 15)
+        return fail(EMLX_ERR_INVALID, "key_cache/value_cache must be 16-byte aligned");
+    MapPair mp;
+    const cuuint64_t NB = (cuuint64_t)pool.num_blocks, Hkv = (cuuint64_t)pool.num_kv_heads, D = (cuuint64_t)pool.head_dim;
+    const cuuint32_t ones[3] = {1, 1, 1};
+    CUresult r1, r2;
+    if (pool.kv_format == EMLX_KV_FLOAT) {
+        const CUtensorMapDataType dt = pool.kv_dtype == EMLX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+        const cuuint64_t dims[3] = {D, Hkv, NB * kTile};
+        const cuuint64_t strides[2] = {D * 2, Hkv * D * 2};
+        const cuuint32_t box[3] = {64, 1, kTile};
+        r1 = enc(&mp.k, dt, 3, pool.key_cache, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        r2 = enc(&mp.v, dt, 3, pool.value_cache, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else {
+        const cuuint64_t bits = (cuuint64_t)pool.kv_format;
+        const cuuint64_t krow = D * bits / 8, vrow = (cuuint64_t)kTile * bits / 8;
+        const cuuint64_t kdims[3] = {krow, Hkv, NB * kTile};
+        const cuuint64_t kstrides[2] = {krow, Hkv * krow};
+        const cuuint32_t kbox[3] = {(cuuint32_t)krow, 1, kTile};
+        r1 = enc(&mp.k, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, pool.key_cache, kdims, kstrides, kbox, ones,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_of((int)krow), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const cuuint64_t vdims[2] = {vrow, NB * Hkv * D};
+        const cuuint64_t vstrides[1] = {vrow};
+        const cuuint32_t vbox[2] = {(cuuint32_t)vrow, (cuuint32_t)D};
+        r2 = enc(&mp.v, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, pool.value_cache, vdims, vstrides, vbox, ones,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_of((int)vrow), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    }
+    if (r1 != CUDA_SUCCESS || r2 != CUDA_SUCCESS)
+        return fail(EMLX_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d, %d)", (int)r1, (int)r2);
+    if (cache.size() > 256) cache.clear();
+    *out = &(cache[key] = mp);
+    return EMLX_OK;
+}
+
+template <int D, int NT, int FMT, bool BF16>
+static int launch_one(const MapPair& maps, const TiledParams& p, cudaStream_t stream) {
+    using C = Cfg<D, NT, FMT>;
+    auto kernel = attn_tiled_kernel<D, NT, FMT, BF16>;
+    static bool configured = false;
+    if (!configured) {
+        EMLX_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        configured = true;
+    }
+    const int grid = min(num_sms(), kMaxGrid);
+    kernel<<<grid, kThreads, C::SMEM, stream>>>(maps.k, maps.v, p);
+    EMLX_LAUNCHED();
+    return EMLX_OK;
+}
+
+template <int D, int NT>
+static int launch_fmt(int fmt, bool bf16, const MapPair& maps, const TiledParams& p, cudaStream_t stream) {
+    if (fmt == EMLX_KV_AFFINE8) return launch_one<D, NT, 8, false>(maps, p, stream);
+    if (fmt == EMLX_KV_AFFINE4) return launch_one<D, NT, 4, false>(maps, p, stream);
+    return bf16 ? launch_one<D, NT, 0, true>(maps, p, stream) : launch_one<D, NT, 0, false>(maps, p, stream);
+}
+
+static int launch_class(int cls, int D, int fmt, bool bf16, const MapPair& maps, const TiledParams& p, cudaStream_t s) {
+    if (D == 128) {
+        if (cls == 0) return launch_fmt<128, 1>(fmt, bf16, maps, p, s);
+        if (cls == 1) return launch_fmt<128, 2>(fmt, bf16, maps, p, s);
+        return launch_fmt<128, 4>(fmt, bf16, maps, p, s);
+    }
+    if (cls == 0) return launch_fmt<64, 1>(fmt, bf16, maps, p, s);
+    if (cls == 1) return launch_fmt<64, 2>(fmt, bf16, maps, p, s);
+    return launch_fmt<64, 4>(fmt, bf16, maps, p, s);
+}
+
+static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* stream, int class_lo, int class_hi) {
+    if (int rc = validate_attn(a, pool, true)) return rc;
+    if (a->total_tokens == 0) return EMLX_OK;
+    const int D = pool->head_dim, Hq = a->num_q_heads, Hkv = pool->num_kv_heads, G = Hq / Hkv;
+    if (pool->block_size != kTile) return fail(EMLX_ERR_UNSUPPORTED, "the tiled kernels need page size %d", kTile);
+    if (D != 64 && D != 128) return fail(EMLX_ERR_UNSUPPORTED, "the tiled kernels need head_dim 64 or 128");
+    if (a->q_dtype == EMLX_F32) return fail(EMLX_ERR_UNSUPPORTED, "the tiled kernels need fp16 or bf16 queries");
+    const bool bf16 = a->q_dtype == EMLX_BF16;
+    if (pool->kv_format == EMLX_KV_FLOAT && pool->kv_dtype != a->q_dtype)
+        return fail(EMLX_ERR_UNSUPPORTED, "the tiled kernels need the pool dtype to equal the query dtype");
+    if (pool->kv_format != EMLX_KV_FLOAT && bf16)
+        return fail(EMLX_ERR_UNSUPPORTED, "affine pools are read with fp16 queries");
+    const PlanLayout L = plan_layout(a->num_seqs, a->total_tokens, Hq, Hkv);
+    const WorkspaceLayout W = workspace_layout(a->num_seqs, a->total_tokens, Hq, Hkv, D);
+    if (a->plan_bytes < (size_t)L.words * 4 || a->workspace_bytes < W.bytes)
+        return fail(EMLX_ERR_WORKSPACE, "plan/workspace smaller than emlx_attn_plan_bytes()/emlx_attn_workspace_bytes()");
+    if (((uintptr_t)a->queries | (uintptr_t)a->out) & 15) return fail(EMLX_ERR_INVALID, "queries/out must be 16-byte aligned");
+    MapPair* maps = nullptr;
+    if (int rc = get_maps(*pool, &maps)) return rc;
+
+    // classes that can hold a sequence of 1..max_query_len tokens (0 = unknown: up to the largest)
+    auto cls_of = [](int rows) { return rows <= 8 ? 0 : (rows <= 16 ? 1 : 2); };
+    const long long hint_rows = (long long)a->max_query_len * G;
+    int lo = cls_of(G), hi = a->max_query_len > 0 ? cls_of(hint_rows > (1 << 20) ? (1 << 20) : (int)hint_rows) : kNumClasses - 1;
+    lo = max(lo, class_lo);
+    hi = min(hi, class_hi);
+    const int32_t* plan = (const int32_t*)a->plan;
+    for (int c = lo; c <= hi; ++c) {
+        TiledParams p;
+        p.q = a->queries; p.out = a->out; p.bt = a->block_tables; p.kv_lens = a->kv_lens; p.qsl = a->query_start_loc;
+        p.hdr = plan + 4 * c;
+        p.unit_seq = plan + L.unit_seq[c]; p.unit_row0 = plan + L.unit_row0[c];
+        p.unit_tile_lo = plan + L.unit_tile_lo[c]; p.unit_cum = plan + L.unit_cum[c];
+        p.counters = (int32_t*)((uint8_t*)a->workspace + W.counter_off[c]);
+        p.slots = (float*)((uint8_t*)a->workspace + W.slots_off);
+        p.status = a->status;
+        p.k_scale = (const __half*)pool->k_scale; p.k_bias = (const __half*)pool->k_bias;
+        p.v_scale = (const __half*)pool->v_scale; p.v_bias = (const __half*)pool->v_bias;
+        p.num_blocks = pool->num_blocks;
+        p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.MB = a->max_blocks_per_seq; p.window = a->sliding_window;
+        p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
+        if (int rc = launch_class(c, D, pool->kv_format, bf16, *maps, p, (cudaStream_t)stream)) return rc;
+    }
+    return EMLX_OK;
+}
+
+}  // namespace emlx
+
 extern "C" {
-size_t emlx_attn_plan_bytes(int32_t, int32_t, int32_t, int32_t) { return 256; }
-size_t emlx_attn_workspace_bytes(int32_t, int32_t, int32_t, int32_t, int32_t) { return 256; }
-int emlx_attn_plan(const int32_t*, const int32_t*, int32_t, int32_t, int32_t, int32_t, int32_t, int32_t, void*, size_t, void*) { return EMLX_OK; }
-int emlx_attn_unified(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx_attn_generic(a, p, s); }
-int emlx_attn_decode(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx_attn_generic(a, p, s); }
-int emlx_attn_prefill(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx_attn_generic(a, p, s); }
+int emlx_attn_unified(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 0, emlx::kNumClasses - 1); }
+int emlx_attn_decode(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 0, 1); }
+int emlx_attn_prefill(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 2, 2); }
 }

@@ -1,0 +1,78 @@
+// Work-list ("plan") and workspace layouts shared by the plan kernel and the tiled attention kernels.
+//
+// A *unit* is up to 8*NT query rows of one sequence (row = query token x GQA head of one KV head,
+// token-major) together with the range of 128-token KV tiles those rows may attend.  Units are sorted
+// into classes by their row count so that each class runs with the smallest tile that holds it:
+//     class 0: rows <= 8   (NT = 1)     decode with Hq/Hkv <= 8
+//     class 1: rows <= 16  (NT = 2)
+//     class 2: 32-row blocks (NT = 4)   spec-verify rows, prefill chunks
+// The work of a class is the flat sequence of (unit, kv head, tile); CTA c of P takes the contiguous
+// slice [c*N/P, (c+1)*N/P).
+#pragma once
+#include "common.cuh"
+
+namespace emlx {
+
+constexpr int kTile = 128;        // tokens per KV tile = page size the tiled kernels require
+constexpr int kNumClasses = 3;
+constexpr int kPlanHeaderWords = 16;
+constexpr int kMaxGrid = 256;     // upper bound on CTAs per launch, sizes the partial-result slots
+constexpr int kMaxRows = 32;      // rows of the largest class
+
+__host__ __device__ inline int class_rows(int c) { return 8 << c; }
+
+struct PlanLayout {
+    int cap[kNumClasses];       // unit capacity per class
+    int unit_seq[kNumClasses];  // word offsets into the plan
+    int unit_row0[kNumClasses];
+    int unit_tile_lo[kNumClasses];
+    int unit_cum[kNumClasses];  // cap + 1 words: exclusive prefix sum of tiles per unit (per KV head)
+    int tmp;                    // S words of scratch for the scans
+    int words;
+};
+
+__host__ __device__ inline PlanLayout plan_layout(int S, int T, int Hq, int Hkv) {
+    PlanLayout L;
+    const int G = Hq / Hkv;
+    int w = kPlanHeaderWords;
+    for (int c = 0; c < kNumClasses; ++c) {
+        L.cap[c] = (c == kNumClasses - 1) ? S + (int)(((long long)T * G + kMaxRows - 1) / kMaxRows) : S;
+        if (L.cap[c] < 1) L.cap[c] = 1;
+        L.unit_seq[c] = w; w += L.cap[c];
+        L.unit_row0[c] = w; w += L.cap[c];
+        L.unit_tile_lo[c] = w; w += L.cap[c];
+        L.unit_cum[c] = w; w += L.cap[c] + 1;
+    }
+    L.tmp = w; w += (S > 0 ? S : 1);
+    L.words = w;
+    return L;
+}
+
+// Workspace: [partial slots: 2 per CTA, fixed size] [arrival counters: one int per (class, unit, kv head)].
+// A slot holds rows x head_dim un-normalised accumulators, then the rows' running maxima, then their
+// running sums.  The counters are zero whenever no kernel is running (the merging CTA resets its counter),
+// and the slot area has a fixed size, so one zero-initialised workspace serves calls of any geometry.
+constexpr int kMaxHeadDimTiled = 128;
+constexpr size_t kSlotFloats = (size_t)kMaxRows * (kMaxHeadDimTiled + 2);
+
+struct WorkspaceLayout {
+    size_t counter_off[kNumClasses];
+    size_t slots_off;
+    size_t bytes;
+};
+
+inline WorkspaceLayout workspace_layout(int S, int T, int Hq, int Hkv, int D) {
+    (void)D;
+    PlanLayout P = plan_layout(S, T, Hq, Hkv);
+    WorkspaceLayout W;
+    W.slots_off = 0;
+    size_t off = (size_t)kMaxGrid * 2 * kSlotFloats * sizeof(float);
+    for (int c = 0; c < kNumClasses; ++c) {
+        W.counter_off[c] = off;
+        off += (size_t)P.cap[c] * Hkv * sizeof(int32_t);
+    }
+    W.bytes = (off + 255) & ~(size_t)255;
+    return W;
+}
+
+}  // namespace emlx

@@ -3,6 +3,9 @@ import sys
 
 import pytest
 
+# validation mode: device status words are read back after every call and outputs start as NaN
+os.environ.setdefault("EASYMLX_B200_CHECK", "1")
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)

@@ -198,7 +198,13 @@ def test_bad_slot_and_overflow_are_flagged():
 
     cache = PageCacheView.init(num_seqs=2, max_seq_len=256, num_kv_heads=2, head_dim=64, block_size=128)
     k = torch.zeros((3, 2, 64), dtype=torch.float16, device="cuda")
-    cache.concatenate_to_cache(k.repeat(1, 2, 1), k, k, cache_metadata=PageMetadata(
-        query_start_loc=build_query_start_loc([3])), slot_ids=[5])
     with pytest.raises(RuntimeError, match="slot id"):
+        cache.concatenate_to_cache(k.repeat(1, 2, 1), k, k, cache_metadata=PageMetadata(
+            query_start_loc=build_query_start_loc([3])), slot_ids=[5])
         cache.check()
+    big = torch.zeros((300, 2, 64), dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="outgrows"):
+        cache.concatenate_to_cache(big.repeat(1, 2, 1), big, big, cache_metadata=PageMetadata(
+            query_start_loc=build_query_start_loc([300])), slot_ids=[1])
+        cache.check()
+    cache.check()  # reported once, then clear
