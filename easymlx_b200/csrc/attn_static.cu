@@ -1,0 +1,66 @@
+// Decode attention for callers that cannot allocate device memory: the work list and the split-KV
+// workspace live in one file-scope device array instead of caller-provided buffers.
+#include "attn_tiled.cuh"
+
+#include <mutex>
+
+namespace {
+
+// Every GPU on which this library runs holds this array from module load until the process exits.
+constexpr size_t kStaticScratchBytes = 10u << 20;  // 10 MiB
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_mu;
+void* g_scratch_addr[kMaxDevices] = {};
+
+// In host code the array's name is only a handle; the device address comes from the runtime, once per
+// device, with that device current.
+int scratch_address(void** out) {
+    int dev = 0;
+    EMLX_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return emlx::fail(EMLX_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (!g_scratch_addr[dev]) {
+        void* ptr = nullptr;
+        EMLX_CUDA_OK(cudaGetSymbolAddress((void**)&ptr, g_static_scratch));
+        if (!ptr) return emlx::fail(EMLX_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        g_scratch_addr[dev] = ptr;
+    }
+    *out = g_scratch_addr[dev];
+    return EMLX_OK;
+}
+
+}  // namespace
+
+extern "C" int emlx_attn_decode_static(const emlx_attn_args* args, const emlx_pool* pool, void* stream) {
+    using namespace emlx;
+    if (!args || !pool) return fail(EMLX_ERR_INVALID, "attention args / pool are NULL");
+    if (pool->num_kv_heads <= 0 || args->num_q_heads <= 0 || args->num_q_heads % pool->num_kv_heads)
+        return fail(EMLX_ERR_INVALID, "num_q_heads must be divisible by num_kv_heads (GQA)");
+    if (args->total_tokens < 0 || args->num_seqs < 0) return fail(EMLX_ERR_INVALID, "total_tokens/num_seqs must be non-negative");
+    if (args->total_tokens == 0) return EMLX_OK;
+    const int S = args->num_seqs, T = args->total_tokens, Hq = args->num_q_heads, Hkv = pool->num_kv_heads;
+    const size_t plan_bytes = (emlx_attn_plan_bytes(S, T, Hq, Hkv) + 255) & ~(size_t)255;
+    const WorkspaceLayout W = workspace_layout(S, T, Hq, Hkv, pool->head_dim);
+    if (plan_bytes + W.bytes > kStaticScratchBytes)
+        return fail(EMLX_ERR_WORKSPACE,
+                    "batch too large for the built-in scratch: %d sequences / %d tokens need %zu bytes, the limit is "
+                    "%zu; use emlx_attn_decode with caller-provided plan and workspace",
+                    S, T, plan_bytes + W.bytes, kStaticScratchBytes);
+    void* base = nullptr;
+    if (int rc = scratch_address(&base)) return rc;
+    unsigned char* plan = (unsigned char*)base;
+    unsigned char* workspace = plan + plan_bytes;
+    // The array keeps whatever the previous call left: the arrival counters must start at zero.
+    EMLX_CUDA_OK(cudaMemsetAsync(workspace + W.counter_off[0], 0, W.bytes - W.counter_off[0], (cudaStream_t)stream));
+    if (int rc = emlx_attn_plan(args->query_start_loc, args->kv_lens, S, T, Hq, Hkv, pool->block_size,
+                                args->sliding_window, plan, plan_bytes, stream))
+        return rc;
+    emlx_attn_args local = *args;
+    local.plan = plan;
+    local.plan_bytes = plan_bytes;
+    local.workspace = workspace;
+    local.workspace_bytes = W.bytes;
+    return emlx_attn_decode(&local, pool, stream);
+}

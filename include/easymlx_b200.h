@@ -150,6 +150,18 @@ int emlx_attn_prefill(const emlx_attn_args* args, const emlx_pool* pool, void* s
  * (operations/kernels/unified_attention.py:187-281).  Needs neither plan nor workspace. */
 int emlx_attn_generic(const emlx_attn_args* args, const emlx_pool* pool, void* stream);
 
+/* Decode attention without caller-provided scratch.  No counterpart in the reference.
+ * For embedders that cannot allocate device memory around this call: a serving process whose allocator has
+ * already reserved all of HBM (a later cudaMalloc for the work list or the split-KV workspace could fail or
+ * fragment the pool), or a step loop that must not take the device-wide synchronisation cudaMalloc/cudaFree
+ * imply.  Same result as emlx_attn_plan + emlx_attn_decode; args->plan/workspace are ignored and the entry
+ * point builds the work list itself.  Scratch is a 10 MiB array built into the library (held by every GPU the
+ * library runs on until the process exits); a batch whose plan + workspace exceed it is rejected with
+ * EMLX_ERR_WORKSPACE (in practice: up to a few thousand sequences / tokens).  The first call on a device looks
+ * up the array's address; make that first call outside any stream capture.  All calls share the array: two
+ * calls that overlap on the GPU (different streams) race, so serialise them.  Calls no allocating routine. */
+int emlx_attn_decode_static(const emlx_attn_args* args, const emlx_pool* pool, void* stream);
+
 /* Number of kernels this library has launched from the calling process (for launch accounting). */
 int64_t emlx_launch_count(void);
 
