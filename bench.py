@@ -242,6 +242,21 @@ def run_ours(args):
         # every rank owns the page pool of its own sequences
         w = workloads.materialize(workloads.describe(args.config, seed=None if rank == 0 else 1000 * rank + 7),
                                   dev, seed=rank)
+    if args.attn_only:
+        # profiling aid: a few bare attention launches over the written pool, nothing else
+        from easymlx_b200.operations.kernels.unified_attention import AttentionCall
+
+        c = w.cache
+        extra = dict(k_scale=c.k_scales, v_scale=c.v_scales, k_bias=c.k_biases, v_bias=c.v_biases) if w.bits else {}
+        call = AttentionCall(w.q, c.key_cache, c.value_cache, c.block_tables,
+                             torch.from_numpy(w.kv_lens.astype(np.int32)).to(dev),
+                             emlx.build_query_start_loc(w.qlens.tolist(), device=dev),
+                             max_query_len=int(w.qlens.max()), **extra).plan()
+        for _ in range(args.attn_only):
+            call.launch()
+        torch.cuda.synchronize()
+        print(json.dumps({"attn_only": args.attn_only, "config": args.config}))
+        return
     step = AttentionStep(w.cache, w.q, w.k, w.v, w.qlens.tolist(), w.slot_ids)
     gathered = None
     if head_shard:
@@ -378,6 +393,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--config", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--attn-only", type=int, default=0, help="run this many bare attention launches and exit (for ncu)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget-tokens", type=int, default=120000)
     args = ap.parse_args()

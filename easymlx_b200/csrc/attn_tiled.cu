@@ -67,9 +67,13 @@ struct Cfg {
     static constexpr int DSL = D / 16;                                   // 16-wide slices of D
     static constexpr int TS = kConsumerWarps / DSL;                      // warps sharing a slice split the tokens
     static constexpr int NPBUF = FMT == 0 ? 1 : GROUPS;
-    static constexpr int PBYTES = NPBUF * ROWS * kPStride;
-    static constexpr int OREDBYTES = TS > 1 ? kConsumerWarps * 16 * ROWS * 4 : 0;
-    static constexpr int FIXED = PBYTES + OREDBYTES + 2 * 32 * 4 + 3 * kConsumerWarps * 32 * 4 + 64 + 2 * 8 * 8;
+    // Two consumer designs share the kernel: up to 16 rows every warp keeps its own softmax state and its own
+    // O^T[D x rows] over its 16 tokens of each tile (no CTA barrier per tile); 32-row units split D across warps.
+    static constexpr bool PRIVATE = NT <= 2;
+    static constexpr int PBYTES = PRIVATE ? ROWS * (D * 2 + 16) : NPBUF * ROWS * kPStride;      // region A
+    static constexpr int OREDBYTES = PRIVATE ? kConsumerWarps * 64 * ROWS * 4                    // region B
+                                             : (TS > 1 ? kConsumerWarps * 16 * ROWS * 4 : 0);
+    static constexpr int FIXED = PBYTES + OREDBYTES + 2 * 32 * 4 + 4 * kConsumerWarps * 32 * 4 + 64 + 2 * 8 * 8;
     static constexpr int STAGES_RAW = (kSmemBudget - FIXED) / STAGE;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM = STAGES * STAGE + FIXED + 1024;
@@ -210,7 +214,7 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
     int* tmax = (int*)(fixed + C::PBYTES + C::OREDBYTES);
     float* wl = (float*)(tmax + 64);
     float* wb = wl + kConsumerWarps * 32;  // [2][warps][32]
-    int* misc = (int*)(wb + 2 * kConsumerWarps * 32);
+    int* misc = (int*)(wb + 3 * kConsumerWarps * 32);
     const int ORD_NEG_INF = f2ord(-INFINITY);
 
     Walk w;
@@ -708,9 +712,15 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
     }
 }
 
+}  // namespace emlx
+
+#include "attn_private.cuh"
+
+namespace emlx {
+
 // ------------------------------------------------------------------------------------------ kernel
 template <int D, int NT, int FMT, bool BF16>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __maxnreg__(224)
 attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const TiledParams p) {
     using C = Cfg<D, NT, FMT>;
     extern __shared__ uint8_t smem_raw[];
@@ -727,7 +737,7 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     uint64_t* full = (uint64_t*)(fixed + C::FIXED - 2 * 8 * 8);
     uint64_t* empty = full + 8;
     int* tmax = (int*)(fixed + C::PBYTES + C::OREDBYTES);
-    volatile int* abort_word = (volatile int*)(tmax + 64 + 3 * kConsumerWarps * 32);  // misc[0]
+    volatile int* abort_word = (volatile int*)(tmax + 64 + 4 * kConsumerWarps * 32);  // misc[0]
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
@@ -745,7 +755,11 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     if (threadIdx.x >= kConsumerThreads) {
         producer_loop<D, NT, FMT>(&kmap, &vmap, p, smem, full, empty, abort_word, f_begin, f_end, num_units);
     } else {
-        consumer_loop<D, NT, FMT, BF16>(p, smem, fixed, full, empty, abort_word, f_begin, f_end, num_units, total_flat, active);
+        if constexpr (C::PRIVATE)
+            consumer_loop_private<D, NT, FMT, BF16>(p, smem, fixed, full, empty, abort_word, f_begin, f_end, num_units,
+                                                    total_flat, active);
+        else
+            consumer_loop<D, NT, FMT, BF16>(p, smem, fixed, full, empty, abort_word, f_begin, f_end, num_units, total_flat, active);
     }
     if (*abort_word && threadIdx.x == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
 }
@@ -801,19 +815,22 @@ static int get_maps(const emlx_pool& pool, MapPair** out) {
         const cuuint64_t dims[3] = {D, Hkv, NB * kTile};
         const cuuint64_t strides[2] = {D * 2, Hkv * D * 2};
         const cuuint32_t box[3] = {64, 1, kTile};
+        // a tile row is D*2 contiguous bytes: do not let L2 promotion pull in the neighbouring head's row
+        const CUtensorMapL2promotion promo = D * 2 >= 256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
         r1 = enc(&mp.k, dt, 3, pool.key_cache, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                 CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         r2 = enc(&mp.v, dt, 3, pool.value_cache, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                 CU_TENSOR_MAP_SWIZZLE_128B, promo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else {
         const cuuint64_t bits = (cuuint64_t)pool.kv_format;
         const cuuint64_t krow = D * bits / 8, vrow = (cuuint64_t)kTile * bits / 8;
         const cuuint64_t kdims[3] = {krow, Hkv, NB * kTile};
         const cuuint64_t kstrides[2] = {krow, Hkv * krow};
         const cuuint32_t kbox[3] = {(cuuint32_t)krow, 1, kTile};
+        const CUtensorMapL2promotion kpromo = krow >= 128 ? CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+                                                          : (krow >= 64 ? CU_TENSOR_MAP_L2_PROMOTION_L2_64B : CU_TENSOR_MAP_L2_PROMOTION_NONE);
         r1 = enc(&mp.k, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, pool.key_cache, kdims, kstrides, kbox, ones,
-                 CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_of((int)krow), CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle_of((int)krow), kpromo, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         const cuuint64_t vdims[2] = {vrow, NB * Hkv * D};
         const cuuint64_t vstrides[1] = {vrow};
         const cuuint32_t vbox[2] = {(cuuint32_t)vrow, (cuuint32_t)D};
