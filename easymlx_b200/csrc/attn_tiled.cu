@@ -720,7 +720,8 @@ namespace emlx {
 
 // ------------------------------------------------------------------------------------------ kernel
 template <int D, int NT, int FMT, bool BF16>
-__global__ void __maxnreg__(224)
+// 9 warps share four 16K-register sub-partitions: three warps on one of them caps a thread at 168 registers
+__global__ void __launch_bounds__(kThreads, 1)
 attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const TiledParams p) {
     using C = Cfg<D, NT, FMT>;
     extern __shared__ uint8_t smem_raw[];
