@@ -2,7 +2,8 @@
 // tokens of each 128-token tile from score to output accumulation, with its own running max / sum and its
 // own O^T[D x rows] accumulators, so consumer warps never meet at a barrier inside the tile loop and drift
 // apart to hide each other's latencies.  The eight partial states are combined once per (unit, head) part.
-// Included by attn_tiled.cu after Cfg, TiledParams, Walk and the small helpers.
+// Part descriptors and Q rows arrive in shared memory from the producer warp, so a part starts without a
+// round trip to global memory.  Included by attn_tiled.cu after Cfg, TiledParams, PartDesc and the helpers.
 #pragma once
 
 namespace emlx {
@@ -13,45 +14,79 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
     return r;
 }
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    return (uint32_t)to_bits16<BF16>(lo) | ((uint32_t)to_bits16<BF16>(hi) << 16);
+    uint32_t r;
+    if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
+// 2^x on the special-function unit; ex2(-inf) = 0
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float2 h2_to_f2(uint32_t v) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&v));
 }
 
 template <int D, int NT, int FMT, bool BF16>
 __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint8_t* stages, uint8_t* fixed,
                                                       uint64_t* full, uint64_t* empty, volatile int* abort_word,
-                                                      long long f_begin, long long f_end, int num_units,
-                                                      long long total_flat, long long active) {
+                                                      long long f_begin, long long f_end, long long total_flat,
+                                                      long long active) {
     using C = Cfg<D, NT, FMT>;
     constexpr int KS = D / 16, MT = D / 16, ROWS = C::ROWS, GROUPS = C::GROUPS;
     constexpr int NG = FMT == 0 ? 1 : GROUPS;
-    constexpr int HALVES = D / 64;  // the cross-warp reduction goes through shared memory 64 columns of D at a time
+    constexpr int RC = C::RED_COLS, RSTRIDE = RC + 4;  // columns of D per cross-warp pass, padded row of the buffer
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
 
-    uint8_t* stage_out = fixed;                       // [ROWS][D*2 + 16] output rows before the coalesced store
-    float* ored = (float*)(fixed + C::PBYTES);        // [warps][64][ROWS]
-    float* rowM = (float*)(fixed + C::PBYTES + C::OREDBYTES);  // [32] merged max, then [32] merged sum
-    float* rowL = rowM + 32;
-    float* wm = rowL + 32;                            // [warps][32] per-warp running max
+    float* ored = (float*)(fixed + C::PBYTES);        // [warps][ROWS][RC + 4]
+    float* wm = (float*)(fixed + C::OFF_W);           // [warps][32] per-warp running max
     float* wl = wm + kConsumerWarps * 32;             // [warps][32] per-warp running sum
     float* wb = wl + kConsumerWarps * 32;             // [2][warps][32] per-warp bias terms of the values
-    int* misc = (int*)(wb + 2 * kConsumerWarps * 32);
-    constexpr int OUT_STRIDE = D * 2 + 16;
+    int* misc = (int*)(fixed + C::OFF_MISC);
+    uint64_t* dfull = full + 16;
+    uint64_t* dempty = full + 20;
 
     // token of the tile that MMA row g (and g + 8) of this warp stands for; the affine formats permute
     // tokens so that the transposed probabilities line up with the way value codes are unpacked
     const int tokA = 16 * warp + (FMT == 0 ? g : (FMT == 8 ? 4 * (g >> 1) + (g & 1) : 4 * (g >> 1) + 2 * (g & 1)));
     const int tokB = tokA + (FMT == 0 ? 8 : (FMT == 8 ? 2 : 1));
 
-    Walk w;
-    w.locate(f_begin, p.unit_cum, num_units, p.Hkv);
+    // ---- per-thread shared-memory offsets inside a stage (they do not change from tile to tile)
+    uint32_t k_off = 0, v_off = 0, kq_off[2][NG > 0 ? NG : 1];
+    if constexpr (FMT == 0) {
+        // ldmatrix rows of K: token 16w + lane%16, 16-byte chunk (k-step, lane/16); XOR swizzle on bits 4..6
+        k_off = (uint32_t)((16 * warp + (lane & 15)) * 128 + ((((lane >> 4) ^ (lane & 7)) & 7) << 4));
+        // ldmatrix.trans rows of V: token 16w + lane%8 + 8*(lane/16), chunk (2*mt + (lane/8)%2)
+        v_off = (uint32_t)(C::KBYTES + (16 * warp + (lane & 7) + 8 * (lane >> 4)) * 128 +
+                           (((((lane >> 3) & 1) ^ (lane & 7)) & 7) << 4));
+    } else {
+        constexpr int KCH = FMT == 8 ? 16 : 8;  // bytes of K codes a thread reads per group and token
+#pragma unroll
+        for (int j = 0; j < NG; ++j) {
+            const int byte = (FMT == 8 ? 64 : 32) * j + KCH * t;
+            kq_off[0][j] = ptx::swz<C::KSW>((uint32_t)(tokA * C::KROW + byte));
+            kq_off[1][j] = ptx::swz<C::KSW>((uint32_t)(tokB * C::KROW + byte));
+        }
+        // V^T rows d = 16*mt + g (+8): the swizzle term does not depend on mt
+        const int vbyte = FMT == 8 ? 16 * warp + 4 * t : 8 * warp + 2 * t;
+        v_off = C::KBYTES + ptx::swz<C::VSW>((uint32_t)(g * C::VROW + vbyte));
+    }
+    (void)k_off; (void)kq_off;
+
     long long f = f_begin;
-    uint32_t it = 0;
+    uint32_t it = 0, part_idx = 0;
 
     while (f < f_end) {
-        const int seq = p.unit_seq[w.u], row0 = p.unit_row0[w.u], tile_lo = p.unit_tile_lo[w.u];
-        const int qs = p.qsl[seq], q_len = p.qsl[seq + 1] - qs, kv_len = p.kv_lens[seq];
-        const int R = q_len * p.G, ctx = kv_len - q_len, head = w.head;
-        const int run = (int)min((long long)(w.ntiles - w.j), f_end - f);
+        // ------------------------------------------------------------------ part descriptor from the producer
+        const uint32_t dslot = part_idx % C::NDESC;
+        ptx::mbar_wait(&dfull[dslot], (part_idx / C::NDESC) & 1, abort_word);
+        const PartDesc* desc = (const PartDesc*)(fixed + (size_t)dslot * C::DESC_BYTES);
+        const int row0 = desc->row0, tile_lo = desc->tile_lo, qs = desc->qs, q_len = desc->q_len;
+        const int kv_len = desc->kv_len, head = desc->head, unit = desc->u, j_first = desc->j, run = desc->run;
+        const int ntiles = desc->ntiles, cum_u = desc->cum_u;
+        const int R = q_len * p.G, ctx = kv_len - q_len;
         const int rows_here = min(ROWS, R - row0);
 
         int row_hi[NT][2], row_lo[NT][2];
@@ -71,37 +106,41 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
         const int hi_min = min(kv_len, ctx + i_first + 1);
         const int lo_max = p.window > 0 ? max(0, min(kv_len - 1, ctx + i_last) - p.window + 1) : 0;
 
+        // Q^T fragments (B operand) from the staged rows; rows past the unit's last one are zero
         uint32_t qf[KS][NT][2];
         float qsum[NG][NT][2];
+        {
+            const uint8_t* qtile = (const uint8_t*)desc + 64;
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-            const int r = row0 + 8 * nt + g;
-            const bool ok = r < R;
-            const int i = ok ? r / p.G : 0, hh = ok ? r - i * p.G : 0;
-            const uint16_t* qrow = (const uint16_t*)p.q + ((long long)(qs + i) * p.Hq + head * p.G + hh) * D;
-            if constexpr (FMT == 0) {
+            for (int nt = 0; nt < NT; ++nt) {
+                const bool ok = 8 * nt + g < rows_here;
+                const uint16_t* qrow = (const uint16_t*)(qtile + (size_t)(8 * nt + g) * C::QSTRIDE);
+                if constexpr (FMT == 0) {
 #pragma unroll
-                for (int ks = 0; ks < KS; ++ks) {
-                    qf[ks][nt][0] = ok ? *(const uint32_t*)(qrow + 16 * ks + 2 * t) : 0u;
-                    qf[ks][nt][1] = ok ? *(const uint32_t*)(qrow + 16 * ks + 2 * t + 8) : 0u;
-                }
-            } else if constexpr (FMT == 8) {
+                    for (int ks = 0; ks < KS; ++ks) {
+                        qf[ks][nt][0] = ok ? *(const uint32_t*)(qrow + 16 * ks + 2 * t) : 0u;
+                        qf[ks][nt][1] = ok ? *(const uint32_t*)(qrow + 16 * ks + 2 * t + 8) : 0u;
+                    }
+                } else if constexpr (FMT == 8) {
 #pragma unroll
-                for (int ks = 0; ks < KS; ++ks) {
-                    const uint2 v = ok ? *(const uint2*)(qrow + 64 * (ks >> 2) + 16 * t + 4 * (ks & 3)) : make_uint2(0u, 0u);
-                    qf[ks][nt][0] = v.x;
-                    qf[ks][nt][1] = v.y;
-                }
-            } else {
+                    for (int ks = 0; ks < KS; ++ks) {
+                        const uint2 v = ok ? *(const uint2*)(qrow + 64 * (ks >> 2) + 16 * t + 4 * (ks & 3)) : make_uint2(0u, 0u);
+                        qf[ks][nt][0] = v.x;
+                        qf[ks][nt][1] = v.y;
+                    }
+                } else {
 #pragma unroll
-                for (int jx = 0; jx < KS / 2; ++jx) {
-                    const uint4 v = ok ? *(const uint4*)(qrow + 64 * (jx >> 1) + 16 * t + 8 * (jx & 1)) : make_uint4(0u, 0u, 0u, 0u);
-                    qf[2 * jx][nt][0] = ptx::prmt(v.x, v.y, 0x5410u);
-                    qf[2 * jx][nt][1] = ptx::prmt(v.z, v.w, 0x5410u);
-                    qf[2 * jx + 1][nt][0] = ptx::prmt(v.x, v.y, 0x7632u);
-                    qf[2 * jx + 1][nt][1] = ptx::prmt(v.z, v.w, 0x7632u);
+                    for (int jx = 0; jx < KS / 2; ++jx) {
+                        const uint4 v = ok ? *(const uint4*)(qrow + 64 * (jx >> 1) + 16 * t + 8 * (jx & 1)) : make_uint4(0u, 0u, 0u, 0u);
+                        qf[2 * jx][nt][0] = ptx::prmt(v.x, v.y, 0x5410u);
+                        qf[2 * jx][nt][1] = ptx::prmt(v.z, v.w, 0x5410u);
+                        qf[2 * jx + 1][nt][0] = ptx::prmt(v.x, v.y, 0x7632u);
+                        qf[2 * jx + 1][nt][1] = ptx::prmt(v.z, v.w, 0x7632u);
+                    }
                 }
             }
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&dempty[dslot]);
         }
         if constexpr (FMT != 0) {
             const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
@@ -131,9 +170,9 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
         for (int jj = 0; jj < run; ++jj, ++it) {
             const uint32_t stage = it % C::STAGES;
             uint8_t* st = stages + (size_t)stage * C::STAGE;
-            const uint32_t ks_base = ptx::smem_u32(st), vs_base = ks_base + C::KBYTES;
+            const uint32_t st_base = ptx::smem_u32(st);
             const __half* sbs = (const __half*)(st + C::KBYTES + C::VBYTES);
-            const int t0 = (tile_lo + w.j + jj) * kTile;
+            const int t0 = (tile_lo + j_first + jj) * kTile;
             const bool interior = (t0 + kTile <= hi_min) && (t0 >= lo_max);
             ptx::mbar_wait(&full[stage], (it / C::STAGES) & 1, abort_word);
 
@@ -144,10 +183,8 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                 for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
                 for (int ks = 0; ks < KS; ++ks) {
-                    const uint32_t off = (uint32_t)((ks >> 2) * (kTile * 128) + (16 * warp + (lane & 15)) * 128 +
-                                                    ((ks & 3) * 2 + (lane >> 4)) * 16);
                     uint32_t a[4];
-                    ptx::ldmatrix_x4(a, ks_base + ptx::swz<3>(off));
+                    ptx::ldmatrix_x4(a, st_base + (ks >> 2) * (kTile * 128) + (k_off ^ (uint32_t)(((ks & 3) * 2) << 4)));
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) ptx::mma_16816<BF16>(s[nt], a, qf[ks][nt]);
                 }
@@ -162,8 +199,8 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) acc[j][nt][0] = acc[j][nt][1] = acc[j][nt][2] = acc[j][nt][3] = 0.f;
                     if constexpr (FMT == 8) {
-                        const uint4 xa = *(const uint4*)(st + ptx::swz<C::KSW>((uint32_t)(tokA * C::KROW + 64 * j + 16 * t)));
-                        const uint4 xb = *(const uint4*)(st + ptx::swz<C::KSW>((uint32_t)(tokB * C::KROW + 64 * j + 16 * t)));
+                        const uint4 xa = *(const uint4*)(st + kq_off[0][j]);
+                        const uint4 xb = *(const uint4*)(st + kq_off[1][j]);
                         const uint32_t wa[4] = {xa.x, xa.y, xa.z, xa.w}, wbv[4] = {xb.x, xb.y, xb.z, xb.w};
 #pragma unroll
                         for (int sidx = 0; sidx < 4; ++sidx) {
@@ -173,8 +210,8 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                             for (int nt = 0; nt < NT; ++nt) ptx::mma_16816<false>(acc[j][nt], a, qf[4 * j + sidx][nt]);
                         }
                     } else {
-                        const uint2 xa = *(const uint2*)(st + ptx::swz<C::KSW>((uint32_t)(tokA * C::KROW + 32 * j + 8 * t)));
-                        const uint2 xb = *(const uint2*)(st + ptx::swz<C::KSW>((uint32_t)(tokB * C::KROW + 32 * j + 8 * t)));
+                        const uint2 xa = *(const uint2*)(st + kq_off[0][j]);
+                        const uint2 xb = *(const uint2*)(st + kq_off[1][j]);
                         const uint32_t wa[2] = {xa.x, xa.y}, wbv[2] = {xb.x, xb.y};
 #pragma unroll
                         for (int x = 0; x < 2; ++x) {
@@ -190,17 +227,32 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                         }
                     }
                 }
+                // S = sum_j scale_j[tok] * 2^24 * acc_j + bias_j[tok] * qsum_j ; scale/bias of both groups in one load
+                float ksc[2][NG], kbi[2][NG];
+#pragma unroll
+                for (int ab = 0; ab < 2; ++ab) {
+                    const int tok = ab ? tokB : tokA;
+                    if constexpr (NG == 2) {
+                        const float2 sv = h2_to_f2(*(const uint32_t*)(sbs + 0 * kTile * GROUPS + tok * 2));
+                        const float2 bv = h2_to_f2(*(const uint32_t*)(sbs + 1 * kTile * GROUPS + tok * 2));
+                        ksc[ab][0] = sv.x; ksc[ab][1] = sv.y; kbi[ab][0] = bv.x; kbi[ab][1] = bv.y;
+                    } else {
+                        ksc[ab][0] = __half2float(sbs[0 * kTile * GROUPS + tok]);
+                        kbi[ab][0] = __half2float(sbs[1 * kTile * GROUPS + tok]);
+                    }
+                }
+                const float k24 = kTwo24 * p.scale_log2e;
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        const int tok = c < 2 ? tokA : tokB;
-                        float v = 0.f;
+                        float v = 0.f, bq = 0.f;
 #pragma unroll
-                        for (int j = 0; j < NG; ++j)
-                            v += __half2float(sbs[0 * kTile * GROUPS + tok * GROUPS + j]) * kTwo24 * acc[j][nt][c] +
-                                 __half2float(sbs[1 * kTile * GROUPS + tok * GROUPS + j]) * qsum[j][nt][c & 1];
-                        s[nt][c] = v * p.scale_log2e;
+                        for (int j = 0; j < NG; ++j) {
+                            v = fmaf(ksc[c >> 1][j], acc[j][nt][c], v);
+                            bq = fmaf(kbi[c >> 1][j], qsum[j][nt][c & 1], bq);
+                        }
+                        s[nt][c] = fmaf(v, k24, bq * p.scale_log2e);
                     }
             }
             if (!interior) {
@@ -238,11 +290,11 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                     const float mx = quad_column_max(fmaxf(s[nt][e], s[nt][2 + e]));
                     const float m_new = fmaxf(m[nt][e], mx);
                     const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-                    corr[nt][e] = exp2f(m[nt][e] - m_safe);
+                    corr[nt][e] = ex2(m[nt][e] - m_safe);
                     rescale |= (m_new != m[nt][e]);
                     m[nt][e] = m_new;
-                    const float pA = exp2f(s[nt][e] - m_safe), pB = exp2f(s[nt][2 + e] - m_safe);
-                    l[nt][e] = l[nt][e] * corr[nt][e] + pA + pB;
+                    const float pA = ex2(s[nt][e] - m_safe), pB = ex2(s[nt][2 + e] - m_safe);
+                    l[nt][e] = fmaf(l[nt][e], corr[nt][e], pA + pB);
                     s[nt][e] = pA;
                     s[nt][2 + e] = pB;
                 }
@@ -261,12 +313,21 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                     pb[0][nt][1] = movmatrix_trans(pack2<BF16>(s[nt][2], s[nt][3]));
                 }
             } else {
+                float vsc[2][NG], vbi[2][NG];
 #pragma unroll
-                for (int j = 0; j < NG; ++j) {
-                    const float vsA = __half2float(sbs[2 * kTile * GROUPS + tokA * GROUPS + j]);
-                    const float vsB = __half2float(sbs[2 * kTile * GROUPS + tokB * GROUPS + j]);
-                    const float vbA = __half2float(sbs[3 * kTile * GROUPS + tokA * GROUPS + j]);
-                    const float vbB = __half2float(sbs[3 * kTile * GROUPS + tokB * GROUPS + j]);
+                for (int ab = 0; ab < 2; ++ab) {
+                    const int tok = ab ? tokB : tokA;
+                    if constexpr (NG == 2) {
+                        const float2 sv = h2_to_f2(*(const uint32_t*)(sbs + 2 * kTile * GROUPS + tok * 2));
+                        const float2 bv = h2_to_f2(*(const uint32_t*)(sbs + 3 * kTile * GROUPS + tok * 2));
+                        vsc[ab][0] = sv.x; vsc[ab][1] = sv.y; vbi[ab][0] = bv.x; vbi[ab][1] = bv.y;
+                    } else {
+                        vsc[ab][0] = __half2float(sbs[2 * kTile * GROUPS + tok]);
+                        vbi[ab][0] = __half2float(sbs[3 * kTile * GROUPS + tok]);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < NG; ++j)
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
                         float sc[4], bi[4];
@@ -274,15 +335,14 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                         for (int c = 0; c < 4; ++c) {
                             // stale scale/bias of unwritten slots may be NaN: select, never multiply by a zero weight
                             const float pv = s[nt][c];
-                            sc[c] = pv > 0.f ? pv * (c < 2 ? vsA : vsB) : 0.f;
-                            bi[c] = pv > 0.f ? pv * (c < 2 ? vbA : vbB) : 0.f;
+                            sc[c] = pv > 0.f ? pv * vsc[c >> 1][j] : 0.f;
+                            bi[c] = pv > 0.f ? pv * vbi[c >> 1][j] : 0.f;
                         }
                         pb[j][nt][0] = movmatrix_trans(pack2<false>(sc[0], sc[1]));
                         pb[j][nt][1] = movmatrix_trans(pack2<false>(sc[2], sc[3]));
 #pragma unroll
-                        for (int e = 0; e < 2; ++e) bsum[j][nt][e] = bsum[j][nt][e] * corr[nt][e] + bi[e] + bi[2 + e];
+                        for (int e = 0; e < 2; ++e) bsum[j][nt][e] = fmaf(bsum[j][nt][e], corr[nt][e], bi[e] + bi[2 + e]);
                     }
-                }
             }
 
             // ---- O^T[D x rows] += V^T[D x 16 tokens] . P^T[16 tokens x rows]
@@ -291,19 +351,17 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                 uint32_t a[4];
                 const int jv = FMT == 0 ? 0 : (16 * mt) / 64;
                 if constexpr (FMT == 0) {
-                    const int tok = 16 * warp + (lane & 7) + 8 * (lane >> 4);
-                    const int ch = 2 * mt + ((lane >> 3) & 1);
-                    ptx::ldmatrix_x4_trans(a, vs_base + ptx::swz<3>((uint32_t)((ch >> 3) * (kTile * 128) + tok * 128 + (ch & 7) * 16)));
+                    ptx::ldmatrix_x4_trans(a, st_base + (mt >> 2) * (kTile * 128) + (v_off ^ (uint32_t)(((2 * mt) & 7) << 4)));
                 } else if constexpr (FMT == 8) {
-                    const uint32_t x = *(const uint32_t*)(st + C::KBYTES + ptx::swz<C::VSW>((uint32_t)((16 * mt + g) * C::VROW + 16 * warp + 4 * t)));
-                    const uint32_t y = *(const uint32_t*)(st + C::KBYTES + ptx::swz<C::VSW>((uint32_t)((16 * mt + g + 8) * C::VROW + 16 * warp + 4 * t)));
+                    const uint32_t x = *(const uint32_t*)(st + v_off + (16 * mt) * C::VROW);
+                    const uint32_t y = *(const uint32_t*)(st + v_off + (16 * mt + 8) * C::VROW);
                     a[0] = ptx::prmt(x, 0u, 0x4140u);
                     a[1] = ptx::prmt(y, 0u, 0x4140u);
                     a[2] = ptx::prmt(x, 0u, 0x4342u);
                     a[3] = ptx::prmt(y, 0u, 0x4342u);
                 } else {
-                    const uint32_t x = *(const uint16_t*)(st + C::KBYTES + ptx::swz<C::VSW>((uint32_t)((16 * mt + g) * C::VROW + 8 * warp + 2 * t)));
-                    const uint32_t y = *(const uint16_t*)(st + C::KBYTES + ptx::swz<C::VSW>((uint32_t)((16 * mt + g + 8) * C::VROW + 8 * warp + 2 * t)));
+                    const uint32_t x = *(const uint16_t*)(st + v_off + (16 * mt) * C::VROW);
+                    const uint32_t y = *(const uint16_t*)(st + v_off + (16 * mt + 8) * C::VROW);
                     const uint32_t z = x | (y << 16);
                     const uint32_t lo = z & 0x0F0F0F0Fu, hi = (z >> 4) & 0x0F0F0F0Fu;
                     a[0] = ptx::prmt(lo, 0u, 0x4140u);
@@ -319,113 +377,97 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
         }
 
         // ------------------------------------------------------------------ combine the eight warps' states
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const float lw = quad_column_sum(l[nt][e]);
-                if (g == 0) {
-                    wm[warp * 32 + 8 * nt + 2 * t + e] = m[nt][e];
-                    wl[warp * 32 + 8 * nt + 2 * t + e] = lw;
-                }
-                if constexpr (FMT != 0) {
-#pragma unroll
-                    for (int j = 0; j < NG; ++j) {
-                        const float bw = quad_column_sum(bsum[j][nt][e]);
-                        if (g == 0) wb[(j * kConsumerWarps + warp) * 32 + 8 * nt + 2 * t + e] = bw;
-                    }
-                }
-            }
-        consumer_sync();
-        float fac[NT][2];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int row = 8 * nt + 2 * t + e;
-                float M = -INFINITY;
-#pragma unroll
-                for (int ww = 0; ww < kConsumerWarps; ++ww) M = fmaxf(M, wm[ww * 32 + row]);
-                const float M_safe = M == -INFINITY ? 0.f : M;
-                float L = 0.f;
-#pragma unroll
-                for (int ww = 0; ww < kConsumerWarps; ++ww) {
-                    const float fw = exp2f(wm[ww * 32 + row] - M_safe);
-                    L += fw * wl[ww * 32 + row];
-                }
-                fac[nt][e] = exp2f(m[nt][e] - M_safe) * (FMT != 0 ? kTwo24 : 1.0f);
-                if (warp == 0 && g == 0) {
-                    rowM[row] = M;
-                    rowL[row] = L;
-                }
-            }
-
-        const long long a_flat = (long long)p.unit_cum[w.u] * p.Hkv + (long long)head * w.ntiles;
-        const long long b_flat = a_flat + w.ntiles;
-        const bool complete = (w.j == 0) && (run == w.ntiles);
+        const long long a_flat = (long long)cum_u * p.Hkv + (long long)head * ntiles;
+        const long long b_flat = a_flat + ntiles;
+        const bool complete = (j_first == 0) && (run == ntiles);
         const long long P = active;
         const int which = (max(a_flat, f_begin) != f_begin) ? 1 : 0;
         float* slot = p.slots + ((size_t)blockIdx.x * 2 + which) * kSlotFloats;
-
-        // sum of the scaled accumulators over warps, 64 columns of D at a time, in warp order
+        float lw[NT][2], bw[NG][NT][2];
 #pragma unroll
-        for (int h = 0; h < HALVES; ++h) {
-            if (h > 0) consumer_sync();  // the previous half has been read
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int mq = 0; mq < 4; ++mq) {
-                const int mt = 4 * h + mq;
+            for (int e = 0; e < 2; ++e) {
+                lw[nt][e] = quad_column_sum(l[nt][e]);
+#pragma unroll
+                for (int j = 0; j < NG; ++j) bw[j][nt][e] = FMT != 0 ? quad_column_sum(bsum[j][nt][e]) : 0.f;
+            }
+        constexpr int PASSES = D / RC, MT_PER_PASS = RC / 16, QUADS = ROWS * RC / 4;
+#pragma unroll
+        for (int pass = 0; pass < PASSES; ++pass) {
+            consumer_sync();  // every warp has left its tile loop / the previous pass has been read
+            if (pass == 0 && g == 0) {
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int row = 8 * nt + 2 * t + e;
+                        wm[warp * 32 + row] = m[nt][e];
+                        wl[warp * 32 + row] = lw[nt][e];
+                        if constexpr (FMT != 0) {
+#pragma unroll
+                            for (int j = 0; j < NG; ++j) wb[(j * kConsumerWarps + warp) * 32 + row] = bw[j][nt][e];
+                        }
+                    }
+            }
+#pragma unroll
+            for (int mq = 0; mq < MT_PER_PASS; ++mq) {
+                const int mt = pass * MT_PER_PASS + mq;
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const int dl = 16 * mq + g + 8 * (c >> 1), row = 8 * nt + 2 * t + (c & 1);
-                        ored[(warp * 64 + dl) * ROWS + row] = o[mt][nt][c] * fac[nt][c & 1];
+                        ored[(warp * ROWS + row) * RSTRIDE + dl] = o[mt][nt][c];
                     }
             }
             consumer_sync();
-            for (int idx = tid; idx < 64 * ROWS; idx += kConsumerThreads) {
-                const int dl = idx / ROWS, row = idx - dl * ROWS, d = 64 * h + dl;
-                float v = 0.f;
+            for (int q = tid; q < QUADS; q += kConsumerThreads) {
+                const int row = q / (RC / 4), dl = 4 * (q - row * (RC / 4)), d = pass * RC + dl;
+                float M = -INFINITY;
 #pragma unroll
-                for (int ww = 0; ww < kConsumerWarps; ++ww) v += ored[(ww * 64 + dl) * ROWS + row];
+                for (int ww = 0; ww < kConsumerWarps; ++ww) M = fmaxf(M, wm[ww * 32 + row]);
+                const float M_safe = M == -INFINITY ? 0.f : M;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                float L = 0.f, bias = 0.f;
+#pragma unroll
+                for (int ww = 0; ww < kConsumerWarps; ++ww) {
+                    const float fw = ex2(wm[ww * 32 + row] - M_safe);
+                    const float4 v = *(const float4*)(ored + (ww * ROWS + row) * RSTRIDE + dl);
+                    acc.x = fmaf(fw, v.x, acc.x); acc.y = fmaf(fw, v.y, acc.y);
+                    acc.z = fmaf(fw, v.z, acc.z); acc.w = fmaf(fw, v.w, acc.w);
+                    L = fmaf(fw, wl[ww * 32 + row], L);
+                    if constexpr (FMT != 0) bias = fmaf(fw, wb[((d / 64) * kConsumerWarps + ww) * 32 + row], bias);
+                }
                 if constexpr (FMT != 0) {
-                    // bias term of this column's scale group: sum_w f_w * sum_tok P * vb
-                    float bt = 0.f;
-                    const float M = rowM[row], M_safe = M == -INFINITY ? 0.f : M;
-#pragma unroll
-                    for (int ww = 0; ww < kConsumerWarps; ++ww)
-                        bt += exp2f(wm[ww * 32 + row] - M_safe) * wb[((d / 64) * kConsumerWarps + ww) * 32 + row];
-                    v += bt;
+                    acc.x = fmaf(acc.x, kTwo24, bias); acc.y = fmaf(acc.y, kTwo24, bias);
+                    acc.z = fmaf(acc.z, kTwo24, bias); acc.w = fmaf(acc.w, kTwo24, bias);
                 }
                 if (complete) {
-                    const float L = rowL[row];
-                    *(uint16_t*)(stage_out + row * OUT_STRIDE + d * 2) = to_bits16<BF16>(L > 0.f ? v / L : 0.f);
+                    const int r = row0 + row;
+                    if (r < R) {
+                        const float inv = L > 0.f ? 1.0f / L : 0.f;
+                        const int i = r / p.G, hh = r - i * p.G;
+                        uint2 packed;
+                        packed.x = pack2<BF16>(acc.x * inv, acc.y * inv);
+                        packed.y = pack2<BF16>(acc.z * inv, acc.w * inv);
+                        *(uint2*)((uint16_t*)p.out + ((long long)(qs + i) * p.Hq + head * p.G + hh) * D + d) = packed;
+                    }
                 } else {
-                    slot[row * D + d] = v;
+                    *(float4*)(slot + row * D + d) = acc;
+                    if (d == 0) {
+                        slot[ROWS * D + row] = M;
+                        slot[ROWS * D + ROWS + row] = L;
+                    }
                 }
             }
         }
-        if (complete) {
-            consumer_sync();
-            constexpr int CH = D / 8;
-            for (int idx = tid; idx < ROWS * CH; idx += kConsumerThreads) {
-                const int row = idx / CH, ch = idx - row * CH, r = row0 + row;
-                if (r < R) {
-                    const int i = r / p.G, hh = r - i * p.G;
-                    uint16_t* dst = (uint16_t*)p.out + ((long long)(qs + i) * p.Hq + head * p.G + hh) * D + ch * 8;
-                    *(uint4*)dst = *(const uint4*)(stage_out + row * OUT_STRIDE + ch * 16);
-                }
-            }
-        } else {
-            if (tid < ROWS) {
-                slot[ROWS * D + tid] = rowM[tid];
-                slot[ROWS * D + ROWS + tid] = rowL[tid];
-            }
+        if (!complete) {
             __threadfence();
             consumer_sync();
             const int c_first = (int)(((a_flat + 1) * P - 1) / total_flat);
             const int c_last = (int)((b_flat * P - 1) / total_flat);
-            int* counter = p.counters + (size_t)w.u * p.Hkv + head;
+            int* counter = p.counters + (size_t)unit * p.Hkv + head;
             if (tid == 0) misc[1] = atomicAdd(counter, 1);
             consumer_sync();
             if (misc[1] == c_last - c_first) {
@@ -445,9 +487,9 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                         const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
                         const float lp = __ldcg(sl + ROWS * D + ROWS + row);
                         if (lp > 0.f) {
-                            const float wgt = exp2f(__ldcg(sl + ROWS * D + row) - M);
-                            acc += wgt * __ldcg(sl + row * D + d);
-                            den += wgt * lp;
+                            const float wgt = ex2(__ldcg(sl + ROWS * D + row) - M);
+                            acc = fmaf(wgt, __ldcg(sl + row * D + d), acc);
+                            den = fmaf(wgt, lp, den);
                         }
                     }
                     const int i = r / p.G, hh = r - i * p.G;
@@ -457,9 +499,8 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                 if (tid == 0) *counter = 0;
             }
         }
-        consumer_sync();
         f += run;
-        w.next_part(p.unit_cum, num_units, p.Hkv);
+        ++part_idx;
     }
 }
 

@@ -42,6 +42,7 @@ struct TiledParams {
     int32_t* counters;
     float* slots;
     int32_t* status;
+    long long* trace;  // optional per-CTA records {start ns, end ns, tiles, 0}
     const __half* k_scale;
     const __half* k_bias;
     const __half* v_scale;
@@ -70,10 +71,28 @@ struct Cfg {
     // Two consumer designs share the kernel: up to 16 rows every warp keeps its own softmax state and its own
     // O^T[D x rows] over its 16 tokens of each tile (no CTA barrier per tile); 32-row units split D across warps.
     static constexpr bool PRIVATE = NT <= 2;
-    static constexpr int PBYTES = PRIVATE ? ROWS * (D * 2 + 16) : NPBUF * ROWS * kPStride;      // region A
-    static constexpr int OREDBYTES = PRIVATE ? kConsumerWarps * 64 * ROWS * 4                    // region B
+    // private design: the producer warp also stages a descriptor and the Q rows of every upcoming part
+    static constexpr int QSTRIDE = D * 2;
+    static constexpr int NDESC = PRIVATE ? (NT == 1 ? 4 : 2) : 0;
+    static constexpr int DESC_BYTES = PRIVATE ? 64 + ROWS * QSTRIDE : 0;
+    static constexpr int SMALL = 2 * 32 * 4 + 4 * kConsumerWarps * 32 * 4 + 64 + 256;  // row stats, per-warp stats, misc, barriers
+    static constexpr int red_bytes(int cols) { return kConsumerWarps * ROWS * (cols + 4) * 4; }
+    static constexpr int stages_with(int fixed) { return (kSmemBudget - fixed) / STAGE > 8 ? 8 : (kSmemBudget - fixed) / STAGE; }
+    static constexpr int PRIV_BASE = NDESC * DESC_BYTES + SMALL;
+    // columns of D summed across warps per pass: the widest buffer that still leaves min(4, best) stages
+    static constexpr int STAGES_BEST = stages_with(PRIV_BASE + red_bytes(16));
+    static constexpr int STAGES_MIN = STAGES_BEST < 4 ? STAGES_BEST : 4;
+    static constexpr int RED_COLS = stages_with(PRIV_BASE + red_bytes(D)) >= STAGES_MIN ? D
+                                    : (D > 64 && stages_with(PRIV_BASE + red_bytes(64)) >= STAGES_MIN) ? 64
+                                    : (stages_with(PRIV_BASE + red_bytes(32)) >= STAGES_MIN) ? 32 : 16;
+    static constexpr int PBYTES = PRIVATE ? NDESC * DESC_BYTES : NPBUF * ROWS * kPStride;        // region A
+    static constexpr int OREDBYTES = PRIVATE ? red_bytes(RED_COLS)                               // region B
                                              : (TS > 1 ? kConsumerWarps * 16 * ROWS * 4 : 0);
-    static constexpr int FIXED = PBYTES + OREDBYTES + 2 * 32 * 4 + 4 * kConsumerWarps * 32 * 4 + 64 + 2 * 8 * 8;
+    static constexpr int OFF_SMALL = PBYTES + OREDBYTES;          // 64 floats of row statistics (tile max / merged max, sum)
+    static constexpr int OFF_W = OFF_SMALL + 2 * 32 * 4;          // 4 x [warps][32] floats
+    static constexpr int OFF_MISC = OFF_W + 4 * kConsumerWarps * 32 * 4;
+    static constexpr int OFF_BAR = OFF_MISC + 64;                 // full[8], empty[8], dfull[4], dempty[4]
+    static constexpr int FIXED = OFF_BAR + 256;
     static constexpr int STAGES_RAW = (kSmemBudget - FIXED) / STAGE;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM = STAGES * STAGE + FIXED + 1024;
@@ -86,6 +105,12 @@ __device__ __forceinline__ int f2ord(float f) {
     return i >= 0 ? i : i ^ 0x7fffffff;
 }
 __device__ __forceinline__ float ord2f(int i) { return __int_as_float(i >= 0 ? i : i ^ 0x7fffffff); }
+
+// What the consumers need to know about one (unit, head) part; written by the producer warp.
+struct PartDesc {
+    int seq, row0, tile_lo, qs, q_len, kv_len, head, u, j, run, ntiles, cum_u, pad[4];
+};
+static_assert(sizeof(PartDesc) == 64, "descriptor header is 64 bytes");
 
 struct Walk {
     int u, head, j, ntiles;
@@ -114,10 +139,14 @@ struct Walk {
 // ------------------------------------------------------------------------------------------ producer
 template <int D, int NT, int FMT>
 __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUtensorMap* vmap, const TiledParams& p,
-                                              uint8_t* stages, uint64_t* full, uint64_t* empty, volatile int* abort_word,
-                                              long long f_begin, long long f_end, int num_units) {
+                                              uint8_t* stages, uint8_t* fixed, uint64_t* full, uint64_t* empty,
+                                              volatile int* abort_word, long long f_begin, long long f_end, int num_units) {
     using C = Cfg<D, NT, FMT>;
     const int lane = threadIdx.x & 31;
+    uint64_t* dfull = full + 16;
+    uint64_t* dempty = full + 20;
+    uint32_t part_idx = 0;
+    (void)dfull; (void)dempty; (void)part_idx; (void)fixed;
     Walk w;
     w.locate(f_begin, p.unit_cum, num_units, p.Hkv);
     long long f = f_begin;
@@ -127,6 +156,29 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
         const int tile_lo = p.unit_tile_lo[w.u];
         const int kv_len = p.kv_lens[seq];
         const int run = (int)min((long long)(w.ntiles - w.j), f_end - f);
+        if constexpr (C::PRIVATE) {
+            // descriptor + Q rows of this part, so that the consumers start it without touching global memory
+            const uint32_t slot = part_idx % C::NDESC, use = part_idx / C::NDESC;
+            if (use > 0) ptx::mbar_wait(&dempty[slot], (use & 1) ^ 1, abort_word);
+            if (lane == 0 && !*abort_word) {
+                PartDesc* d = (PartDesc*)(fixed + (size_t)slot * C::DESC_BYTES);
+                const int row0 = p.unit_row0[w.u], qs = p.qsl[seq], q_len = p.qsl[seq + 1] - qs;
+                const int R = q_len * p.G, rows_here = min(C::ROWS, R - row0);
+                d->seq = seq; d->row0 = row0; d->tile_lo = tile_lo; d->qs = qs; d->q_len = q_len; d->kv_len = kv_len;
+                d->head = w.head; d->u = w.u; d->j = w.j; d->run = run; d->ntiles = w.ntiles; d->cum_u = p.unit_cum[w.u];
+                ptx::mbar_arrive_expect_tx(&dfull[slot], (uint32_t)(rows_here * D * 2));
+                uint8_t* qdst = (uint8_t*)d + 64;
+                for (int r = row0; r < row0 + rows_here;) {
+                    const int i = r / p.G, hh = r - i * p.G;
+                    const int n = min(row0 + rows_here - r, p.G - hh);  // rows of token i inside this unit
+                    const uint16_t* src = (const uint16_t*)p.q + ((long long)(qs + i) * p.Hq + w.head * p.G + hh) * D;
+                    ptx::bulk_load(qdst + (size_t)(r - row0) * C::QSTRIDE, src, (uint32_t)(n * D * 2), &dfull[slot]);
+                    r += n;
+                }
+            }
+            __syncwarp();
+            ++part_idx;
+        }
         for (int base = 0; base < run; base += 32) {
             const int idx = tile_lo + w.j + base + lane;
             int page = -1;
@@ -211,10 +263,10 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
 
     uint8_t* Ps = fixed;
     float* ored = (float*)(fixed + C::PBYTES);
-    int* tmax = (int*)(fixed + C::PBYTES + C::OREDBYTES);
-    float* wl = (float*)(tmax + 64);
+    int* tmax = (int*)(fixed + C::OFF_SMALL);
+    float* wl = (float*)(fixed + C::OFF_W);
     float* wb = wl + kConsumerWarps * 32;  // [2][warps][32]
-    int* misc = (int*)(wb + 3 * kConsumerWarps * 32);
+    int* misc = (int*)(fixed + C::OFF_MISC);
     const int ORD_NEG_INF = f2ord(-INFINITY);
 
     Walk w;
@@ -735,15 +787,26 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* fixed = smem + (size_t)C::STAGES * C::STAGE;
-    uint64_t* full = (uint64_t*)(fixed + C::FIXED - 2 * 8 * 8);
+    uint64_t* full = (uint64_t*)(fixed + C::OFF_BAR);
     uint64_t* empty = full + 8;
-    int* tmax = (int*)(fixed + C::PBYTES + C::OREDBYTES);
-    volatile int* abort_word = (volatile int*)(tmax + 64 + 4 * kConsumerWarps * 32);  // misc[0]
+    uint64_t* dfull = full + 16;
+    uint64_t* dempty = full + 20;
+    int* tmax = (int*)(fixed + C::OFF_SMALL);
+    volatile int* abort_word = (volatile int*)(fixed + C::OFF_MISC);  // misc[0]
 
     if (threadIdx.x == 0) {
+        if (p.trace) {
+            long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            p.trace[4 * blockIdx.x + 0] = now;
+        }
         for (int s = 0; s < C::STAGES; ++s) {
             ptx::mbar_init(&full[s], 1);
             ptx::mbar_init(&empty[s], kConsumerWarps);
+        }
+        for (int s = 0; s < C::NDESC; ++s) {
+            ptx::mbar_init(&dfull[s], 1);
+            ptx::mbar_init(&dempty[s], kConsumerWarps);
         }
         *abort_word = 0;
         ptx::fence_barrier_init();
@@ -754,15 +817,20 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     __syncthreads();
 
     if (threadIdx.x >= kConsumerThreads) {
-        producer_loop<D, NT, FMT>(&kmap, &vmap, p, smem, full, empty, abort_word, f_begin, f_end, num_units);
+        producer_loop<D, NT, FMT>(&kmap, &vmap, p, smem, fixed, full, empty, abort_word, f_begin, f_end, num_units);
     } else {
         if constexpr (C::PRIVATE)
-            consumer_loop_private<D, NT, FMT, BF16>(p, smem, fixed, full, empty, abort_word, f_begin, f_end, num_units,
-                                                    total_flat, active);
+            consumer_loop_private<D, NT, FMT, BF16>(p, smem, fixed, full, empty, abort_word, f_begin, f_end, total_flat, active);
         else
             consumer_loop<D, NT, FMT, BF16>(p, smem, fixed, full, empty, abort_word, f_begin, f_end, num_units, total_flat, active);
     }
     if (*abort_word && threadIdx.x == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
+    if (p.trace && threadIdx.x == 0) {
+        long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        p.trace[4 * blockIdx.x + 1] = now;
+        p.trace[4 * blockIdx.x + 2] = f_end - f_begin;
+    }
 }
 
 // ------------------------------------------------------------------------------------------ host
@@ -879,6 +947,9 @@ static int launch_class(int cls, int D, int fmt, bool bf16, const MapPair& maps,
     return launch_fmt<64, 4>(fmt, bf16, maps, p, s);
 }
 
+static long long* g_trace = nullptr;
+void set_trace(long long* buf) { g_trace = buf; }
+
 static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* stream, int class_lo, int class_hi) {
     if (int rc = validate_attn(a, pool, true)) return rc;
     if (a->total_tokens == 0) return EMLX_OK;
@@ -915,6 +986,7 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
         p.counters = (int32_t*)((uint8_t*)a->workspace + W.counter_off[c]);
         p.slots = (float*)((uint8_t*)a->workspace + W.slots_off);
         p.status = a->status;
+        p.trace = g_trace;
         p.k_scale = (const __half*)pool->k_scale; p.k_bias = (const __half*)pool->k_bias;
         p.v_scale = (const __half*)pool->v_scale; p.v_bias = (const __half*)pool->v_bias;
         p.num_blocks = pool->num_blocks;
@@ -928,6 +1000,7 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
 }  // namespace emlx
 
 extern "C" {
+void emlx_set_trace_buffer(int64_t* records) { emlx::set_trace((long long*)records); }
 int emlx_attn_unified(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 0, emlx::kNumClasses - 1); }
 int emlx_attn_decode(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 0, 1); }
 int emlx_attn_prefill(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 2, 2); }

@@ -162,6 +162,10 @@ int emlx_attn_generic(const emlx_attn_args* args, const emlx_pool* pool, void* s
  * calls that overlap on the GPU (different streams) race, so serialise them.  Calls no allocating routine. */
 int emlx_attn_decode_static(const emlx_attn_args* args, const emlx_pool* pool, void* stream);
 
+/* Tracing aid: when `records` is a device buffer of 4 * 256 int64, every CTA of the tiled attention kernels
+ * writes {start ns, end ns, tiles processed, 0} (GPU global timer) at index 4 * blockIdx.x; NULL turns it off. */
+void emlx_set_trace_buffer(int64_t* records);
+
 /* Number of kernels this library has launched from the calling process (for launch accounting). */
 int64_t emlx_launch_count(void);
 
