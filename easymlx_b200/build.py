@@ -45,7 +45,7 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
         stale = force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(src), newest_header)
         if not stale:
             continue
-        cmd = [_nvcc(), *NVCC_FLAGS, "-I", INCLUDE, "-c", src, "-o", obj]
+        cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("EMLX_NVCC_EXTRA", "").split(), "-I", INCLUDE, "-c", src, "-o", obj]
         if ptxas_info:
             cmd += ["-Xptxas", "-v"]
         if verbose:

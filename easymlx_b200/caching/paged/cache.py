@@ -105,13 +105,15 @@ class PageMetadata:
     slot_ids: tuple[int, ...] | None = None
     # filled by concatenate_to_cache: upper bound of query tokens per sequence known on the host (0 = unknown)
     max_query_len: int = field(default=0, compare=False)
+    # attention work list built on the GPU together with the metadata: (buffer, num_q_heads, sliding_window)
+    plan: tp.Any | None = field(default=None, compare=False)
 
     def with_cache_state(self, *, block_tables, kv_lens, block_size: int) -> "PageMetadata":
         return PageMetadata(
             query_start_loc=self.query_start_loc, block_tables=block_tables, kv_lens=kv_lens,
             block_size=int(block_size), sliding_window=self.sliding_window,
             is_single_token_decode=self.is_single_token_decode, slot_ids=self.slot_ids,
-            max_query_len=self.max_query_len,
+            max_query_len=self.max_query_len, plan=self.plan,
         )
 
     def with_sliding_window(self, sliding_window: int | None) -> "PageMetadata":
@@ -285,7 +287,7 @@ class PageCacheView:
 
     # ------------------------------------------------------------------ writes
     def _write_batch(self, keys: torch.Tensor, values: torch.Tensor, query_lens_dev: torch.Tensor,
-                     slots_dev: torch.Tensor, total_tokens: int):
+                     slots_dev: torch.Tensor, total_tokens: int, plan_for: tuple | None = None):
         """Metadata kernel + write kernel for one packed batch.  Returns ``(qsl, block_tables, kv_lens)``
         of the scheduled rows; ``self.kv_lens`` is advanced in place."""
         nv.require_cuda(keys, values, self.key_cache)
@@ -300,10 +302,17 @@ class PageCacheView:
             raise ValueError("block_tables and kv_lens must be int32")
         if not (self.block_tables.is_contiguous() and self.kv_lens.is_contiguous()):
             raise ValueError("block_tables and kv_lens must be contiguous")
+        plan = None
+        hq = window = max_q = plan_bytes = 0
+        if plan_for is not None and self.block_size == 128 and total_tokens > 0:
+            hq, window, max_q = plan_for
+            plan_bytes = int(lib.emlx_attn_plan_bytes(s, total_tokens, hq, self.num_kv_heads))
+            plan = torch.empty(plan_bytes, dtype=torch.uint8, device=dev)
         nv.check(lib.emlx_build_metadata(
             nv.ptr(query_lens_dev), nv.ptr(slots_dev), s, total_tokens, nv.ptr(self.block_tables), self.num_seqs,
             self.blocks_per_seq, nv.ptr(self.kv_lens), self.block_size, 1, nv.ptr(qsl), nv.ptr(bt), nv.ptr(lens),
-            nv.ptr(slot_mapping), self.num_blocks, nv.ptr(self.status), stream))
+            nv.ptr(slot_mapping), self.num_blocks, nv.ptr(self.status), hq, self.num_kv_heads, window, max_q,
+            nv.ptr(plan), plan_bytes, stream))
         if total_tokens > 0:
             if keys.shape != values.shape:
                 raise ValueError("key and value must have the same shape")
@@ -317,7 +326,7 @@ class PageCacheView:
                                        nv.ptr(slot_mapping), pool, nv.ptr(self.status), stream))
         if _CHECK:
             self.check()
-        return qsl, bt, lens
+        return qsl, bt, lens, (None if plan is None else (plan, hq, window))
 
     def append(self, seq_idx: int, key: torch.Tensor, value: torch.Tensor) -> None:
         """Append ``[num_tokens, num_kv_heads, head_dim]`` rows to one slot (``cache.py:834-872``)."""
@@ -390,11 +399,13 @@ class PageCacheView:
                 qlens_dev = (qsl_in[1:len(slots) + 1] - qsl_in[:len(slots)]).to(device=dev, dtype=torch.int32).contiguous()
                 single = bool(getattr(cache_metadata, "is_single_token_decode", False)) and total == len(slots)
                 max_q = 1 if single else 0
-        qsl, bt, lens = self._write_batch(keys, values, qlens_dev, _uploaded.get(slots, dev), total)
+        window = int(getattr(cache_metadata, "sliding_window", None) or 0)
+        qsl, bt, lens, plan = self._write_batch(keys, values, qlens_dev, _uploaded.get(slots, dev), total,
+                                                plan_for=(int(queries.shape[1]), window, max_q))
         meta = PageMetadata(
             query_start_loc=qsl, sliding_window=getattr(cache_metadata, "sliding_window", None),
             is_single_token_decode=bool(getattr(cache_metadata, "is_single_token_decode", False)) or single,
-            slot_ids=getattr(cache_metadata, "slot_ids", None) or slots, max_query_len=max_q,
+            slot_ids=getattr(cache_metadata, "slot_ids", None) or slots, max_query_len=max_q, plan=plan,
         ).with_cache_state(block_tables=bt, kv_lens=lens, block_size=self.block_size)
         return queries, self.key_cache, self.value_cache, meta
 

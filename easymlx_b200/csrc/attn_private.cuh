@@ -175,6 +175,11 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
             const int t0 = (tile_lo + j_first + jj) * kTile;
             const bool interior = (t0 + kTile <= hi_min) && (t0 >= lo_max);
             ptx::mbar_wait(&full[stage], (it / C::STAGES) & 1, abort_word);
+#ifdef EMLX_EXPERIMENT_STREAM_ONLY  // measurement aid: consume the tiles without any arithmetic
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&empty[stage]);
+            continue;
+#endif
 
             // ---- scores of this warp's 16 tokens against every row
             float s[NT][4];
@@ -331,12 +336,21 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
 #pragma unroll
                     for (int nt = 0; nt < NT; ++nt) {
                         float sc[4], bi[4];
+                        if (interior) {
 #pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            // stale scale/bias of unwritten slots may be NaN: select, never multiply by a zero weight
-                            const float pv = s[nt][c];
-                            sc[c] = pv > 0.f ? pv * vsc[c >> 1][j] : 0.f;
-                            bi[c] = pv > 0.f ? pv * vbi[c >> 1][j] : 0.f;
+                            for (int c = 0; c < 4; ++c) {
+                                sc[c] = s[nt][c] * vsc[c >> 1][j];
+                                bi[c] = s[nt][c] * vbi[c >> 1][j];
+                            }
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < 4; ++c) {
+                                // slots past the sequence end hold stale scale/bias bytes (possibly NaN): select,
+                                // never multiply them by a zero weight
+                                const float pv = s[nt][c];
+                                sc[c] = pv > 0.f ? pv * vsc[c >> 1][j] : 0.f;
+                                bi[c] = pv > 0.f ? pv * vbi[c >> 1][j] : 0.f;
+                            }
                         }
                         pb[j][nt][0] = movmatrix_trans(pack2<false>(sc[0], sc[1]));
                         pb[j][nt][1] = movmatrix_trans(pack2<false>(sc[2], sc[3]));

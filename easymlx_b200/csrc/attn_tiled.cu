@@ -11,7 +11,7 @@
 // so that one page read serves every query row of its KV head.  A slice that ends inside a
 // (unit, head) writes an un-normalised partial; the CTA that delivers the last partial merges all of
 // them in CTA order (deterministic), so no CTA ever waits for another.
-#include "attn_tiled.cuh"
+#include "plan_device.cuh"
 #include "ptx.cuh"
 
 #include <map>
@@ -970,10 +970,8 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
     MapPair* maps = nullptr;
     if (int rc = get_maps(*pool, &maps)) return rc;
 
-    // classes that can hold a sequence of 1..max_query_len tokens (0 = unknown: up to the largest)
-    auto cls_of = [](int rows) { return rows <= 8 ? 0 : (rows <= 16 ? 1 : 2); };
-    const long long hint_rows = (long long)a->max_query_len * G;
-    int lo = cls_of(G), hi = a->max_query_len > 0 ? cls_of(hint_rows > (1 << 20) ? (1 << 20) : (int)hint_rows) : kNumClasses - 1;
+    int lo, hi;
+    class_range(G, a->max_query_len, lo, hi);
     lo = max(lo, class_lo);
     hi = min(hi, class_hi);
     const int32_t* plan = (const int32_t*)a->plan;

@@ -1,7 +1,7 @@
 // Batch metadata on the GPU: prefix sum of query lengths, gather of the scheduled slots' page-table
 // rows and lengths, per-token slot mapping.  One CTA; the batch is a few thousand integers.
 #include "common.cuh"
-#include "scan.cuh"
+#include "plan_device.cuh"
 
 namespace emlx {
 
@@ -9,7 +9,8 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
     const int32_t* __restrict__ query_lens, const int32_t* __restrict__ slot_ids, int S, int T,
     const int32_t* __restrict__ bt_all, int num_slots, int MB, int32_t* kv_lens_all, int bs, int advance,
     int32_t* __restrict__ qsl, int32_t* __restrict__ bt_out, int32_t* __restrict__ kv_out,
-    int64_t* __restrict__ slot_mapping, int64_t num_blocks, int32_t* status) {
+    int64_t* __restrict__ slot_mapping, int64_t num_blocks, int32_t* status, int32_t* plan, PlanLayout L, int G,
+    int window, int class_lo, int class_hi) {
     __shared__ int32_t scan_smem[kMetaThreads / 32 + 1];
     const int tid = threadIdx.x;
 
@@ -45,6 +46,9 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
     }
     __syncthreads();  // qsl and kv_out of this CTA are now visible to all its threads
 
+    // attention work list in the same launch (lengths after the write are final here)
+    if (plan != nullptr) build_plan(qsl, kv_out, S, G, window, class_lo, class_hi, plan, L, scan_smem);
+
     if (slot_mapping == nullptr) return;
     const int n = min(T, total);
     for (int t = tid; t < T; t += kMetaThreads) {
@@ -74,7 +78,8 @@ extern "C" int emlx_build_metadata(const int32_t* query_lens, const int32_t* slo
                                    int32_t max_blocks_per_seq, int32_t* kv_lens_all, int32_t block_size,
                                    int32_t advance_kv_lens, int32_t* query_start_loc, int32_t* block_tables,
                                    int32_t* kv_lens, int64_t* slot_mapping, int64_t num_blocks, int32_t* status,
-                                   void* stream) {
+                                   int32_t num_q_heads, int32_t num_kv_heads, int32_t sliding_window,
+                                   int32_t max_query_len, void* plan, size_t plan_bytes, void* stream) {
     using namespace emlx;
     if (num_seqs < 0 || total_tokens < 0) return fail(EMLX_ERR_INVALID, "num_seqs/total_tokens must be non-negative");
     if (block_size <= 0 || max_blocks_per_seq <= 0 || num_slots <= 0)
@@ -82,9 +87,22 @@ extern "C" int emlx_build_metadata(const int32_t* query_lens, const int32_t* slo
     if (!query_start_loc || !kv_lens_all || !block_tables_all || (num_seqs > 0 && (!query_lens || !slot_ids)))
         return fail(EMLX_ERR_INVALID, "build_metadata: NULL input");
     if (num_seqs > 0 && (!block_tables || !kv_lens)) return fail(EMLX_ERR_INVALID, "build_metadata: NULL output");
+    PlanLayout L{};
+    int class_lo = 0, class_hi = -1, G = 1;
+    if (plan) {
+        if (num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % num_kv_heads)
+            return fail(EMLX_ERR_INVALID, "num_q_heads must be divisible by num_kv_heads (GQA)");
+        if (block_size != kTile) return fail(EMLX_ERR_UNSUPPORTED, "the attention work list needs page size %d", kTile);
+        L = plan_layout(num_seqs, total_tokens, num_q_heads, num_kv_heads);
+        if (plan_bytes < (size_t)L.words * sizeof(int32_t))
+            return fail(EMLX_ERR_WORKSPACE, "plan buffer smaller than emlx_attn_plan_bytes()");
+        G = num_q_heads / num_kv_heads;
+        class_range(G, max_query_len, class_lo, class_hi);
+    }
     build_metadata_kernel<<<1, kMetaThreads, 0, (cudaStream_t)stream>>>(
         query_lens, slot_ids, num_seqs, total_tokens, block_tables_all, num_slots, max_blocks_per_seq, kv_lens_all,
-        block_size, advance_kv_lens, query_start_loc, block_tables, kv_lens, slot_mapping, num_blocks, status);
+        block_size, advance_kv_lens, query_start_loc, block_tables, kv_lens, slot_mapping, num_blocks, status,
+        (int32_t*)plan, L, G, sliding_window, class_lo, class_hi);
     EMLX_LAUNCHED();
     return EMLX_OK;
 }

@@ -1,0 +1,126 @@
+// Device routine that builds the tiled kernels' work list; called by the stand-alone plan kernel and, fused,
+// by the batch-metadata kernel.  One CTA of kMetaThreads threads; sequences are handled 1024 at a time with
+// register-resident block scans (two per class), so the whole list costs a few microseconds.
+#pragma once
+#include "attn_tiled.cuh"
+#include "scan.cuh"
+
+namespace emlx {
+
+__device__ __forceinline__ int unit_class(int rows) { return rows <= 8 ? 0 : (rows <= 16 ? 1 : 2); }
+
+// Exclusive prefix of one value per thread across the CTA; `total` receives the CTA-wide sum.
+__device__ __forceinline__ int block_scan_value(int v, int32_t* smem /* [33] */, int& total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    __syncthreads();  // smem free from the previous use
+    if (lane == 31) smem[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const int wsum = smem[lane];
+        int wi = wsum;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, wi, o);
+            if (lane >= o) wi += up;
+        }
+        smem[lane] = wi - wsum;
+        if (lane == 31) smem[32] = wi;
+    }
+    __syncthreads();
+    total = smem[32];
+    return smem[warp] + incl - v;
+}
+
+// Tile range of the rows [row0, row1) of a sequence: first tile and number of tiles (at least one, so that a
+// unit without keys still produces zero rows).
+__device__ __forceinline__ void unit_tiles(int row0, int row1, int G, int q_len, int kv_len, int window, int& tile_lo,
+                                           int& ntiles) {
+    const int ctx = kv_len - q_len;
+    const int i_min = row0 / G, i_max = (row1 - 1) / G;
+    const int hi = min(kv_len, ctx + i_max + 1);
+    const int lo = window > 0 ? max(0, min(kv_len - 1, ctx + i_min) - window + 1) : 0;
+    tile_lo = 0;
+    ntiles = 1;
+    if (hi > 0 && hi > lo) {
+        tile_lo = lo / kTile;
+        ntiles = (hi + kTile - 1) / kTile - tile_lo;
+    }
+}
+
+__device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv_lens, int S, int G, int window,
+                                           int class_lo, int class_hi, int32_t* plan, const PlanLayout& L,
+                                           int32_t* scan_smem) {
+    const int tid = threadIdx.x;
+    for (int c = 0; c < kNumClasses; ++c) {
+        if (c < class_lo || c > class_hi) {
+            if (tid == 0) { plan[4 * c + 0] = 0; plan[4 * c + 1] = 0; }
+            continue;
+        }
+        const int rows_c = class_rows(c);
+        int32_t* unit_seq = plan + L.unit_seq[c];
+        int32_t* unit_row0 = plan + L.unit_row0[c];
+        int32_t* unit_tile_lo = plan + L.unit_tile_lo[c];
+        int32_t* unit_cum = plan + L.unit_cum[c];
+        int32_t* seq_off = plan + L.tmp;  // first unit of every sequence in this class
+        // pass 1: units per sequence -> first-unit offsets
+        int num_units = 0;
+        for (int s0 = 0; s0 < S; s0 += kMetaThreads) {
+            const int s = s0 + tid;
+            int n = 0;
+            if (s < S) {
+                const int q_len = qsl[s + 1] - qsl[s], rows = q_len * G;
+                if (q_len > 0 && unit_class(rows) == c) n = (rows + rows_c - 1) / rows_c;
+            }
+            int n_total;
+            const int off = num_units + block_scan_value(n, scan_smem, n_total);
+            if (s < S) seq_off[s] = off;
+            num_units += n_total;
+        }
+        __syncthreads();
+        // pass 2: one thread per unit: owner sequence by binary search, tile range, running tile prefix
+        int tile_base = 0;
+        for (int i0 = 0; i0 < num_units; i0 += kMetaThreads) {
+            const int idx = i0 + tid;
+            int nt = 0;
+            if (idx < num_units) {
+                int lo = 0, hi = S;  // largest s with seq_off[s] <= idx
+                while (hi - lo > 1) {
+                    const int mid = (lo + hi) >> 1;
+                    if (seq_off[mid] <= idx) lo = mid; else hi = mid;
+                }
+                const int s = lo, u = idx - seq_off[s];
+                const int q_len = qsl[s + 1] - qsl[s], rows = q_len * G;
+                int tile_lo;
+                unit_tiles(u * rows_c, min(rows, (u + 1) * rows_c), G, q_len, kv_lens[s], window, tile_lo, nt);
+                unit_seq[idx] = s;
+                unit_row0[idx] = u * rows_c;
+                unit_tile_lo[idx] = tile_lo;
+            }
+            int t_total;
+            const int t_off = tile_base + block_scan_value(nt, scan_smem, t_total);
+            if (idx < num_units) unit_cum[idx] = t_off;
+            tile_base += t_total;
+        }
+        if (tid == 0) {
+            unit_cum[num_units] = tile_base;
+            plan[4 * c + 0] = num_units;
+            plan[4 * c + 1] = tile_base;
+        }
+        __syncthreads();  // seq_off is reused by the next class
+    }
+}
+
+// classes that can hold a sequence of 1..max_query_len tokens with G rows per token (0 = unknown: all of them)
+inline void class_range(int G, int max_query_len, int& lo, int& hi) {
+    auto cls_of = [](long long rows) { return rows <= 8 ? 0 : (rows <= 16 ? 1 : 2); };
+    lo = cls_of(G);
+    hi = max_query_len > 0 ? cls_of((long long)max_query_len * G) : kNumClasses - 1;
+}
+
+}  // namespace emlx

@@ -136,7 +136,7 @@ class AttentionCall:
     def __init__(self, queries, key_cache, value_cache, block_tables, kv_lens, query_start_loc, *,
                  softmax_scale: float | None = None, sliding_window: int | None = None,
                  k_scale=None, v_scale=None, k_bias=None, v_bias=None, kernel: str | None = None,
-                 max_query_len: int = 0):
+                 max_query_len: int = 0, plan=None):
         nv.require_cuda(queries, key_cache, value_cache)
         dev = queries.device
         affine = key_cache.dtype == torch.uint8
@@ -187,17 +187,22 @@ class AttentionCall:
             hkv = self.pool.num_kv_heads
             self.plan_bytes = int(lib.emlx_attn_plan_bytes(self.num_seqs, self.total, self.hq, hkv))
             ws_bytes = int(lib.emlx_attn_workspace_bytes(self.num_seqs, self.total, self.hq, hkv, self.d))
-            self.plan_buf = _scratch.get(dev, "plan", self.plan_bytes, zero=False)
+            self.planned = False
+            if plan is not None and plan[1] == self.hq and plan[2] == self.window and plan[0].numel() >= self.plan_bytes:
+                self.plan_buf, self.planned = plan[0], True   # built together with the batch metadata
+            else:
+                self.plan_buf = _scratch.get(dev, "plan", self.plan_bytes, zero=False)
             self.workspace = _scratch.get(dev, "workspace", ws_bytes, zero=True)
             a.plan, a.plan_bytes = self.plan_buf.data_ptr(), self.plan_bytes
             a.workspace, a.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
 
     def plan(self) -> "AttentionCall":
-        if self.total and self.kernel != "generic":
+        if self.total and self.kernel != "generic" and not self.planned:
             nv.check(nv.lib().emlx_attn_plan(
                 nv.ptr(self.query_start_loc), nv.ptr(self.kv_lens), self.num_seqs, self.total, self.hq,
-                self.pool.num_kv_heads, self.pool.block_size, self.window, nv.ptr(self.plan_buf), self.plan_bytes,
-                nv.stream_ptr(self.device)))
+                self.pool.num_kv_heads, self.pool.block_size, self.window, int(self.args.max_query_len),
+                nv.ptr(self.plan_buf), self.plan_bytes, nv.stream_ptr(self.device)))
+            self.planned = True
         return self
 
     def launch(self) -> torch.Tensor:
@@ -239,6 +244,7 @@ def paged_attention(
     v_bias: torch.Tensor | None = None,
     kernel: str | None = None,
     max_query_len: int = 0,
+    plan=None,
 ) -> torch.Tensor:
     """Ragged causal attention of packed queries over a paged KV pool.
 
@@ -256,7 +262,8 @@ def paged_attention(
         max_query_len = 1
     return AttentionCall(queries, key_cache, value_cache, block_tables, kv_lens, query_start_loc,
                          softmax_scale=softmax_scale, sliding_window=sliding_window, k_scale=k_scale, v_scale=v_scale,
-                         k_bias=k_bias, v_bias=v_bias, kernel=kernel, max_query_len=max_query_len).plan().launch()
+                         k_bias=k_bias, v_bias=v_bias, kernel=kernel, max_query_len=max_query_len,
+                         plan=plan).plan().launch()
 
 
 @OperationRegistry.register
@@ -307,7 +314,8 @@ class UnifiedAttention(BaseOperation):
             query, key, value, cache_metadata.block_tables, cache_metadata.kv_lens, cache_metadata.query_start_loc,
             softmax_scale=scale, sliding_window=cache_metadata.sliding_window,
             single_token_decode=cache_metadata.is_single_token_decode,
-            max_query_len=int(getattr(cache_metadata, "max_query_len", 0) or 0), **extra,
+            max_query_len=int(getattr(cache_metadata, "max_query_len", 0) or 0),
+            plan=getattr(cache_metadata, "plan", None), **extra,
         )
         return AttentionOutput(attention_outputs=outputs, cache_view=cache_view)
 

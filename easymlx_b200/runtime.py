@@ -38,6 +38,7 @@ class AttentionStep:
         self.out: torch.Tensor | None = None
         self.graph: torch.cuda.CUDAGraph | None = None
         self.launches_per_step = 0
+        self.steps_per_graph = 1
 
     def _eager(self) -> torch.Tensor:
         if self.rewind:
@@ -50,8 +51,11 @@ class AttentionStep:
         return op(query=self.q, key=kc, value=vc, cache_metadata=meta, cache_view=self.cache,
                   scale=self.performer.scale).attention_outputs
 
-    def capture(self, warmup: int = 3) -> "AttentionStep":
-        """Run the step eagerly a few times on a side stream, then record it into a CUDA graph."""
+    def capture(self, warmup: int = 3, steps_per_graph: int = 1) -> "AttentionStep":
+        """Run the step eagerly a few times on a side stream, then record it into a CUDA graph.
+
+        ``steps_per_graph`` > 1 records that many consecutive steps in one graph, the way an engine step holds
+        one attention step per transformer layer; ``step()`` then advances by that many steps per call."""
         side = torch.cuda.Stream(device=self.q.device)
         side.wait_stream(torch.cuda.current_stream(self.q.device))
         with torch.cuda.stream(side):
@@ -62,8 +66,10 @@ class AttentionStep:
         graph = torch.cuda.CUDAGraph()
         before = nv.launch_count()
         with torch.cuda.graph(graph):
-            self.out = self._eager()
-        self.launches_per_step = nv.launch_count() - before
+            for _ in range(max(1, steps_per_graph)):
+                self.out = self._eager()
+        self.steps_per_graph = max(1, steps_per_graph)
+        self.launches_per_step = (nv.launch_count() - before) // self.steps_per_graph
         self.graph = graph
         return self
 
