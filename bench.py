@@ -265,7 +265,7 @@ def run_ours(args):
     def one_step():
         out = step.step()
         if head_shard:
-            dist.all_gather_into_tensor(gathered, out)
+            dist.all_gather_into_tensor(gathered.view(-1, *out.shape[1:]), out)
         return out
 
     for _ in range(2):
@@ -322,7 +322,7 @@ def run_ours(args):
         w.q.copy_(hq, non_blocking=True); w.k.copy_(hk, non_blocking=True); w.v.copy_(hv, non_blocking=True)
         out = step1.step()
         if head_shard:
-            dist.all_gather_into_tensor(gathered, out)
+            dist.all_gather_into_tensor(gathered.view(-1, *out.shape[1:]), out)
         hout.copy_(gathered[rank] if head_shard else out, non_blocking=True)
 
     for _ in range(3):
