@@ -50,11 +50,12 @@ SIGNATURES = {
     "emlx_launch_count": (C.c_int64, []),
     "emlx_read_status": (C.c_int, [_P, _P]),
     "emlx_build_metadata": (C.c_int, [_P, _P, _I32, _I32, _P, _I32, _I32, _P, _I32, _I32, _P, _P, _P, _P, _I64, _P,
-                                     _I32, _I32, _I32, _I32, _P, C.c_size_t, _P]),
+                                     _I32, _I32, _I32, _I32, _I32, _P, C.c_size_t, _P]),
     "emlx_kv_write": (C.c_int, [_P, _P, _I32, _I32, _P, C.POINTER(Pool), _P, _P]),
     "emlx_attn_plan_bytes": (C.c_size_t, [_I32, _I32, _I32, _I32]),
     "emlx_attn_workspace_bytes": (C.c_size_t, [_I32, _I32, _I32, _I32, _I32]),
-    "emlx_attn_plan": (C.c_int, [_P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _P, C.c_size_t, _P]),
+    "emlx_attn_plan": (C.c_int, [_P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _P, C.c_size_t, _P]),
+    "emlx_attn_plan_flags": (C.c_int, [_I32, _I32, _I32, _I32]),
     "emlx_attn_unified": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
     "emlx_attn_decode": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
     "emlx_attn_prefill": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),

@@ -303,16 +303,18 @@ class PageCacheView:
         if not (self.block_tables.is_contiguous() and self.kv_lens.is_contiguous()):
             raise ValueError("block_tables and kv_lens must be contiguous")
         plan = None
-        hq = window = max_q = plan_bytes = 0
+        hq = window = max_q = plan_bytes = flags = 0
         if plan_for is not None and self.block_size == 128 and total_tokens > 0:
             hq, window, max_q = plan_for
+            flags = int(lib.emlx_attn_plan_flags(self.cache_bits if self.is_affine else nv.KV_FLOAT, hq,
+                                                 self.num_kv_heads, self.head_dim))
             plan_bytes = int(lib.emlx_attn_plan_bytes(s, total_tokens, hq, self.num_kv_heads))
             plan = torch.empty(plan_bytes, dtype=torch.uint8, device=dev)
         nv.check(lib.emlx_build_metadata(
             nv.ptr(query_lens_dev), nv.ptr(slots_dev), s, total_tokens, nv.ptr(self.block_tables), self.num_seqs,
             self.blocks_per_seq, nv.ptr(self.kv_lens), self.block_size, 1, nv.ptr(qsl), nv.ptr(bt), nv.ptr(lens),
             nv.ptr(slot_mapping), self.num_blocks, nv.ptr(self.status), hq, self.num_kv_heads, window, max_q,
-            nv.ptr(plan), plan_bytes, stream))
+            flags, nv.ptr(plan), plan_bytes, stream))
         if total_tokens > 0:
             if keys.shape != values.shape:
                 raise ValueError("key and value must have the same shape")

@@ -6,10 +6,10 @@ namespace emlx {
 
 __global__ void __launch_bounds__(kMetaThreads) attn_plan_kernel(const int32_t* __restrict__ qsl,
                                                                  const int32_t* __restrict__ kv_lens, int S, int G,
-                                                                 int window, int class_lo, int class_hi, int32_t* plan,
-                                                                 PlanLayout L) {
+                                                                 int window, int class_lo, int class_hi, bool wide,
+                                                                 int32_t* plan, PlanLayout L) {
     __shared__ int32_t scan_smem[kMetaThreads / 32 + 1];
-    build_plan(qsl, kv_lens, S, G, window, class_lo, class_hi, plan, L, scan_smem);
+    build_plan(qsl, kv_lens, S, G, window, class_lo, class_hi, wide, plan, L, scan_smem);
 }
 
 }  // namespace emlx
@@ -29,7 +29,7 @@ size_t emlx_attn_workspace_bytes(int32_t num_seqs, int32_t total_tokens, int32_t
 
 int emlx_attn_plan(const int32_t* query_start_loc, const int32_t* kv_lens, int32_t num_seqs, int32_t total_tokens,
                    int32_t num_q_heads, int32_t num_kv_heads, int32_t block_size, int32_t sliding_window,
-                   int32_t max_query_len, void* plan, size_t plan_bytes, void* stream) {
+                   int32_t max_query_len, int32_t plan_flags, void* plan, size_t plan_bytes, void* stream) {
     using namespace emlx;
     if (num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % num_kv_heads)
         return fail(EMLX_ERR_INVALID, "num_q_heads must be divisible by num_kv_heads (GQA)");
@@ -40,10 +40,11 @@ int emlx_attn_plan(const int32_t* query_start_loc, const int32_t* kv_lens, int32
     if (num_seqs > 0 && (!query_start_loc || !kv_lens)) return fail(EMLX_ERR_INVALID, "attn_plan: NULL input");
     PlanLayout L = plan_layout(num_seqs, total_tokens, num_q_heads, num_kv_heads);
     int class_lo, class_hi;
-    class_range(num_q_heads / num_kv_heads, max_query_len, class_lo, class_hi);
+    const bool wide = (plan_flags & kPlanWideUnits) != 0;
+    class_range(num_q_heads / num_kv_heads, max_query_len, wide, class_lo, class_hi);
     attn_plan_kernel<<<1, kMetaThreads, 0, (cudaStream_t)stream>>>(query_start_loc, kv_lens, num_seqs,
                                                                     num_q_heads / num_kv_heads, sliding_window, class_lo,
-                                                                    class_hi, (int32_t*)plan, L);
+                                                                    class_hi, wide, (int32_t*)plan, L);
     EMLX_LAUNCHED();
     return EMLX_OK;
 }

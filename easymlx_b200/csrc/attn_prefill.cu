@@ -1,0 +1,437 @@
+// Prefill-chunk attention on the 5th-generation tensor cores (tcgen05 + TMEM), sm_100a only.
+//
+// Work unit: 128 query rows of one sequence (row = query token x GQA head of one KV head, token-major) and
+// one KV head; the plan lists the KV tiles (128-token pages) the rows may attend.  Per tile
+//     S[128 rows x 128 tokens]  = Q . K^T     tcgen05.mma, both operands K-major in shared memory (TMA, 128B swizzle),
+//                                             fp32 accumulator in TMEM columns [0, 128)
+//     softmax                                  four warps, one TMEM lane (= one row) per thread: no cross-thread reduction;
+//                                             P is written to shared memory as the next A operand
+//     O_tile[128 rows x D]      = P . V        tcgen05.mma, V read in place as an MN-major B operand, TMEM columns [128, 128+D)
+//     O = O * corr + O_tile                    in registers of the softmax threads
+// Warp roles: 0-3 softmax, 4 TMA producer, 5 MMA issuer (and TMEM owner).  All waits are bounded.
+#include "plan_device.cuh"
+#include "ptx.cuh"
+#include "tensor_maps.cuh"
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace emlx {
+
+constexpr int kPfThreads = 192;
+constexpr int kPfRows = 128;
+
+struct PrefillParams {
+    void* out;
+    const int32_t* bt;
+    const int32_t* kv_lens;
+    const int32_t* qsl;
+    const int32_t* hdr;
+    const int32_t* unit_seq;
+    const int32_t* unit_row0;
+    const int32_t* unit_tile_lo;
+    const int32_t* unit_cum;
+    int32_t* status;
+    long long num_blocks;
+    int Hq, Hkv, G, MB, window;
+    float scale_log2e;
+};
+
+template <int D>
+struct PfCfg {
+    static constexpr int HALVES = D / 64;
+    static constexpr int QBYTES = kPfRows * D * 2;
+    static constexpr int KBYTES = kTile * D * 2;
+    static constexpr int STAGE = 2 * KBYTES;
+    static constexpr int PBYTES = kPfRows * kTile * 2;
+    static constexpr int STAGES = D == 128 ? 2 : 4;
+    static constexpr int OFF_Q = 0;
+    static constexpr int OFF_P = QBYTES;
+    static constexpr int OFF_KV = OFF_P + PBYTES;
+    static constexpr int OFF_BAR = OFF_KV + STAGES * STAGE;
+    static constexpr int SMEM = OFF_BAR + 256 + 1024;
+    static constexpr int TMEM_COLS = 256;  // S: 128 columns, O_tile: D columns
+};
+
+// ------------------------------------------------------------------ tcgen05 wrappers
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_u32(smem_dst)), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(ptx::smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor: 128-byte swizzle, 8-row groups 1024 bytes apart (stride offset); the leading
+// offset is the distance between 64-element blocks along the contiguous dimension of an MN-major operand.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;  // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor for kind::f16: fp32 accumulate, fp16 or bf16 inputs, A K-major, B K- or MN-major.
+__host__ __device__ constexpr uint32_t instr_desc(int M, int N, bool bf16, bool b_mn_major) {
+    return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) | ((b_mn_major ? 1u : 0u) << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+
+struct PfBarriers {
+    uint64_t q_full, item_done, s_ready, p_ready, o_ready, o_free;
+    uint64_t kv_full[4], kv_empty[4];
+    uint32_t tmem_base;
+    int abort_word;
+};
+
+template <int D, bool BF16>
+__global__ void __launch_bounds__(kPfThreads, 1)
+attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
+                    const __grid_constant__ CUtensorMap vmap, const PrefillParams p) {
+    using C = PfCfg<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint8_t* q_smem = smem + C::OFF_Q;
+    uint8_t* p_smem = smem + C::OFF_P;
+    uint8_t* kv_smem = smem + C::OFF_KV;
+    PfBarriers* bars = (PfBarriers*)(smem + C::OFF_BAR);
+    volatile int* abort_word = &bars->abort_word;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    const int num_units = p.hdr[0];
+    const long long items = (long long)num_units * p.Hkv;
+    if ((long long)blockIdx.x >= items) return;  // uniform, before any barrier or TMEM allocation
+
+    if (tid == 0) {
+        ptx::mbar_init(&bars->q_full, 1);
+        ptx::mbar_init(&bars->item_done, 128);
+        ptx::mbar_init(&bars->s_ready, 1);
+        ptx::mbar_init(&bars->p_ready, 128);
+        ptx::mbar_init(&bars->o_ready, 1);
+        ptx::mbar_init(&bars->o_free, 128);
+        for (int s = 0; s < C::STAGES; ++s) {
+            ptx::mbar_init(&bars->kv_full[s], 1);
+            ptx::mbar_init(&bars->kv_empty[s], 1);
+        }
+        bars->abort_word = 0;
+        ptx::fence_barrier_init();
+        ptx::prefetch_tensormap(&qmap);
+        ptx::prefetch_tensormap(&kmap);
+        ptx::prefetch_tensormap(&vmap);
+    }
+    if (warp == 5) tmem_alloc(&bars->tmem_base, C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars->tmem_base;
+    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
+
+    if (warp == 4) {
+        // ------------------------------------------------------------------ TMA producer
+        uint32_t kt = 0, k = 0;
+        for (long long item = blockIdx.x; item < items && !*abort_word; item += gridDim.x, ++k) {
+            const int u = (int)(item / p.Hkv), head = (int)(item - (long long)u * p.Hkv);
+            const int seq = p.unit_seq[u], row0 = p.unit_row0[u], tile_lo = p.unit_tile_lo[u];
+            const int ntiles = p.unit_cum[u + 1] - p.unit_cum[u];
+            const int qs = p.qsl[seq], kv_len = p.kv_lens[seq];
+            if (k > 0) ptx::mbar_wait(&bars->item_done, (k - 1) & 1, abort_word);
+            if (lane == 0 && !*abort_word) {
+                ptx::mbar_arrive_expect_tx(&bars->q_full, C::QBYTES);
+#pragma unroll
+                for (int h = 0; h < C::HALVES; ++h)
+                    ptx::tma_load_3d(q_smem + h * (kPfRows * 128), &qmap, &bars->q_full, 64 * h, head * p.G, qs + row0 / p.G);
+            }
+            for (int base = 0; base < ntiles; base += 32) {
+                const int idx = tile_lo + base + lane;
+                int page = -1;
+                if (base + lane < ntiles && idx < p.MB) page = p.bt[(long long)seq * p.MB + idx];
+                const int cnt = min(32, ntiles - base);
+                for (int i = 0; i < cnt; ++i, ++kt) {
+                    const int pg = __shfl_sync(0xffffffffu, page, i);
+                    const uint32_t stage = kt % C::STAGES, use = kt / C::STAGES;
+                    if (use > 0) ptx::mbar_wait(&bars->kv_empty[stage], (use & 1) ^ 1, abort_word);
+                    if (lane == 0 && !*abort_word) {
+                        const bool bad = pg < 0 || pg >= p.num_blocks;
+                        if (bad && (long long)(tile_lo + base + i) * kTile < kv_len) flag_error(p.status, EMLX_DEV_BAD_PAGE);
+                        const int tok0 = bad ? -kTile : pg * kTile;  // out-of-range coordinates read as zeros
+                        uint8_t* st = kv_smem + (size_t)stage * C::STAGE;
+                        ptx::mbar_arrive_expect_tx(&bars->kv_full[stage], C::STAGE);
+#pragma unroll
+                        for (int h = 0; h < C::HALVES; ++h) {
+                            ptx::tma_load_3d(st + h * (kTile * 128), &kmap, &bars->kv_full[stage], 64 * h, head, tok0);
+                            ptx::tma_load_3d(st + C::KBYTES + h * (kTile * 128), &vmap, &bars->kv_full[stage], 64 * h, head, tok0);
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+        }
+    } else if (warp == 5) {
+        // ------------------------------------------------------------------ MMA issuer
+        constexpr uint32_t idesc_qk = instr_desc(128, 128, BF16, false);
+        constexpr uint32_t idesc_pv = instr_desc(128, D, BF16, true);
+        const uint32_t q_addr = ptx::smem_u32(q_smem), p_addr = ptx::smem_u32(p_smem);
+        uint32_t kt = 0, k = 0;
+        for (long long item = blockIdx.x; item < items && !*abort_word; item += gridDim.x, ++k) {
+            const int u = (int)(item / p.Hkv);
+            const int ntiles = p.unit_cum[u + 1] - p.unit_cum[u];
+            ptx::mbar_wait(&bars->q_full, k & 1, abort_word);
+            tc_fence_after();
+            for (int j = 0; j < ntiles; ++j, ++kt) {
+                const uint32_t stage = kt % C::STAGES;
+                const uint32_t k_addr = ptx::smem_u32(kv_smem + (size_t)stage * C::STAGE), v_addr = k_addr + C::KBYTES;
+                ptx::mbar_wait(&bars->kv_full[stage], (kt / C::STAGES) & 1, abort_word);
+                tc_fence_after();
+                if (lane == 0 && !*abort_word) {
+#pragma unroll
+                    for (int ks = 0; ks < D / 16; ++ks) {
+                        const uint32_t off = (ks >> 2) * (kTile * 128) + (ks & 3) * 32;
+                        tc_mma_f16(tmem_S, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), idesc_qk, ks > 0);
+                    }
+                    tc_commit(&bars->s_ready);
+                }
+                __syncwarp();
+                ptx::mbar_wait(&bars->p_ready, kt & 1, abort_word);
+                if (kt > 0) ptx::mbar_wait(&bars->o_free, (kt - 1) & 1, abort_word);
+                tc_fence_after();
+                if (lane == 0 && !*abort_word) {
+#pragma unroll
+                    for (int kk = 0; kk < kTile / 16; ++kk) {
+                        const uint32_t poff = (kk >> 2) * (kPfRows * 128) + (kk & 3) * 32;
+                        tc_mma_f16(tmem_O, smem_desc(p_addr + poff, 16, 1024),
+                                   smem_desc(v_addr + kk * (16 * 128), kTile * 128, 1024), idesc_pv, kk > 0);
+                    }
+                    tc_commit(&bars->o_ready);
+                    tc_commit(&bars->kv_empty[stage]);
+                }
+                __syncwarp();
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax: one row per thread
+        const int r = tid;
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        uint32_t kt = 0;
+        for (long long item = blockIdx.x; item < items; item += gridDim.x) {
+            const int u = (int)(item / p.Hkv), head = (int)(item - (long long)u * p.Hkv);
+            const int seq = p.unit_seq[u], row0 = p.unit_row0[u], tile_lo = p.unit_tile_lo[u];
+            const int ntiles = p.unit_cum[u + 1] - p.unit_cum[u];
+            const int qs = p.qsl[seq], q_len = p.qsl[seq + 1] - qs, kv_len = p.kv_lens[seq];
+            const int R = q_len * p.G, ctx = kv_len - q_len;
+            const int rows_here = min(kPfRows, R - row0);
+            const int rr = min(row0 + r, R - 1), ti = rr / p.G;
+            int hi = min(kv_len, ctx + ti + 1);
+            int lo = p.window > 0 ? max(0, min(kv_len - 1, ctx + ti) - p.window + 1) : 0;
+            if (hi <= 0) { hi = 0; lo = 0; }
+            const int i_first = row0 / p.G, i_last = (row0 + rows_here - 1) / p.G;
+            const int hi_min = min(kv_len, ctx + i_first + 1);
+            const int lo_max = p.window > 0 ? max(0, min(kv_len - 1, ctx + i_last) - p.window + 1) : 0;
+
+            float m = -INFINITY, l = 0.f, o[D];
+#pragma unroll
+            for (int d = 0; d < D; ++d) o[d] = 0.f;
+
+            for (int j = 0; j < ntiles; ++j, ++kt) {
+                const int t0 = (tile_lo + j) * kTile;
+                const bool interior = (t0 + kTile <= hi_min) && (t0 >= lo_max);
+                const uint32_t stage = kt % C::STAGES;
+                ptx::mbar_wait(&bars->s_ready, kt & 1, abort_word);
+                tc_fence_after();
+                float mx = -INFINITY;
+#pragma unroll 1
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    float v[32];
+                    tmem_ld32(tmem_S + lane_addr + 32 * c4, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int tok = t0 + 32 * c4 + i;
+                        const bool ok = interior || (tok >= lo && tok < hi);
+                        mx = fmaxf(mx, ok ? v[i] : -INFINITY);
+                    }
+                }
+                const float m_new = fmaxf(m, mx * p.scale_log2e);
+                const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+                float corr, lsum = 0.f;
+                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(corr) : "f"(m - m_safe));
+                m = m_new;
+#pragma unroll 1
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    float v[32];
+                    tmem_ld32(tmem_S + lane_addr + 32 * c4, v);
+                    uint32_t packed[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float p0, p1;
+                        const int tok = t0 + 32 * c4 + i;
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(v[i], p.scale_log2e, -m_safe)));
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(v[i + 1], p.scale_log2e, -m_safe)));
+                        if (!interior) {
+                            if (tok < lo || tok >= hi) p0 = 0.f;
+                            if (tok + 1 < lo || tok + 1 >= hi) p1 = 0.f;
+                        }
+                        lsum += p0 + p1;
+                        if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed[i / 2]) : "f"(p1), "f"(p0));
+                        else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed[i / 2]) : "f"(p1), "f"(p0));
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const int c16 = 4 * c4 + q;
+                        uint8_t* dst = p_smem + (c16 >> 3) * (kPfRows * 128) + r * 128 + (((c16 & 7) ^ (r & 7)) << 4);
+                        *(uint4*)dst = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                    }
+                }
+                l = fmaf(l, corr, lsum);
+                if (t0 + kTile > kv_len) {
+                    // token rows of V past the sequence end are stale memory: clear them (thread r owns token r)
+                    if (r >= max(0, kv_len - t0)) {
+                        uint8_t* vrow = kv_smem + (size_t)stage * C::STAGE + C::KBYTES + r * 128;
+#pragma unroll
+                        for (int h = 0; h < C::HALVES; ++h)
+#pragma unroll
+                            for (int c = 0; c < 8; ++c) *(uint4*)(vrow + h * (kTile * 128) + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+                ptx::fence_proxy_async();
+                tc_fence_before();
+                ptx::mbar_arrive(&bars->p_ready);
+
+                ptx::mbar_wait(&bars->o_ready, kt & 1, abort_word);
+                tc_fence_after();
+#pragma unroll
+                for (int c4 = 0; c4 < D / 32; ++c4) {
+                    float v[32];
+                    tmem_ld32(tmem_O + lane_addr + 32 * c4, v);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[32 * c4 + i] = fmaf(o[32 * c4 + i], corr, v[i]);
+                }
+                tc_fence_before();
+                ptx::mbar_arrive(&bars->o_free);
+            }
+            const float inv = l > 0.f ? 1.0f / l : 0.f;
+            if (row0 + r < R) {
+                const int i = (row0 + r) / p.G, hh = (row0 + r) - i * p.G;
+                uint4* dst = (uint4*)((uint16_t*)p.out + ((long long)(qs + i) * p.Hq + head * p.G + hh) * D);
+#pragma unroll
+                for (int c = 0; c < D / 8; ++c) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        if constexpr (BF16)
+                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(o[8 * c + 2 * e + 1] * inv), "f"(o[8 * c + 2 * e] * inv));
+                        else
+                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(o[8 * c + 2 * e + 1] * inv), "f"(o[8 * c + 2 * e] * inv));
+                    }
+                    dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            ptx::mbar_arrive(&bars->item_done);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if (*abort_word && tid == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
+}
+
+// ------------------------------------------------------------------------------------------ host
+bool prefill_supported(int kv_format, int num_q_heads, int num_kv_heads, int head_dim) {
+    if (kv_format != EMLX_KV_FLOAT || num_kv_heads <= 0 || num_q_heads % num_kv_heads) return false;
+    const int G = num_q_heads / num_kv_heads;
+    return (head_dim == 64 || head_dim == 128) && G <= kPfRows && kPfRows % G == 0;
+}
+
+// Q is [T, Hq, D]; a box of {64 columns, G heads, 128/G tokens} lands in shared memory as 128 rows in the
+// unit's row order (token-major, then GQA head), 128 bytes per row and swizzled like the K/V tiles.
+static int make_q_map(const emlx_attn_args* a, int D, int G, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::map<std::tuple<const void*, int, int, int, int, int>, CUtensorMap> cache;
+    auto key = std::make_tuple(a->queries, a->total_tokens, a->num_q_heads, D, G, a->q_dtype);
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) {
+        *out = it->second;
+        return EMLX_OK;
+    }
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return fail(EMLX_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)a->num_q_heads, (cuuint64_t)a->total_tokens};
+    const cuuint64_t strides[2] = {(cuuint64_t)D * 2, (cuuint64_t)a->num_q_heads * D * 2};
+    const cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(kPfRows / G)};
+    const cuuint32_t ones[3] = {1, 1, 1};
+    const CUtensorMapDataType dt = a->q_dtype == EMLX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap m;
+    CUresult r = enc(&m, dt, 3, const_cast<void*>(a->queries), dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(EMLX_ERR_CUDA, "cuTensorMapEncodeTiled failed for the query tensor (%d)", (int)r);
+    if (cache.size() > 256) cache.clear();
+    cache[key] = m;
+    *out = m;
+    return EMLX_OK;
+}
+
+template <int D, bool BF16>
+static int launch_pf(const CUtensorMap& qmap, const MapPair& maps, const PrefillParams& p, cudaStream_t stream) {
+    using C = PfCfg<D>;
+    auto kernel = attn_prefill_kernel<D, BF16>;
+    static bool configured = false;
+    if (!configured) {
+        EMLX_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
+        configured = true;
+    }
+    kernel<<<num_sms(), kPfThreads, C::SMEM, stream>>>(qmap, maps.k, maps.v, p);
+    EMLX_LAUNCHED();
+    return EMLX_OK;
+}
+
+int launch_prefill(const emlx_attn_args* a, const emlx_pool* pool, const int32_t* plan_class_hdr, const int32_t* unit_seq,
+                   const int32_t* unit_row0, const int32_t* unit_tile_lo, const int32_t* unit_cum, const MapPair& maps,
+                   cudaStream_t stream) {
+    const int D = pool->head_dim, Hq = a->num_q_heads, Hkv = pool->num_kv_heads, G = Hq / Hkv;
+    if (!prefill_supported(pool->kv_format, Hq, Hkv, D))
+        return fail(EMLX_ERR_UNSUPPORTED, "the tcgen05 prefill kernel needs an fp16/bf16 pool, head_dim 64/128 and 128 %% (Hq/Hkv) == 0");
+    CUtensorMap qmap;
+    if (int rc = make_q_map(a, D, G, &qmap)) return rc;
+    PrefillParams p;
+    p.out = a->out; p.bt = a->block_tables; p.kv_lens = a->kv_lens; p.qsl = a->query_start_loc;
+    p.hdr = plan_class_hdr; p.unit_seq = unit_seq; p.unit_row0 = unit_row0; p.unit_tile_lo = unit_tile_lo; p.unit_cum = unit_cum;
+    p.status = a->status; p.num_blocks = pool->num_blocks;
+    p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.MB = a->max_blocks_per_seq; p.window = a->sliding_window;
+    p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
+    const bool bf16 = a->q_dtype == EMLX_BF16;
+    if (D == 128) return bf16 ? launch_pf<128, true>(qmap, maps, p, stream) : launch_pf<128, false>(qmap, maps, p, stream);
+    return bf16 ? launch_pf<64, true>(qmap, maps, p, stream) : launch_pf<64, false>(qmap, maps, p, stream);
+}
+
+}  // namespace emlx

@@ -55,7 +55,7 @@ extern "C" int emlx_attn_decode_static(const emlx_attn_args* args, const emlx_po
     // The array keeps whatever the previous call left: the arrival counters must start at zero.
     EMLX_CUDA_OK(cudaMemsetAsync(workspace + W.counter_off[0], 0, W.bytes - W.counter_off[0], (cudaStream_t)stream));
     if (int rc = emlx_attn_plan(args->query_start_loc, args->kv_lens, S, T, Hq, Hkv, pool->block_size,
-                                args->sliding_window, args->max_query_len, plan, plan_bytes, stream))
+                                args->sliding_window, args->max_query_len, 0, plan, plan_bytes, stream))
         return rc;
     emlx_attn_args local = *args;
     local.plan = plan;

@@ -13,6 +13,7 @@
 // them in CTA order (deterministic), so no CTA ever waits for another.
 #include "plan_device.cuh"
 #include "ptx.cuh"
+#include "tensor_maps.cuh"
 
 #include <map>
 #include <mutex>
@@ -834,11 +835,7 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------------ host
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
+EncodeTiledFn encode_fn() {
     static EncodeTiledFn fn = nullptr;
     static std::once_flag once;
     std::call_once(once, [] {
@@ -855,12 +852,8 @@ static CUtensorMapSwizzle swizzle_of(int row_bytes) {
     return row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 
-struct MapPair {
-    CUtensorMap k, v;
-};
-
 // Tensor maps depend only on the pool's address and geometry; they are encoded once and cached.
-static int get_maps(const emlx_pool& pool, MapPair** out) {
+int get_maps(const emlx_pool& pool, MapPair** out) {
     static std::mutex mu;
     static std::map<std::tuple<void*, void*, long long, int, int, int, int>, MapPair> cache;
     auto key = std::make_tuple(pool.key_cache, pool.value_cache, (long long)pool.num_blocks, pool.num_kv_heads,
@@ -970,12 +963,19 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
     MapPair* maps = nullptr;
     if (int rc = get_maps(*pool, &maps)) return rc;
 
+    const bool wide = prefill_supported(pool->kv_format, Hq, Hkv, D);
     int lo, hi;
-    class_range(G, a->max_query_len, lo, hi);
+    class_range(G, a->max_query_len, wide, lo, hi);
     lo = max(lo, class_lo);
     hi = min(hi, class_hi);
     const int32_t* plan = (const int32_t*)a->plan;
     for (int c = lo; c <= hi; ++c) {
+        if (c == 3) {
+            if (int rc = launch_prefill(a, pool, plan + 4 * c, plan + L.unit_seq[c], plan + L.unit_row0[c],
+                                        plan + L.unit_tile_lo[c], plan + L.unit_cum[c], *maps, (cudaStream_t)stream))
+                return rc;
+            continue;
+        }
         TiledParams p;
         p.q = a->queries; p.out = a->out; p.bt = a->block_tables; p.kv_lens = a->kv_lens; p.qsl = a->query_start_loc;
         p.hdr = plan + 4 * c;
@@ -1000,6 +1000,9 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
 extern "C" {
 void emlx_set_trace_buffer(int64_t* records) { emlx::set_trace((long long*)records); }
 int emlx_attn_unified(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 0, emlx::kNumClasses - 1); }
-int emlx_attn_decode(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 0, 1); }
-int emlx_attn_prefill(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 2, 2); }
+int emlx_attn_decode(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 0, 2); }
+int emlx_attn_prefill(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 3, 3); }
+int emlx_attn_plan_flags(int32_t kv_format, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim) {
+    return emlx::prefill_supported(kv_format, num_q_heads, num_kv_heads, head_dim) ? emlx::kPlanWideUnits : 0;
+}
 }

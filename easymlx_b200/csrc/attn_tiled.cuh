@@ -5,7 +5,8 @@
 // into classes by their row count so that each class runs with the smallest tile that holds it:
 //     class 0: rows <= 8   (NT = 1)     decode with Hq/Hkv <= 8
 //     class 1: rows <= 16  (NT = 2)
-//     class 2: 32-row blocks (NT = 4)   spec-verify rows, prefill chunks
+//     class 2: rows <= 32  (NT = 4)     spec-verify rows (or, without wide units, every longer row set in 32-row blocks)
+//     class 3: 128-row blocks           prefill chunks, for the tcgen05 kernel (only with kPlanWideUnits)
 // The work of a class is the flat sequence of (unit, kv head, tile); CTA c of P takes the contiguous
 // slice [c*N/P, (c+1)*N/P).
 #pragma once
@@ -14,12 +15,16 @@
 namespace emlx {
 
 constexpr int kTile = 128;        // tokens per KV tile = page size the tiled kernels require
-constexpr int kNumClasses = 3;
+constexpr int kNumClasses = 4;
+constexpr int kPlanWideUnits = 1;  // plan flag: cut sequences with more than 32 rows into 128-row units (class 3)
 constexpr int kPlanHeaderWords = 16;
 constexpr int kMaxGrid = 256;     // upper bound on CTAs per launch, sizes the partial-result slots
 constexpr int kMaxRows = 32;      // rows of the largest class
 
-__host__ __device__ inline int class_rows(int c) { return 8 << c; }
+__host__ __device__ inline int class_rows(int c) { return c < 3 ? 8 << c : 128; }
+__host__ __device__ inline int unit_class(int rows, bool wide) {
+    return rows <= 8 ? 0 : (rows <= 16 ? 1 : ((!wide || rows <= 32) ? 2 : 3));
+}
 
 struct PlanLayout {
     int cap[kNumClasses];       // unit capacity per class
@@ -36,7 +41,7 @@ __host__ __device__ inline PlanLayout plan_layout(int S, int T, int Hq, int Hkv)
     const int G = Hq / Hkv;
     int w = kPlanHeaderWords;
     for (int c = 0; c < kNumClasses; ++c) {
-        L.cap[c] = (c == kNumClasses - 1) ? S + (int)(((long long)T * G + kMaxRows - 1) / kMaxRows) : S;
+        L.cap[c] = c < 2 ? S : S + (int)(((long long)T * G + class_rows(c) - 1) / class_rows(c));
         if (L.cap[c] < 1) L.cap[c] = 1;
         L.unit_seq[c] = w; w += L.cap[c];
         L.unit_row0[c] = w; w += L.cap[c];

@@ -7,7 +7,6 @@
 
 namespace emlx {
 
-__device__ __forceinline__ int unit_class(int rows) { return rows <= 8 ? 0 : (rows <= 16 ? 1 : 2); }
 
 // Exclusive prefix of one value per thread across the CTA; `total` receives the CTA-wide sum.
 __device__ __forceinline__ int block_scan_value(int v, int32_t* smem /* [33] */, int& total) {
@@ -54,8 +53,8 @@ __device__ __forceinline__ void unit_tiles(int row0, int row1, int G, int q_len,
 }
 
 __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv_lens, int S, int G, int window,
-                                           int class_lo, int class_hi, int32_t* plan, const PlanLayout& L,
-                                           int32_t* scan_smem) {
+                                           int class_lo, int class_hi, bool wide, int32_t* plan,
+                                           const PlanLayout& L, int32_t* scan_smem) {
     const int tid = threadIdx.x;
     for (int c = 0; c < kNumClasses; ++c) {
         if (c < class_lo || c > class_hi) {
@@ -75,7 +74,7 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
             int n = 0;
             if (s < S) {
                 const int q_len = qsl[s + 1] - qsl[s], rows = q_len * G;
-                if (q_len > 0 && unit_class(rows) == c) n = (rows + rows_c - 1) / rows_c;
+                if (q_len > 0 && unit_class(rows, wide) == c) n = (rows + rows_c - 1) / rows_c;
             }
             int n_total;
             const int off = num_units + block_scan_value(n, scan_smem, n_total);
@@ -117,10 +116,10 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
 }
 
 // classes that can hold a sequence of 1..max_query_len tokens with G rows per token (0 = unknown: all of them)
-inline void class_range(int G, int max_query_len, int& lo, int& hi) {
-    auto cls_of = [](long long rows) { return rows <= 8 ? 0 : (rows <= 16 ? 1 : 2); };
-    lo = cls_of(G);
-    hi = max_query_len > 0 ? cls_of((long long)max_query_len * G) : kNumClasses - 1;
+inline void class_range(int G, int max_query_len, bool wide, int& lo, int& hi) {
+    lo = unit_class(G, wide);
+    const long long rows = (long long)max_query_len * G;
+    hi = max_query_len > 0 ? unit_class(rows > (1 << 20) ? (1 << 20) : (int)rows, wide) : (wide ? 3 : 2);
 }
 
 }  // namespace emlx

@@ -201,6 +201,7 @@ class AttentionCall:
             nv.check(nv.lib().emlx_attn_plan(
                 nv.ptr(self.query_start_loc), nv.ptr(self.kv_lens), self.num_seqs, self.total, self.hq,
                 self.pool.num_kv_heads, self.pool.block_size, self.window, int(self.args.max_query_len),
+                int(nv.lib().emlx_attn_plan_flags(self.pool.kv_format, self.hq, self.pool.num_kv_heads, self.d)),
                 nv.ptr(self.plan_buf), self.plan_bytes, nv.stream_ptr(self.device)))
             self.planned = True
         return self

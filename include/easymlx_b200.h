@@ -122,7 +122,7 @@ int emlx_build_metadata(const int32_t* query_lens, const int32_t* slot_ids, int3
                         int64_t num_blocks, int32_t* status,
                         /* optional: also build the attention work list in the same launch (plan == NULL: skip) */
                         int32_t num_q_heads, int32_t num_kv_heads, int32_t sliding_window, int32_t max_query_len,
-                        void* plan, size_t plan_bytes, void* stream);
+                        int32_t plan_flags, void* plan, size_t plan_bytes, void* stream);
 
 /* (1) Paged KV write.  Replaces the scatter of PageCacheView.concatenate_to_cache
  * (caching/paged/cache.py:1186-1190,1278-1282) and, for AFFINE pools, the quantised-write hook
@@ -138,7 +138,11 @@ size_t emlx_attn_workspace_bytes(int32_t num_seqs, int32_t total_tokens, int32_t
                                  int32_t head_dim);
 int emlx_attn_plan(const int32_t* query_start_loc, const int32_t* kv_lens, int32_t num_seqs, int32_t total_tokens,
                    int32_t num_q_heads, int32_t num_kv_heads, int32_t block_size, int32_t sliding_window,
-                   int32_t max_query_len /* host hint, 0 = unknown */, void* plan, size_t plan_bytes, void* stream);
+                   int32_t max_query_len /* host hint, 0 = unknown */, int32_t plan_flags /* emlx_attn_plan_flags() */,
+                   void* plan, size_t plan_bytes, void* stream);
+/* Flags a plan should be built with for this pool and head geometry: bit 0 = cut sequences with more than 32
+ * query rows into 128-row units for the tcgen05 prefill kernel (fp16/bf16 pools, 128 % (Hq/Hkv) == 0). */
+int emlx_attn_plan_flags(int32_t kv_format, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim);
 
 /* (5) Unified ragged attention: decode rows and prefill chunks of one packed batch in one call.
  * Replaces paged_attention() (operations/kernels/unified_attention.py:1377-1512) and the Metal
