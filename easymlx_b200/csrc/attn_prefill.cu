@@ -43,15 +43,16 @@ struct PfCfg {
     static constexpr int HALVES = D / 64;
     static constexpr int QBYTES = kPfRows * D * 2;
     static constexpr int KBYTES = kTile * D * 2;
-    static constexpr int STAGE = 2 * KBYTES;
     static constexpr int PBYTES = kPfRows * kTile * 2;
-    static constexpr int STAGES = D == 128 ? 2 : 4;
+    static constexpr int KST = D == 128 ? 3 : 4;  // K tiles are needed one tile ahead of V (QK of tile j+1 precedes PV of tile j)
+    static constexpr int VST = D == 128 ? 2 : 4;
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_P = QBYTES;
-    static constexpr int OFF_KV = OFF_P + PBYTES;
-    static constexpr int OFF_BAR = OFF_KV + STAGES * STAGE;
+    static constexpr int OFF_K = OFF_P + PBYTES;
+    static constexpr int OFF_V = OFF_K + KST * KBYTES;
+    static constexpr int OFF_BAR = OFF_V + VST * KBYTES;
     static constexpr int SMEM = OFF_BAR + 256 + 1024;
-    static constexpr int TMEM_COLS = 256;  // S: 128 columns, O_tile: D columns
+    static constexpr int TMEM_COLS = 512;  // S (two buffers): columns [0,128) and [128,256); O: [256, 256 + D)
 };
 
 // ------------------------------------------------------------------ tcgen05 wrappers
@@ -92,6 +93,29 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory matrix descriptor: 128-byte swizzle, 8-row groups 1024 bytes apart (stride offset); the leading
 // offset is the distance between 64-element blocks along the contiguous dimension of an MN-major operand.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -110,8 +134,8 @@ __host__ __device__ constexpr uint32_t instr_desc(int M, int N, bool bf16, bool 
 }
 
 struct PfBarriers {
-    uint64_t q_full, item_done, s_ready, p_ready, o_ready, o_free;
-    uint64_t kv_full[4], kv_empty[4];
+    uint64_t q_full, item_done, s_ready[2], p_ready, o_ready;  // o_ready: PV of a tile complete
+    uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
     uint32_t tmem_base;
     int abort_word;
 };
@@ -125,7 +149,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_smem = smem + C::OFF_Q;
     uint8_t* p_smem = smem + C::OFF_P;
-    uint8_t* kv_smem = smem + C::OFF_KV;
+    uint8_t* k_smem = smem + C::OFF_K;
+    uint8_t* v_smem = smem + C::OFF_V;
     PfBarriers* bars = (PfBarriers*)(smem + C::OFF_BAR);
     volatile int* abort_word = &bars->abort_word;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -137,13 +162,15 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
     if (tid == 0) {
         ptx::mbar_init(&bars->q_full, 1);
         ptx::mbar_init(&bars->item_done, 128);
-        ptx::mbar_init(&bars->s_ready, 1);
+        ptx::mbar_init(&bars->s_ready[0], 1);
+        ptx::mbar_init(&bars->s_ready[1], 1);
         ptx::mbar_init(&bars->p_ready, 128);
         ptx::mbar_init(&bars->o_ready, 1);
-        ptx::mbar_init(&bars->o_free, 128);
-        for (int s = 0; s < C::STAGES; ++s) {
-            ptx::mbar_init(&bars->kv_full[s], 1);
-            ptx::mbar_init(&bars->kv_empty[s], 1);
+        for (int s = 0; s < 4; ++s) {
+            ptx::mbar_init(&bars->k_full[s], 1);
+            ptx::mbar_init(&bars->k_empty[s], 1);
+            ptx::mbar_init(&bars->v_full[s], 1);
+            ptx::mbar_init(&bars->v_empty[s], 1);
         }
         bars->abort_word = 0;
         ptx::fence_barrier_init();
@@ -156,7 +183,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
-    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
+    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256;
 
     if (warp == 4) {
         // ------------------------------------------------------------------ TMA producer
@@ -180,19 +207,23 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 const int cnt = min(32, ntiles - base);
                 for (int i = 0; i < cnt; ++i, ++kt) {
                     const int pg = __shfl_sync(0xffffffffu, page, i);
-                    const uint32_t stage = kt % C::STAGES, use = kt / C::STAGES;
-                    if (use > 0) ptx::mbar_wait(&bars->kv_empty[stage], (use & 1) ^ 1, abort_word);
+                    const bool bad = pg < 0 || pg >= p.num_blocks;
+                    const int tok0 = bad ? -kTile : pg * kTile;  // out-of-range coordinates read as zeros
+                    if (lane == 0 && bad && (long long)(tile_lo + base + i) * kTile < kv_len) flag_error(p.status, EMLX_DEV_BAD_PAGE);
+                    const uint32_t ks = kt % C::KST, vs = kt % C::VST;
+                    if (kt >= C::KST) ptx::mbar_wait(&bars->k_empty[ks], ((kt / C::KST) & 1) ^ 1, abort_word);
                     if (lane == 0 && !*abort_word) {
-                        const bool bad = pg < 0 || pg >= p.num_blocks;
-                        if (bad && (long long)(tile_lo + base + i) * kTile < kv_len) flag_error(p.status, EMLX_DEV_BAD_PAGE);
-                        const int tok0 = bad ? -kTile : pg * kTile;  // out-of-range coordinates read as zeros
-                        uint8_t* st = kv_smem + (size_t)stage * C::STAGE;
-                        ptx::mbar_arrive_expect_tx(&bars->kv_full[stage], C::STAGE);
+                        ptx::mbar_arrive_expect_tx(&bars->k_full[ks], C::KBYTES);
 #pragma unroll
-                        for (int h = 0; h < C::HALVES; ++h) {
-                            ptx::tma_load_3d(st + h * (kTile * 128), &kmap, &bars->kv_full[stage], 64 * h, head, tok0);
-                            ptx::tma_load_3d(st + C::KBYTES + h * (kTile * 128), &vmap, &bars->kv_full[stage], 64 * h, head, tok0);
-                        }
+                        for (int h = 0; h < C::HALVES; ++h)
+                            ptx::tma_load_3d(k_smem + (size_t)ks * C::KBYTES + h * (kTile * 128), &kmap, &bars->k_full[ks], 64 * h, head, tok0);
+                    }
+                    if (kt >= C::VST) ptx::mbar_wait(&bars->v_empty[vs], ((kt / C::VST) & 1) ^ 1, abort_word);
+                    if (lane == 0 && !*abort_word) {
+                        ptx::mbar_arrive_expect_tx(&bars->v_full[vs], C::KBYTES);
+#pragma unroll
+                        for (int h = 0; h < C::HALVES; ++h)
+                            ptx::tma_load_3d(v_smem + (size_t)vs * C::KBYTES + h * (kTile * 128), &vmap, &bars->v_full[vs], 64 * h, head, tok0);
                     }
                     __syncwarp();
                 }
@@ -209,32 +240,42 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             const int ntiles = p.unit_cum[u + 1] - p.unit_cum[u];
             ptx::mbar_wait(&bars->q_full, k & 1, abort_word);
             tc_fence_after();
-            for (int j = 0; j < ntiles; ++j, ++kt) {
-                const uint32_t stage = kt % C::STAGES;
-                const uint32_t k_addr = ptx::smem_u32(kv_smem + (size_t)stage * C::STAGE), v_addr = k_addr + C::KBYTES;
-                ptx::mbar_wait(&bars->kv_full[stage], (kt / C::STAGES) & 1, abort_word);
+            // S is double-buffered in TMEM: QK of tile j+1 is issued before PV of tile j, so the tensor pipe
+            // works while the softmax warps are busy with tile j
+            auto issue_qk = [&](uint32_t t) {
+                const uint32_t stage = t % C::KST;
+                const uint32_t k_addr = ptx::smem_u32(k_smem + (size_t)stage * C::KBYTES);
+                ptx::mbar_wait(&bars->k_full[stage], (t / C::KST) & 1, abort_word);
                 tc_fence_after();
                 if (lane == 0 && !*abort_word) {
 #pragma unroll
                     for (int ks = 0; ks < D / 16; ++ks) {
                         const uint32_t off = (ks >> 2) * (kTile * 128) + (ks & 3) * 32;
-                        tc_mma_f16(tmem_S, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024), idesc_qk, ks > 0);
+                        tc_mma_f16(tmem_S + (t & 1) * 128, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024),
+                                   idesc_qk, ks > 0);
                     }
-                    tc_commit(&bars->s_ready);
+                    tc_commit(&bars->s_ready[t & 1]);
+                    tc_commit(&bars->k_empty[stage]);
                 }
                 __syncwarp();
+            };
+            issue_qk(kt);
+            for (int j = 0; j < ntiles; ++j, ++kt) {
+                if (j + 1 < ntiles) issue_qk(kt + 1);
+                const uint32_t stage = kt % C::VST;
+                const uint32_t v_addr = ptx::smem_u32(v_smem + (size_t)stage * C::KBYTES);
+                ptx::mbar_wait(&bars->v_full[stage], (kt / C::VST) & 1, abort_word);
                 ptx::mbar_wait(&bars->p_ready, kt & 1, abort_word);
-                if (kt > 0) ptx::mbar_wait(&bars->o_free, (kt - 1) & 1, abort_word);
                 tc_fence_after();
                 if (lane == 0 && !*abort_word) {
 #pragma unroll
                     for (int kk = 0; kk < kTile / 16; ++kk) {
                         const uint32_t poff = (kk >> 2) * (kPfRows * 128) + (kk & 3) * 32;
                         tc_mma_f16(tmem_O, smem_desc(p_addr + poff, 16, 1024),
-                                   smem_desc(v_addr + kk * (16 * 128), kTile * 128, 1024), idesc_pv, kk > 0);
+                                   smem_desc(v_addr + kk * (16 * 128), kTile * 128, 1024), idesc_pv, j > 0 || kk > 0);
                     }
                     tc_commit(&bars->o_ready);
-                    tc_commit(&bars->kv_empty[stage]);
+                    tc_commit(&bars->v_empty[stage]);
                 }
                 __syncwarp();
             }
@@ -259,64 +300,80 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             const int hi_min = min(kv_len, ctx + i_first + 1);
             const int lo_max = p.window > 0 ? max(0, min(kv_len - 1, ctx + i_last) - p.window + 1) : 0;
 
-            float m = -INFINITY, l = 0.f, o[D];
-#pragma unroll
-            for (int d = 0; d < D; ++d) o[d] = 0.f;
+            // m_ref is the maximum the stored probabilities and O refer to; it follows the true running maximum
+            // lazily (only when that grew by more than 2^8), so O in TMEM is rarely rescaled
+            float m_ref = -INFINITY, l = 0.f;
 
             for (int j = 0; j < ntiles; ++j, ++kt) {
                 const int t0 = (tile_lo + j) * kTile;
                 const bool interior = (t0 + kTile <= hi_min) && (t0 >= lo_max);
-                const uint32_t stage = kt % C::STAGES;
-                ptx::mbar_wait(&bars->s_ready, kt & 1, abort_word);
+                ptx::mbar_wait(&bars->s_ready[kt & 1], (kt >> 1) & 1, abort_word);
                 tc_fence_after();
+                uint32_t sv[128];
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4) tmem_ld32_nowait(tmem_S + (kt & 1) * 128 + lane_addr + 32 * c4, sv + 32 * c4);
+                tmem_wait_ld();
                 float mx = -INFINITY;
-#pragma unroll 1
-                for (int c4 = 0; c4 < 4; ++c4) {
-                    float v[32];
-                    tmem_ld32(tmem_S + lane_addr + 32 * c4, v);
+                if (interior) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int tok = t0 + 32 * c4 + i;
-                        const bool ok = interior || (tok >= lo && tok < hi);
-                        mx = fmaxf(mx, ok ? v[i] : -INFINITY);
+                    for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 128; ++i) {
+                        const int tok = t0 + i;
+                        if (tok < lo || tok >= hi) sv[i] = 0xff800000u;  // -inf
+                        mx = fmaxf(mx, __uint_as_float(sv[i]));
                     }
                 }
-                const float m_new = fmaxf(m, mx * p.scale_log2e);
-                const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-                float corr, lsum = 0.f;
-                asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(corr) : "f"(m - m_safe));
-                m = m_new;
+                const float m_new = mx * p.scale_log2e;
+                const bool grow = (j == 0) ? true : (m_new > m_ref + 8.0f);
+                float corr = 1.0f;
+                if (grow) {
+                    const float m_tgt = fmaxf(m_ref, m_new);
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(corr) : "f"(m_ref - (m_tgt == -INFINITY ? 0.f : m_tgt)));
+                    m_ref = m_tgt;
+                }
+                // PV of the previous tile has to be complete before P is overwritten and before O is touched
+                if (j > 0) {
+                    ptx::mbar_wait(&bars->o_ready, (kt - 1) & 1, abort_word);
+                    tc_fence_after();
+                    if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-                for (int c4 = 0; c4 < 4; ++c4) {
-                    float v[32];
-                    tmem_ld32(tmem_S + lane_addr + 32 * c4, v);
-                    uint32_t packed[16];
+                        for (int c4 = 0; c4 < D / 32; ++c4) {
+                            uint32_t ov[32];
+                            tmem_ld32_nowait(tmem_O + lane_addr + 32 * c4, ov);
+                            tmem_wait_ld();
 #pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float p0, p1;
-                        const int tok = t0 + 32 * c4 + i;
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(v[i], p.scale_log2e, -m_safe)));
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(v[i + 1], p.scale_log2e, -m_safe)));
-                        if (!interior) {
-                            if (tok < lo || tok >= hi) p0 = 0.f;
-                            if (tok + 1 < lo || tok + 1 >= hi) p1 = 0.f;
+                            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                            tmem_st32(tmem_O + lane_addr + 32 * c4, ov);
                         }
-                        lsum += p0 + p1;
-                        if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed[i / 2]) : "f"(p1), "f"(p0));
-                        else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed[i / 2]) : "f"(p1), "f"(p0));
-                    }
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const int c16 = 4 * c4 + q;
-                        uint8_t* dst = p_smem + (c16 >> 3) * (kPfRows * 128) + r * 128 + (((c16 & 7) ^ (r & 7)) << 4);
-                        *(uint4*)dst = make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                        l *= corr;
                     }
                 }
-                l = fmaf(l, corr, lsum);
+                const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;
+                const float neg_m = -m_safe;
+                float lsum = 0.f;
+#pragma unroll
+                for (int c16 = 0; c16 < 16; ++c16) {
+                    uint32_t packed[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        float p0, p1;
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(sv[8 * c16 + 2 * e]), p.scale_log2e, neg_m)));
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(sv[8 * c16 + 2 * e + 1]), p.scale_log2e, neg_m)));
+                        lsum += p0 + p1;
+                        if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
+                        else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
+                    }
+                    uint8_t* dst = p_smem + (c16 >> 3) * (kPfRows * 128) + r * 128 + (((c16 & 7) ^ (r & 7)) << 4);
+                    *(uint4*)dst = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                }
+                l += lsum;
                 if (t0 + kTile > kv_len) {
                     // token rows of V past the sequence end are stale memory: clear them (thread r owns token r)
+                    ptx::mbar_wait(&bars->v_full[kt % C::VST], (kt / C::VST) & 1, abort_word);
                     if (r >= max(0, kv_len - t0)) {
-                        uint8_t* vrow = kv_smem + (size_t)stage * C::STAGE + C::KBYTES + r * 128;
+                        uint8_t* vrow = v_smem + (size_t)(kt % C::VST) * C::KBYTES + r * 128;
 #pragma unroll
                         for (int h = 0; h < C::HALVES; ++h)
 #pragma unroll
@@ -326,36 +383,34 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 ptx::fence_proxy_async();
                 tc_fence_before();
                 ptx::mbar_arrive(&bars->p_ready);
-
-                ptx::mbar_wait(&bars->o_ready, kt & 1, abort_word);
-                tc_fence_after();
-#pragma unroll
-                for (int c4 = 0; c4 < D / 32; ++c4) {
-                    float v[32];
-                    tmem_ld32(tmem_O + lane_addr + 32 * c4, v);
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[32 * c4 + i] = fmaf(o[32 * c4 + i], corr, v[i]);
-                }
-                tc_fence_before();
-                ptx::mbar_arrive(&bars->o_free);
             }
+            // the last PV, then this row of O
+            ptx::mbar_wait(&bars->o_ready, (kt - 1) & 1, abort_word);
+            tc_fence_after();
             const float inv = l > 0.f ? 1.0f / l : 0.f;
-            if (row0 + r < R) {
-                const int i = (row0 + r) / p.G, hh = (row0 + r) - i * p.G;
-                uint4* dst = (uint4*)((uint16_t*)p.out + ((long long)(qs + i) * p.Hq + head * p.G + hh) * D);
+            const bool store = row0 + r < R;
+            const int oi = (row0 + r) / p.G, ohh = (row0 + r) - oi * p.G;
+            uint4* dst = (uint4*)((uint16_t*)p.out + ((long long)(qs + oi) * p.Hq + head * p.G + ohh) * D);
+#pragma unroll 1
+            for (int c4 = 0; c4 < D / 32; ++c4) {
+                uint32_t ov[32];
+                tmem_ld32_nowait(tmem_O + lane_addr + 32 * c4, ov);
+                tmem_wait_ld();
+                if (store) {
 #pragma unroll
-                for (int c = 0; c < D / 8; ++c) {
-                    uint32_t w[4];
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t w[4];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        if constexpr (BF16)
-                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(o[8 * c + 2 * e + 1] * inv), "f"(o[8 * c + 2 * e] * inv));
-                        else
-                            asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(o[8 * c + 2 * e + 1] * inv), "f"(o[8 * c + 2 * e] * inv));
+                        for (int e = 0; e < 4; ++e) {
+                            const float x0 = __uint_as_float(ov[8 * c + 2 * e]) * inv, x1 = __uint_as_float(ov[8 * c + 2 * e + 1]) * inv;
+                            if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(x1), "f"(x0));
+                            else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w[e]) : "f"(x1), "f"(x0));
+                        }
+                        dst[4 * c4 + c] = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                    dst[c] = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
+            tc_fence_before();
             ptx::mbar_arrive(&bars->item_done);
         }
     }
