@@ -7,9 +7,9 @@ namespace emlx {
 __global__ void __launch_bounds__(kMetaThreads) attn_plan_kernel(const int32_t* __restrict__ qsl,
                                                                  const int32_t* __restrict__ kv_lens, int S, int G,
                                                                  int window, int class_lo, int class_hi, bool wide,
-                                                                 int32_t* plan, PlanLayout L) {
+                                                                 int Hkv, int num_ctas, int32_t* plan, PlanLayout L) {
     __shared__ int32_t scan_smem[kMetaThreads / 32 + 1];
-    build_plan(qsl, kv_lens, S, G, window, class_lo, class_hi, wide, plan, L, scan_smem);
+    build_plan(qsl, kv_lens, S, G, window, class_lo, class_hi, wide, Hkv, num_ctas, plan, L, scan_smem);
 }
 
 }  // namespace emlx
@@ -44,7 +44,8 @@ int emlx_attn_plan(const int32_t* query_start_loc, const int32_t* kv_lens, int32
     class_range(num_q_heads / num_kv_heads, max_query_len, wide, class_lo, class_hi);
     attn_plan_kernel<<<1, kMetaThreads, 0, (cudaStream_t)stream>>>(query_start_loc, kv_lens, num_seqs,
                                                                     num_q_heads / num_kv_heads, sliding_window, class_lo,
-                                                                    class_hi, wide, (int32_t*)plan, L);
+                                                                    class_hi, wide, num_kv_heads, min(num_sms(), kMaxGrid),
+                                                                    (int32_t*)plan, L);
     EMLX_LAUNCHED();
     return EMLX_OK;
 }

@@ -479,25 +479,27 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
         if (!complete) {
             __threadfence();
             consumer_sync();
-            const int c_first = (int)(((a_flat + 1) * P - 1) / total_flat);
-            const int c_last = (int)((b_flat * P - 1) / total_flat);
+            const int c_first = slice_owner(p.cta_start, (int)P, a_flat), c_last = slice_owner(p.cta_start, (int)P, b_flat - 1);
+            const int nparts = slices_in_use(p.cta_start, c_first, c_last);
             int* counter = p.counters + (size_t)unit * p.Hkv + head;
             if (tid == 0) misc[1] = atomicAdd(counter, 1);
             consumer_sync();
-            if (misc[1] == c_last - c_first) {
+            if (misc[1] == nparts - 1) {
                 __threadfence();
                 for (int idx = tid; idx < ROWS * D; idx += kConsumerThreads) {
                     const int row = idx / D, d = idx - row * D, r = row0 + row;
                     if (r >= R) continue;
                     float M = -INFINITY;
                     for (int c = c_first; c <= c_last; ++c) {
-                        const long long cb = total_flat * c / P;
+                        const long long cb = p.cta_start[c];
+                        if (cb >= p.cta_start[c + 1]) continue;
                         const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
                         if (__ldcg(sl + ROWS * D + ROWS + row) > 0.f) M = fmaxf(M, __ldcg(sl + ROWS * D + row));
                     }
                     float acc = 0.f, den = 0.f;
                     for (int c = c_first; c <= c_last; ++c) {
-                        const long long cb = total_flat * c / P;
+                        const long long cb = p.cta_start[c];
+                        if (cb >= p.cta_start[c + 1]) continue;
                         const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
                         const float lp = __ldcg(sl + ROWS * D + ROWS + row);
                         if (lp > 0.f) {

@@ -40,6 +40,7 @@ struct TiledParams {
     const int32_t* unit_row0;
     const int32_t* unit_tile_lo;
     const int32_t* unit_cum;
+    const int32_t* cta_start;  // [gridDim.x + 1] first flat tile of every CTA's slice
     int32_t* counters;
     float* slots;
     int32_t* status;
@@ -99,6 +100,21 @@ struct Cfg {
     static constexpr int SMEM = STAGES * STAGE + FIXED + 1024;
     static_assert(STAGES >= 2, "shared memory holds fewer than two stages");
 };
+
+// CTA whose slice holds flat tile f: the largest c with start[c] <= f (CTAs with empty slices are skipped by construction)
+__device__ __forceinline__ int slice_owner(const int32_t* start, int P, long long f) {
+    int lo = 0, hi = P;
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (start[mid] <= f) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+__device__ __forceinline__ int slices_in_use(const int32_t* start, int c_first, int c_last) {
+    int n = 0;
+    for (int c = c_first; c <= c_last; ++c) n += start[c] < start[c + 1] ? 1 : 0;
+    return n;
+}
 
 // ordered-int encoding so that atomicMax on ints orders floats
 __device__ __forceinline__ int f2ord(float f) {
@@ -725,25 +741,27 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
             }
             __threadfence();
             consumer_sync();
-            const int c_first = (int)(((a_flat + 1) * P - 1) / total_flat);
-            const int c_last = (int)((b_flat * P - 1) / total_flat);
+            const int c_first = slice_owner(p.cta_start, (int)P, a_flat), c_last = slice_owner(p.cta_start, (int)P, b_flat - 1);
+            const int nparts = slices_in_use(p.cta_start, c_first, c_last);
             int* counter = p.counters + (size_t)w.u * p.Hkv + head;
             if (tid == 0) misc[1] = atomicAdd(counter, 1);
             consumer_sync();
-            if (misc[1] == c_last - c_first) {
+            if (misc[1] == nparts - 1) {
                 __threadfence();
                 for (int idx = tid; idx < ROWS * D; idx += kConsumerThreads) {
                     const int row = idx / D, d = idx - row * D, r = row0 + row;
                     if (r >= R) continue;
                     float M = -INFINITY;
                     for (int c = c_first; c <= c_last; ++c) {
-                        const long long cb = total_flat * c / P;
+                        const long long cb = p.cta_start[c];
+                        if (cb >= p.cta_start[c + 1]) continue;
                         const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
                         if (__ldcg(sl + ROWS * D + ROWS + row) > 0.f) M = fmaxf(M, __ldcg(sl + ROWS * D + row));
                     }
                     float acc = 0.f, den = 0.f;
                     for (int c = c_first; c <= c_last; ++c) {
-                        const long long cb = total_flat * c / P;
+                        const long long cb = p.cta_start[c];
+                        if (cb >= p.cta_start[c + 1]) continue;
                         const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
                         const float lp = __ldcg(sl + ROWS * D + ROWS + row);
                         if (lp > 0.f) {
@@ -780,11 +798,10 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     extern __shared__ uint8_t smem_raw[];
     const int num_units = p.hdr[0];
     const long long total_flat = (long long)p.hdr[1] * p.Hkv;
-    // min(grid, tiles) CTAs take one contiguous, non-empty slice each; the others have nothing to do
-    const long long active = total_flat < (long long)gridDim.x ? total_flat : (long long)gridDim.x;
-    if ((long long)blockIdx.x >= active) return;  // uniform, before any barrier exists
-    const long long f_begin = total_flat * blockIdx.x / active;
-    const long long f_end = total_flat * (blockIdx.x + 1) / active;
+    // every CTA takes the contiguous slice the plan cut for it; a CTA without tiles has nothing to do
+    const long long f_begin = p.cta_start[blockIdx.x], f_end = p.cta_start[blockIdx.x + 1];
+    if (f_begin >= f_end) return;  // uniform, before any barrier exists
+    const long long active = gridDim.x;
 
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* fixed = smem + (size_t)C::STAGES * C::STAGE;
@@ -981,6 +998,7 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
         p.hdr = plan + 4 * c;
         p.unit_seq = plan + L.unit_seq[c]; p.unit_row0 = plan + L.unit_row0[c];
         p.unit_tile_lo = plan + L.unit_tile_lo[c]; p.unit_cum = plan + L.unit_cum[c];
+        p.cta_start = plan + L.cta_start[c];
         p.counters = (int32_t*)((uint8_t*)a->workspace + W.counter_off[c]);
         p.slots = (float*)((uint8_t*)a->workspace + W.slots_off);
         p.status = a->status;

@@ -8,7 +8,8 @@
 //     class 2: rows <= 32  (NT = 4)     spec-verify rows (or, without wide units, every longer row set in 32-row blocks)
 //     class 3: 128-row blocks           prefill chunks, for the tcgen05 kernel (only with kPlanWideUnits)
 // The work of a class is the flat sequence of (unit, kv head, tile); CTA c of P takes the contiguous
-// slice [c*N/P, (c+1)*N/P).
+// slice [start[c], start[c+1]); the plan chooses the boundaries so that tiles + 1.5 x (unit, head) parts is equal
+// across CTAs (a part boundary costs about as much as one and a half tiles).
 #pragma once
 #include "common.cuh"
 
@@ -23,7 +24,7 @@ constexpr int kMaxRows = 32;      // rows of the largest class
 
 __host__ __device__ inline int class_rows(int c) { return c < 3 ? 8 << c : 128; }
 __host__ __device__ inline int unit_class(int rows, bool wide) {
-    return rows <= 8 ? 0 : (rows <= 16 ? 1 : ((!wide || rows <= 32) ? 2 : 3));
+    return rows <= 8 ? 0 : (rows <= 16 ? 1 : (!wide ? 2 : 3));
 }
 
 struct PlanLayout {
@@ -32,6 +33,7 @@ struct PlanLayout {
     int unit_row0[kNumClasses];
     int unit_tile_lo[kNumClasses];
     int unit_cum[kNumClasses];  // cap + 1 words: exclusive prefix sum of tiles per unit (per KV head)
+    int cta_start[kNumClasses]; // kMaxGrid + 1 words: first flat tile of every CTA's slice (cost-balanced)
     int tmp;                    // S words of scratch for the scans
     int words;
 };
@@ -47,6 +49,7 @@ __host__ __device__ inline PlanLayout plan_layout(int S, int T, int Hq, int Hkv)
         L.unit_row0[c] = w; w += L.cap[c];
         L.unit_tile_lo[c] = w; w += L.cap[c];
         L.unit_cum[c] = w; w += L.cap[c] + 1;
+        L.cta_start[c] = w; w += kMaxGrid + 1;
     }
     L.tmp = w; w += (S > 0 ? S : 1);
     L.words = w;

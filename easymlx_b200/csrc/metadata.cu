@@ -10,7 +10,7 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
     const int32_t* __restrict__ bt_all, int num_slots, int MB, int32_t* kv_lens_all, int bs, int advance,
     int32_t* __restrict__ qsl, int32_t* __restrict__ bt_out, int32_t* __restrict__ kv_out,
     int64_t* __restrict__ slot_mapping, int64_t num_blocks, int32_t* status, int32_t* plan, PlanLayout L, int G,
-    int window, int class_lo, int class_hi, bool wide) {
+    int window, int class_lo, int class_hi, bool wide, int Hkv, int num_ctas) {
     __shared__ int32_t scan_smem[kMetaThreads / 32 + 1];
     const int tid = threadIdx.x;
 
@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
     __syncthreads();  // qsl and kv_out of this CTA are now visible to all its threads
 
     // attention work list in the same launch (lengths after the write are final here)
-    if (plan != nullptr) build_plan(qsl, kv_out, S, G, window, class_lo, class_hi, wide, plan, L, scan_smem);
+    if (plan != nullptr) build_plan(qsl, kv_out, S, G, window, class_lo, class_hi, wide, Hkv, num_ctas, plan, L, scan_smem);
 
     if (slot_mapping == nullptr) return;
     const int n = min(T, total);
@@ -103,7 +103,8 @@ extern "C" int emlx_build_metadata(const int32_t* query_lens, const int32_t* slo
     build_metadata_kernel<<<1, kMetaThreads, 0, (cudaStream_t)stream>>>(
         query_lens, slot_ids, num_seqs, total_tokens, block_tables_all, num_slots, max_blocks_per_seq, kv_lens_all,
         block_size, advance_kv_lens, query_start_loc, block_tables, kv_lens, slot_mapping, num_blocks, status,
-        (int32_t*)plan, L, G, sliding_window, class_lo, class_hi, (plan_flags & kPlanWideUnits) != 0);
+        (int32_t*)plan, L, G, sliding_window, class_lo, class_hi, (plan_flags & kPlanWideUnits) != 0, num_kv_heads,
+        min(num_sms(), kMaxGrid));
     EMLX_LAUNCHED();
     return EMLX_OK;
 }

@@ -53,12 +53,13 @@ __device__ __forceinline__ void unit_tiles(int row0, int row1, int G, int q_len,
 }
 
 __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv_lens, int S, int G, int window,
-                                           int class_lo, int class_hi, bool wide, int32_t* plan,
-                                           const PlanLayout& L, int32_t* scan_smem) {
+                                           int class_lo, int class_hi, bool wide, int Hkv, int num_ctas,
+                                           int32_t* plan, const PlanLayout& L, int32_t* scan_smem) {
     const int tid = threadIdx.x;
     for (int c = 0; c < kNumClasses; ++c) {
         if (c < class_lo || c > class_hi) {
             if (tid == 0) { plan[4 * c + 0] = 0; plan[4 * c + 1] = 0; }
+            for (int i = tid; i <= num_ctas; i += kMetaThreads) plan[L.cta_start[c] + i] = 0;
             continue;
         }
         const int rows_c = class_rows(c);
@@ -111,7 +112,31 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
             plan[4 * c + 0] = num_units;
             plan[4 * c + 1] = tile_base;
         }
-        __syncthreads();  // seq_off is reused by the next class
+        __syncthreads();  // unit_cum is complete; seq_off is reused by the next class
+        // slice boundaries: equal shares of cost = 2 per tile + 3 per (unit, head) part, in half-tile units
+        for (int i = tid; i <= num_ctas; i += kMetaThreads) {
+            long long start = (long long)tile_base * Hkv;
+            if (i < num_ctas && num_units > 0) {
+                const long long total = (long long)Hkv * (2LL * tile_base + 3LL * num_units);
+                const long long target = total * i / num_ctas;
+                int lo = 0, hi = num_units;  // largest u with cost_before(u) <= target
+                while (hi - lo > 1) {
+                    const int mid = (lo + hi) >> 1;
+                    if ((long long)Hkv * (2LL * unit_cum[mid] + 3LL * mid) <= target) lo = mid; else hi = mid;
+                }
+                const int u = lo, nt = unit_cum[u + 1] - unit_cum[u];
+                const long long rem = target - (long long)Hkv * (2LL * unit_cum[u] + 3LL * u);
+                const long long per_head = 2LL * nt + 3;
+                const int head = (int)min((long long)Hkv - 1, rem / per_head);
+                const long long r2 = rem - head * per_head;
+                const int j = r2 <= 3 ? 0 : (int)min((long long)nt, (r2 - 3 + 1) / 2);
+                start = (long long)unit_cum[u] * Hkv + (long long)head * nt + j;
+            } else if (num_units == 0) {
+                start = 0;
+            }
+            plan[L.cta_start[c] + i] = (int)start;
+        }
+        __syncthreads();
     }
 }
 
