@@ -287,7 +287,8 @@ class PageCacheView:
 
     # ------------------------------------------------------------------ writes
     def _write_batch(self, keys: torch.Tensor, values: torch.Tensor, query_lens_dev: torch.Tensor,
-                     slots_dev: torch.Tensor, total_tokens: int, plan_for: tuple | None = None):
+                     slots_dev: torch.Tensor, total_tokens: int, plan_for: tuple | None = None,
+                     advance: bool = True):
         """Metadata kernel + write kernel for one packed batch.  Returns ``(qsl, block_tables, kv_lens)``
         of the scheduled rows; ``self.kv_lens`` is advanced in place."""
         nv.require_cuda(keys, values, self.key_cache)
@@ -312,8 +313,8 @@ class PageCacheView:
             plan = torch.empty(plan_bytes, dtype=torch.uint8, device=dev)
         nv.check(lib.emlx_build_metadata(
             nv.ptr(query_lens_dev), nv.ptr(slots_dev), s, total_tokens, nv.ptr(self.block_tables), self.num_seqs,
-            self.blocks_per_seq, nv.ptr(self.kv_lens), self.block_size, 1, nv.ptr(qsl), nv.ptr(bt), nv.ptr(lens),
-            nv.ptr(slot_mapping), self.num_blocks, nv.ptr(self.status), hq, self.num_kv_heads, window, max_q,
+            self.blocks_per_seq, nv.ptr(self.kv_lens), self.block_size, 1 if advance else 0, nv.ptr(qsl), nv.ptr(bt),
+            nv.ptr(lens), nv.ptr(slot_mapping), self.num_blocks, nv.ptr(self.status), hq, self.num_kv_heads, window, max_q,
             flags, nv.ptr(plan), plan_bytes, stream))
         if total_tokens > 0:
             if keys.shape != values.shape:
@@ -368,13 +369,15 @@ class PageCacheView:
     def concatenate_to_cache(self, queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, *,
                              cache_metadata: tp.Any, rope: tp.Any = None,
                              slot_ids: tp.Sequence[int] | None = None,
-                             query_lens: tp.Sequence[int] | None = None):
+                             query_lens: tp.Sequence[int] | None = None, advance: bool = True):
         """Append the batch's K/V to the pool and resolve the metadata (``cache.py:1088-1306``).
 
         Returns ``(prepared_queries, key_cache, value_cache, resolved_metadata)``; the metadata carries the
         scheduled slots' page-table rows and their lengths after the write.  ``slot_ids`` and
         ``query_lens`` are host sequences, as in the reference; when ``query_lens`` is omitted the lengths
-        are derived on the device from ``cache_metadata.query_start_loc``.
+        are derived on the device from ``cache_metadata.query_start_loc``.  ``advance=False`` (an extension)
+        writes the rows and resolves the metadata but leaves ``self.kv_lens`` untouched, so that the same batch
+        can be replayed (benchmarks, speculative what-if steps).
         """
         if rope is not None:
             raise NotImplementedError("RoPE inside the cache write is not provided yet; rotate q/k before the call")
@@ -403,7 +406,7 @@ class PageCacheView:
                 max_q = 1 if single else 0
         window = int(getattr(cache_metadata, "sliding_window", None) or 0)
         qsl, bt, lens, plan = self._write_batch(keys, values, qlens_dev, _uploaded.get(slots, dev), total,
-                                                plan_for=(int(queries.shape[1]), window, max_q))
+                                                plan_for=(int(queries.shape[1]), window, max_q), advance=advance)
         meta = PageMetadata(
             query_start_loc=qsl, sliding_window=getattr(cache_metadata, "sliding_window", None),
             is_single_token_decode=bool(getattr(cache_metadata, "is_single_token_decode", False)) or single,

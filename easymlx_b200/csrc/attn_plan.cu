@@ -9,6 +9,8 @@ __global__ void __launch_bounds__(kMetaThreads) attn_plan_kernel(const int32_t* 
                                                                  int window, int class_lo, int class_hi, bool wide,
                                                                  int Hkv, int num_ctas, int32_t* plan, PlanLayout L) {
     __shared__ int32_t scan_smem[kMetaThreads / 32 + 1];
+    grid_dep_wait();
+    grid_dep_launch();
     build_plan(qsl, kv_lens, S, G, window, class_lo, class_hi, wide, Hkv, num_ctas, plan, L, scan_smem);
 }
 

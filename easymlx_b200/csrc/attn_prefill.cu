@@ -155,6 +155,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
     volatile int* abort_word = &bars->abort_word;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
+    grid_dep_wait();  // the plan, the pool and the queries come from earlier kernels
+    grid_dep_launch();
     const int num_units = p.hdr[0];
     const long long items = (long long)num_units * p.Hkv;
     if ((long long)blockIdx.x >= items) return;  // uniform, before any barrier or TMEM allocation
@@ -465,7 +467,7 @@ static int launch_pf(const CUtensorMap& qmap, const MapPair& maps, const Prefill
         EMLX_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
         configured = true;
     }
-    kernel<<<num_sms(), kPfThreads, C::SMEM, stream>>>(qmap, maps.k, maps.v, p);
+    EMLX_CUDA_OK(launch_pdl(kernel, num_sms(), kPfThreads, C::SMEM, stream, qmap, maps.k, maps.v, p));
     EMLX_LAUNCHED();
     return EMLX_OK;
 }

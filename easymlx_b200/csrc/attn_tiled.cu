@@ -796,13 +796,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const TiledParams p) {
     using C = Cfg<D, NT, FMT>;
     extern __shared__ uint8_t smem_raw[];
-    const int num_units = p.hdr[0];
-    const long long total_flat = (long long)p.hdr[1] * p.Hkv;
-    // every CTA takes the contiguous slice the plan cut for it; a CTA without tiles has nothing to do
-    const long long f_begin = p.cta_start[blockIdx.x], f_end = p.cta_start[blockIdx.x + 1];
-    if (f_begin >= f_end) return;  // uniform, before any barrier exists
-    const long long active = gridDim.x;
-
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* fixed = smem + (size_t)C::STAGES * C::STAGE;
     uint64_t* full = (uint64_t*)(fixed + C::OFF_BAR);
@@ -833,6 +826,15 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     }
     if (threadIdx.x < 64) tmax[threadIdx.x] = f2ord(-INFINITY);
     __syncthreads();
+    // everything above is independent of earlier kernels; the plan, the pool and the queries are not
+    grid_dep_wait();
+    grid_dep_launch();
+    const int num_units = p.hdr[0];
+    const long long total_flat = (long long)p.hdr[1] * p.Hkv;
+    // every CTA takes the contiguous slice the plan cut for it; a CTA without tiles has nothing to do
+    const long long f_begin = p.cta_start[blockIdx.x], f_end = p.cta_start[blockIdx.x + 1];
+    if (f_begin >= f_end) return;  // uniform for the CTA, and no thread waits on a barrier yet
+    const long long active = gridDim.x;
 
     if (threadIdx.x >= kConsumerThreads) {
         producer_loop<D, NT, FMT>(&kmap, &vmap, p, smem, fixed, full, empty, abort_word, f_begin, f_end, num_units);
@@ -934,7 +936,7 @@ static int launch_one(const MapPair& maps, const TiledParams& p, cudaStream_t st
         configured = true;
     }
     const int grid = min(num_sms(), kMaxGrid);
-    kernel<<<grid, kThreads, C::SMEM, stream>>>(maps.k, maps.v, p);
+    EMLX_CUDA_OK(launch_pdl(kernel, grid, kThreads, C::SMEM, stream, maps.k, maps.v, p));
     EMLX_LAUNCHED();
     return EMLX_OK;
 }

@@ -89,6 +89,8 @@ __device__ __forceinline__ void write_affine_rows(const TIn* krow, const TIn* vr
 
 template <typename TIn>
 __global__ void __launch_bounds__(256) kv_write_kernel(WriteParams w) {
+    grid_dep_wait();  // the slot mapping comes from the metadata kernel
+    grid_dep_launch();
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const emlx_pool& p = w.pool;
@@ -148,9 +150,9 @@ extern "C" int emlx_kv_write(const void* keys, const void* values, int32_t in_dt
     const unsigned blocks = (unsigned)((warps * 32 + threads - 1) / threads);
     cudaStream_t s = (cudaStream_t)stream;
     switch (in_dtype) {
-        case EMLX_F16: kv_write_kernel<__half><<<blocks, threads, 0, s>>>(w); break;
-        case EMLX_BF16: kv_write_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>(w); break;
-        case EMLX_F32: kv_write_kernel<float><<<blocks, threads, 0, s>>>(w); break;
+        case EMLX_F16: EMLX_CUDA_OK(launch_pdl(kv_write_kernel<__half>, blocks, threads, 0, s, w)); break;
+        case EMLX_BF16: EMLX_CUDA_OK(launch_pdl(kv_write_kernel<__nv_bfloat16>, blocks, threads, 0, s, w)); break;
+        case EMLX_F32: EMLX_CUDA_OK(launch_pdl(kv_write_kernel<float>, blocks, threads, 0, s, w)); break;
         default: return fail(EMLX_ERR_INVALID, "unknown in_dtype %d", in_dtype);
     }
     EMLX_LAUNCHED();

@@ -12,31 +12,56 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
     int64_t* __restrict__ slot_mapping, int64_t num_blocks, int32_t* status, int32_t* plan, PlanLayout L, int G,
     int window, int class_lo, int class_hi, bool wide, int Hkv, int num_ctas) {
     __shared__ int32_t scan_smem[kMetaThreads / 32 + 1];
+    // batches of up to kSmemSeqs sequences keep their prefix sums and lengths in shared memory: every later phase
+    // (work list, slot mapping) then reads them without an L2 round trip
+    constexpr int kSmemSeqs = 2048, kSmemUnits = 4096;
+    __shared__ int32_t s_q[kSmemSeqs + 1], s_kv[kSmemSeqs], s_off[kSmemSeqs], s_cum[kSmemUnits];
     const int tid = threadIdx.x;
+    grid_dep_wait();  // a preceding attention kernel may still be reading the plan buffer and the lengths
+    grid_dep_launch();
+    const bool small = S <= kSmemSeqs;
+    int32_t* qv = small ? s_q : qsl;
+    int32_t* kvv = small ? s_kv : kv_out;
 
-    for (int i = tid; i < S; i += kMetaThreads) qsl[i] = max(query_lens[i], 0);
-    if (tid == 0) qsl[S] = 0;
-    __syncthreads();
-    const int total = block_exclusive_scan(qsl, S, scan_smem);
+    int carry = 0;
+    for (int i0 = 0; i0 < S; i0 += kMetaThreads) {
+        const int i = i0 + tid;
+        int q_len = 0, slot = -1, base = 0;
+        if (i < S) {
+            q_len = max(query_lens[i], 0);
+            slot = slot_ids[i];
+            if (slot >= 0 && slot < num_slots) base = kv_lens_all[slot];
+            else flag_error(status, EMLX_DEV_BAD_SLOT);
+        }
+        int chunk_total;
+        const int excl = carry + block_scan_value(q_len, scan_smem, chunk_total);
+        if (i < S) {
+            const bool ok = slot >= 0 && slot < num_slots;
+            const int after = ok ? base + q_len : 0;
+            if (ok && after > MB * bs) flag_error(status, EMLX_DEV_OVERFLOW);
+            qv[i] = excl;
+            kvv[i] = after;
+            if (small) {
+                qsl[i] = excl;
+                kv_out[i] = after;
+            }
+            if (ok && advance) kv_lens_all[slot] = after;
+        }
+        carry += chunk_total;
+    }
+    const int total = carry;
     if (tid == 0) {
-        qsl[S] = total;
+        qv[S] = total;
+        if (small) qsl[S] = total;
         if (total != T) flag_error(status, EMLX_DEV_TOKEN_MISMATCH);
     }
+    __syncthreads();
 
-    // lengths after the step, for the scheduled rows
-    for (int i = tid; i < S; i += kMetaThreads) {
-        int slot = slot_ids[i];
-        if (slot < 0 || slot >= num_slots) {
-            flag_error(status, EMLX_DEV_BAD_SLOT);
-            kv_out[i] = 0;
-            continue;
-        }
-        int q_len = max(query_lens[i], 0);
-        int after = kv_lens_all[slot] + q_len;
-        if (after > MB * bs) flag_error(status, EMLX_DEV_OVERFLOW);
-        kv_out[i] = after;
-        if (advance) kv_lens_all[slot] = after;
-    }
+    // attention work list in the same launch (lengths after the write are final here)
+    if (plan != nullptr)
+        build_plan(qv, kvv, S, G, window, class_lo, class_hi, wide, Hkv, num_ctas, plan, L, scan_smem,
+                   small ? s_off : nullptr, s_cum, kSmemUnits);
+
     // gathered page-table rows
     const int64_t cells = (int64_t)S * MB;
     for (int64_t c = tid; c < cells; c += kMetaThreads) {
@@ -44,21 +69,17 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
         int slot = slot_ids[row];
         bt_out[c] = (slot >= 0 && slot < num_slots) ? bt_all[(int64_t)slot * MB + col] : -1;
     }
-    __syncthreads();  // qsl and kv_out of this CTA are now visible to all its threads
-
-    // attention work list in the same launch (lengths after the write are final here)
-    if (plan != nullptr) build_plan(qsl, kv_out, S, G, window, class_lo, class_hi, wide, Hkv, num_ctas, plan, L, scan_smem);
 
     if (slot_mapping == nullptr) return;
     const int n = min(T, total);
     for (int t = tid; t < T; t += kMetaThreads) {
         int64_t dst = -1;
         if (t < n) {
-            int s = find_sequence(qsl, S, t);
+            int s = find_sequence(qv, S, t);
             int slot = s >= 0 ? slot_ids[s] : -1;
             if (slot >= 0 && slot < num_slots) {
-                int q_len = qsl[s + 1] - qsl[s];
-                int pos = kv_out[s] - q_len + (t - qsl[s]);
+                int q_len = qv[s + 1] - qv[s];
+                int pos = kvv[s] - q_len + (t - qv[s]);
                 int page_idx = pos / bs;
                 if (page_idx < MB) {
                     int page = bt_all[(int64_t)slot * MB + page_idx];
@@ -100,11 +121,11 @@ extern "C" int emlx_build_metadata(const int32_t* query_lens, const int32_t* slo
         G = num_q_heads / num_kv_heads;
         class_range(G, max_query_len, (plan_flags & kPlanWideUnits) != 0, class_lo, class_hi);
     }
-    build_metadata_kernel<<<1, kMetaThreads, 0, (cudaStream_t)stream>>>(
+    EMLX_CUDA_OK(launch_pdl(build_metadata_kernel, 1, kMetaThreads, 0, (cudaStream_t)stream,
         query_lens, slot_ids, num_seqs, total_tokens, block_tables_all, num_slots, max_blocks_per_seq, kv_lens_all,
         block_size, advance_kv_lens, query_start_loc, block_tables, kv_lens, slot_mapping, num_blocks, status,
         (int32_t*)plan, L, G, sliding_window, class_lo, class_hi, (plan_flags & kPlanWideUnits) != 0, num_kv_heads,
-        min(num_sms(), kMaxGrid));
+        min(num_sms(), kMaxGrid)));
     EMLX_LAUNCHED();
     return EMLX_OK;
 }

@@ -54,7 +54,9 @@ __device__ __forceinline__ void unit_tiles(int row0, int row1, int G, int q_len,
 
 __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv_lens, int S, int G, int window,
                                            int class_lo, int class_hi, bool wide, int Hkv, int num_ctas,
-                                           int32_t* plan, const PlanLayout& L, int32_t* scan_smem) {
+                                           int32_t* plan, const PlanLayout& L, int32_t* scan_smem,
+                                           int32_t* seq_off_buf = nullptr, int32_t* cum_smem = nullptr,
+                                           int cum_cap = 0) {
     const int tid = threadIdx.x;
     for (int c = 0; c < kNumClasses; ++c) {
         if (c < class_lo || c > class_hi) {
@@ -67,7 +69,9 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
         int32_t* unit_row0 = plan + L.unit_row0[c];
         int32_t* unit_tile_lo = plan + L.unit_tile_lo[c];
         int32_t* unit_cum = plan + L.unit_cum[c];
-        int32_t* seq_off = plan + L.tmp;  // first unit of every sequence in this class
+        // first unit of every sequence in this class; shared memory when the caller has room for it (a global
+        // store followed by a load from another thread costs an L2 round trip per phase)
+        int32_t* seq_off = seq_off_buf ? seq_off_buf : plan + L.tmp;
         // pass 1: units per sequence -> first-unit offsets
         int num_units = 0;
         for (int s0 = 0; s0 < S; s0 += kMetaThreads) {
@@ -104,15 +108,20 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
             }
             int t_total;
             const int t_off = tile_base + block_scan_value(nt, scan_smem, t_total);
-            if (idx < num_units) unit_cum[idx] = t_off;
+            if (idx < num_units) {
+                unit_cum[idx] = t_off;
+                if (idx < cum_cap) cum_smem[idx] = t_off;
+            }
             tile_base += t_total;
         }
         if (tid == 0) {
             unit_cum[num_units] = tile_base;
+            if (num_units < cum_cap) cum_smem[num_units] = tile_base;
             plan[4 * c + 0] = num_units;
             plan[4 * c + 1] = tile_base;
         }
         __syncthreads();  // unit_cum is complete; seq_off is reused by the next class
+        const int32_t* cum = num_units < cum_cap ? cum_smem : unit_cum;
         // slice boundaries: equal shares of cost = 2 per tile + 3 per (unit, head) part, in half-tile units
         for (int i = tid; i <= num_ctas; i += kMetaThreads) {
             long long start = (long long)tile_base * Hkv;
@@ -122,15 +131,15 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
                 int lo = 0, hi = num_units;  // largest u with cost_before(u) <= target
                 while (hi - lo > 1) {
                     const int mid = (lo + hi) >> 1;
-                    if ((long long)Hkv * (2LL * unit_cum[mid] + 3LL * mid) <= target) lo = mid; else hi = mid;
+                    if ((long long)Hkv * (2LL * cum[mid] + 3LL * mid) <= target) lo = mid; else hi = mid;
                 }
-                const int u = lo, nt = unit_cum[u + 1] - unit_cum[u];
-                const long long rem = target - (long long)Hkv * (2LL * unit_cum[u] + 3LL * u);
+                const int u = lo, nt = cum[u + 1] - cum[u];
+                const long long rem = target - (long long)Hkv * (2LL * cum[u] + 3LL * u);
                 const long long per_head = 2LL * nt + 3;
                 const int head = (int)min((long long)Hkv - 1, rem / per_head);
                 const long long r2 = rem - head * per_head;
                 const int j = r2 <= 3 ? 0 : (int)min((long long)nt, (r2 - 3 + 1) / 2);
-                start = (long long)unit_cum[u] * Hkv + (long long)head * nt + j;
+                start = (long long)cum[u] * Hkv + (long long)head * nt + j;
             } else if (num_units == 0) {
                 start = 0;
             }

@@ -18,8 +18,9 @@ from .layers.attention import AttentionPerformer
 class AttentionStep:
     """``step()`` = restore the slots' lengths, write the new K/V rows, attend.
 
-    ``rewind=True`` puts ``kv_lens`` back to their values at construction before every step, so that the
-    same batch can be replayed any number of times (benchmarks); a serving loop passes ``rewind=False``.
+    ``rewind=True`` leaves the cache's ``kv_lens`` at their values (the step's rows are written and attended,
+    the lengths are not advanced), so that the same batch can be replayed any number of times (benchmarks); a
+    serving loop passes ``rewind=False``.
     """
 
     def __init__(self, cache: PageCacheView, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, query_lens,
@@ -41,12 +42,10 @@ class AttentionStep:
         self.steps_per_graph = 1
 
     def _eager(self) -> torch.Tensor:
-        if self.rewind:
-            self.cache.kv_lens.copy_(self._base_lens)
-        if self._meta_lens is None:
-            return self.performer(self.q, self.k, self.v, cache_view=self.cache, cache_metadata=self._meta)
+        # rewind: the slots' lengths are left as they were, so the same batch can be replayed
         _, kc, vc, meta = self.cache.concatenate_to_cache(self.q, self.k, self.v, cache_metadata=self._meta,
-                                                          slot_ids=self.slot_ids, query_lens=self._meta_lens)
+                                                          slot_ids=self.slot_ids, query_lens=self.query_lens,
+                                                          advance=not self.rewind)
         op = self.performer.executor.mixin_impl
         return op(query=self.q, key=kc, value=vc, cache_metadata=meta, cache_view=self.cache,
                   scale=self.performer.scale).attention_outputs
