@@ -30,6 +30,12 @@ class Pool(C.Structure):
     ]
 
 
+class Rope(C.Structure):
+    _fields_ = [("inv_freq", C.c_void_p), ("dims", C.c_int32), ("traditional", C.c_int32),
+                ("position_scale", C.c_float), ("mscale", C.c_float), ("head_dim_if_no_pool", C.c_int32),
+                ("reserved", C.c_int32)]
+
+
 class AttnArgs(C.Structure):
     _fields_ = [
         ("queries", C.c_void_p), ("out", C.c_void_p), ("block_tables", C.c_void_p), ("kv_lens", C.c_void_p),
@@ -49,9 +55,10 @@ SIGNATURES = {
     "emlx_abi_version": (C.c_int, []),
     "emlx_launch_count": (C.c_int64, []),
     "emlx_read_status": (C.c_int, [_P, _P]),
-    "emlx_build_metadata": (C.c_int, [_P, _P, _I32, _I32, _P, _I32, _I32, _P, _I32, _I32, _P, _P, _P, _P, _I64, _P,
+    "emlx_build_metadata": (C.c_int, [_P, _P, _I32, _I32, _P, _I32, _I32, _P, _I32, _I32, _P, _P, _P, _P, _P, _I64, _P,
                                      _I32, _I32, _I32, _I32, _I32, _P, C.c_size_t, _P]),
     "emlx_kv_write": (C.c_int, [_P, _P, _I32, _I32, _P, C.POINTER(Pool), _P, _P]),
+    "emlx_kv_write_rope": (C.c_int, [_P, _P, _I32, _P, _P, _I32, _I32, _P, _P, C.POINTER(Rope), C.POINTER(Pool), _P, _P]),
     "emlx_attn_plan_bytes": (C.c_size_t, [_I32, _I32, _I32, _I32]),
     "emlx_attn_workspace_bytes": (C.c_size_t, [_I32, _I32, _I32, _I32, _I32]),
     "emlx_attn_plan": (C.c_int, [_P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _P, C.c_size_t, _P]),

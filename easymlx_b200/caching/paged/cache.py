@@ -288,7 +288,7 @@ class PageCacheView:
     # ------------------------------------------------------------------ writes
     def _write_batch(self, keys: torch.Tensor, values: torch.Tensor, query_lens_dev: torch.Tensor,
                      slots_dev: torch.Tensor, total_tokens: int, plan_for: tuple | None = None,
-                     advance: bool = True):
+                     advance: bool = True, rope=None, queries: torch.Tensor | None = None):
         """Metadata kernel + write kernel for one packed batch.  Returns ``(qsl, block_tables, kv_lens)``
         of the scheduled rows; ``self.kv_lens`` is advanced in place."""
         nv.require_cuda(keys, values, self.key_cache)
@@ -299,6 +299,8 @@ class PageCacheView:
         bt = torch.empty((s, self.blocks_per_seq), dtype=torch.int32, device=dev)
         lens = torch.empty(s, dtype=torch.int32, device=dev)
         slot_mapping = torch.empty(max(total_tokens, 1), dtype=torch.int64, device=dev)
+        positions = torch.empty(max(total_tokens, 1), dtype=torch.int32, device=dev) if rope is not None else None
+        rotated_q = None
         if self.block_tables.dtype != torch.int32 or self.kv_lens.dtype != torch.int32:
             raise ValueError("block_tables and kv_lens must be int32")
         if not (self.block_tables.is_contiguous() and self.kv_lens.is_contiguous()):
@@ -314,7 +316,7 @@ class PageCacheView:
         nv.check(lib.emlx_build_metadata(
             nv.ptr(query_lens_dev), nv.ptr(slots_dev), s, total_tokens, nv.ptr(self.block_tables), self.num_seqs,
             self.blocks_per_seq, nv.ptr(self.kv_lens), self.block_size, 1 if advance else 0, nv.ptr(qsl), nv.ptr(bt),
-            nv.ptr(lens), nv.ptr(slot_mapping), self.num_blocks, nv.ptr(self.status), hq, self.num_kv_heads, window, max_q,
+            nv.ptr(lens), nv.ptr(slot_mapping), nv.ptr(positions), self.num_blocks, nv.ptr(self.status), hq, self.num_kv_heads, window, max_q,
             flags, nv.ptr(plan), plan_bytes, stream))
         if total_tokens > 0:
             if keys.shape != values.shape:
@@ -325,11 +327,23 @@ class PageCacheView:
                 raise ValueError("key and value must have the same dtype")
             keys, values = keys.contiguous(), values.contiguous()
             pool = self.native_pool()
-            nv.check(lib.emlx_kv_write(nv.ptr(keys), nv.ptr(values), nv.dtype_code(keys.dtype), total_tokens,
-                                       nv.ptr(slot_mapping), pool, nv.ptr(self.status), stream))
+            if rope is None:
+                nv.check(lib.emlx_kv_write(nv.ptr(keys), nv.ptr(values), nv.dtype_code(keys.dtype), total_tokens,
+                                           nv.ptr(slot_mapping), pool, nv.ptr(self.status), stream))
+            else:
+                if not hasattr(rope, "native"):
+                    raise TypeError("rope must be an easymlx_b200.layers.rotary.RotaryEmbedding (see get_rope)")
+                if queries.dtype != keys.dtype:
+                    raise ValueError("queries and keys must have the same dtype when RoPE is fused into the write")
+                queries = queries.contiguous()
+                rotated_q = torch.empty_like(queries)
+                nv.check(lib.emlx_kv_write_rope(
+                    nv.ptr(queries), nv.ptr(rotated_q), int(queries.shape[1]), nv.ptr(keys), nv.ptr(values),
+                    nv.dtype_code(keys.dtype), total_tokens, nv.ptr(slot_mapping), nv.ptr(positions),
+                    rope.native(dev), pool, nv.ptr(self.status), stream))
         if _CHECK:
             self.check()
-        return qsl, bt, lens, (None if plan is None else (plan, hq, window))
+        return qsl, bt, lens, (None if plan is None else (plan, hq, window)), rotated_q
 
     def append(self, seq_idx: int, key: torch.Tensor, value: torch.Tensor) -> None:
         """Append ``[num_tokens, num_kv_heads, head_dim]`` rows to one slot (``cache.py:834-872``)."""
@@ -343,7 +357,7 @@ class PageCacheView:
             raise IndexError(f"Invalid seq_idx {seq_idx}")
         n = int(key.shape[0])
         dev = self.key_cache.device
-        self._write_batch(key, value, _uploaded.get((n,), dev), _uploaded.get((int(seq_idx),), dev), n)
+        self._write_batch(key, value, _uploaded.get((n,), dev), _uploaded.get((int(seq_idx),), dev), n)  # noqa
 
     def reset(self, seq_idx: int) -> None:
         """Zero a slot's length.  (The reference also zero-fills the slot's pages; stale rows beyond
@@ -373,14 +387,13 @@ class PageCacheView:
         """Append the batch's K/V to the pool and resolve the metadata (``cache.py:1088-1306``).
 
         Returns ``(prepared_queries, key_cache, value_cache, resolved_metadata)``; the metadata carries the
-        scheduled slots' page-table rows and their lengths after the write.  ``slot_ids`` and
+        scheduled slots' page-table rows and their lengths after the write.  ``rope`` (a ``RotaryEmbedding``) is
+        applied to queries and keys at each token's position in its sequence, inside the write kernel.  ``slot_ids`` and
         ``query_lens`` are host sequences, as in the reference; when ``query_lens`` is omitted the lengths
         are derived on the device from ``cache_metadata.query_start_loc``.  ``advance=False`` (an extension)
         writes the rows and resolves the metadata but leaves ``self.kv_lens`` untouched, so that the same batch
         can be replayed (benchmarks, speculative what-if steps).
         """
-        if rope is not None:
-            raise NotImplementedError("RoPE inside the cache write is not provided yet; rotate q/k before the call")
         if slot_ids is None:
             slot_ids = getattr(cache_metadata, "slot_ids", None) or ()
         slots = tuple(int(s) for s in slot_ids)
@@ -405,8 +418,11 @@ class PageCacheView:
                 single = bool(getattr(cache_metadata, "is_single_token_decode", False)) and total == len(slots)
                 max_q = 1 if single else 0
         window = int(getattr(cache_metadata, "sliding_window", None) or 0)
-        qsl, bt, lens, plan = self._write_batch(keys, values, qlens_dev, _uploaded.get(slots, dev), total,
-                                                plan_for=(int(queries.shape[1]), window, max_q), advance=advance)
+        qsl, bt, lens, plan, rotated_q = self._write_batch(
+            keys, values, qlens_dev, _uploaded.get(slots, dev), total,
+            plan_for=(int(queries.shape[1]), window, max_q), advance=advance, rope=rope, queries=queries)
+        if rotated_q is not None:
+            queries = rotated_q
         meta = PageMetadata(
             query_start_loc=qsl, sliding_window=getattr(cache_metadata, "sliding_window", None),
             is_single_token_decode=bool(getattr(cache_metadata, "is_single_token_decode", False)) or single,

@@ -12,16 +12,53 @@ struct WriteParams {
     emlx_pool pool;
     int T;
     int32_t* status;
+    // rotary embedding fused into the write (rope_dims == 0: off)
+    const void* q_in;
+    void* q_out;
+    const int32_t* positions;
+    const float* inv_freq;
+    int Hq, rope_dims, traditional, has_pool;
+    float pos_scale, mscale;
+};
+
+// Element d of a row after the rotary embedding at position `pos`: pairs are (i, i + dims/2), or (2i, 2i + 1) in the
+// "traditional" layout; angle = pos * pos_scale * inv_freq[i]; elements past rope_dims pass through.  The result is
+// rounded to the input dtype, as a separate rotation step that returns an array of that dtype would.
+template <typename TIn>
+__device__ __forceinline__ float rope_elem(const TIn* row, int d, int pos, const WriteParams& w) {
+    const float x = to_f32<TIn>(row[d]);
+    if (d >= w.rope_dims) return x;
+    const int half = w.rope_dims >> 1;
+    const bool first = w.traditional ? ((d & 1) == 0) : (d < half);
+    const int i = w.traditional ? (d >> 1) : (first ? d : d - half);
+    const int partner = w.traditional ? (d ^ 1) : (first ? d + half : d - half);
+    const float y = to_f32<TIn>(row[partner]);
+    float sn, cs;
+    sincosf((float)pos * w.pos_scale * w.inv_freq[i], &sn, &cs);
+    const float a = (first ? x : y) * w.mscale, b = (first ? y : x) * w.mscale;
+    const float r = first ? a * cs - b * sn : a * sn + b * cs;
+    return to_f32<TIn>(from_f32<TIn>(r));
+}
+
+// Reads element d of a new row, rotated when `pos` >= 0.
+template <typename TIn>
+struct RowReader {
+    const TIn* row;
+    int pos;  // -1: no rotation
+    const WriteParams* w;
+    __device__ __forceinline__ float operator()(int d) const {
+        return pos >= 0 ? rope_elem<TIn>(row, d, pos, *w) : to_f32<TIn>(row[d]);
+    }
 };
 
 template <typename TIn, typename TOut>
-__device__ __forceinline__ void copy_row(const TIn* __restrict__ src, TOut* __restrict__ dst, int D, int lane) {
-    for (int d = lane; d < D; d += 32) dst[d] = from_f32<TOut>(to_f32<TIn>(src[d]));
+__device__ __forceinline__ void copy_row(const RowReader<TIn>& src, TOut* __restrict__ dst, int D, int lane) {
+    for (int d = lane; d < D; d += 32) dst[d] = from_f32<TOut>(src(d));
 }
 
 template <typename TIn>
-__device__ __forceinline__ void write_float_row(const TIn* src, void* cache, int kv_dtype, int64_t elem_off, int D,
-                                                int lane) {
+__device__ __forceinline__ void write_float_row(const RowReader<TIn>& src, void* cache, int kv_dtype, int64_t elem_off,
+                                                int D, int lane) {
     if (kv_dtype == EMLX_F16) copy_row(src, (__half*)cache + elem_off, D, lane);
     else if (kv_dtype == EMLX_BF16) copy_row(src, (__nv_bfloat16*)cache + elem_off, D, lane);
     else copy_row(src, (float*)cache + elem_off, D, lane);
@@ -45,8 +82,8 @@ __device__ __forceinline__ void quantize_group(float x0, float x1, int& c0, int&
 }
 
 template <typename TIn, int BITS>
-__device__ __forceinline__ void write_affine_rows(const TIn* krow, const TIn* vrow, const emlx_pool& p, int64_t page,
-                                                  int off, int h, int lane) {
+__device__ __forceinline__ void write_affine_rows(const RowReader<TIn>& krow, const RowReader<TIn>& vrow,
+                                                  const emlx_pool& p, int64_t page, int off, int h, int lane) {
     const int D = p.head_dim, bs = p.block_size, Hkv = p.num_kv_heads, groups = D / kQuantGroup;
     const int64_t sb_base = ((page * Hkv + h) * bs + off) * groups;
     // keys: token-major codes [NB, bs, Hkv, D*BITS/8]
@@ -57,14 +94,14 @@ __device__ __forceinline__ void write_affine_rows(const TIn* krow, const TIn* vr
         const int d0 = g * kQuantGroup + 2 * lane;
         int c0, c1;
         __half s, b;
-        quantize_group<BITS>(to_f32<TIn>(krow[d0]), to_f32<TIn>(krow[d0 + 1]), c0, c1, s, b);
+        quantize_group<BITS>(krow(d0), krow(d0 + 1), c0, c1, s, b);
         if (BITS == 8) *(uchar2*)(kdst + d0) = make_uchar2((unsigned char)c0, (unsigned char)c1);
         else kdst[d0 >> 1] = (uint8_t)(c0 | (c1 << 4));
         if (lane == 0) {
             ((__half*)p.k_scale)[sb_base + g] = s;
             ((__half*)p.k_bias)[sb_base + g] = b;
         }
-        quantize_group<BITS>(to_f32<TIn>(vrow[d0]), to_f32<TIn>(vrow[d0 + 1]), c0, c1, s, b);
+        quantize_group<BITS>(vrow(d0), vrow(d0 + 1), c0, c1, s, b);
         if (BITS == 8) {
             vdst[(int64_t)d0 * bs + off] = (uint8_t)c0;
             vdst[(int64_t)(d0 + 1) * bs + off] = (uint8_t)c1;
@@ -95,7 +132,17 @@ __global__ void __launch_bounds__(256) kv_write_kernel(WriteParams w) {
     const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const emlx_pool& p = w.pool;
     const int Hkv = p.num_kv_heads, D = p.head_dim;
-    if (warp >= (int64_t)w.T * Hkv) return;
+    const int64_t kv_warps = w.has_pool ? (int64_t)w.T * Hkv : 0;
+    if (warp >= kv_warps) {
+        // rotated queries: one warp per (token, q head)
+        const int64_t qw = warp - kv_warps;
+        if (w.q_out == nullptr || qw >= (int64_t)w.T * w.Hq) return;
+        const int t = (int)(qw / w.Hq);
+        const RowReader<TIn> q{(const TIn*)w.q_in + qw * D, w.positions[t], &w};
+        TIn* dst = (TIn*)w.q_out + qw * D;
+        for (int d = lane; d < D; d += 32) dst[d] = from_f32<TIn>(q(d));
+        return;
+    }
     const int t = (int)(warp / Hkv), h = (int)(warp - (int64_t)t * Hkv);
     const int64_t slot = w.slot_mapping[t];
     if (slot < 0) return;
@@ -103,8 +150,8 @@ __global__ void __launch_bounds__(256) kv_write_kernel(WriteParams w) {
         if (lane == 0) flag_error(w.status, EMLX_DEV_BAD_PAGE);
         return;
     }
-    const TIn* krow = (const TIn*)w.keys + ((int64_t)t * Hkv + h) * D;
-    const TIn* vrow = (const TIn*)w.values + ((int64_t)t * Hkv + h) * D;
+    const RowReader<TIn> krow{(const TIn*)w.keys + ((int64_t)t * Hkv + h) * D, w.rope_dims > 0 ? w.positions[t] : -1, &w};
+    const RowReader<TIn> vrow{(const TIn*)w.values + ((int64_t)t * Hkv + h) * D, -1, &w};
     if (p.kv_format == EMLX_KV_FLOAT) {
         const int64_t off = (slot * Hkv + h) * D;
         write_float_row(krow, p.key_cache, p.kv_dtype, off, D, lane);
@@ -137,18 +184,13 @@ int validate_pool(const emlx_pool* pool) {
 
 }  // namespace emlx
 
-extern "C" int emlx_kv_write(const void* keys, const void* values, int32_t in_dtype, int32_t total_tokens,
-                             const int64_t* slot_mapping, const emlx_pool* pool, int32_t* status, void* stream) {
-    using namespace emlx;
-    if (int rc = validate_pool(pool)) return rc;
-    if (total_tokens < 0) return fail(EMLX_ERR_INVALID, "total_tokens must be non-negative");
-    if (total_tokens == 0) return EMLX_OK;
-    if (!keys || !values || !slot_mapping) return fail(EMLX_ERR_INVALID, "kv_write: NULL input");
-    WriteParams w{keys, values, slot_mapping, *pool, total_tokens, status};
-    const int64_t warps = (int64_t)total_tokens * pool->num_kv_heads;
+namespace emlx {
+
+static int launch_write(WriteParams& w, int in_dtype, cudaStream_t s) {
+    const int64_t warps = (w.has_pool ? (int64_t)w.T * w.pool.num_kv_heads : 0) + (w.q_out ? (int64_t)w.T * w.Hq : 0);
+    if (warps == 0) return EMLX_OK;
     const int threads = 256;
     const unsigned blocks = (unsigned)((warps * 32 + threads - 1) / threads);
-    cudaStream_t s = (cudaStream_t)stream;
     switch (in_dtype) {
         case EMLX_F16: EMLX_CUDA_OK(launch_pdl(kv_write_kernel<__half>, blocks, threads, 0, s, w)); break;
         case EMLX_BF16: EMLX_CUDA_OK(launch_pdl(kv_write_kernel<__nv_bfloat16>, blocks, threads, 0, s, w)); break;
@@ -157,4 +199,51 @@ extern "C" int emlx_kv_write(const void* keys, const void* values, int32_t in_dt
     }
     EMLX_LAUNCHED();
     return EMLX_OK;
+}
+
+}  // namespace emlx
+
+extern "C" int emlx_kv_write(const void* keys, const void* values, int32_t in_dtype, int32_t total_tokens,
+                             const int64_t* slot_mapping, const emlx_pool* pool, int32_t* status, void* stream) {
+    using namespace emlx;
+    if (int rc = validate_pool(pool)) return rc;
+    if (total_tokens < 0) return fail(EMLX_ERR_INVALID, "total_tokens must be non-negative");
+    if (total_tokens == 0) return EMLX_OK;
+    if (!keys || !values || !slot_mapping) return fail(EMLX_ERR_INVALID, "kv_write: NULL input");
+    WriteParams w{};
+    w.keys = keys; w.values = values; w.slot_mapping = slot_mapping; w.pool = *pool; w.T = total_tokens; w.status = status;
+    w.has_pool = 1;
+    return launch_write(w, in_dtype, (cudaStream_t)stream);
+}
+
+extern "C" int emlx_kv_write_rope(const void* queries, void* queries_out, int32_t num_q_heads, const void* keys,
+                                  const void* values, int32_t in_dtype, int32_t total_tokens,
+                                  const int64_t* slot_mapping, const int32_t* token_positions, const emlx_rope* rope,
+                                  const emlx_pool* pool, int32_t* status, void* stream) {
+    using namespace emlx;
+    if (!rope || !rope->inv_freq) return fail(EMLX_ERR_INVALID, "rope parameters are NULL");
+    if (rope->dims <= 0 || (rope->dims & 1)) return fail(EMLX_ERR_INVALID, "rope dims must be positive and even");
+    if (total_tokens < 0) return fail(EMLX_ERR_INVALID, "total_tokens must be non-negative");
+    if (total_tokens == 0) return EMLX_OK;
+    if (!token_positions) return fail(EMLX_ERR_INVALID, "token_positions is NULL");
+    WriteParams w{};
+    w.T = total_tokens; w.status = status;
+    if (pool) {
+        if (int rc = validate_pool(pool)) return rc;
+        if (!keys || !values || !slot_mapping) return fail(EMLX_ERR_INVALID, "kv_write_rope: NULL key/value input");
+        if (rope->dims > pool->head_dim) return fail(EMLX_ERR_INVALID, "rope dims exceed head_dim");
+        w.keys = keys; w.values = values; w.slot_mapping = slot_mapping; w.pool = *pool; w.has_pool = 1;
+    } else if (rope->head_dim_if_no_pool <= 0 || rope->dims > rope->head_dim_if_no_pool) {
+        return fail(EMLX_ERR_INVALID, "without a pool, rope->head_dim_if_no_pool must give the row width");
+    } else {
+        w.pool.head_dim = rope->head_dim_if_no_pool;
+        w.pool.num_kv_heads = 1;
+    }
+    if (queries_out) {
+        if (!queries || num_q_heads <= 0) return fail(EMLX_ERR_INVALID, "kv_write_rope: queries / num_q_heads missing");
+        w.q_in = queries; w.q_out = queries_out; w.Hq = num_q_heads;
+    }
+    w.positions = token_positions; w.inv_freq = rope->inv_freq; w.rope_dims = rope->dims;
+    w.traditional = rope->traditional; w.pos_scale = rope->position_scale; w.mscale = rope->mscale;
+    return launch_write(w, in_dtype, (cudaStream_t)stream);
 }

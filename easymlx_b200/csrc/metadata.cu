@@ -9,7 +9,8 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
     const int32_t* __restrict__ query_lens, const int32_t* __restrict__ slot_ids, int S, int T,
     const int32_t* __restrict__ bt_all, int num_slots, int MB, int32_t* kv_lens_all, int bs, int advance,
     int32_t* __restrict__ qsl, int32_t* __restrict__ bt_out, int32_t* __restrict__ kv_out,
-    int64_t* __restrict__ slot_mapping, int64_t num_blocks, int32_t* status, int32_t* plan, PlanLayout L, int G,
+    int64_t* __restrict__ slot_mapping, int32_t* __restrict__ token_positions, int64_t num_blocks, int32_t* status,
+    int32_t* plan, PlanLayout L, int G,
     int window, int class_lo, int class_hi, bool wide, int Hkv, int num_ctas) {
     __shared__ int32_t scan_smem[kMetaThreads / 32 + 1];
     // batches of up to kSmemSeqs sequences keep their prefix sums and lengths in shared memory: every later phase
@@ -74,12 +75,14 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
     const int n = min(T, total);
     for (int t = tid; t < T; t += kMetaThreads) {
         int64_t dst = -1;
+        int pos_out = 0;
         if (t < n) {
             int s = find_sequence(qv, S, t);
             int slot = s >= 0 ? slot_ids[s] : -1;
             if (slot >= 0 && slot < num_slots) {
                 int q_len = qv[s + 1] - qv[s];
                 int pos = kvv[s] - q_len + (t - qv[s]);
+                pos_out = pos;
                 int page_idx = pos / bs;
                 if (page_idx < MB) {
                     int page = bt_all[(int64_t)slot * MB + page_idx];
@@ -89,6 +92,7 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
             }
         }
         slot_mapping[t] = dst;
+        if (token_positions) token_positions[t] = pos_out;
     }
 }
 
@@ -98,8 +102,8 @@ extern "C" int emlx_build_metadata(const int32_t* query_lens, const int32_t* slo
                                    int32_t total_tokens, const int32_t* block_tables_all, int32_t num_slots,
                                    int32_t max_blocks_per_seq, int32_t* kv_lens_all, int32_t block_size,
                                    int32_t advance_kv_lens, int32_t* query_start_loc, int32_t* block_tables,
-                                   int32_t* kv_lens, int64_t* slot_mapping, int64_t num_blocks, int32_t* status,
-                                   int32_t num_q_heads, int32_t num_kv_heads, int32_t sliding_window,
+                                   int32_t* kv_lens, int64_t* slot_mapping, int32_t* token_positions,
+                                   int64_t num_blocks, int32_t* status, int32_t num_q_heads, int32_t num_kv_heads, int32_t sliding_window,
                                    int32_t max_query_len, int32_t plan_flags, void* plan, size_t plan_bytes,
                                    void* stream) {
     using namespace emlx;
@@ -123,8 +127,8 @@ extern "C" int emlx_build_metadata(const int32_t* query_lens, const int32_t* slo
     }
     EMLX_CUDA_OK(launch_pdl(build_metadata_kernel, 1, kMetaThreads, 0, (cudaStream_t)stream,
         query_lens, slot_ids, num_seqs, total_tokens, block_tables_all, num_slots, max_blocks_per_seq, kv_lens_all,
-        block_size, advance_kv_lens, query_start_loc, block_tables, kv_lens, slot_mapping, num_blocks, status,
-        (int32_t*)plan, L, G, sliding_window, class_lo, class_hi, (plan_flags & kPlanWideUnits) != 0, num_kv_heads,
+        block_size, advance_kv_lens, query_start_loc, block_tables, kv_lens, slot_mapping, token_positions, num_blocks,
+        status, (int32_t*)plan, L, G, sliding_window, class_lo, class_hi, (plan_flags & kPlanWideUnits) != 0, num_kv_heads,
         min(num_sms(), kMaxGrid)));
     EMLX_LAUNCHED();
     return EMLX_OK;

@@ -1,0 +1,3 @@
+from .rotary import RotaryEmbedding, get_rope
+
+__all__ = ("RotaryEmbedding", "get_rope")

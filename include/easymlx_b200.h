@@ -119,6 +119,7 @@ int emlx_build_metadata(const int32_t* query_lens, const int32_t* slot_ids, int3
                         const int32_t* block_tables_all, int32_t num_slots, int32_t max_blocks_per_seq,
                         int32_t* kv_lens_all, int32_t block_size, int32_t advance_kv_lens,
                         int32_t* query_start_loc, int32_t* block_tables, int32_t* kv_lens, int64_t* slot_mapping,
+                        int32_t* token_positions /* out, [T], position of every new row in its sequence; may be NULL */,
                         int64_t num_blocks, int32_t* status,
                         /* optional: also build the attention work list in the same launch (plan == NULL: skip) */
                         int32_t num_q_heads, int32_t num_kv_heads, int32_t sliding_window, int32_t max_query_len,
@@ -129,6 +130,29 @@ int emlx_build_metadata(const int32_t* query_lens, const int32_t* slot_ids, int3
  * (caching/paged/cache.py:1171-1184).  keys/values are [T, Hkv, D] in `in_dtype`, contiguous. */
 int emlx_kv_write(const void* keys, const void* values, int32_t in_dtype, int32_t total_tokens,
                   const int64_t* slot_mapping, const emlx_pool* pool, int32_t* status, void* stream);
+
+/* Rotary embedding parameters: angle of pair i at position p is p * position_scale / freqs[i] with
+ * inv_freq[i] = 1 / freqs[i]; pairs are (i, i + dims/2), or (2i, 2i+1) when `traditional`; the rotated slice is
+ * multiplied by mscale.  Covers the reference's default / linear / llama3 / yarn variants, which all reduce to
+ * mx.fast.rope(x, dims, traditional, base | freqs, scale, offset) (layers/rotary/_rotary.py:123-131,213-221,369-370). */
+typedef struct emlx_rope {
+    const float* inv_freq;        /* device, [dims / 2]                                     */
+    int32_t dims;                 /* rotated leading dimensions of every head, even, <= D   */
+    int32_t traditional;
+    float position_scale;
+    float mscale;
+    int32_t head_dim_if_no_pool;  /* row width when emlx_kv_write_rope is called without a pool */
+    int32_t reserved;
+} emlx_rope;
+
+/* (1)+(f1) Paged KV write with the rotary embedding fused in.  Replaces the RoPE calls inside
+ * PageCacheView.concatenate_to_cache (caching/paged/cache.py:1161-1166,1225-1231) together with the scatter:
+ * keys are rotated at token_positions[t] as they are read and then stored / quantised; queries are rotated into
+ * queries_out in the same launch (queries_out == NULL: keys only; pool == NULL: queries only). */
+int emlx_kv_write_rope(const void* queries, void* queries_out, int32_t num_q_heads, const void* keys,
+                       const void* values, int32_t in_dtype, int32_t total_tokens, const int64_t* slot_mapping,
+                       const int32_t* token_positions, const emlx_rope* rope, const emlx_pool* pool, int32_t* status,
+                       void* stream);
 
 /* Work list for the tiled attention kernels, built on the GPU from query_start_loc / kv_lens
  * (replaces the host-side classification of _is_single_token_decode,
