@@ -68,6 +68,7 @@ SIGNATURES = {
     "emlx_attn_prefill": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
     "emlx_attn_generic": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
     "emlx_set_trace_buffer": (None, [_P]),
+    "emlx_selftest_wait_timeout": (C.c_int, [_P, C.c_uint32, _P]),
     "emlx_attn_decode_static": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
 }
 

@@ -1,6 +1,7 @@
 // Decode attention for callers that cannot allocate device memory: the work list and the split-KV
 // workspace live in one file-scope device array instead of caller-provided buffers.
 #include "attn_tiled.cuh"
+#include "ptx.cuh"
 
 #include <mutex>
 
@@ -63,4 +64,32 @@ extern "C" int emlx_attn_decode_static(const emlx_attn_args* args, const emlx_po
     local.workspace = workspace;
     local.workspace_bytes = W.bytes;
     return emlx_attn_decode(&local, pool, stream);
+}
+
+// ------------------------------------------------------------------------------------------ wait self-test
+namespace emlx {
+// One warp waits on a barrier that nothing ever completes; the bounded wait gives up after `limit` polls, the
+// kernel records EMLX_DEV_WAIT_TIMEOUT and returns normally.  The context stays usable.
+__global__ void wait_timeout_selftest_kernel(int32_t* status, uint32_t limit) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_word;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(&bar, 1);
+        abort_word = 0;
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+    const bool done = ptx::mbar_wait(&bar, 0, &abort_word, limit);
+    __syncthreads();
+    if (threadIdx.x == 0 && (!done || abort_word)) flag_error(status, EMLX_DEV_WAIT_TIMEOUT);
+}
+}  // namespace emlx
+
+extern "C" int emlx_selftest_wait_timeout(int32_t* status, uint32_t poll_limit, void* stream) {
+    using namespace emlx;
+    if (!status) return fail(EMLX_ERR_INVALID, "status pointer is NULL");
+    if (poll_limit == 0 || poll_limit > (1u << 20)) return fail(EMLX_ERR_INVALID, "poll_limit must be in [1, 2^20]");
+    wait_timeout_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, poll_limit);
+    EMLX_LAUNCHED();
+    return EMLX_OK;
 }

@@ -39,9 +39,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // CTA-wide abort word is set and the call returns false; callers keep going without waiting so that
 // every thread still reaches its barriers and the kernel ends.
 constexpr uint32_t kWaitLimit = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word,
+                                          uint32_t limit = kWaitLimit) {
     if (*abort_word) return false;
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((i & 255) == 255) {
             if (*abort_word) return false;

@@ -193,6 +193,11 @@ int emlx_attn_generic(const emlx_attn_args* args, const emlx_pool* pool, void* s
  * calls that overlap on the GPU (different streams) race, so serialise them.  Calls no allocating routine. */
 int emlx_attn_decode_static(const emlx_attn_args* args, const emlx_pool* pool, void* stream);
 
+/* Failure-detection self-test: launches one warp that waits, with the kernels' bounded-wait routine and a limit of
+ * `poll_limit` polls, on a barrier that is never completed; the wait gives up, the kernel ORs EMLX_DEV_WAIT_TIMEOUT
+ * into *status and returns normally (nothing faults, the context stays usable). */
+int emlx_selftest_wait_timeout(int32_t* status, uint32_t poll_limit, void* stream);
+
 /* Tracing aid: when `records` is a device buffer of 4 * 256 int64, every CTA of the tiled attention kernels
  * writes {start ns, end ns, tiles processed, 0} (GPU global timer) at index 4 * blockIdx.x; NULL turns it off. */
 void emlx_set_trace_buffer(int64_t* records);

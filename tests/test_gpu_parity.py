@@ -208,3 +208,35 @@ def test_bad_slot_and_overflow_are_flagged():
             query_start_loc=build_query_start_loc([300])), slot_ids=[1])
         cache.check()
     cache.check()  # reported once, then clear
+
+
+def test_bounded_wait_reports_a_timeout_and_leaves_the_context_usable():
+    """Failure detection without a fault: a wait that nothing satisfies runs out and is reported through the status
+    word; afterwards the same context runs a normal batch."""
+    from easymlx_b200 import _native as nv
+
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lib, stream = nv.lib(), nv.stream_ptr(status.device)
+    nv.check(lib.emlx_selftest_wait_timeout(nv.ptr(status), 4096, stream))
+    rc = lib.emlx_read_status(nv.ptr(status), stream)
+    assert rc == nv.EMLX_ERR_DEVICE and b"timed out" in lib.emlx_last_error()
+    x = cases.attention_inputs(**cases.ATTENTION_CASES["attn_f16_decode_d64"])
+    assert torch.isfinite(_run(x, None)).all()
+
+
+@pytest.mark.parametrize("name", ["attn_f16_decode_d128", "attn_f16_mixed_d128", "attn_f16_specverify", "attn_f16_mixed_d64"])
+def test_bfloat16_queries_and_pool(name):
+    from easymlx_b200 import paged_attention
+
+    x = cases.attention_inputs(**cases.ATTENTION_CASES[name])
+    q = torch.from_numpy(x["q"]).float().bfloat16().cuda()
+    kc = torch.from_numpy(x["key_cache"]).float().bfloat16().cuda()
+    vc = torch.from_numpy(x["value_cache"]).float().bfloat16().cuda()
+    out = paged_attention(q, kc, vc, dev(x["block_tables"]), dev(x["kv_lens"]), dev(x["query_start_loc"]),
+                          softmax_scale=x["scale"], sliding_window=x["window"])
+    assert out.dtype == torch.bfloat16
+    want = opa.paged_attention_rows(q.float().cpu().numpy(), kc.float().cpu().numpy(), vc.float().cpu().numpy(),
+                                    x["block_tables"], x["kv_lens"], x["query_start_loc"], softmax_scale=x["scale"],
+                                    sliding_window=x["window"])
+    # bf16 keeps 8 significant bits: probabilities and outputs are rounded to 2^-9 relative
+    assert_close(out, want, atol=4e-3, rtol=2e-2)
