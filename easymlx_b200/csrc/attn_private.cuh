@@ -75,10 +75,12 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
     }
     (void)k_off; (void)kq_off;
 
-    long long f = f_begin;
+    uint64_t* mfull = full + 24;
+    long long remaining = f_end - f_begin;  // the producer decides the order of the parts; only their total is fixed
     uint32_t it = 0, part_idx = 0;
+    int posted = 0;
 
-    while (f < f_end) {
+    while (remaining > 0) {
         // ------------------------------------------------------------------ part descriptor from the producer
         const uint32_t dslot = part_idx % C::NDESC;
         ptx::mbar_wait(&dfull[dslot], (part_idx / C::NDESC) & 1, abort_word);
@@ -390,6 +392,10 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
             if (lane == 0) ptx::mbar_arrive(&empty[stage]);
         }
 
+#ifdef EMLX_TRACE_PARTS  // measurement aid: {tile loop end, part end, tiles, flags} for the first parts of a CTA
+        long long trace_t0 = 0;
+        if (p.trace && tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(trace_t0));
+#endif
         // ------------------------------------------------------------------ combine the eight warps' states
         const long long a_flat = (long long)cum_u * p.Hkv + (long long)head * ntiles;
         const long long b_flat = a_flat + ntiles;
@@ -477,46 +483,101 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
             }
         }
         if (!complete) {
-            __threadfence();
-            consumer_sync();
-            const int c_first = slice_owner(p.cta_start, (int)P, a_flat), c_last = slice_owner(p.cta_start, (int)P, b_flat - 1);
-            const int nparts = slices_in_use(p.cta_start, c_first, c_last);
-            int* counter = p.counters + (size_t)unit * p.Hkv + head;
-            if (tid == 0) misc[1] = atomicAdd(counter, 1);
-            consumer_sync();
-            if (misc[1] == nparts - 1) {
-                __threadfence();
-                for (int idx = tid; idx < ROWS * D; idx += kConsumerThreads) {
-                    const int row = idx / D, d = idx - row * D, r = row0 + row;
-                    if (r >= R) continue;
-                    float M = -INFINITY;
-                    for (int c = c_first; c <= c_last; ++c) {
-                        const long long cb = p.cta_start[c];
-                        if (cb >= p.cta_start[c + 1]) continue;
-                        const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
-                        if (__ldcg(sl + ROWS * D + ROWS + row) > 0.f) M = fmaxf(M, __ldcg(sl + ROWS * D + row));
-                    }
-                    float acc = 0.f, den = 0.f;
-                    for (int c = c_first; c <= c_last; ++c) {
-                        const long long cb = p.cta_start[c];
-                        if (cb >= p.cta_start[c + 1]) continue;
-                        const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
-                        const float lp = __ldcg(sl + ROWS * D + ROWS + row);
-                        if (lp > 0.f) {
-                            const float wgt = ex2(__ldcg(sl + ROWS * D + row) - M);
-                            acc = fmaf(wgt, __ldcg(sl + row * D + d), acc);
-                            den = fmaf(wgt, lp, den);
-                        }
-                    }
-                    const int i = r / p.G, hh = r - i * p.G;
-                    ((uint16_t*)p.out)[((long long)(qs + i) * p.Hq + head * p.G + hh) * D + d] =
-                        to_bits16<BF16>(den > 0.f ? acc / den : 0.f);
-                }
-                if (tid == 0) *counter = 0;
+            // hand the part to the merge warp: the request, then one arrival per warp after its slot stores
+            if (tid == 0) {
+                MergeRequest* rq = (MergeRequest*)(fixed + C::OFF_MAIL) + posted;
+                rq->kind = 1; rq->row0 = row0; rq->rows = R; rq->qs = qs; rq->head = head; rq->unit = unit;
+                rq->ntiles = ntiles; rq->cum_u = cum_u;
             }
+            __syncwarp();
+            if (lane == 0 && posted < 2) ptx::mbar_arrive(&mfull[posted]);
+            ++posted;
         }
-        f += run;
+#ifdef EMLX_TRACE_PARTS
+        if (p.trace && tid == 0 && part_idx < 16) {
+            long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            long long* rec = p.trace + 1024 + ((size_t)blockIdx.x * 16 + part_idx) * 4;
+            rec[0] = trace_t0; rec[1] = now; rec[2] = run; rec[3] = complete ? 0 : 1;
+        }
+#endif
+        remaining -= run;
         ++part_idx;
+    }
+    // a slice has at most two unfinished parts (its first and its last); tell the merge warp that no more follow
+    for (; posted < 2; ++posted) {
+        if (tid == 0) ((MergeRequest*)(fixed + C::OFF_MAIL))[posted].kind = 2;
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&mfull[posted]);
+    }
+}
+
+// The merge warp.  For every unfinished part the consumers hand over: make the slot visible to the GPU, count the
+// arrival on the (unit, head) counter, and when this was the last of the unit's parts, fold all of them in slice
+// order (so the result does not depend on which CTA came last) and write the rows.
+template <int D, int NT, int FMT, bool BF16>
+__device__ __forceinline__ void merge_warp_loop(const TiledParams& p, uint8_t* fixed, uint64_t* full,
+                                                volatile int* abort_word, int active) {
+    using C = Cfg<D, NT, FMT>;
+    constexpr int ROWS = C::ROWS;
+    const int lane = threadIdx.x & 31;
+    uint64_t* mfull = full + 24;
+    for (int e = 0; e < 2; ++e) {
+        // the consumers may take their whole slice before they post: sleep between polls, give up after seconds
+        bool ok = false;
+        for (uint32_t i = 0; i < (1u << 22) && !ok && !*abort_word; ++i) {
+            ok = ptx::mbar_try_wait(&mfull[e], 0);
+            if (!ok) __nanosleep(i < 64 ? 200 : 2000);
+        }
+        if (!ok) {
+            if (!*abort_word) *abort_word = 1;
+            if (lane == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
+            return;
+        }
+        const MergeRequest rq = ((const MergeRequest*)(fixed + C::OFF_MAIL))[e];
+        if (rq.kind != 1) return;
+        const long long a_flat = (long long)rq.cum_u * p.Hkv + (long long)rq.head * rq.ntiles;
+        const long long b_flat = a_flat + rq.ntiles;
+        const int c_first = slice_owner(p.cta_start, active, a_flat), c_last = slice_owner(p.cta_start, active, b_flat - 1);
+        const int nparts = slices_in_use(p.cta_start, c_first, c_last);
+        int* counter = p.counters + (size_t)rq.unit * p.Hkv + rq.head;
+        __threadfence();  // the consumers' slot stores, seen through the barrier, become visible GPU-wide
+        int ticket = 0;
+        if (lane == 0) ticket = atomicAdd(counter, 1);
+        ticket = __shfl_sync(0xffffffffu, ticket, 0);
+        if (ticket != nparts - 1) continue;
+        __threadfence();
+        for (int row = 0; row < ROWS; ++row) {
+            const int r = rq.row0 + row;
+            if (r >= rq.rows) break;
+            float M = -INFINITY;
+            for (int c = c_first; c <= c_last; ++c) {
+                const long long cb = p.cta_start[c];
+                if (cb >= p.cta_start[c + 1]) continue;
+                const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
+                if (__ldcg(sl + ROWS * D + ROWS + row) > 0.f) M = fmaxf(M, __ldcg(sl + ROWS * D + row));
+            }
+            float acc[D / 32], den = 0.f;
+#pragma unroll
+            for (int k = 0; k < D / 32; ++k) acc[k] = 0.f;
+            for (int c = c_first; c <= c_last; ++c) {
+                const long long cb = p.cta_start[c];
+                if (cb >= p.cta_start[c + 1]) continue;
+                const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
+                const float lp = __ldcg(sl + ROWS * D + ROWS + row);
+                if (lp > 0.f) {
+                    const float wgt = ex2(__ldcg(sl + ROWS * D + row) - M);
+#pragma unroll
+                    for (int k = 0; k < D / 32; ++k) acc[k] = fmaf(wgt, __ldcg(sl + row * D + 32 * k + lane), acc[k]);
+                    den = fmaf(wgt, lp, den);
+                }
+            }
+            const int i = r / p.G, hh = r - i * p.G;
+            uint16_t* dst = (uint16_t*)p.out + ((long long)(rq.qs + i) * p.Hq + rq.head * p.G + hh) * D;
+#pragma unroll
+            for (int k = 0; k < D / 32; ++k) dst[32 * k + lane] = to_bits16<BF16>(den > 0.f ? acc[k] / den : 0.f);
+        }
+        if (lane == 0) *counter = 0;
     }
 }
 

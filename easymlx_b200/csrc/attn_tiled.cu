@@ -25,7 +25,7 @@ int validate_attn(const emlx_attn_args* a, const emlx_pool* pool, bool need_plan
 
 constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
-constexpr int kThreads = kConsumerThreads + 32;
+constexpr int kThreads = kConsumerThreads + 64;  // + the producer warp and the split-merge warp
 constexpr int kPStride = kTile * 2 + 16;  // bytes per row of a P buffer (padding keeps ldmatrix conflict-free)
 constexpr int kSmemBudget = 227 * 1024 - 1024;  // dynamic shared memory minus alignment slack
 
@@ -44,7 +44,7 @@ struct TiledParams {
     int32_t* counters;
     float* slots;
     int32_t* status;
-    long long* trace;  // optional per-CTA records {start ns, end ns, tiles, 0}
+    long long* trace;  // optional per-CTA records {start ns, end ns, tiles, SM id}
     const __half* k_scale;
     const __half* k_bias;
     const __half* v_scale;
@@ -77,7 +77,7 @@ struct Cfg {
     static constexpr int QSTRIDE = D * 2;
     static constexpr int NDESC = PRIVATE ? (NT == 1 ? 4 : 2) : 0;
     static constexpr int DESC_BYTES = PRIVATE ? 64 + ROWS * QSTRIDE : 0;
-    static constexpr int SMALL = 2 * 32 * 4 + 4 * kConsumerWarps * 32 * 4 + 64 + 256;  // row stats, per-warp stats, misc, barriers
+    static constexpr int SMALL = 2 * 32 * 4 + 4 * kConsumerWarps * 32 * 4 + 64 + 256 + 128;  // row stats, per-warp stats, misc, barriers, requests
     static constexpr int red_bytes(int cols) { return kConsumerWarps * ROWS * (cols + 4) * 4; }
     static constexpr int stages_with(int fixed) { return (kSmemBudget - fixed) / STAGE > 8 ? 8 : (kSmemBudget - fixed) / STAGE; }
     static constexpr int PRIV_BASE = NDESC * DESC_BYTES + SMALL;
@@ -93,8 +93,9 @@ struct Cfg {
     static constexpr int OFF_SMALL = PBYTES + OREDBYTES;          // 64 floats of row statistics (tile max / merged max, sum)
     static constexpr int OFF_W = OFF_SMALL + 2 * 32 * 4;          // 4 x [warps][32] floats
     static constexpr int OFF_MISC = OFF_W + 4 * kConsumerWarps * 32 * 4;
-    static constexpr int OFF_BAR = OFF_MISC + 64;                 // full[8], empty[8], dfull[4], dempty[4]
-    static constexpr int FIXED = OFF_BAR + 256;
+    static constexpr int OFF_BAR = OFF_MISC + 64;                 // full[8], empty[8], dfull[4], dempty[4], mfull[2]
+    static constexpr int OFF_MAIL = OFF_BAR + 256;                // two split-merge requests
+    static constexpr int FIXED = OFF_MAIL + 128;
     static constexpr int STAGES_RAW = (kSmemBudget - FIXED) / STAGE;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM = STAGES * STAGE + FIXED + 1024;
@@ -128,6 +129,14 @@ struct PartDesc {
     int seq, row0, tile_lo, qs, q_len, kv_len, head, u, j, run, ntiles, cum_u, pad[4];
 };
 static_assert(sizeof(PartDesc) == 64, "descriptor header is 64 bytes");
+
+// A part that covers only some of its unit's tiles leaves its partial result in this CTA's slot and hands the rest
+// (publish, count, merge when it was the last one) to the merge warp through one of these.
+struct MergeRequest {
+    int kind;  // 1 = a part to publish, 2 = no further request from this CTA
+    int row0, rows, qs, head, unit, ntiles, cum_u;
+};
+static_assert(sizeof(MergeRequest) == 32, "two requests fit the mail area");
 
 struct Walk {
     int u, head, j, ntiles;
@@ -165,14 +174,27 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
     uint32_t part_idx = 0;
     (void)dfull; (void)dempty; (void)part_idx; (void)fixed;
     Walk w;
-    w.locate(f_begin, p.unit_cum, num_units, p.Hkv);
-    long long f = f_begin;
+    // Order of the slice's parts.  When the slice ends inside a unit, that unfinished part goes first: both parts
+    // that need a merge with a neighbouring CTA are then done early and their merges run behind the other parts.
+    long long range_lo[2] = {f_begin, f_begin}, range_hi[2] = {f_end, f_begin};
+    if constexpr (C::PRIVATE) {
+        w.locate(f_end - 1, p.unit_cum, num_units, p.Hkv);
+        const long long a_last = (long long)p.unit_cum[w.u] * p.Hkv + (long long)w.head * w.ntiles;
+        if (a_last + w.ntiles > f_end && a_last > f_begin) {
+            range_lo[0] = a_last; range_hi[0] = f_end;
+            range_lo[1] = f_begin; range_hi[1] = a_last;
+        }
+    }
     uint32_t it = 0;
-    while (f < f_end && !*abort_word) {
+    for (int rg = 0; rg < 2; ++rg) {
+    long long f = range_lo[rg];
+    const long long f_stop = range_hi[rg];
+    if (f < f_stop) w.locate(f, p.unit_cum, num_units, p.Hkv);
+    while (f < f_stop && !*abort_word) {
         const int seq = p.unit_seq[w.u];
         const int tile_lo = p.unit_tile_lo[w.u];
         const int kv_len = p.kv_lens[seq];
-        const int run = (int)min((long long)(w.ntiles - w.j), f_end - f);
+        const int run = (int)min((long long)(w.ntiles - w.j), f_stop - f);
         if constexpr (C::PRIVATE) {
             // descriptor + Q rows of this part, so that the consumers start it without touching global memory
             const uint32_t slot = part_idx % C::NDESC, use = part_idx / C::NDESC;
@@ -236,6 +258,7 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
         }
         f += run;
         w.next_part(p.unit_cum, num_units, p.Hkv);
+    }
     }
 }
 
@@ -819,6 +842,7 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             ptx::mbar_init(&dfull[s], 1);
             ptx::mbar_init(&dempty[s], kConsumerWarps);
         }
+        for (int s = 0; s < 2; ++s) ptx::mbar_init(&full[24 + s], kConsumerWarps);
         *abort_word = 0;
         ptx::fence_barrier_init();
         ptx::prefetch_tensormap(&kmap);
@@ -836,7 +860,10 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     if (f_begin >= f_end) return;  // uniform for the CTA, and no thread waits on a barrier yet
     const long long active = gridDim.x;
 
-    if (threadIdx.x >= kConsumerThreads) {
+    if (threadIdx.x >= kConsumerThreads + 32) {
+        if constexpr (C::PRIVATE) merge_warp_loop<D, NT, FMT, BF16>(p, fixed, full, abort_word, (int)active);
+        return;
+    } else if (threadIdx.x >= kConsumerThreads) {
         producer_loop<D, NT, FMT>(&kmap, &vmap, p, smem, fixed, full, empty, abort_word, f_begin, f_end, num_units);
     } else {
         if constexpr (C::PRIVATE)
@@ -850,6 +877,9 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
         p.trace[4 * blockIdx.x + 1] = now;
         p.trace[4 * blockIdx.x + 2] = f_end - f_begin;
+        unsigned smid;
+        asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
+        p.trace[4 * blockIdx.x + 3] = smid;
     }
 }
 
