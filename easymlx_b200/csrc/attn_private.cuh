@@ -547,35 +547,57 @@ __device__ __forceinline__ void merge_warp_loop(const TiledParams& p, uint8_t* f
         ticket = __shfl_sync(0xffffffffu, ticket, 0);
         if (ticket != nparts - 1) continue;
         __threadfence();
-        for (int row = 0; row < ROWS; ++row) {
-            const int r = rq.row0 + row;
-            if (r >= rq.rows) break;
-            float M = -INFINITY;
+        // Lane r < ROWS first folds the parts' (max, sum) pairs of row r, so that the loads of the partial rows
+        // below depend on nothing but addresses and all of them can be in flight together.
+        const int rows_here = min(ROWS, rq.rows - rq.row0);
+        const int lrow = lane < ROWS ? lane : 0;
+        float M = -INFINITY;
+        for (int c = c_first; c <= c_last; ++c) {
+            const long long cb = p.cta_start[c];
+            if (cb >= p.cta_start[c + 1]) continue;
+            const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
+            const float mp = __ldcg(sl + ROWS * D + lrow), lp = __ldcg(sl + ROWS * D + ROWS + lrow);
+            if (lp > 0.f) M = fmaxf(M, mp);
+        }
+        float acc[ROWS][D / 32], den = 0.f;
+#pragma unroll
+        for (int row = 0; row < ROWS; ++row)
+#pragma unroll
+            for (int k = 0; k < D / 32; ++k) acc[row][k] = 0.f;
+        {
+#pragma unroll 1
             for (int c = c_first; c <= c_last; ++c) {
                 const long long cb = p.cta_start[c];
                 if (cb >= p.cta_start[c + 1]) continue;
                 const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
-                if (__ldcg(sl + ROWS * D + ROWS + row) > 0.f) M = fmaxf(M, __ldcg(sl + ROWS * D + row));
-            }
-            float acc[D / 32], den = 0.f;
+                const float mp = __ldcg(sl + ROWS * D + lrow), lp = __ldcg(sl + ROWS * D + ROWS + lrow);
+                const float wgt = lp > 0.f ? ex2(mp - M) : 0.f;
+                den = fmaf(wgt, lp, den);
+                float v[ROWS][D / 32];
 #pragma unroll
-            for (int k = 0; k < D / 32; ++k) acc[k] = 0.f;
-            for (int c = c_first; c <= c_last; ++c) {
-                const long long cb = p.cta_start[c];
-                if (cb >= p.cta_start[c + 1]) continue;
-                const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
-                const float lp = __ldcg(sl + ROWS * D + ROWS + row);
-                if (lp > 0.f) {
-                    const float wgt = ex2(__ldcg(sl + ROWS * D + row) - M);
+                for (int row = 0; row < ROWS; ++row)
 #pragma unroll
-                    for (int k = 0; k < D / 32; ++k) acc[k] = fmaf(wgt, __ldcg(sl + row * D + 32 * k + lane), acc[k]);
-                    den = fmaf(wgt, lp, den);
+                    for (int k = 0; k < D / 32; ++k) v[row][k] = row < rows_here ? __ldcg(sl + row * D + 32 * k + lane) : 0.f;
+#pragma unroll
+                for (int row = 0; row < ROWS; ++row) {
+                    const float wr = __shfl_sync(0xffffffffu, wgt, row);
+                    if (wr != 0.f) {
+#pragma unroll
+                        for (int k = 0; k < D / 32; ++k) acc[row][k] = fmaf(wr, v[row][k], acc[row][k]);
+                    }
                 }
             }
-            const int i = r / p.G, hh = r - i * p.G;
-            uint16_t* dst = (uint16_t*)p.out + ((long long)(rq.qs + i) * p.Hq + rq.head * p.G + hh) * D;
+        }
 #pragma unroll
-            for (int k = 0; k < D / 32; ++k) dst[32 * k + lane] = to_bits16<BF16>(den > 0.f ? acc[k] / den : 0.f);
+        for (int row = 0; row < ROWS; ++row) {
+            const float dr = __shfl_sync(0xffffffffu, den, row);
+            const int r = rq.row0 + row;
+            if (r < rq.rows) {
+                const int i = r / p.G, hh = r - i * p.G;
+                uint16_t* dst = (uint16_t*)p.out + ((long long)(rq.qs + i) * p.Hq + rq.head * p.G + hh) * D;
+#pragma unroll
+                for (int k = 0; k < D / 32; ++k) dst[32 * k + lane] = to_bits16<BF16>(dr > 0.f ? acc[row][k] / dr : 0.f);
+            }
         }
         if (lane == 0) *counter = 0;
     }
