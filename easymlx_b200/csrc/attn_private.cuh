@@ -412,7 +412,7 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
 #pragma unroll
                 for (int j = 0; j < NG; ++j) bw[j][nt][e] = FMT != 0 ? quad_column_sum(bsum[j][nt][e]) : 0.f;
             }
-        constexpr int PASSES = D / RC, MT_PER_PASS = RC / 16, QUADS = ROWS * RC / 4;
+        constexpr int PASSES = D / RC, MT_PER_PASS = RC / 16;
 #pragma unroll
         for (int pass = 0; pass < PASSES; ++pass) {
             consumer_sync();  // every warp has left its tile loop / the previous pass has been read
@@ -438,11 +438,11 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const int dl = 16 * mq + g + 8 * (c >> 1), row = 8 * nt + 2 * t + (c & 1);
-                        ored[(warp * ROWS + row) * RSTRIDE + dl] = o[mt][nt][c];
+                        if (row < rows_here) ored[(warp * ROWS + row) * RSTRIDE + dl] = o[mt][nt][c];
                     }
             }
             consumer_sync();
-            for (int q = tid; q < QUADS; q += kConsumerThreads) {
+            for (int q = tid; q < rows_here * (RC / 4); q += kConsumerThreads) {  // rows past the unit's last one hold nothing
                 const int row = q / (RC / 4), dl = 4 * (q - row * (RC / 4)), d = pass * RC + dl;
                 float M = -INFINITY;
 #pragma unroll
@@ -524,11 +524,14 @@ __device__ __forceinline__ void merge_warp_loop(const TiledParams& p, uint8_t* f
     uint64_t* mfull = full + 24;
     for (int e = 0; e < 2; ++e) {
         // the consumers may take their whole slice before they post: sleep between polls, give up after seconds
-        bool ok = false;
-        for (uint32_t i = 0; i < (1u << 22) && !ok && !*abort_word; ++i) {
-            ok = ptx::mbar_try_wait(&mfull[e], 0);
-            if (!ok) __nanosleep(i < 64 ? 200 : 2000);
+        int ok = 0;
+        if (lane == 0) {
+            for (uint32_t i = 0; i < (1u << 22) && !ok && !*abort_word; ++i) {
+                ok = ptx::mbar_try_wait(&mfull[e], 0) ? 1 : 0;
+                if (!ok) __nanosleep(i < 64 ? 200 : 2000);
+            }
         }
+        ok = __shfl_sync(0xffffffffu, ok, 0);  // one decision for the warp; the shuffle also orders the lanes' reads
         if (!ok) {
             if (!*abort_word) *abort_word = 1;
             if (lane == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
@@ -538,7 +541,8 @@ __device__ __forceinline__ void merge_warp_loop(const TiledParams& p, uint8_t* f
         if (rq.kind != 1) return;
         const long long a_flat = (long long)rq.cum_u * p.Hkv + (long long)rq.head * rq.ntiles;
         const long long b_flat = a_flat + rq.ntiles;
-        const int c_first = slice_owner(p.cta_start, active, a_flat), c_last = slice_owner(p.cta_start, active, b_flat - 1);
+        const int c_first = warp_last_true(0, active, lane, [&](int c) { return p.cta_start[c] <= a_flat; });
+        const int c_last = warp_last_true(0, active, lane, [&](int c) { return p.cta_start[c] <= b_flat - 1; });
         const int nparts = slices_in_use(p.cta_start, c_first, c_last);
         int* counter = p.counters + (size_t)rq.unit * p.Hkv + rq.head;
         __threadfence();  // the consumers' slot stores, seen through the barrier, become visible GPU-wide

@@ -41,6 +41,7 @@ struct TiledParams {
     const int32_t* unit_tile_lo;
     const int32_t* unit_cum;
     const int32_t* cta_start;  // [gridDim.x + 1] first flat tile of every CTA's slice
+    const int32_t* cta_unit;   // [gridDim.x + 1] a unit at or before the one holding that tile
     int32_t* counters;
     float* slots;
     int32_t* status;
@@ -102,6 +103,21 @@ struct Cfg {
     static_assert(STAGES >= 2, "shared memory holds fewer than two stages");
 };
 
+// Largest index in [lo, hi) for which the monotone predicate holds (it holds at lo), found by a whole warp: every
+// round probes 32 points at once, so a table of a few hundred entries takes two dependent loads instead of nine.
+template <typename Pred>
+__device__ __forceinline__ int warp_last_true(int lo, int hi, int lane, Pred holds) {
+    while (hi - lo > 1) {
+        const int step = (hi - lo + 31) / 32;
+        const int idx = lo + (lane + 1) * step;
+        const bool ok = idx < hi && holds(idx);
+        const int k = __popc(__ballot_sync(0xffffffffu, ok));
+        hi = min(hi, lo + (k + 1) * step);
+        lo = lo + k * step;
+    }
+    return lo;
+}
+
 // CTA whose slice holds flat tile f: the largest c with start[c] <= f (CTAs with empty slices are skipped by construction)
 __device__ __forceinline__ int slice_owner(const int32_t* start, int P, long long f) {
     int lo = 0, hi = P;
@@ -152,6 +168,16 @@ struct Walk {
         head = (int)(rem / ntiles);
         j = (int)(rem - (long long)head * ntiles);
     }
+    // the same result from a nearby unit: a step or two instead of a search
+    __device__ __forceinline__ void locate_near(long long f, int hint, const int32_t* cum, int num_units, int Hkv) {
+        u = min(max(hint, 0), num_units - 1);
+        while (u > 0 && (long long)cum[u] * Hkv > f) --u;
+        while (u + 1 < num_units && (long long)cum[u + 1] * Hkv <= f) ++u;
+        ntiles = cum[u + 1] - cum[u];
+        long long rem = f - (long long)cum[u] * Hkv;
+        head = (int)(rem / ntiles);
+        j = (int)(rem - (long long)head * ntiles);
+    }
     __device__ __forceinline__ void next_part(const int32_t* cum, int num_units, int Hkv) {
         j = 0;
         if (++head == Hkv) {
@@ -177,11 +203,12 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
     // Order of the slice's parts.  When the slice ends inside a unit, that unfinished part goes first: both parts
     // that need a merge with a neighbouring CTA are then done early and their merges run behind the other parts.
     long long range_lo[2] = {f_begin, f_begin}, range_hi[2] = {f_end, f_begin};
+    int range_hint[2] = {p.cta_unit[blockIdx.x], p.cta_unit[blockIdx.x]};
     if constexpr (C::PRIVATE) {
-        w.locate(f_end - 1, p.unit_cum, num_units, p.Hkv);
+        w.locate_near(f_end - 1, p.cta_unit[blockIdx.x + 1], p.unit_cum, num_units, p.Hkv);
         const long long a_last = (long long)p.unit_cum[w.u] * p.Hkv + (long long)w.head * w.ntiles;
         if (a_last + w.ntiles > f_end && a_last > f_begin) {
-            range_lo[0] = a_last; range_hi[0] = f_end;
+            range_lo[0] = a_last; range_hi[0] = f_end; range_hint[0] = w.u;
             range_lo[1] = f_begin; range_hi[1] = a_last;
         }
     }
@@ -189,12 +216,15 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
     for (int rg = 0; rg < 2; ++rg) {
     long long f = range_lo[rg];
     const long long f_stop = range_hi[rg];
-    if (f < f_stop) w.locate(f, p.unit_cum, num_units, p.Hkv);
+    if (f < f_stop) w.locate_near(f, range_hint[rg], p.unit_cum, num_units, p.Hkv);
     while (f < f_stop && !*abort_word) {
         const int seq = p.unit_seq[w.u];
         const int tile_lo = p.unit_tile_lo[w.u];
         const int kv_len = p.kv_lens[seq];
         const int run = (int)min((long long)(w.ntiles - w.j), f_stop - f);
+        // page ids of the part's first tiles: requested before the descriptor is built so that both latencies overlap
+        int page_first = -1;
+        if (lane < run && tile_lo + w.j + lane < p.MB) page_first = p.bt[(long long)seq * p.MB + tile_lo + w.j + lane];
         if constexpr (C::PRIVATE) {
             // descriptor + Q rows of this part, so that the consumers start it without touching global memory
             const uint32_t slot = part_idx % C::NDESC, use = part_idx / C::NDESC;
@@ -220,8 +250,11 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
         }
         for (int base = 0; base < run; base += 32) {
             const int idx = tile_lo + w.j + base + lane;
-            int page = -1;
-            if (base + lane < run && idx < p.MB) page = p.bt[(long long)seq * p.MB + idx];
+            int page = page_first;
+            if (base > 0) {
+                page = -1;
+                if (base + lane < run && idx < p.MB) page = p.bt[(long long)seq * p.MB + idx];
+            }
             const int cnt = min(32, run - base);
             for (int i = 0; i < cnt; ++i) {
                 int pg = __shfl_sync(0xffffffffu, page, i);
@@ -1031,6 +1064,7 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
         p.unit_seq = plan + L.unit_seq[c]; p.unit_row0 = plan + L.unit_row0[c];
         p.unit_tile_lo = plan + L.unit_tile_lo[c]; p.unit_cum = plan + L.unit_cum[c];
         p.cta_start = plan + L.cta_start[c];
+        p.cta_unit = plan + L.cta_unit[c];
         p.counters = (int32_t*)((uint8_t*)a->workspace + W.counter_off[c]);
         p.slots = (float*)((uint8_t*)a->workspace + W.slots_off);
         p.status = a->status;

@@ -19,6 +19,10 @@ constexpr int kTile = 128;        // tokens per KV tile = page size the tiled ke
 constexpr int kNumClasses = 4;
 constexpr int kPlanWideUnits = 1;  // plan flag: cut sequences with more than 32 rows into 128-row units (class 3)
 constexpr int kPlanHeaderWords = 16;
+// relative cost of a tile and of a part boundary when slices are cut: measured 1 : 2.3 on the 8-row decode kernel;
+// the 128-row kernel keeps 1 : 1.5
+constexpr long long kTileCost = 4;
+__host__ __device__ constexpr long long part_cost(int cls) { return cls == 3 ? 6 : 9; }
 constexpr int kMaxGrid = 256;     // upper bound on CTAs per launch, sizes the partial-result slots
 constexpr int kMaxRows = 32;      // rows of the largest class
 
@@ -34,6 +38,7 @@ struct PlanLayout {
     int unit_tile_lo[kNumClasses];
     int unit_cum[kNumClasses];  // cap + 1 words: exclusive prefix sum of tiles per unit (per KV head)
     int cta_start[kNumClasses]; // kMaxGrid + 1 words: first flat tile of every CTA's slice (cost-balanced)
+    int cta_unit[kNumClasses];  // kMaxGrid + 1 words: a unit at or before the one that holds that tile (search hint)
     int tmp;                    // S words of scratch for the scans
     int words;
 };
@@ -50,6 +55,7 @@ __host__ __device__ inline PlanLayout plan_layout(int S, int T, int Hq, int Hkv)
         L.unit_tile_lo[c] = w; w += L.cap[c];
         L.unit_cum[c] = w; w += L.cap[c] + 1;
         L.cta_start[c] = w; w += kMaxGrid + 1;
+        L.cta_unit[c] = w; w += kMaxGrid + 1;
     }
     L.tmp = w; w += (S > 0 ? S : 1);
     L.words = w;

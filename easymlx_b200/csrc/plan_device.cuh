@@ -61,7 +61,7 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
     for (int c = 0; c < kNumClasses; ++c) {
         if (c < class_lo || c > class_hi) {
             if (tid == 0) { plan[4 * c + 0] = 0; plan[4 * c + 1] = 0; }
-            for (int i = tid; i <= num_ctas; i += kMetaThreads) plan[L.cta_start[c] + i] = 0;
+            for (int i = tid; i <= num_ctas; i += kMetaThreads) { plan[L.cta_start[c] + i] = 0; plan[L.cta_unit[c] + i] = 0; }
             continue;
         }
         const int rows_c = class_rows(c);
@@ -122,27 +122,33 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
         }
         __syncthreads();  // unit_cum is complete; seq_off is reused by the next class
         const int32_t* cum = num_units < cum_cap ? cum_smem : unit_cum;
-        // slice boundaries: equal shares of cost = 2 per tile + 3 per (unit, head) part, in half-tile units
+        // slice boundaries: equal shares of cost, kTileCost per tile + kPartCost per (unit, head) part (measured on
+        // the 8-row decode kernel: a part boundary costs about as much as 2.3 tiles)
         for (int i = tid; i <= num_ctas; i += kMetaThreads) {
             long long start = (long long)tile_base * Hkv;
+            int first_unit = num_units;
+            const long long kPartCost = part_cost(c);
             if (i < num_ctas && num_units > 0) {
-                const long long total = (long long)Hkv * (2LL * tile_base + 3LL * num_units);
+                const long long total = (long long)Hkv * (kTileCost * tile_base + kPartCost * num_units);
                 const long long target = total * i / num_ctas;
                 int lo = 0, hi = num_units;  // largest u with cost_before(u) <= target
                 while (hi - lo > 1) {
                     const int mid = (lo + hi) >> 1;
-                    if ((long long)Hkv * (2LL * cum[mid] + 3LL * mid) <= target) lo = mid; else hi = mid;
+                    if ((long long)Hkv * (kTileCost * cum[mid] + kPartCost * mid) <= target) lo = mid; else hi = mid;
                 }
                 const int u = lo, nt = cum[u + 1] - cum[u];
-                const long long rem = target - (long long)Hkv * (2LL * cum[u] + 3LL * u);
-                const long long per_head = 2LL * nt + 3;
+                const long long rem = target - (long long)Hkv * (kTileCost * cum[u] + kPartCost * u);
+                const long long per_head = kTileCost * nt + kPartCost;
                 const int head = (int)min((long long)Hkv - 1, rem / per_head);
                 const long long r2 = rem - head * per_head;
-                const int j = r2 <= 3 ? 0 : (int)min((long long)nt, (r2 - 3 + 1) / 2);
+                const int j = r2 <= kPartCost ? 0 : (int)min((long long)nt, (r2 - kPartCost + kTileCost / 2) / kTileCost);
                 start = (long long)cum[u] * Hkv + (long long)head * nt + j;
+                first_unit = u;
             } else if (num_units == 0) {
                 start = 0;
+                first_unit = 0;
             }
+            plan[L.cta_unit[c] + i] = first_unit;
             plan[L.cta_start[c] + i] = (int)start;
         }
         __syncthreads();
