@@ -70,6 +70,13 @@ SIGNATURES = {
     "emlx_set_trace_buffer": (None, [_P]),
     "emlx_selftest_wait_timeout": (C.c_int, [_P, C.c_uint32, _P]),
     "emlx_attn_decode_static": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
+    "emlx_gather_last_tokens": (C.c_int, [_P, C.c_int32, C.c_int64, _P, C.c_int32, _P, _P, _P]),
+    "emlx_pad_token_ids": (C.c_int, [_P, C.c_int32, _P, C.c_int32, C.c_int32, _P, _P]),
+    "emlx_page_staging_bytes": (C.c_int64, [C.POINTER(Pool)]),
+    "emlx_copy_blocks": (C.c_int, [C.POINTER(Pool), _P, C.c_int32, _P, C.c_int64, _P, _P]),
+    "emlx_zero_pages": (C.c_int, [C.POINTER(Pool), _P, C.c_int32, _P]),
+    "emlx_rows_assign": (C.c_int, [_P, _P, C.c_int32, C.c_int32, C.c_int32, _P, C.c_int32, C.c_int32, _P]),
+    "emlx_rows_update": (C.c_int, [_P, _P, C.c_int32, C.c_int32, _P, C.c_int32, C.c_int32, _P, _P]),
 }
 
 _lib = None

@@ -380,6 +380,60 @@ class PageCacheView:
         for i in seq_indices:
             self.reset(int(i))
 
+    # ------------------------------------------------------------------ page maintenance
+    def _int32_on_device(self, values, cols: int | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
+        """(device int32 tensor, host copy or None when the caller passed a device tensor)."""
+        dev = self.key_cache.device
+        if isinstance(values, torch.Tensor) and values.is_cuda:
+            t = values.to(dtype=torch.int32).contiguous()
+            host = None
+        else:
+            host = torch.as_tensor(values, dtype=torch.int32).reshape(-1, cols) if cols else \
+                torch.as_tensor(values, dtype=torch.int32).reshape(-1)
+            t = host.to(dev)
+        return t, host
+
+    def copy_blocks(self, block_mapping, *, assume_independent: bool = False) -> None:
+        """Copy-on-write page copies (``caching/paged/cache.py:944-972``): ``block_mapping [num_pairs, 2]`` holds
+        ``(src_block, dst_block)`` rows; every destination receives its source as it was before the call.
+
+        A mapping given on the host is inspected: when no page is both read and written and no destination
+        repeats, one in-place launch does it.  Otherwise (or for a device-resident mapping, unless
+        ``assume_independent``) the pages go through a staging buffer in two launches."""
+        if isinstance(block_mapping, torch.Tensor):
+            if block_mapping.ndim != 2 or block_mapping.shape[1] != 2:
+                raise ValueError("block_mapping must be rank-2 with shape [num_pairs, 2]")
+        mapping, host = self._int32_on_device(block_mapping, cols=2)
+        if mapping.ndim != 2 or mapping.shape[1] != 2:
+            raise ValueError("block_mapping must be rank-2 with shape [num_pairs, 2]")
+        pairs = int(mapping.shape[0])
+        if pairs == 0:
+            return
+        independent = assume_independent
+        if host is not None:
+            src, dst = set(host[:, 0].tolist()), host[:, 1].tolist()
+            independent = len(set(dst)) == len(dst) and not (src & set(dst))
+        pool = self.native_pool()
+        lib = nv.lib()
+        dev = self.key_cache.device
+        staging, staging_bytes = None, 0
+        if not independent:
+            staging_bytes = pairs * int(lib.emlx_page_staging_bytes(pool))
+            staging = torch.empty(staging_bytes, dtype=torch.uint8, device=dev)
+        nv.check(lib.emlx_copy_blocks(pool, nv.ptr(mapping), pairs, nv.ptr(staging), staging_bytes, nv.ptr(self.status),
+                                      nv.stream_ptr(dev)))
+        if _CHECK:
+            self.check()
+
+    def zero_pages(self, page_ids) -> None:
+        """Zero the listed pages in every array of the pool; ids below zero or past the pool are skipped
+        (``inference/esurge/runners/model_runner.py:1058-1094``)."""
+        ids, _ = self._int32_on_device(page_ids)
+        if ids.numel() == 0:
+            return
+        dev = self.key_cache.device
+        nv.check(nv.lib().emlx_zero_pages(self.native_pool(), nv.ptr(ids), int(ids.numel()), nv.stream_ptr(dev)))
+
     def concatenate_to_cache(self, queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, *,
                              cache_metadata: tp.Any, rope: tp.Any = None,
                              slot_ids: tp.Sequence[int] | None = None,
@@ -486,6 +540,11 @@ class PageCache:
     def clear(self) -> None:
         for view in self.views:
             view.clear()
+
+    def copy_blocks(self, block_mapping) -> None:
+        """Copy pages in every layer's pool (``caching/paged/cache.py:1437-1445``)."""
+        for view in self.views:
+            view.copy_blocks(block_mapping)
 
 
 __all__ = ("PageCache", "PageCacheConfig", "PageCacheView", "PageMetadata", "build_query_start_loc")

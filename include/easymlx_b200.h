@@ -198,6 +198,48 @@ int emlx_attn_decode_static(const emlx_attn_args* args, const emlx_pool* pool, v
  * into *status and returns normally (nothing faults, the context stays usable). */
 int emlx_selftest_wait_timeout(int32_t* status, uint32_t poll_limit, void* stream);
 
+/* ---- batch and page-table maintenance on the device (no host synchronisation; bound by HBM or launch latency) ---- */
+
+/* out[s] = rows[query_start_loc[s+1] - 1] for s in [0, S): the last token's row of every sequence of a packed
+ * [T, row_bytes] array (hidden states).  Replaces _extract_last_tokens, modules/_base/causal_lm_module.py:176-207
+ * (take at qsl[1:] - 1; an index of -1 wraps to the last row as mx.take does).  An index outside [0, T) sets
+ * EMLX_DEV_TOKEN_MISMATCH in *status (may be NULL) and leaves that output row untouched. */
+int emlx_gather_last_tokens(const void* rows, int32_t total_tokens, int64_t row_bytes, const int32_t* query_start_loc,
+                            int32_t num_seqs, void* out, int32_t* status, void* stream);
+
+/* out[s, i] = i < len(s) ? flat_ids[query_start_loc[s] + i] : 0, out is int32 [S, max_query_len].  Replaces the
+ * compiled batch padder of inference/esurge/runners/model_runner.py:1250-1269. */
+int emlx_pad_token_ids(const int32_t* flat_ids, int32_t total_tokens, const int32_t* query_start_loc, int32_t num_seqs,
+                       int32_t max_query_len, int32_t* out, void* stream);
+
+/* Copy-on-write page copies: for every (src, dst) row of block_mapping [num_pairs, 2] (device, int32) copy page src to
+ * page dst in every array of the pool (codes, and scales / biases of an affine pool).  Replaces
+ * PageCacheView.copy_blocks, caching/paged/cache.py:944-972, whose kernel reads every source from the pool as it
+ * was before the call.  With `staging` (device, 16-byte aligned, num_pairs * emlx_page_staging_bytes(pool) bytes)
+ * the copy keeps exactly that meaning for any mapping (two launches through the staging area); with staging == NULL
+ * pages are copied in place in one launch, which is only equivalent when no page is both a source and a
+ * destination and no destination repeats.  A page id outside [0, NB) skips its pair and sets EMLX_DEV_BAD_PAGE. */
+int64_t emlx_page_staging_bytes(const emlx_pool* pool);
+int emlx_copy_blocks(const emlx_pool* pool, const int32_t* block_mapping, int32_t num_pairs, void* staging,
+                     int64_t staging_bytes, int32_t* status, void* stream);
+
+/* Zero pages page_ids[0..count) (device, int32) in every array of the pool; ids outside [0, NB) are skipped, as
+ * _zero_pages does (inference/esurge/runners/model_runner.py:1058-1094). */
+int emlx_zero_pages(const emlx_pool* pool, const int32_t* page_ids, int32_t count, void* stream);
+
+/* block_tables[row, :] = -1; block_tables[row, :count] = page_ids (device, count clipped to MB);
+ * kv_lens[row] = max(cached_tokens, 0).  Replaces _assign_row_mapping, model_runner.py:1096-1131; a row outside
+ * the table is EMLX_ERR_INVALID (the reference raises RuntimeError). */
+int emlx_rows_assign(int32_t* block_tables, int32_t* kv_lens, int32_t num_slots, int32_t max_blocks_per_seq, int32_t row,
+                     const int32_t* page_ids, int32_t count, int32_t cached_tokens, void* stream);
+
+/* Apply `count` row operations in order.  mode 0: ops is [count, 2] (from, to) and each pair moves row `from` onto
+ * row `to`, then clears `from` (table row = -1, length = 0): compact_rows, model_runner.py:1215-1241.  mode 1: each
+ * pair swaps the two rows: _move_cache_row, model_runner.py:1192-1213.  mode 2: ops is [count] rows to clear:
+ * _clear_row_mapping, model_runner.py:1010-1025.  Rows outside the table are skipped and set EMLX_DEV_BAD_SLOT. */
+int emlx_rows_update(int32_t* block_tables, int32_t* kv_lens, int32_t num_slots, int32_t max_blocks_per_seq,
+                     const int32_t* ops, int32_t count, int32_t mode, int32_t* status, void* stream);
+
 /* Tracing aid: when `records` is a device buffer of 4 * 256 int64, every CTA of the tiled attention kernels
  * writes {start ns, end ns, tiles processed, 0} (GPU global timer) at index 4 * blockIdx.x; NULL turns it off. */
 void emlx_set_trace_buffer(int64_t* records);

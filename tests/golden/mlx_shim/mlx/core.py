@@ -164,6 +164,22 @@ def maximum(a, b):
     return array(np.maximum(_raw(a), _raw(b)))
 
 
+def minimum(a, b):
+    return array(np.minimum(_raw(a), _raw(b)))
+
+
+def take(a, indices, axis=None):
+    return array(np.take(_raw(a), _raw(indices), axis=axis))
+
+
+def cumsum(a, axis=None):
+    return array(np.cumsum(_raw(a), axis=axis))
+
+
+def compile(fn, *_, **__):
+    return fn
+
+
 def where(cond, a, b):
     return array(np.where(_raw(cond), _raw(a), _raw(b)))
 
