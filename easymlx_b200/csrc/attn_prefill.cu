@@ -32,6 +32,7 @@ struct PrefillParams {
     const int32_t* unit_row0;
     const int32_t* unit_tile_lo;
     const int32_t* unit_cum;
+    const int32_t* unit_order;  // units by decreasing number of tiles
     int32_t* status;
     long long num_blocks;
     int Hq, Hkv, G, MB, window;
@@ -160,6 +161,16 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
     const int num_units = p.hdr[0];
     const long long items = (long long)num_units * p.Hkv;
     if ((long long)blockIdx.x >= items) return;  // uniform, before any barrier or TMEM allocation
+    // Items (unit, head) are dealt out in the order of decreasing length, back and forth over the CTAs (round k goes
+    // 0..P-1 when k is even and P-1..0 when it is odd), which keeps the CTAs' totals within about one item.
+    auto item_of = [&](uint32_t k, int& u, int& head) -> bool {
+        const long long P = gridDim.x;
+        const long long idx = (long long)k * P + ((k & 1) ? P - 1 - blockIdx.x : blockIdx.x);
+        if (idx >= items) return false;
+        u = p.unit_order[idx / p.Hkv];
+        head = (int)(idx % p.Hkv);
+        return true;
+    };
 
     if (tid == 0) {
         ptx::mbar_init(&bars->q_full, 1);
@@ -190,8 +201,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
     if (warp == 4) {
         // ------------------------------------------------------------------ TMA producer
         uint32_t kt = 0, k = 0;
-        for (long long item = blockIdx.x; item < items && !*abort_word; item += gridDim.x, ++k) {
-            const int u = (int)(item / p.Hkv), head = (int)(item - (long long)u * p.Hkv);
+        int u, head;
+        for (; item_of(k, u, head) && !*abort_word; ++k) {
             const int seq = p.unit_seq[u], row0 = p.unit_row0[u], tile_lo = p.unit_tile_lo[u];
             const int ntiles = p.unit_cum[u + 1] - p.unit_cum[u];
             const int qs = p.qsl[seq], kv_len = p.kv_lens[seq];
@@ -237,8 +248,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
         constexpr uint32_t idesc_pv = instr_desc(128, D, BF16, true);
         const uint32_t q_addr = ptx::smem_u32(q_smem), p_addr = ptx::smem_u32(p_smem);
         uint32_t kt = 0, k = 0;
-        for (long long item = blockIdx.x; item < items && !*abort_word; item += gridDim.x, ++k) {
-            const int u = (int)(item / p.Hkv);
+        int u, head;
+        for (; item_of(k, u, head) && !*abort_word; ++k) {
             const int ntiles = p.unit_cum[u + 1] - p.unit_cum[u];
             ptx::mbar_wait(&bars->q_full, k & 1, abort_word);
             tc_fence_after();
@@ -287,8 +298,8 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
         const int r = tid;
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         uint32_t kt = 0;
-        for (long long item = blockIdx.x; item < items; item += gridDim.x) {
-            const int u = (int)(item / p.Hkv), head = (int)(item - (long long)u * p.Hkv);
+        int u, head;
+        for (uint32_t k = 0; item_of(k, u, head); ++k) {
             const int seq = p.unit_seq[u], row0 = p.unit_row0[u], tile_lo = p.unit_tile_lo[u];
             const int ntiles = p.unit_cum[u + 1] - p.unit_cum[u];
             const int qs = p.qsl[seq], q_len = p.qsl[seq + 1] - qs, kv_len = p.kv_lens[seq];
@@ -473,8 +484,8 @@ static int launch_pf(const CUtensorMap& qmap, const MapPair& maps, const Prefill
 }
 
 int launch_prefill(const emlx_attn_args* a, const emlx_pool* pool, const int32_t* plan_class_hdr, const int32_t* unit_seq,
-                   const int32_t* unit_row0, const int32_t* unit_tile_lo, const int32_t* unit_cum, const MapPair& maps,
-                   cudaStream_t stream) {
+                   const int32_t* unit_row0, const int32_t* unit_tile_lo, const int32_t* unit_cum, const int32_t* unit_order,
+                   const MapPair& maps, cudaStream_t stream) {
     const int D = pool->head_dim, Hq = a->num_q_heads, Hkv = pool->num_kv_heads, G = Hq / Hkv;
     if (!prefill_supported(pool->kv_format, Hq, Hkv, D))
         return fail(EMLX_ERR_UNSUPPORTED, "the tcgen05 prefill kernel needs an fp16/bf16 pool, head_dim 64/128 and 128 %% (Hq/Hkv) == 0");
@@ -482,7 +493,7 @@ int launch_prefill(const emlx_attn_args* a, const emlx_pool* pool, const int32_t
     if (int rc = make_q_map(a, D, G, &qmap)) return rc;
     PrefillParams p;
     p.out = a->out; p.bt = a->block_tables; p.kv_lens = a->kv_lens; p.qsl = a->query_start_loc;
-    p.hdr = plan_class_hdr; p.unit_seq = unit_seq; p.unit_row0 = unit_row0; p.unit_tile_lo = unit_tile_lo; p.unit_cum = unit_cum;
+    p.hdr = plan_class_hdr; p.unit_seq = unit_seq; p.unit_row0 = unit_row0; p.unit_tile_lo = unit_tile_lo; p.unit_cum = unit_cum; p.unit_order = unit_order;
     p.status = a->status; p.num_blocks = pool->num_blocks;
     p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.MB = a->max_blocks_per_seq; p.window = a->sliding_window;
     p.scale_log2e = a->softmax_scale * 1.4426950408889634f;

@@ -1054,7 +1054,8 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
     for (int c = lo; c <= hi; ++c) {
         if (c == 3) {
             if (int rc = launch_prefill(a, pool, plan + 4 * c, plan + L.unit_seq[c], plan + L.unit_row0[c],
-                                        plan + L.unit_tile_lo[c], plan + L.unit_cum[c], *maps, (cudaStream_t)stream))
+                                        plan + L.unit_tile_lo[c], plan + L.unit_cum[c], plan + L.unit_order, *maps,
+                                        (cudaStream_t)stream))
                 return rc;
             continue;
         }

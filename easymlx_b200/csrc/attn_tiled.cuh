@@ -39,6 +39,7 @@ struct PlanLayout {
     int unit_cum[kNumClasses];  // cap + 1 words: exclusive prefix sum of tiles per unit (per KV head)
     int cta_start[kNumClasses]; // kMaxGrid + 1 words: first flat tile of every CTA's slice (cost-balanced)
     int cta_unit[kNumClasses];  // kMaxGrid + 1 words: a unit at or before the one that holds that tile (search hint)
+    int unit_order;             // class 3 only, cap words: units by decreasing number of tiles
     int tmp;                    // S words of scratch for the scans
     int words;
 };
@@ -57,6 +58,7 @@ __host__ __device__ inline PlanLayout plan_layout(int S, int T, int Hq, int Hkv)
         L.cta_start[c] = w; w += kMaxGrid + 1;
         L.cta_unit[c] = w; w += kMaxGrid + 1;
     }
+    L.unit_order = w; w += L.cap[3];
     L.tmp = w; w += (S > 0 ? S : 1);
     L.words = w;
     return L;

@@ -7,6 +7,7 @@
 
 namespace emlx {
 
+constexpr int kOrderBins = 1024;  // tile-count bins of the class-3 unit order (longer units share the last bin)
 
 // Exclusive prefix of one value per thread across the CTA; `total` receives the CTA-wide sum.
 __device__ __forceinline__ int block_scan_value(int v, int32_t* smem /* [33] */, int& total) {
@@ -121,6 +122,26 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
             plan[4 * c + 1] = tile_base;
         }
         __syncthreads();  // unit_cum is complete; seq_off is reused by the next class
+        if (c == 3) {
+            // the 128-row kernel hands whole (unit, head) items to its CTAs: list the units by decreasing number of
+            // tiles (counting sort; the order among equals does not matter) so that dealing them out stays balanced
+            __shared__ int32_t bins[kOrderBins];
+            int32_t* order = plan + L.unit_order;
+            for (int b = tid; b < kOrderBins; b += kMetaThreads) bins[b] = 0;
+            __syncthreads();
+            for (int u = tid; u < num_units; u += kMetaThreads)
+                atomicAdd(&bins[kOrderBins - 1 - min(unit_cum[u + 1] - unit_cum[u], kOrderBins - 1)], 1);
+            __syncthreads();
+            static_assert(kOrderBins == kMetaThreads, "one bin per thread");
+            int n_total;
+            const int first = block_scan_value(bins[tid], scan_smem, n_total);
+            __syncthreads();
+            bins[tid] = first;
+            __syncthreads();
+            for (int u = tid; u < num_units; u += kMetaThreads)
+                order[atomicAdd(&bins[kOrderBins - 1 - min(unit_cum[u + 1] - unit_cum[u], kOrderBins - 1)], 1)] = u;
+            __syncthreads();
+        }
         const int32_t* cum = num_units < cum_cap ? cum_smem : unit_cum;
         // slice boundaries: equal shares of cost, kTileCost per tile + kPartCost per (unit, head) part (measured on
         // the 8-row decode kernel: a part boundary costs about as much as 2.3 tiles)
