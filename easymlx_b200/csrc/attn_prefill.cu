@@ -4,13 +4,11 @@
 // one KV head; the plan lists the KV tiles (128-token pages) the rows may attend.  Per tile
 //     S[128 rows x 128 tokens]  = Q . K^T     tcgen05.mma, both operands K-major in shared memory (TMA, 128B swizzle),
 //                                             fp32 accumulator in TMEM columns [0, 128)
-//     softmax                                  eight warps: a row (= one TMEM lane) is shared by two threads, one per half of
-//                                             the tile's 128 columns, which trade their row maxima through shared memory;
+//     softmax                                  four warps, one TMEM lane (= one row) per thread: no cross-thread reduction;
 //                                             P is written to shared memory as the next A operand
 //     O_tile[128 rows x D]      = P . V        tcgen05.mma, V read in place as an MN-major B operand, TMEM columns [128, 128+D)
 //     O = O * corr + O_tile                    in registers of the softmax threads
-// Warp roles: 0-7 softmax (warp w and w + 4 share TMEM lanes 32 (w % 4) ..), 8 TMA producer, 9 MMA issuer (and TMEM
-// owner).  All waits are bounded.
+// Warp roles: 0-3 softmax, 4 TMA producer, 5 MMA issuer (and TMEM owner).  All waits are bounded.
 #include "plan_device.cuh"
 #include "ptx.cuh"
 #include "tensor_maps.cuh"
@@ -21,8 +19,7 @@
 
 namespace emlx {
 
-constexpr int kPfThreads = 320;
-constexpr int kPfSoftmaxThreads = 256;
+constexpr int kPfThreads = 192;
 constexpr int kPfRows = 128;
 
 struct PrefillParams {
@@ -55,7 +52,7 @@ struct PfCfg {
     static constexpr int OFF_K = OFF_P + PBYTES;
     static constexpr int OFF_V = OFF_K + KST * KBYTES;
     static constexpr int OFF_BAR = OFF_V + VST * KBYTES;
-    static constexpr int SMEM = OFF_BAR + 3072;  // the 1024-byte aligned base is asked of the compiler, not padded for
+    static constexpr int SMEM = OFF_BAR + 256 + 1024;
     static constexpr int TMEM_COLS = 512;  // S (two buffers): columns [0,128) and [128,256); O: [256, 256 + D)
 };
 
@@ -142,24 +139,15 @@ struct PfBarriers {
     uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
     uint32_t tmem_base;
     int abort_word;
-    // [exchange parity][column half][row]: what the two threads of a row trade (the tile's row maximum; at the end of
-    // an item the partial row sum).  Successive exchanges alternate between the two buffers, so a value is always
-    // read before the slot is written again.
-    float xchg[2][2][kPfRows];
 };
-static_assert(sizeof(PfBarriers) <= 3072, "barrier block outgrew its share of shared memory");
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kPfThreads, 1)
 attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_constant__ CUtensorMap kmap,
                     const __grid_constant__ CUtensorMap vmap, const PrefillParams p) {
     using C = PfCfg<D>;
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    uint8_t* smem = smem_raw;
-    if (((uintptr_t)smem_raw & 1023) != 0) {  // the swizzled tiles need it; uniform for the CTA, nothing is pending yet
-        if (threadIdx.x == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
-        return;
-    }
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_smem = smem + C::OFF_Q;
     uint8_t* p_smem = smem + C::OFF_P;
     uint8_t* k_smem = smem + C::OFF_K;
@@ -186,10 +174,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
 
     if (tid == 0) {
         ptx::mbar_init(&bars->q_full, 1);
-        ptx::mbar_init(&bars->item_done, kPfSoftmaxThreads);
+        ptx::mbar_init(&bars->item_done, 128);
         ptx::mbar_init(&bars->s_ready[0], 1);
         ptx::mbar_init(&bars->s_ready[1], 1);
-        ptx::mbar_init(&bars->p_ready, kPfSoftmaxThreads);
+        ptx::mbar_init(&bars->p_ready, 128);
         ptx::mbar_init(&bars->o_ready, 1);
         for (int s = 0; s < 4; ++s) {
             ptx::mbar_init(&bars->k_full[s], 1);
@@ -203,14 +191,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
         ptx::prefetch_tensormap(&kmap);
         ptx::prefetch_tensormap(&vmap);
     }
-    if (warp == 9) tmem_alloc(&bars->tmem_base, C::TMEM_COLS);
+    if (warp == 5) tmem_alloc(&bars->tmem_base, C::TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
     const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256;
 
-    if (warp == 8) {
+    if (warp == 4) {
         // ------------------------------------------------------------------ TMA producer
         uint32_t kt = 0, k = 0;
         int u, head;
@@ -254,7 +242,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 }
             }
         }
-    } else if (warp == 9) {
+    } else if (warp == 5) {
         // ------------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc_qk = instr_desc(128, 128, BF16, false);
         constexpr uint32_t idesc_pv = instr_desc(128, D, BF16, true);
@@ -306,13 +294,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             }
         }
     } else {
-        // ------------------------------------------------------------------ softmax: two threads per row
-        constexpr int HC = kTile / 2;  // score columns per thread
-        constexpr int OC = D / 2;      // output columns per thread
-        const int r = tid & (kPfRows - 1), half = tid >> 7;
-        const int pair_bar = 1 + (warp & 3);  // named barrier of the two warps that share this warp's rows
-        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-        uint32_t kt = 0, xk = 0;  // tiles consumed, exchanges done
+        // ------------------------------------------------------------------ softmax: one row per thread
+        const int r = tid;
+        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        uint32_t kt = 0;
         int u, head;
         for (uint32_t k = 0; item_of(k, u, head); ++k) {
             const int seq = p.unit_seq[u], row0 = p.unit_row0[u], tile_lo = p.unit_tile_lo[u];
@@ -329,8 +314,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             const int lo_max = p.window > 0 ? max(0, min(kv_len - 1, ctx + i_last) - p.window + 1) : 0;
 
             // m_ref is the maximum the stored probabilities and O refer to; it follows the true running maximum
-            // lazily (only when that grew by more than 2^8), so O in TMEM is rarely rescaled.  l is this thread's
-            // share of the row sum (its columns only).
+            // lazily (only when that grew by more than 2^8), so O in TMEM is rarely rescaled
             float m_ref = -INFINITY, l = 0.f;
 
             for (int j = 0; j < ntiles; ++j, ++kt) {
@@ -338,28 +322,22 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 const bool interior = (t0 + kTile <= hi_min) && (t0 >= lo_max);
                 ptx::mbar_wait(&bars->s_ready[kt & 1], (kt >> 1) & 1, abort_word);
                 tc_fence_after();
-                uint32_t sv[HC];
+                uint32_t sv[128];
 #pragma unroll
-                for (int c4 = 0; c4 < HC / 32; ++c4)
-                    tmem_ld32_nowait(tmem_S + (kt & 1) * 128 + lane_addr + HC * half + 32 * c4, sv + 32 * c4);
+                for (int c4 = 0; c4 < 4; ++c4) tmem_ld32_nowait(tmem_S + (kt & 1) * 128 + lane_addr + 32 * c4, sv + 32 * c4);
                 tmem_wait_ld();
                 float mx = -INFINITY;
                 if (interior) {
 #pragma unroll
-                    for (int i = 0; i < HC; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
+                    for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
                 } else {
 #pragma unroll
-                    for (int i = 0; i < HC; ++i) {
-                        const int tok = t0 + HC * half + i;
+                    for (int i = 0; i < 128; ++i) {
+                        const int tok = t0 + i;
                         if (tok < lo || tok >= hi) sv[i] = 0xff800000u;  // -inf
                         mx = fmaxf(mx, __uint_as_float(sv[i]));
                     }
                 }
-                // the row's other half
-                bars->xchg[xk & 1][half][r] = mx;
-                ptx::named_barrier(pair_bar, 64);
-                mx = fmaxf(mx, bars->xchg[xk & 1][half ^ 1][r]);
-                ++xk;
                 const float m_new = mx * p.scale_log2e;
                 const bool grow = (j == 0) ? true : (m_new > m_ref + 8.0f);
                 float corr = 1.0f;
@@ -374,68 +352,62 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                     tc_fence_after();
                     if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-                        for (int c4 = 0; c4 < OC / 32; ++c4) {
+                        for (int c4 = 0; c4 < D / 32; ++c4) {
                             uint32_t ov[32];
-                            tmem_ld32_nowait(tmem_O + lane_addr + OC * half + 32 * c4, ov);
+                            tmem_ld32_nowait(tmem_O + lane_addr + 32 * c4, ov);
                             tmem_wait_ld();
 #pragma unroll
                             for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
-                            tmem_st32(tmem_O + lane_addr + OC * half + 32 * c4, ov);
+                            tmem_st32(tmem_O + lane_addr + 32 * c4, ov);
                         }
                         l *= corr;
                     }
                 }
                 const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;
                 const float neg_m = -m_safe;
-                float ls0 = 0.f, ls1 = 0.f;
+                float lsum = 0.f;
 #pragma unroll
-                for (int c16 = 0; c16 < HC / 8; ++c16) {
+                for (int c16 = 0; c16 < 16; ++c16) {
                     uint32_t packed[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         float p0, p1;
                         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(sv[8 * c16 + 2 * e]), p.scale_log2e, neg_m)));
                         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(sv[8 * c16 + 2 * e + 1]), p.scale_log2e, neg_m)));
-                        ls0 += p0;
-                        ls1 += p1;
+                        lsum += p0 + p1;
                         if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
                         else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
                     }
-                    // columns [64 half, 64 half + 64) of P are the half-th 128-byte block of the row
-                    uint8_t* dst = p_smem + half * (kPfRows * 128) + r * 128 + ((c16 ^ (r & 7)) << 4);
+                    uint8_t* dst = p_smem + (c16 >> 3) * (kPfRows * 128) + r * 128 + (((c16 & 7) ^ (r & 7)) << 4);
                     *(uint4*)dst = make_uint4(packed[0], packed[1], packed[2], packed[3]);
                 }
-                l += ls0 + ls1;
+                l += lsum;
                 if (t0 + kTile > kv_len) {
-                    // token rows of V past the sequence end are stale memory: clear them (threads (r, half) share token r)
+                    // token rows of V past the sequence end are stale memory: clear them (thread r owns token r)
                     ptx::mbar_wait(&bars->v_full[kt % C::VST], (kt / C::VST) & 1, abort_word);
                     if (r >= max(0, kv_len - t0)) {
                         uint8_t* vrow = v_smem + (size_t)(kt % C::VST) * C::KBYTES + r * 128;
 #pragma unroll
                         for (int h = 0; h < C::HALVES; ++h)
 #pragma unroll
-                            for (int c = 0; c < 4; ++c) *(uint4*)(vrow + h * (kTile * 128) + (4 * half + c) * 16) = make_uint4(0u, 0u, 0u, 0u);
+                            for (int c = 0; c < 8; ++c) *(uint4*)(vrow + h * (kTile * 128) + c * 16) = make_uint4(0u, 0u, 0u, 0u);
                     }
                 }
                 ptx::fence_proxy_async();
                 tc_fence_before();
                 ptx::mbar_arrive(&bars->p_ready);
             }
-            // the row's sum: both halves, then the last PV, then this thread's columns of O
-            bars->xchg[xk & 1][half][r] = l;
-            ptx::named_barrier(pair_bar, 64);
-            l += bars->xchg[xk & 1][half ^ 1][r];
-            ++xk;
+            // the last PV, then this row of O
             ptx::mbar_wait(&bars->o_ready, (kt - 1) & 1, abort_word);
             tc_fence_after();
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             const bool store = row0 + r < R;
             const int oi = (row0 + r) / p.G, ohh = (row0 + r) - oi * p.G;
-            uint4* dst = (uint4*)((uint16_t*)p.out + ((long long)(qs + oi) * p.Hq + head * p.G + ohh) * D + OC * half);
+            uint4* dst = (uint4*)((uint16_t*)p.out + ((long long)(qs + oi) * p.Hq + head * p.G + ohh) * D);
 #pragma unroll 1
-            for (int c4 = 0; c4 < OC / 32; ++c4) {
+            for (int c4 = 0; c4 < D / 32; ++c4) {
                 uint32_t ov[32];
-                tmem_ld32_nowait(tmem_O + lane_addr + OC * half + 32 * c4, ov);
+                tmem_ld32_nowait(tmem_O + lane_addr + 32 * c4, ov);
                 tmem_wait_ld();
                 if (store) {
 #pragma unroll
@@ -457,7 +429,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if (warp == 5) tmem_dealloc(tmem_base, C::TMEM_COLS);
     if (*abort_word && tid == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
 }
 
