@@ -5,8 +5,9 @@
 //     S[128 rows x 128 tokens]  = Q . K^T     tcgen05.mma, both operands K-major in shared memory (TMA, 128B swizzle),
 //                                             fp32 accumulator in TMEM columns [0, 128)
 //     softmax                                  four warps, one TMEM lane (= one row) per thread: no cross-thread reduction;
-//                                             P is written to shared memory as the next A operand
-//     O_tile[128 rows x D]      = P . V        tcgen05.mma, V read in place as an MN-major B operand, TMEM columns [128, 128+D)
+//                                             P goes back to TMEM (16-bit, two per column) as the next A operand, so the
+//                                             shared-memory port only carries K and V
+//     O_tile[128 rows x D]      = P . V        tcgen05.mma with A from TMEM, V read in place as an MN-major B operand
 //     O = O * corr + O_tile                    in registers of the softmax threads
 // Warp roles: 0-3 softmax, 4 TMA producer, 5 MMA issuer (and TMEM owner).  All waits are bounded.
 #include "plan_device.cuh"
@@ -44,16 +45,14 @@ struct PfCfg {
     static constexpr int HALVES = D / 64;
     static constexpr int QBYTES = kPfRows * D * 2;
     static constexpr int KBYTES = kTile * D * 2;
-    static constexpr int PBYTES = kPfRows * kTile * 2;
     static constexpr int KST = D == 128 ? 3 : 4;  // K tiles are needed one tile ahead of V (QK of tile j+1 precedes PV of tile j)
-    static constexpr int VST = D == 128 ? 2 : 4;
+    static constexpr int VST = D == 128 ? 3 : 4;
     static constexpr int OFF_Q = 0;
-    static constexpr int OFF_P = QBYTES;
-    static constexpr int OFF_K = OFF_P + PBYTES;
+    static constexpr int OFF_K = OFF_Q + QBYTES;
     static constexpr int OFF_V = OFF_K + KST * KBYTES;
     static constexpr int OFF_BAR = OFF_V + VST * KBYTES;
     static constexpr int SMEM = OFF_BAR + 256 + 1024;
-    static constexpr int TMEM_COLS = 512;  // S (two buffers): columns [0,128) and [128,256); O: [256, 256 + D)
+    static constexpr int TMEM_COLS = 512;  // S (two buffers): columns [0,128) and [128,256); O: [256, 256 + D); P: [384, 448)
 };
 
 // ------------------------------------------------------------------ tcgen05 wrappers
@@ -76,6 +75,14 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
+        : "memory");
+}
+// A operand read from tensor memory (row = lane, two 16-bit elements of the contraction axis per 32-bit column)
+__device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
         : "memory");
 }
 // 32 consecutive fp32 columns of this thread's TMEM lane
@@ -149,7 +156,6 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint8_t* q_smem = smem + C::OFF_Q;
-    uint8_t* p_smem = smem + C::OFF_P;
     uint8_t* k_smem = smem + C::OFF_K;
     uint8_t* v_smem = smem + C::OFF_V;
     PfBarriers* bars = (PfBarriers*)(smem + C::OFF_BAR);
@@ -196,7 +202,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
-    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256;
+    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256, tmem_P = tmem_base + 384;
 
     if (warp == 4) {
         // ------------------------------------------------------------------ TMA producer
@@ -246,7 +252,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
         // ------------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc_qk = instr_desc(128, 128, BF16, false);
         constexpr uint32_t idesc_pv = instr_desc(128, D, BF16, true);
-        const uint32_t q_addr = ptx::smem_u32(q_smem), p_addr = ptx::smem_u32(p_smem);
+        const uint32_t q_addr = ptx::smem_u32(q_smem);
         uint32_t kt = 0, k = 0;
         int u, head;
         for (; item_of(k, u, head) && !*abort_word; ++k) {
@@ -283,9 +289,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 if (lane == 0 && !*abort_word) {
 #pragma unroll
                     for (int kk = 0; kk < kTile / 16; ++kk) {
-                        const uint32_t poff = (kk >> 2) * (kPfRows * 128) + (kk & 3) * 32;
-                        tc_mma_f16(tmem_O, smem_desc(p_addr + poff, 16, 1024),
-                                   smem_desc(v_addr + kk * (16 * 128), kTile * 128, 1024), idesc_pv, j > 0 || kk > 0);
+                        // 16 tokens of P = 8 packed columns of TMEM
+                        tc_mma_f16_ts(tmem_O, tmem_P + kk * 8, smem_desc(v_addr + kk * (16 * 128), kTile * 128, 1024), idesc_pv,
+                                      j > 0 || kk > 0);
                     }
                     tc_commit(&bars->o_ready);
                     tc_commit(&bars->v_empty[stage]);
@@ -365,22 +371,23 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 }
                 const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;
                 const float neg_m = -m_safe;
-                float lsum = 0.f;
+                float ls0 = 0.f, ls1 = 0.f;
 #pragma unroll
-                for (int c16 = 0; c16 < 16; ++c16) {
-                    uint32_t packed[4];
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t packed[32];
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
+                    for (int e = 0; e < 32; ++e) {
                         float p0, p1;
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(sv[8 * c16 + 2 * e]), p.scale_log2e, neg_m)));
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(sv[8 * c16 + 2 * e + 1]), p.scale_log2e, neg_m)));
-                        lsum += p0 + p1;
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(sv[64 * h + 2 * e]), p.scale_log2e, neg_m)));
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(sv[64 * h + 2 * e + 1]), p.scale_log2e, neg_m)));
+                        ls0 += p0;
+                        ls1 += p1;
                         if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
                         else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
                     }
-                    uint8_t* dst = p_smem + (c16 >> 3) * (kPfRows * 128) + r * 128 + (((c16 & 7) ^ (r & 7)) << 4);
-                    *(uint4*)dst = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                    tmem_st32(tmem_P + lane_addr + 32 * h, packed);  // tokens [64h, 64h + 64) of this row
                 }
+                const float lsum = ls0 + ls1;
                 l += lsum;
                 if (t0 + kTile > kv_len) {
                     // token rows of V past the sequence end are stale memory: clear them (thread r owns token r)
