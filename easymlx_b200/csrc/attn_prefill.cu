@@ -20,6 +20,12 @@
 
 namespace emlx {
 
+#ifdef EMLX_TRACE_PREFILL
+#define PF_STAMP(cond, tile, slot) do { if (p.trace && blockIdx.x == 0 && (cond) && (tile) < 256) p.trace[(tile) * 8 + (slot)] = clock64(); } while (0)
+#else
+#define PF_STAMP(cond, tile, slot) do { } while (0)
+#endif
+
 constexpr int kPfThreads = 192;
 constexpr int kPfRows = 128;
 
@@ -35,6 +41,7 @@ struct PrefillParams {
     const int32_t* unit_cum;
     const int32_t* unit_order;  // units by decreasing number of tiles
     int32_t* status;
+    long long* trace;  // measurement aid (only with EMLX_TRACE_PREFILL): per-tile cycle stamps of CTA 0
     long long num_blocks;
     int Hq, Hkv, G, MB, window;
     float scale_log2e;
@@ -52,7 +59,7 @@ struct PfCfg {
     static constexpr int OFF_V = OFF_K + KST * KBYTES;
     static constexpr int OFF_BAR = OFF_V + VST * KBYTES;
     static constexpr int SMEM = OFF_BAR + 256 + 1024;
-    static constexpr int TMEM_COLS = 512;  // S (two buffers): columns [0,128) and [128,256); O: [256, 256 + D); P: [384, 448)
+    static constexpr int TMEM_COLS = 512;  // S (two buffers): columns [0,128) and [128,256); O: [256, 256 + D); Q: [384, 384 + D/2); P of a tile overwrites the first 64 columns of its S
 };
 
 // ------------------------------------------------------------------ tcgen05 wrappers
@@ -142,8 +149,13 @@ __host__ __device__ constexpr uint32_t instr_desc(int M, int N, bool bf16, bool 
 }
 
 struct PfBarriers {
-    uint64_t q_full, item_done, s_ready[2], p_ready, o_ready;  // o_ready: PV of a tile complete
-    uint64_t k_full[4], k_empty[4], v_full[4], v_empty[4];
+    // q_tmem: Q copied to TMEM.  qk_done[t & 3] / pv_done[t & 3]: the QK / PV product of tile t is complete; each is
+    // committed once and read by two parties (QK: the softmax warps, for S, and the producer, for the K slot; PV: the
+    // softmax warps, for O, and the producer, for the V slot) because a commit costs the issuing thread as much as an
+    // MMA.  Four barriers each, so that no waiter can fall two phases behind the barrier it waits on.
+    // p_ready[t & 1]: P of tile t written over its S.
+    uint64_t q_full, q_tmem, item_done, qk_done[4], p_ready[2], pv_done[4];
+    uint64_t k_full[4], v_full[4];
     uint32_t tmem_base;
     int abort_word;
 };
@@ -180,16 +192,15 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
 
     if (tid == 0) {
         ptx::mbar_init(&bars->q_full, 1);
+        ptx::mbar_init(&bars->q_tmem, 128);
         ptx::mbar_init(&bars->item_done, 128);
-        ptx::mbar_init(&bars->s_ready[0], 1);
-        ptx::mbar_init(&bars->s_ready[1], 1);
-        ptx::mbar_init(&bars->p_ready, 128);
-        ptx::mbar_init(&bars->o_ready, 1);
+        ptx::mbar_init(&bars->p_ready[0], 128);
+        ptx::mbar_init(&bars->p_ready[1], 128);
         for (int s = 0; s < 4; ++s) {
+            ptx::mbar_init(&bars->qk_done[s], 1);
+            ptx::mbar_init(&bars->pv_done[s], 1);
             ptx::mbar_init(&bars->k_full[s], 1);
-            ptx::mbar_init(&bars->k_empty[s], 1);
             ptx::mbar_init(&bars->v_full[s], 1);
-            ptx::mbar_init(&bars->v_empty[s], 1);
         }
         bars->abort_word = 0;
         ptx::fence_barrier_init();
@@ -202,7 +213,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
-    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256, tmem_P = tmem_base + 384;
+    const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256, tmem_Q = tmem_base + 384;
 
     if (warp == 4) {
         // ------------------------------------------------------------------ TMA producer
@@ -219,62 +230,89 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 for (int h = 0; h < C::HALVES; ++h)
                     ptx::tma_load_3d(q_smem + h * (kPfRows * 128), &qmap, &bars->q_full, 64 * h, head * p.G, qs + row0 / p.G);
             }
-            for (int base = 0; base < ntiles; base += 32) {
+            // K runs two tiles ahead of V: the K slot of tile t is free as soon as QK of tile t - 3 is done, long before
+            // the V slot that PV of tile t - 3 still reads, and one warp issuing both in step would hold K back
+            auto load_pages = [&](int base) -> int {
                 const int idx = tile_lo + base + lane;
-                int page = -1;
-                if (base + lane < ntiles && idx < p.MB) page = p.bt[(long long)seq * p.MB + idx];
-                const int cnt = min(32, ntiles - base);
-                for (int i = 0; i < cnt; ++i, ++kt) {
-                    const int pg = __shfl_sync(0xffffffffu, page, i);
-                    const bool bad = pg < 0 || pg >= p.num_blocks;
-                    const int tok0 = bad ? -kTile : pg * kTile;  // out-of-range coordinates read as zeros
-                    if (lane == 0 && bad && (long long)(tile_lo + base + i) * kTile < kv_len) flag_error(p.status, EMLX_DEV_BAD_PAGE);
-                    const uint32_t ks = kt % C::KST, vs = kt % C::VST;
-                    if (kt >= C::KST) ptx::mbar_wait(&bars->k_empty[ks], ((kt / C::KST) & 1) ^ 1, abort_word);
+                return (base + lane < ntiles && idx < p.MB) ? p.bt[(long long)seq * p.MB + idx] : -1;
+            };
+            int pg_cur = load_pages(0), pg_next = load_pages(32), base = 0;
+            auto page_of = [&](int i) -> int {  // tile i of the item, base <= i < base + 64; every lane takes part
+                const int a = __shfl_sync(0xffffffffu, pg_cur, (i - base) & 31), b = __shfl_sync(0xffffffffu, pg_next, (i - base) & 31);
+                return i - base < 32 ? a : b;
+            };
+            auto issue = [&](int i, bool is_k) {
+                const uint32_t t = kt + (uint32_t)i;
+                const int pg = page_of(i);
+                const bool bad = pg < 0 || pg >= p.num_blocks;
+                const int tok0 = bad ? -kTile : pg * kTile;  // out-of-range coordinates read as zeros
+                if (is_k) {
+                    if (lane == 0 && bad && (long long)(tile_lo + i) * kTile < kv_len) flag_error(p.status, EMLX_DEV_BAD_PAGE);
+                    const uint32_t ks = t % C::KST;
+                    if (t >= C::KST) ptx::mbar_wait(&bars->qk_done[(t - C::KST) & 3], ((t - C::KST) >> 2) & 1, abort_word);
                     if (lane == 0 && !*abort_word) {
                         ptx::mbar_arrive_expect_tx(&bars->k_full[ks], C::KBYTES);
 #pragma unroll
                         for (int h = 0; h < C::HALVES; ++h)
                             ptx::tma_load_3d(k_smem + (size_t)ks * C::KBYTES + h * (kTile * 128), &kmap, &bars->k_full[ks], 64 * h, head, tok0);
                     }
-                    if (kt >= C::VST) ptx::mbar_wait(&bars->v_empty[vs], ((kt / C::VST) & 1) ^ 1, abort_word);
+                } else {
+                    const uint32_t vs = t % C::VST;
+                    if (t >= C::VST) ptx::mbar_wait(&bars->pv_done[(t - C::VST) & 3], ((t - C::VST) >> 2) & 1, abort_word);
                     if (lane == 0 && !*abort_word) {
                         ptx::mbar_arrive_expect_tx(&bars->v_full[vs], C::KBYTES);
 #pragma unroll
                         for (int h = 0; h < C::HALVES; ++h)
                             ptx::tma_load_3d(v_smem + (size_t)vs * C::KBYTES + h * (kTile * 128), &vmap, &bars->v_full[vs], 64 * h, head, tok0);
                     }
-                    __syncwarp();
+                }
+                __syncwarp();
+            };
+            issue(0, true);
+            if (ntiles > 1) issue(1, true);
+            for (int i = 0; i < ntiles; ++i) {
+                if (i + 2 < ntiles) issue(i + 2, true);
+                issue(i, false);
+                if (i + 1 == base + 32) {  // tiles up to base + 34 have been looked up: the older half is done with
+                    base += 32;
+                    pg_cur = pg_next;
+                    pg_next = load_pages(base + 32);
                 }
             }
+            kt += (uint32_t)ntiles;
         }
     } else if (warp == 5) {
         // ------------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc_qk = instr_desc(128, 128, BF16, false);
         constexpr uint32_t idesc_pv = instr_desc(128, D, BF16, true);
-        const uint32_t q_addr = ptx::smem_u32(q_smem);
+        const uint64_t k_desc0 = smem_desc(ptx::smem_u32(k_smem), 16, 1024);
+        const uint64_t v_desc0 = smem_desc(ptx::smem_u32(v_smem), kTile * 128, 1024);
         uint32_t kt = 0, k = 0;
         int u, head;
         for (; item_of(k, u, head) && !*abort_word; ++k) {
             const int ntiles = p.unit_cum[u + 1] - p.unit_cum[u];
-            ptx::mbar_wait(&bars->q_full, k & 1, abort_word);
+            ptx::mbar_wait(&bars->q_tmem, k & 1, abort_word);  // the item's Q rows are in TMEM
             tc_fence_after();
             // S is double-buffered in TMEM: QK of tile j+1 is issued before PV of tile j, so the tensor pipe
             // works while the softmax warps are busy with tile j
+            // Descriptors differ from tile to tile and from k-step to k-step only in their address field (bits 0-13,
+            // the shared-memory address / 16): one add per instruction instead of rebuilding them.  Q is read from
+            // TMEM (the softmax warps copied it there), so the shared-memory port only serves K here.
             auto issue_qk = [&](uint32_t t) {
                 const uint32_t stage = t % C::KST;
-                const uint32_t k_addr = ptx::smem_u32(k_smem + (size_t)stage * C::KBYTES);
-                ptx::mbar_wait(&bars->k_full[stage], (t / C::KST) & 1, abort_word);
+                const bool ok = ptx::mbar_wait(&bars->k_full[stage], (t / C::KST) & 1, abort_word);
                 tc_fence_after();
-                if (lane == 0 && !*abort_word) {
+                PF_STAMP(lane == 0, t, 4);
+                if (lane == 0 && ok) {
+                    const uint64_t kd = k_desc0 + (uint64_t)(stage * (C::KBYTES >> 4));
+                    const uint32_t s_tmem = tmem_S + (t & 1) * 128;
 #pragma unroll
                     for (int ks = 0; ks < D / 16; ++ks) {
-                        const uint32_t off = (ks >> 2) * (kTile * 128) + (ks & 3) * 32;
-                        tc_mma_f16(tmem_S + (t & 1) * 128, smem_desc(q_addr + off, 16, 1024), smem_desc(k_addr + off, 16, 1024),
-                                   idesc_qk, ks > 0);
+                        constexpr int kHalf = (kTile * 128) >> 4;
+                        const uint32_t off = (uint32_t)((ks >> 2) * kHalf + (ks & 3) * 2);  // in 16-byte units
+                        tc_mma_f16_ts(s_tmem, tmem_Q + ks * 8, kd + off, idesc_qk, ks > 0);
                     }
-                    tc_commit(&bars->s_ready[t & 1]);
-                    tc_commit(&bars->k_empty[stage]);
+                    tc_commit(&bars->qk_done[t & 3]);
                 }
                 __syncwarp();
             };
@@ -282,20 +320,23 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             for (int j = 0; j < ntiles; ++j, ++kt) {
                 if (j + 1 < ntiles) issue_qk(kt + 1);
                 const uint32_t stage = kt % C::VST;
-                const uint32_t v_addr = ptx::smem_u32(v_smem + (size_t)stage * C::KBYTES);
-                ptx::mbar_wait(&bars->v_full[stage], (kt / C::VST) & 1, abort_word);
-                ptx::mbar_wait(&bars->p_ready, kt & 1, abort_word);
+                bool ok = ptx::mbar_wait(&bars->v_full[stage], (kt / C::VST) & 1, abort_word);
+                PF_STAMP(lane == 0, kt, 5);
+                ok = ptx::mbar_wait(&bars->p_ready[kt & 1], (kt >> 1) & 1, abort_word) && ok;
                 tc_fence_after();
-                if (lane == 0 && !*abort_word) {
+                PF_STAMP(lane == 0, kt, 6);
+                if (lane == 0 && ok) {
+                    const uint64_t vd = v_desc0 + (uint64_t)(stage * (C::KBYTES >> 4));
 #pragma unroll
                     for (int kk = 0; kk < kTile / 16; ++kk) {
-                        // 16 tokens of P = 8 packed columns of TMEM
-                        tc_mma_f16_ts(tmem_O, tmem_P + kk * 8, smem_desc(v_addr + kk * (16 * 128), kTile * 128, 1024), idesc_pv,
-                                      j > 0 || kk > 0);
+                        // 16 tokens of P = 8 packed columns at the start of this tile's S buffer (the pipe runs MMAs in
+                        // issue order, so QK of tile kt + 2 overwrites the buffer only after this product has read it);
+                        // 16 token rows of V = 2048 bytes further on
+                        tc_mma_f16_ts(tmem_O, tmem_S + (kt & 1) * 128 + kk * 8, vd + (uint64_t)(kk * ((16 * 128) >> 4)), idesc_pv, j > 0 || kk > 0);
                     }
-                    tc_commit(&bars->o_ready);
-                    tc_commit(&bars->v_empty[stage]);
+                    tc_commit(&bars->pv_done[kt & 3]);
                 }
+                PF_STAMP(lane == 0, kt, 7);
                 __syncwarp();
             }
         }
@@ -319,6 +360,21 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             const int hi_min = min(kv_len, ctx + i_first + 1);
             const int lo_max = p.window > 0 ? max(0, min(kv_len - 1, ctx + i_last) - p.window + 1) : 0;
 
+            // this row of Q: shared memory (TMA, swizzled) -> TMEM, two 16-bit elements per column, as the A operand of QK
+            ptx::mbar_wait(&bars->q_full, k & 1, abort_word);
+#pragma unroll
+            for (int h = 0; h < C::HALVES; ++h) {
+                uint32_t qv[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = *(const uint4*)(q_smem + h * (kPfRows * 128) + r * 128 + ((c ^ (r & 7)) << 4));
+                    qv[4 * c] = v.x; qv[4 * c + 1] = v.y; qv[4 * c + 2] = v.z; qv[4 * c + 3] = v.w;
+                }
+                tmem_st32(tmem_Q + lane_addr + 32 * h, qv);
+            }
+            tc_fence_before();
+            ptx::mbar_arrive(&bars->q_tmem);
+
             // m_ref is the maximum the stored probabilities and O refer to; it follows the true running maximum
             // lazily (only when that grew by more than 2^8), so O in TMEM is rarely rescaled
             float m_ref = -INFINITY, l = 0.f;
@@ -326,24 +382,27 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             for (int j = 0; j < ntiles; ++j, ++kt) {
                 const int t0 = (tile_lo + j) * kTile;
                 const bool interior = (t0 + kTile <= hi_min) && (t0 >= lo_max);
-                ptx::mbar_wait(&bars->s_ready[kt & 1], (kt >> 1) & 1, abort_word);
+                ptx::mbar_wait(&bars->qk_done[kt & 3], (kt >> 2) & 1, abort_word);
                 tc_fence_after();
+                PF_STAMP(tid == 0, kt, 0);
                 uint32_t sv[128];
 #pragma unroll
                 for (int c4 = 0; c4 < 4; ++c4) tmem_ld32_nowait(tmem_S + (kt & 1) * 128 + lane_addr + 32 * c4, sv + 32 * c4);
                 tmem_wait_ld();
-                float mx = -INFINITY;
-                if (interior) {
-#pragma unroll
-                    for (int i = 0; i < 128; ++i) mx = fmaxf(mx, __uint_as_float(sv[i]));
-                } else {
+                if (!interior) {
 #pragma unroll
                     for (int i = 0; i < 128; ++i) {
                         const int tok = t0 + i;
                         if (tok < lo || tok >= hi) sv[i] = 0xff800000u;  // -inf
-                        mx = fmaxf(mx, __uint_as_float(sv[i]));
                     }
                 }
+                float mx8[8];  // eight independent chains instead of one of 128 dependent maxima
+#pragma unroll
+                for (int i = 0; i < 8; ++i) mx8[i] = __uint_as_float(sv[i]);
+#pragma unroll
+                for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(sv[i]));
+                const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+                PF_STAMP(tid == 0, kt, 1);
                 const float m_new = mx * p.scale_log2e;
                 const bool grow = (j == 0) ? true : (m_new > m_ref + 8.0f);
                 float corr = 1.0f;
@@ -352,26 +411,26 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(corr) : "f"(m_ref - (m_tgt == -INFINITY ? 0.f : m_tgt)));
                     m_ref = m_tgt;
                 }
-                // PV of the previous tile has to be complete before P is overwritten and before O is touched
-                if (j > 0) {
-                    ptx::mbar_wait(&bars->o_ready, (kt - 1) & 1, abort_word);
+                // O is only touched when the reference maximum moves (rare): every earlier PV must be complete then.
+                // P needs no such wait: it replaces this tile's own S, which nothing else uses until QK of tile kt + 2.
+                if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                    ptx::mbar_wait(&bars->pv_done[(kt - 1) & 3], ((kt - 1) >> 2) & 1, abort_word);
                     tc_fence_after();
-                    if (__any_sync(0xffffffffu, grow)) {
 #pragma unroll 1
-                        for (int c4 = 0; c4 < D / 32; ++c4) {
-                            uint32_t ov[32];
-                            tmem_ld32_nowait(tmem_O + lane_addr + 32 * c4, ov);
-                            tmem_wait_ld();
+                    for (int c4 = 0; c4 < D / 32; ++c4) {
+                        uint32_t ov[32];
+                        tmem_ld32_nowait(tmem_O + lane_addr + 32 * c4, ov);
+                        tmem_wait_ld();
 #pragma unroll
-                            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
-                            tmem_st32(tmem_O + lane_addr + 32 * c4, ov);
-                        }
-                        l *= corr;
+                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                        tmem_st32(tmem_O + lane_addr + 32 * c4, ov);
                     }
+                    l *= corr;
                 }
+                PF_STAMP(tid == 0, kt, 2);
                 const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;
                 const float neg_m = -m_safe;
-                float ls0 = 0.f, ls1 = 0.f;
+                float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     uint32_t packed[32];
@@ -380,14 +439,13 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                         float p0, p1;
                         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(sv[64 * h + 2 * e]), p.scale_log2e, neg_m)));
                         asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(sv[64 * h + 2 * e + 1]), p.scale_log2e, neg_m)));
-                        ls0 += p0;
-                        ls1 += p1;
+                        if (e & 1) { ls2 += p0; ls3 += p1; } else { ls0 += p0; ls1 += p1; }
                         if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
                         else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
                     }
-                    tmem_st32(tmem_P + lane_addr + 32 * h, packed);  // tokens [64h, 64h + 64) of this row
+                    tmem_st32(tmem_S + (kt & 1) * 128 + lane_addr + 32 * h, packed);  // tokens [64h, 64h + 64) of this row
                 }
-                const float lsum = ls0 + ls1;
+                const float lsum = (ls0 + ls1) + (ls2 + ls3);
                 l += lsum;
                 if (t0 + kTile > kv_len) {
                     // token rows of V past the sequence end are stale memory: clear them (thread r owns token r)
@@ -399,13 +457,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
 #pragma unroll
                             for (int c = 0; c < 8; ++c) *(uint4*)(vrow + h * (kTile * 128) + c * 16) = make_uint4(0u, 0u, 0u, 0u);
                     }
+                    ptx::fence_proxy_async();  // the tensor core reads V through the async proxy
                 }
-                ptx::fence_proxy_async();
                 tc_fence_before();
-                ptx::mbar_arrive(&bars->p_ready);
+                PF_STAMP(tid == 0, kt, 3);
+                ptx::mbar_arrive(&bars->p_ready[kt & 1]);
             }
             // the last PV, then this row of O
-            ptx::mbar_wait(&bars->o_ready, (kt - 1) & 1, abort_word);
+            ptx::mbar_wait(&bars->pv_done[(kt - 1) & 3], ((kt - 1) >> 2) & 1, abort_word);
             tc_fence_after();
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             const bool store = row0 + r < R;
@@ -501,7 +560,7 @@ int launch_prefill(const emlx_attn_args* a, const emlx_pool* pool, const int32_t
     PrefillParams p;
     p.out = a->out; p.bt = a->block_tables; p.kv_lens = a->kv_lens; p.qsl = a->query_start_loc;
     p.hdr = plan_class_hdr; p.unit_seq = unit_seq; p.unit_row0 = unit_row0; p.unit_tile_lo = unit_tile_lo; p.unit_cum = unit_cum; p.unit_order = unit_order;
-    p.status = a->status; p.num_blocks = pool->num_blocks;
+    p.status = a->status; p.num_blocks = pool->num_blocks; p.trace = trace_buffer();
     p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.MB = a->max_blocks_per_seq; p.window = a->sliding_window;
     p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
     const bool bf16 = a->q_dtype == EMLX_BF16;

@@ -398,9 +398,7 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
 #endif
         // ------------------------------------------------------------------ combine the eight warps' states
         const long long a_flat = (long long)cum_u * p.Hkv + (long long)head * ntiles;
-        const long long b_flat = a_flat + ntiles;
         const bool complete = (j_first == 0) && (run == ntiles);
-        const long long P = active;
         const int which = (max(a_flat, f_begin) != f_begin) ? 1 : 0;
         float* slot = p.slots + ((size_t)blockIdx.x * 2 + which) * kSlotFloats;
         float lw[NT][2], bw[NG][NT][2];

@@ -1024,6 +1024,7 @@ static int launch_class(int cls, int D, int fmt, bool bf16, const MapPair& maps,
 
 static long long* g_trace = nullptr;
 void set_trace(long long* buf) { g_trace = buf; }
+long long* trace_buffer() { return g_trace; }
 
 static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* stream, int class_lo, int class_hi) {
     if (int rc = validate_attn(a, pool, true)) return rc;

@@ -41,6 +41,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr uint32_t kWaitLimit = 1u << 22;
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word,
                                           uint32_t limit = kWaitLimit) {
+    if (mbar_try_wait(bar, parity)) return true;  // the common case costs one instruction and no abort-word load
     if (*abort_word) return false;
     for (uint32_t i = 0; i < limit; ++i) {
         if (mbar_try_wait(bar, parity)) return true;

@@ -20,6 +20,7 @@ int get_maps(const emlx_pool& pool, MapPair** out);
 int launch_prefill(const emlx_attn_args* a, const emlx_pool* pool, const int32_t* plan_class_hdr, const int32_t* unit_seq,
                    const int32_t* unit_row0, const int32_t* unit_tile_lo, const int32_t* unit_cum, const int32_t* unit_order,
                    const MapPair& maps, cudaStream_t stream);
+long long* trace_buffer();  // the optional tracing buffer (NULL = off)
 bool prefill_supported(int kv_format, int num_q_heads, int num_kv_heads, int head_dim);
 
 }  // namespace emlx
