@@ -51,19 +51,6 @@ struct RowReader {
     }
 };
 
-template <typename TIn, typename TOut>
-__device__ __forceinline__ void copy_row(const RowReader<TIn>& src, TOut* __restrict__ dst, int D, int lane) {
-    for (int d = lane; d < D; d += 32) dst[d] = from_f32<TOut>(src(d));
-}
-
-template <typename TIn>
-__device__ __forceinline__ void write_float_row(const RowReader<TIn>& src, void* cache, int kv_dtype, int64_t elem_off,
-                                                int D, int lane) {
-    if (kv_dtype == EMLX_F16) copy_row(src, (__half*)cache + elem_off, D, lane);
-    else if (kv_dtype == EMLX_BF16) copy_row(src, (__nv_bfloat16*)cache + elem_off, D, lane);
-    else copy_row(src, (float*)cache + elem_off, D, lane);
-}
-
 // Quantise one group of 64 elements held two per lane.  Arithmetic is spelled with the
 // round-to-nearest intrinsics so that no contraction or fast-math option can change the codes.
 template <int BITS>
@@ -81,30 +68,43 @@ __device__ __forceinline__ void quantize_group(float x0, float x1, int& c0, int&
     c1 = (int)fminf(fmaxf(q1, 0.0f), levels);
 }
 
+constexpr int kMaxGroups = 4;  // head_dim <= 256
+
+// Codes, scale and bias of one (token, head): computed before the destination is known, stored afterwards.
+struct QuantRow {
+    int c0[kMaxGroups], c1[kMaxGroups];
+    __half s[kMaxGroups], b[kMaxGroups];
+};
+
 template <typename TIn, int BITS>
-__device__ __forceinline__ void write_affine_rows(const RowReader<TIn>& krow, const RowReader<TIn>& vrow,
-                                                  const emlx_pool& p, int64_t page, int off, int h, int lane) {
+__device__ __forceinline__ void quantize_row(const RowReader<TIn>& row, int groups, int lane, QuantRow& q) {
+#pragma unroll
+    for (int g = 0; g < kMaxGroups; ++g) {
+        if (g < groups) {
+            const int d0 = g * kQuantGroup + 2 * lane;
+            quantize_group<BITS>(row(d0), row(d0 + 1), q.c0[g], q.c1[g], q.s[g], q.b[g]);
+        }
+    }
+}
+
+template <int BITS>
+__device__ __forceinline__ void store_affine_rows(const QuantRow& kq, const QuantRow& vq, const emlx_pool& p, int64_t page,
+                                                  int off, int h, int lane) {
     const int D = p.head_dim, bs = p.block_size, Hkv = p.num_kv_heads, groups = D / kQuantGroup;
     const int64_t sb_base = ((page * Hkv + h) * bs + off) * groups;
     // keys: token-major codes [NB, bs, Hkv, D*BITS/8]
     uint8_t* kdst = (uint8_t*)p.key_cache + ((page * bs + off) * Hkv + h) * (int64_t)(D * BITS / 8);
     // values: [NB, Hkv, D, bs*BITS/8], the tokens of one element are contiguous
     uint8_t* vdst = (uint8_t*)p.value_cache + (page * Hkv + h) * (int64_t)D * (bs * BITS / 8);
-    for (int g = 0; g < groups; ++g) {
+#pragma unroll
+    for (int g = 0; g < kMaxGroups; ++g) {
+        if (g >= groups) break;
         const int d0 = g * kQuantGroup + 2 * lane;
-        int c0, c1;
-        __half s, b;
-        quantize_group<BITS>(krow(d0), krow(d0 + 1), c0, c1, s, b);
-        if (BITS == 8) *(uchar2*)(kdst + d0) = make_uchar2((unsigned char)c0, (unsigned char)c1);
-        else kdst[d0 >> 1] = (uint8_t)(c0 | (c1 << 4));
-        if (lane == 0) {
-            ((__half*)p.k_scale)[sb_base + g] = s;
-            ((__half*)p.k_bias)[sb_base + g] = b;
-        }
-        quantize_group<BITS>(vrow(d0), vrow(d0 + 1), c0, c1, s, b);
+        if (BITS == 8) *(uchar2*)(kdst + d0) = make_uchar2((unsigned char)kq.c0[g], (unsigned char)kq.c1[g]);
+        else kdst[d0 >> 1] = (uint8_t)(kq.c0[g] | (kq.c1[g] << 4));
         if (BITS == 8) {
-            vdst[(int64_t)d0 * bs + off] = (uint8_t)c0;
-            vdst[(int64_t)(d0 + 1) * bs + off] = (uint8_t)c1;
+            vdst[(int64_t)d0 * bs + off] = (uint8_t)vq.c0[g];
+            vdst[(int64_t)(d0 + 1) * bs + off] = (uint8_t)vq.c1[g];
         } else {
             // two tokens share a byte; tokens of the same batch may land in the same 32-bit word, so the
             // nibble is replaced with word atomics (each nibble has exactly one writer per batch)
@@ -114,19 +114,26 @@ __device__ __forceinline__ void write_affine_rows(const RowReader<TIn>& krow, co
                 uint8_t* byte = vdst + (int64_t)(d0 + e) * (bs / 2) + (off >> 1);
                 unsigned int* word = (unsigned int*)((uintptr_t)byte & ~(uintptr_t)3);
                 atomicAnd(word, ~(0xFu << shift));
-                atomicOr(word, (unsigned int)(e ? c1 : c0) << shift);
+                atomicOr(word, (unsigned int)(e ? vq.c1[g] : vq.c0[g]) << shift);
             }
         }
         if (lane == 0) {
-            ((__half*)p.v_scale)[sb_base + g] = s;
-            ((__half*)p.v_bias)[sb_base + g] = b;
+            ((__half*)p.k_scale)[sb_base + g] = kq.s[g];
+            ((__half*)p.k_bias)[sb_base + g] = kq.b[g];
+            ((__half*)p.v_scale)[sb_base + g] = vq.s[g];
+            ((__half*)p.v_bias)[sb_base + g] = vq.b[g];
         }
     }
 }
 
 template <typename TIn>
 __global__ void __launch_bounds__(256) kv_write_kernel(WriteParams w) {
-    grid_dep_wait();  // the slot mapping comes from the metadata kernel
+    // Everything up to the stores is independent of the metadata kernel unless the rows are rotated (the rotation
+    // needs the token positions that kernel writes): read and quantise the rows first, wait for the predecessor
+    // only then.  The inputs themselves come from launches that precede the metadata kernel, which has already
+    // waited for them by the time it lets this grid start.
+    const bool early = w.rope_dims == 0;
+    if (!early) grid_dep_wait();
     grid_dep_launch();
     const int lane = threadIdx.x & 31;
     const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -134,7 +141,7 @@ __global__ void __launch_bounds__(256) kv_write_kernel(WriteParams w) {
     const int Hkv = p.num_kv_heads, D = p.head_dim;
     const int64_t kv_warps = w.has_pool ? (int64_t)w.T * Hkv : 0;
     if (warp >= kv_warps) {
-        // rotated queries: one warp per (token, q head)
+        // rotated queries: one warp per (token, q head); only launched with a rotation, so the wait is behind us
         const int64_t qw = warp - kv_warps;
         if (w.q_out == nullptr || qw >= (int64_t)w.T * w.Hq) return;
         const int t = (int)(qw / w.Hq);
@@ -144,23 +151,55 @@ __global__ void __launch_bounds__(256) kv_write_kernel(WriteParams w) {
         return;
     }
     const int t = (int)(warp / Hkv), h = (int)(warp - (int64_t)t * Hkv);
+    const RowReader<TIn> krow{(const TIn*)w.keys + ((int64_t)t * Hkv + h) * D, w.rope_dims > 0 ? w.positions[t] : -1, &w};
+    const RowReader<TIn> vrow{(const TIn*)w.values + ((int64_t)t * Hkv + h) * D, -1, &w};
+    const int groups = D / kQuantGroup;
+    QuantRow kq, vq;
+    float kf[8], vf[8];  // float pools: head_dim <= 256, element d = lane + 32 i
+    if (p.kv_format == EMLX_KV_AFFINE8) {
+        quantize_row<TIn, 8>(krow, groups, lane, kq);
+        quantize_row<TIn, 8>(vrow, groups, lane, vq);
+    } else if (p.kv_format == EMLX_KV_AFFINE4) {
+        quantize_row<TIn, 4>(krow, groups, lane, kq);
+        quantize_row<TIn, 4>(vrow, groups, lane, vq);
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int d = lane + 32 * i;
+            kf[i] = d < D ? krow(d) : 0.f;
+            vf[i] = d < D ? vrow(d) : 0.f;
+        }
+    }
+    if (early) grid_dep_wait();
     const int64_t slot = w.slot_mapping[t];
     if (slot < 0) return;
     if (slot >= p.num_blocks * p.block_size) {
         if (lane == 0) flag_error(w.status, EMLX_DEV_BAD_PAGE);
         return;
     }
-    const RowReader<TIn> krow{(const TIn*)w.keys + ((int64_t)t * Hkv + h) * D, w.rope_dims > 0 ? w.positions[t] : -1, &w};
-    const RowReader<TIn> vrow{(const TIn*)w.values + ((int64_t)t * Hkv + h) * D, -1, &w};
     if (p.kv_format == EMLX_KV_FLOAT) {
         const int64_t off = (slot * Hkv + h) * D;
-        write_float_row(krow, p.key_cache, p.kv_dtype, off, D, lane);
-        write_float_row(vrow, p.value_cache, p.kv_dtype, off, D, lane);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int d = lane + 32 * i;
+            if (d < D) {
+                if (p.kv_dtype == EMLX_F16) {
+                    ((__half*)p.key_cache)[off + d] = __float2half_rn(kf[i]);
+                    ((__half*)p.value_cache)[off + d] = __float2half_rn(vf[i]);
+                } else if (p.kv_dtype == EMLX_BF16) {
+                    ((__nv_bfloat16*)p.key_cache)[off + d] = __float2bfloat16_rn(kf[i]);
+                    ((__nv_bfloat16*)p.value_cache)[off + d] = __float2bfloat16_rn(vf[i]);
+                } else {
+                    ((float*)p.key_cache)[off + d] = kf[i];
+                    ((float*)p.value_cache)[off + d] = vf[i];
+                }
+            }
+        }
     } else {
         const int64_t page = slot / p.block_size;
         const int in_page = (int)(slot - page * p.block_size);
-        if (p.kv_format == EMLX_KV_AFFINE8) write_affine_rows<TIn, 8>(krow, vrow, p, page, in_page, h, lane);
-        else write_affine_rows<TIn, 4>(krow, vrow, p, page, in_page, h, lane);
+        if (p.kv_format == EMLX_KV_AFFINE8) store_affine_rows<8>(kq, vq, p, page, in_page, h, lane);
+        else store_affine_rows<4>(kq, vq, p, page, in_page, h, lane);
     }
 }
 
@@ -169,6 +208,7 @@ int validate_pool(const emlx_pool* pool) {
     if (!pool->key_cache || !pool->value_cache) return fail(EMLX_ERR_INVALID, "key_cache/value_cache is NULL");
     if (pool->num_blocks <= 0 || pool->block_size <= 0 || pool->num_kv_heads <= 0 || pool->head_dim <= 0)
         return fail(EMLX_ERR_INVALID, "pool geometry must be positive");
+    if (pool->head_dim > 256) return fail(EMLX_ERR_UNSUPPORTED, "head_dim %d > 256", pool->head_dim);
     if (pool->kv_format == EMLX_KV_FLOAT) {
         if (pool->kv_dtype < EMLX_F16 || pool->kv_dtype > EMLX_F32) return fail(EMLX_ERR_INVALID, "unknown kv_dtype");
     } else if (pool->kv_format == EMLX_KV_AFFINE8 || pool->kv_format == EMLX_KV_AFFINE4) {

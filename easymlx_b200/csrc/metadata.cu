@@ -5,6 +5,12 @@
 
 namespace emlx {
 
+#ifdef EMLX_TRACE_META
+#define META_STAMP(k) do { if (threadIdx.x == 0) g_meta_trace[k] = clock64(); } while (0)
+#else
+#define META_STAMP(k) do { } while (0)
+#endif
+
 __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
     const int32_t* __restrict__ query_lens, const int32_t* __restrict__ slot_ids, int S, int T,
     const int32_t* __restrict__ bt_all, int num_slots, int MB, int32_t* kv_lens_all, int bs, int advance,
@@ -18,8 +24,19 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
     constexpr int kSmemSeqs = 2048, kSmemUnits = 4096;
     __shared__ int32_t s_q[kSmemSeqs + 1], s_kv[kSmemSeqs], s_off[kSmemSeqs], s_cum[kSmemUnits];
     const int tid = threadIdx.x;
-    grid_dep_wait();  // a preceding attention kernel may still be reading the plan buffer and the lengths
+    META_STAMP(0);
+    // The first 1024 sequences' inputs are read before waiting for the predecessor: they come from the host or from
+    // launches older than it (the lengths were last written by the previous metadata launch), so their latency
+    // overlaps the predecessor's tail.
+    int pre_q = 0, pre_slot = -1, pre_base = 0;
+    if (tid < S) {
+        pre_q = max(query_lens[tid], 0);
+        pre_slot = slot_ids[tid];
+        if (pre_slot >= 0 && pre_slot < num_slots) pre_base = kv_lens_all[pre_slot];
+    }
+    grid_dep_wait();  // a preceding attention kernel may still be reading the plan buffer and the gathered lengths
     grid_dep_launch();
+    META_STAMP(1);
     const bool small = S <= kSmemSeqs;
     int32_t* qv = small ? s_q : qsl;
     int32_t* kvv = small ? s_kv : kv_out;
@@ -29,10 +46,14 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
         const int i = i0 + tid;
         int q_len = 0, slot = -1, base = 0;
         if (i < S) {
-            q_len = max(query_lens[i], 0);
-            slot = slot_ids[i];
-            if (slot >= 0 && slot < num_slots) base = kv_lens_all[slot];
-            else flag_error(status, EMLX_DEV_BAD_SLOT);
+            if (i0 == 0) {
+                q_len = pre_q; slot = pre_slot; base = pre_base;
+            } else {
+                q_len = max(query_lens[i], 0);
+                slot = slot_ids[i];
+                if (slot >= 0 && slot < num_slots) base = kv_lens_all[slot];
+            }
+            if (slot < 0 || slot >= num_slots) flag_error(status, EMLX_DEV_BAD_SLOT);
         }
         int chunk_total;
         const int excl = carry + block_scan_value(q_len, scan_smem, chunk_total);
@@ -57,46 +78,97 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
         if (total != T) flag_error(status, EMLX_DEV_TOKEN_MISMATCH);
     }
     __syncthreads();
+    META_STAMP(2);
+
+    // The page-table gather and the slot mapping do not depend on the work list: their first batch of loads is
+    // issued here, before the work list is built, and stored afterwards, so that their two dependent round trips
+    // run behind that computation.
+    const int64_t cells = (int64_t)S * MB;
+    constexpr int kBatch = 4;
+    int g_val[kBatch];
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+        const int64_t c = tid + (int64_t)k * kMetaThreads;
+        g_val[k] = -1;
+        if (c < cells) {
+            const int row = (int)(c / MB), col = (int)(c - (int64_t)row * MB);
+            const int slot = slot_ids[row];
+            if (slot >= 0 && slot < num_slots) g_val[k] = bt_all[(int64_t)slot * MB + col];
+        }
+    }
+    const int n_tok = min(T, total);
+    // slot mapping of token t in two halves: everything up to the page-table load, and the address from the page
+    struct TokenProbe { int pos, off, page; bool live; };
+    auto probe_token = [&](int t) -> TokenProbe {
+        TokenProbe r{0, 0, -1, false};
+        if (t >= n_tok) return r;
+        const int s = find_sequence(qv, S, t);
+        const int slot = s >= 0 ? slot_ids[s] : -1;
+        if (slot < 0 || slot >= num_slots) return r;
+        const int q_len = qv[s + 1] - qv[s];
+        r.pos = kvv[s] - q_len + (t - qv[s]);
+        const int page_idx = r.pos / bs;
+        if (page_idx >= MB) return r;
+        r.off = r.pos - page_idx * bs;
+        r.page = bt_all[(int64_t)slot * MB + page_idx];  // not consumed before the work list is built
+        r.live = true;
+        return r;
+    };
+    TokenProbe probe{0, 0, -1, false};
+    if (slot_mapping != nullptr && tid < T) probe = probe_token(tid);
 
     // attention work list in the same launch (lengths after the write are final here)
     if (plan != nullptr)
         build_plan(qv, kvv, S, G, window, class_lo, class_hi, wide, Hkv, num_ctas, plan, L, scan_smem,
                    small ? s_off : nullptr, s_cum, kSmemUnits);
 
-    // gathered page-table rows
-    const int64_t cells = (int64_t)S * MB;
-    for (int64_t c = tid; c < cells; c += kMetaThreads) {
-        int row = (int)(c / MB), col = (int)(c - (int64_t)row * MB);
-        int slot = slot_ids[row];
-        bt_out[c] = (slot >= 0 && slot < num_slots) ? bt_all[(int64_t)slot * MB + col] : -1;
+    META_STAMP(3);
+    // gathered page-table rows: the preloaded batch, then the rest
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+        const int64_t c = tid + (int64_t)k * kMetaThreads;
+        if (c < cells) bt_out[c] = g_val[k];
     }
-
-    if (slot_mapping == nullptr) return;
-    const int n = min(T, total);
-    for (int t = tid; t < T; t += kMetaThreads) {
-        int64_t dst = -1;
-        int pos_out = 0;
-        if (t < n) {
-            int s = find_sequence(qv, S, t);
-            int slot = s >= 0 ? slot_ids[s] : -1;
-            if (slot >= 0 && slot < num_slots) {
-                int q_len = qv[s + 1] - qv[s];
-                int pos = kvv[s] - q_len + (t - qv[s]);
-                pos_out = pos;
-                int page_idx = pos / bs;
-                if (page_idx < MB) {
-                    int page = bt_all[(int64_t)slot * MB + page_idx];
-                    if (page >= 0 && page < num_blocks) dst = (int64_t)page * bs + (pos - page_idx * bs);
-                    else flag_error(status, EMLX_DEV_BAD_PAGE);
-                }
+    for (int64_t c0 = tid + (int64_t)kBatch * kMetaThreads; c0 < cells; c0 += (int64_t)kBatch * kMetaThreads) {
+        int v[kBatch];
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+            const int64_t c = c0 + (int64_t)k * kMetaThreads;
+            v[k] = -1;
+            if (c < cells) {
+                const int row = (int)(c / MB), col = (int)(c - (int64_t)row * MB);
+                const int slot = slot_ids[row];
+                if (slot >= 0 && slot < num_slots) v[k] = bt_all[(int64_t)slot * MB + col];
             }
         }
-        slot_mapping[t] = dst;
-        if (token_positions) token_positions[t] = pos_out;
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+            const int64_t c = c0 + (int64_t)k * kMetaThreads;
+            if (c < cells) bt_out[c] = v[k];
+        }
     }
+    META_STAMP(4);
+    if (slot_mapping == nullptr) return;
+    for (int t = tid; t < T; t += kMetaThreads) {
+        if (t >= kMetaThreads) probe = probe_token(t);
+        int64_t dst = -1;
+        if (probe.live) {
+            if (probe.page >= 0 && probe.page < num_blocks) dst = (int64_t)probe.page * bs + probe.off;
+            else flag_error(status, EMLX_DEV_BAD_PAGE);
+        }
+        slot_mapping[t] = dst;
+        if (token_positions) token_positions[t] = probe.pos;
+    }
+    META_STAMP(5);
 }
 
 }  // namespace emlx
+
+#ifdef EMLX_TRACE_META
+extern "C" __attribute__((visibility("default"))) int emlx_debug_meta_trace(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, emlx::g_meta_trace, sizeof(long long) * 32);
+}
+#endif
 
 extern "C" int emlx_build_metadata(const int32_t* query_lens, const int32_t* slot_ids, int32_t num_seqs,
                                    int32_t total_tokens, const int32_t* block_tables_all, int32_t num_slots,

@@ -7,6 +7,10 @@
 
 namespace emlx {
 
+#ifdef EMLX_TRACE_META
+static __device__ long long g_meta_trace[32];  // measurement aid, one copy per translation unit
+#endif
+
 constexpr int kOrderBins = 1024;  // tile-count bins of the class-3 unit order (longer units share the last bin)
 
 // Exclusive prefix of one value per thread across the CTA; `total` receives the CTA-wide sum.
@@ -73,6 +77,9 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
         // first unit of every sequence in this class; shared memory when the caller has room for it (a global
         // store followed by a load from another thread costs an L2 round trip per phase)
         int32_t* seq_off = seq_off_buf ? seq_off_buf : plan + L.tmp;
+#ifdef EMLX_TRACE_META
+        if (threadIdx.x == 0 && c == class_lo) g_meta_trace[8] = clock64();
+#endif
         // pass 1: units per sequence -> first-unit offsets
         int num_units = 0;
         for (int s0 = 0; s0 < S; s0 += kMetaThreads) {
@@ -88,6 +95,9 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
             num_units += n_total;
         }
         __syncthreads();
+#ifdef EMLX_TRACE_META
+        if (threadIdx.x == 0 && c == class_lo) g_meta_trace[9] = clock64();
+#endif
         // pass 2: one thread per unit: owner sequence by binary search, tile range, running tile prefix
         int tile_base = 0;
         for (int i0 = 0; i0 < num_units; i0 += kMetaThreads) {
@@ -142,6 +152,9 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
                 order[atomicAdd(&bins[kOrderBins - 1 - min(unit_cum[u + 1] - unit_cum[u], kOrderBins - 1)], 1)] = u;
             __syncthreads();
         }
+#ifdef EMLX_TRACE_META
+        if (threadIdx.x == 0 && c == class_lo) g_meta_trace[10] = clock64();
+#endif
         const int32_t* cum = num_units < cum_cap ? cum_smem : unit_cum;
         // slice boundaries: equal shares of cost, kTileCost per tile + kPartCost per (unit, head) part (measured on
         // the 8-row decode kernel: a part boundary costs about as much as 2.3 tiles)
@@ -151,7 +164,9 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
             const long long kPartCost = part_cost(c);
             if (i < num_ctas && num_units > 0) {
                 const long long total = (long long)Hkv * (kTileCost * tile_base + kPartCost * num_units);
-                const long long target = total * i / num_ctas;
+                // 64-bit division is a long software routine; the totals of any realistic batch fit 32 bits
+                const long long target = total * num_ctas < (1LL << 31) ? (long long)((unsigned)(total * i) / (unsigned)num_ctas)
+                                                                        : total * i / num_ctas;
                 int lo = 0, hi = num_units;  // largest u with cost_before(u) <= target
                 while (hi - lo > 1) {
                     const int mid = (lo + hi) >> 1;
@@ -160,7 +175,8 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
                 const int u = lo, nt = cum[u + 1] - cum[u];
                 const long long rem = target - (long long)Hkv * (kTileCost * cum[u] + kPartCost * u);
                 const long long per_head = kTileCost * nt + kPartCost;
-                const int head = (int)min((long long)Hkv - 1, rem / per_head);
+                const int head = (int)min((long long)Hkv - 1,
+                                          rem < (1LL << 31) ? (long long)((unsigned)rem / (unsigned)per_head) : rem / per_head);
                 const long long r2 = rem - head * per_head;
                 const int j = r2 <= kPartCost ? 0 : (int)min((long long)nt, (r2 - kPartCost + kTileCost / 2) / kTileCost);
                 start = (long long)cum[u] * Hkv + (long long)head * nt + j;
