@@ -1,0 +1,78 @@
+"""Shapes that stretch the work split: one unit spread over every CTA of the grid (merge of more than a hundred
+partial results), prefill items with far more than 64 KV tiles (several page-id batches in the producer), and the
+same with a sliding window.  The fast kernels are compared with the coverage kernel (independent code path) and
+must repeat bit for bit."""
+
+import numpy as np
+import pytest
+import torch
+
+from gpu_util import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _pool(hkv, d, lens, bits, seed):
+    from easymlx_b200 import PageCacheView
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    pages = [-(-int(n) // 128) for n in lens]
+    cache = PageCacheView.init(num_seqs=len(lens), max_seq_len=max(pages) * 128, num_kv_heads=hkv, head_dim=d,
+                               block_size=128, cache_dtype=(f"affine{bits}" if bits else None), device="cuda")
+    for a in (cache.key_cache, cache.value_cache):
+        if a.dtype == torch.uint8:
+            a.copy_(torch.randint(0, 256, a.shape, device="cuda", generator=g, dtype=torch.uint8))
+        else:
+            a.copy_(torch.randn(a.shape, device="cuda", generator=g).to(a.dtype))
+    if bits:
+        for a in (cache.k_scales, cache.v_scales):
+            a.copy_((torch.rand(a.shape, device="cuda", generator=g) * 0.05 + 0.01).to(a.dtype))
+        for a in (cache.k_biases, cache.v_biases):
+            a.copy_((torch.rand(a.shape, device="cuda", generator=g) - 0.5).to(a.dtype))
+    return cache
+
+
+def _run(cache, q, qlens, kv_lens, kernel, window=None):
+    import easymlx_b200 as emlx
+    extra = dict(k_scale=cache.k_scales, v_scale=cache.v_scales, k_bias=cache.k_biases, v_bias=cache.v_biases) \
+        if cache.is_affine else {}
+    return emlx.paged_attention(q, cache.key_cache, cache.value_cache, cache.block_tables,
+                                torch.tensor(kv_lens, dtype=torch.int32, device="cuda"),
+                                emlx.build_query_start_loc(qlens, device="cuda"), max_query_len=max(qlens),
+                                sliding_window=window, kernel=kernel, **extra)
+
+
+@pytest.mark.parametrize("bits", [0, 8, 4])
+def test_one_decode_row_over_the_whole_grid(bits):
+    # 150 000 keys of one KV head: 1172 tiles over 148 CTAs, every CTA holds one part of the same unit
+    hq, hkv, d, kv = 4, 1, 128, 150_000
+    cache = _pool(hkv, d, [kv], bits, seed=bits)
+    q = torch.randn(1, hq, d, device="cuda", dtype=torch.float16)
+    fast = _run(cache, q, [1], [kv], None)
+    ref = _run(cache, q, [1], [kv], "generic")
+    assert_close(fast, ref.float().cpu().numpy())
+    assert torch.equal(fast, _run(cache, q, [1], [kv], None))
+
+
+@pytest.mark.parametrize("window", [None, 5000])
+def test_prefill_chunk_after_a_long_context(window):
+    # 256 new tokens after 20 000 cached ones: 32 x 128-row units x 2 KV heads, up to 159 KV tiles per item
+    hq, hkv, d, q_len, prior = 16, 2, 128, 256, 20_000
+    cache = _pool(hkv, d, [prior + q_len], 0, seed=11)
+    q = torch.randn(q_len, hq, d, device="cuda", dtype=torch.float16)
+    fast = _run(cache, q, [q_len], [prior + q_len], None, window)
+    ref = _run(cache, q, [q_len], [prior + q_len], "generic", window)
+    assert_close(fast, ref.float().cpu().numpy())
+    assert torch.equal(fast, _run(cache, q, [q_len], [prior + q_len], None, window))
+
+
+def test_mixed_lengths_with_empty_and_single_token_sequences():
+    # query lengths 0, 1, 3 (one 8-row unit ... 24 rows), 40 and 130 tokens in one batch, ragged contexts
+    hq, hkv, d = 16, 2, 128
+    qlens = [1, 0, 3, 40, 1, 130]
+    prior = [700, 0, 129, 5, 4000, 300]
+    kv = [a + b for a, b in zip(qlens, prior)]
+    cache = _pool(hkv, d, [max(n, 1) for n in kv], 0, seed=5)
+    q = torch.randn(sum(qlens), hq, d, device="cuda", dtype=torch.float16)
+    fast = _run(cache, q, qlens, kv, None)
+    ref = _run(cache, q, qlens, kv, "generic")
+    assert_close(fast, ref.float().cpu().numpy())

@@ -128,7 +128,7 @@ def _pool_arrays(view):
 def test_copy_blocks_all_pool_arrays(bits, mapping, host):
     from easymlx_b200 import PageCacheView
     v = PageCacheView.init(num_seqs=4, max_seq_len=1024, num_kv_heads=2, head_dim=128, block_size=128,
-                           cache_bits=bits or None, device="cuda")
+                           cache_dtype=(f"affine{bits}" if bits else None), device="cuda")
     g = torch.Generator(device="cuda").manual_seed(bits)
     for a in _pool_arrays(v):
         if a.dtype == torch.uint8:
