@@ -1,5 +1,7 @@
-"""eSurge-side batch and page-table helpers (device resident)."""
+"""eSurge-side batch format and page-table helpers (device resident)."""
 
-from .runners.model_runner import PageTableRunner, extract_last_tokens
+from .runners import PageTableRunner, ScheduledSequence, StepBatch, build_positions, extract_last_tokens, prepare_step
+from .scheduler import ScheduledRequest, SchedulerStepOutput, make_decode_slice, make_prefill_slice
 
-__all__ = ("PageTableRunner", "extract_last_tokens")
+__all__ = ("PageTableRunner", "ScheduledRequest", "ScheduledSequence", "SchedulerStepOutput", "StepBatch", "build_positions",
+           "extract_last_tokens", "make_decode_slice", "make_prefill_slice", "prepare_step")

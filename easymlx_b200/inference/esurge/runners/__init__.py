@@ -1,3 +1,4 @@
-from .model_runner import PageTableRunner, extract_last_tokens
+from .execution_types import ScheduledSequence, build_positions
+from .model_runner import PageTableRunner, StepBatch, extract_last_tokens, prepare_step
 
-__all__ = ("PageTableRunner", "extract_last_tokens")
+__all__ = ("PageTableRunner", "ScheduledSequence", "StepBatch", "build_positions", "extract_last_tokens", "prepare_step")

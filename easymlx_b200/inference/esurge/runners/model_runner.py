@@ -16,12 +16,14 @@ tables the attention kernels read never leave the GPU.  Method names and meaning
 from __future__ import annotations
 
 import typing as tp
+from dataclasses import dataclass
 
 import torch
 
 from ...._native import EMLX_OK  # noqa: F401  (re-exported for callers that test return codes)
 from .... import _native as nv
-from ....caching.paged.cache import PageCacheView, _uploaded, build_query_start_loc
+from ....caching.paged.cache import PageCacheView, PageMetadata, _uploaded, build_query_start_loc
+from .execution_types import ScheduledSequence, build_positions
 
 
 def _status_ptr(cache: PageCacheView):
@@ -133,4 +135,40 @@ class PageTableRunner:
         return out, query_lens
 
 
-__all__ = ("PageTableRunner", "extract_last_tokens")
+
+
+@dataclass
+class StepBatch:
+    """The packed batch of one step, resident on the device, in the form the attention path takes it."""
+
+    token_ids: torch.Tensor          # int32 [T]
+    positions: torch.Tensor          # int32 [T]
+    query_lens: list[int]
+    slot_ids: tuple[int, ...]
+    cache_metadata: PageMetadata
+
+
+def prepare_step(runner: PageTableRunner, sequences: tp.Sequence[ScheduledSequence], *, bind_pages: bool = True,
+                 device=None) -> StepBatch:
+    """Turn the scheduler's selection into the kernels' inputs: bind each row's pages (when the sequence carries
+    them), flatten token ids and positions, and build the metadata for ``concatenate_to_cache`` /
+    ``paged_attention`` (``model_runner.py:1308-1500`` does the same on the host, per forward step)."""
+    if device is None:
+        device = runner.kv_caches[0].block_tables.device if runner.kv_caches else "cuda"
+    if bind_pages:
+        for seq in sequences:
+            if seq.page_ids:
+                runner._assign_row_mapping(int(seq.row_index), list(seq.page_ids), cached_tokens=int(seq.num_computed_tokens))
+    flat, query_lens = runner._flatten_sequence_tokens(sequences, device=device)
+    pos = [p for row in build_positions(sequences) for p in row]
+    positions = torch.tensor(pos, dtype=torch.int32)
+    if torch.device(device).type == "cuda":
+        positions = positions.pin_memory().to(device, non_blocking=True)
+    slot_ids = tuple(int(s.row_index) for s in sequences)
+    single = bool(sequences) and all(n == 1 for n in query_lens)
+    meta = PageMetadata(query_start_loc=build_query_start_loc(query_lens, device=device), slot_ids=slot_ids,
+                        is_single_token_decode=single, max_query_len=max(query_lens, default=0))
+    return StepBatch(token_ids=flat, positions=positions, query_lens=query_lens, slot_ids=slot_ids, cache_metadata=meta)
+
+
+__all__ = ("PageTableRunner", "ScheduledSequence", "StepBatch", "extract_last_tokens", "prepare_step")

@@ -23,7 +23,8 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
-RUNNER_METHODS = ("_clear_row_mapping", "_page_ids_array", "_copy_cache_row", "_zero_indexed_cache_rows", "_zero_pages",
+SCHEDULER_METHODS = ("_make_prefill_slice", "_make_decode_slice")
+RUNNER_METHODS = ("_build_positions", "_clear_row_mapping", "_page_ids_array", "_copy_cache_row", "_zero_indexed_cache_rows", "_zero_pages",
                   "_assign_row_mapping", "_move_cache_row", "compact_rows", "_flatten_sequence_tokens",
                   "_get_compiled_batch_padder", "_pad_batch_token_ids")
 MODULE_METHODS = ("_extract_last_tokens",)
@@ -132,6 +133,31 @@ def main() -> None:
     meta = types.SimpleNamespace(query_start_loc=mx.array(qsl), is_single_token_decode=False)
     last = lm_cls()._extract_last_tokens(mx.array(hidden), meta)
     out.update(last_hidden=hidden, last_qsl=qsl, last_out=np.asarray(last))
+
+    # ---- scheduler slices and positions (scheduler/scheduler.py:327-372, model_runner.py:1292-1306)
+    sched_cls = type("Sched", (), extract_methods(os.path.join(root, "inference", "esurge", "scheduler", "scheduler.py"),
+                                                  ("Scheduler",), SCHEDULER_METHODS, {"EngineRequest": object}))
+    cases = []
+    prompt = list(range(100, 140))
+    for computed, budget, chunked, threshold in [(0, 64, False, None), (0, 16, False, None), (8, 64, True, 12),
+                                                 (35, 64, True, 12), (40, 64, True, 12), (3, 0, True, 12), (3, 7, True, 0)]:
+        sch = sched_cls()
+        sch.scheduler_config = types.SimpleNamespace(long_prefill_token_threshold=threshold, chunked_prefill_enabled=chunked)
+        req = types.SimpleNamespace(remaining_prefill_tokens=len(prompt) - computed, num_computed_tokens=computed,
+                                    all_token_ids=prompt)
+        ids, count = sch._make_prefill_slice(req, budget)
+        cases.append([computed, budget, int(chunked), -1 if threshold is None else threshold, count] + list(ids) + [-1] * (64 - len(ids)))
+    out["prefill_slices"] = np.asarray(cases, dtype=np.int32)
+    dcases = []
+    for generated, prm, gen_budget, budget in [([7, 8, 9], [1, 2], 5, 3), ([], [1, 2], 5, 3), ([], [], 5, 3), ([4], [1], 0, 3), ([4], [1], 2, 0)]:
+        sch = sched_cls()
+        req = types.SimpleNamespace(generated_token_ids=generated, prompt_token_ids=prm, remaining_generation_budget=gen_budget)
+        ids, count = sch._make_decode_slice(req, budget)
+        dcases.append([len(generated), len(prm), gen_budget, budget, count, ids[0] if ids else -1])
+    out["decode_slices"] = np.asarray(dcases, dtype=np.int32)
+    SeqP = namedtuple("SeqP", "token_ids num_computed_tokens")
+    pos = runner_cls._build_positions([SeqP([1, 2, 3], 5), SeqP([9], 0), SeqP([], 4), SeqP([1, 1], 127)])
+    out["positions_flat"] = np.asarray([p for row in pos for p in row], dtype=np.int32)
 
     np.savez_compressed(args.out, **out)
     print(f"wrote {args.out}: {sorted(out)}")

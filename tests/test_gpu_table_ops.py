@@ -154,3 +154,40 @@ def test_copy_blocks_validation():
         v.copy_blocks([[0, v.num_blocks + 3]])  # a page past the pool: skipped and reported
     assert torch.equal(v.key_cache, before)
     PageCache([v]).copy_blocks([[0, 1]])
+
+
+def test_prepare_step_drives_write_and_attention():
+    """Scheduler selection -> bound rows, packed ids / positions, metadata -> KV write + attention, against the oracle."""
+    from easymlx_b200 import AttentionPerformer, PageCacheView
+    from easymlx_b200.inference.esurge import PageTableRunner, ScheduledSequence, extract_last_tokens, prepare_step
+    from oracle import paged_attention as opa
+
+    hq, hkv, d, bs = 8, 2, 64, 128
+    cache = PageCacheView.init(num_seqs=4, max_seq_len=512, num_kv_heads=hkv, head_dim=d, block_size=bs, device="cuda",
+                               num_blocks=16)
+    cache.block_tables.fill_(-1)
+    runner = PageTableRunner([cache])
+    seqs = [ScheduledSequence("a", 2, list(range(40)), 0, page_ids=(5, 9)),       # a 40-token prefill chunk in row 2
+            ScheduledSequence("b", 0, [7], 0, page_ids=(3,))]                      # a first decode token in row 0
+    batch = prepare_step(runner, seqs)
+    assert batch.query_lens == [40, 1] and batch.slot_ids == (2, 0)
+    np.testing.assert_array_equal(batch.token_ids.cpu().numpy(), np.asarray(list(range(40)) + [7], dtype=np.int32))
+    np.testing.assert_array_equal(batch.positions.cpu().numpy(), np.asarray(list(range(40)) + [0], dtype=np.int32))
+    np.testing.assert_array_equal(cache.block_tables[2, :3].cpu().numpy(), [5, 9, -1])
+    np.testing.assert_array_equal(cache.block_tables[0, :2].cpu().numpy(), [3, -1])
+
+    g = torch.Generator(device="cuda").manual_seed(1)
+    t = sum(batch.query_lens)
+    q = torch.randn(t, hq, d, device="cuda", generator=g).half()
+    k = torch.randn(t, hkv, d, device="cuda", generator=g).half()
+    v = torch.randn(t, hkv, d, device="cuda", generator=g).half()
+    out = AttentionPerformer(scale=d ** -0.5)(q, k, v, cache_view=cache, cache_metadata=batch.cache_metadata)
+    cache.check()
+    want = opa.paged_attention_rows(q.cpu().numpy(), cache.key_cache.cpu().numpy(), cache.value_cache.cpu().numpy(),
+                                    cache.block_tables[[2, 0]].cpu().numpy(), np.asarray([40, 1], dtype=np.int32),
+                                    np.asarray([0, 40, 41], dtype=np.int32), softmax_scale=d ** -0.5)
+    from gpu_util import assert_close
+    assert_close(out, want)
+    hidden = out.reshape(t, hq * d)
+    last = extract_last_tokens(hidden, batch.cache_metadata)
+    assert torch.equal(last, hidden[[39, 40]])
