@@ -352,7 +352,7 @@ def run_ours(args):
     from easymlx_b200.operations.kernels.unified_attention import AttentionCall
 
     call = AttentionCall(w.q, w.cache.key_cache, w.cache.value_cache, w.cache.block_tables, meta_lens, qsl,
-                         max_query_len=int(w.qlens.max()), **extra)
+                         max_query_len=int(w.qlens.max()), query_len_set=sorted(set(int(x) for x in w.qlens if x > 0)), **extra)
     call.plan()
     call.launch()
     torch.cuda.synchronize()

@@ -42,7 +42,7 @@ class AttnArgs(C.Structure):
         ("query_start_loc", C.c_void_p),
         ("total_tokens", C.c_int32), ("num_seqs", C.c_int32), ("num_q_heads", C.c_int32),
         ("max_blocks_per_seq", C.c_int32), ("q_dtype", C.c_int32), ("sliding_window", C.c_int32),
-        ("softmax_scale", C.c_float), ("max_query_len", C.c_int32),
+        ("softmax_scale", C.c_float), ("max_query_len", C.c_int32), ("row_class_mask", C.c_int32),
         ("plan", C.c_void_p), ("plan_bytes", C.c_size_t), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p),
     ]
@@ -70,6 +70,7 @@ SIGNATURES = {
     "emlx_set_trace_buffer": (None, [_P]),
     "emlx_selftest_wait_timeout": (C.c_int, [_P, C.c_uint32, _P]),
     "emlx_attn_decode_static": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
+    "emlx_attn_row_class": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
     "emlx_gather_last_tokens": (C.c_int, [_P, C.c_int32, C.c_int64, _P, C.c_int32, _P, _P, _P]),
     "emlx_pad_token_ids": (C.c_int, [_P, C.c_int32, _P, C.c_int32, C.c_int32, _P, _P]),
     "emlx_page_staging_bytes": (C.c_int64, [C.POINTER(Pool)]),

@@ -105,6 +105,9 @@ class PageMetadata:
     slot_ids: tuple[int, ...] | None = None
     # filled by concatenate_to_cache: upper bound of query tokens per sequence known on the host (0 = unknown)
     max_query_len: int = field(default=0, compare=False)
+    # filled by concatenate_to_cache: the distinct query lengths of the batch when the host knows them; lets the
+    # attention call skip the kernels of row classes the batch does not contain
+    query_len_set: tuple[int, ...] | None = field(default=None, compare=False)
     # attention work list built on the GPU together with the metadata: (buffer, num_q_heads, sliding_window)
     plan: tp.Any | None = field(default=None, compare=False)
 
@@ -113,7 +116,7 @@ class PageMetadata:
             query_start_loc=self.query_start_loc, block_tables=block_tables, kv_lens=kv_lens,
             block_size=int(block_size), sliding_window=self.sliding_window,
             is_single_token_decode=self.is_single_token_decode, slot_ids=self.slot_ids,
-            max_query_len=self.max_query_len, plan=self.plan,
+            max_query_len=self.max_query_len, plan=self.plan, query_len_set=self.query_len_set,
         )
 
     def with_sliding_window(self, sliding_window: int | None) -> "PageMetadata":
@@ -121,7 +124,7 @@ class PageMetadata:
             query_start_loc=self.query_start_loc, block_tables=self.block_tables, kv_lens=self.kv_lens,
             block_size=self.block_size, sliding_window=sliding_window,
             is_single_token_decode=self.is_single_token_decode, slot_ids=self.slot_ids,
-            max_query_len=self.max_query_len,
+            max_query_len=self.max_query_len, query_len_set=self.query_len_set,
         )
 
 
@@ -454,6 +457,7 @@ class PageCacheView:
         dev = self.key_cache.device
         total = int(queries.shape[0])
         max_q = 0
+        qlens = None
         if query_lens is not None:
             qlens = tuple(max(0, int(q)) for q in query_lens)
             qlens_dev = _uploaded.get(qlens, dev)
@@ -481,6 +485,7 @@ class PageCacheView:
             query_start_loc=qsl, sliding_window=getattr(cache_metadata, "sliding_window", None),
             is_single_token_decode=bool(getattr(cache_metadata, "is_single_token_decode", False)) or single,
             slot_ids=getattr(cache_metadata, "slot_ids", None) or slots, max_query_len=max_q, plan=plan,
+            query_len_set=None if qlens is None else tuple(sorted(set(q for q in qlens if q > 0))),
         ).with_cache_state(block_tables=bt, kv_lens=lens, block_size=self.block_size)
         return queries, self.key_cache, self.value_cache, meta
 

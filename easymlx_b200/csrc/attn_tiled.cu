@@ -1053,6 +1053,7 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
     hi = min(hi, class_hi);
     const int32_t* plan = (const int32_t*)a->plan;
     for (int c = lo; c <= hi; ++c) {
+        if (a->row_class_mask != 0 && !((a->row_class_mask >> c) & 1)) continue;  // the caller knows this class is empty
         if (c == 3) {
             if (int rc = launch_prefill(a, pool, plan + 4 * c, plan + L.unit_seq[c], plan + L.unit_row0[c],
                                         plan + L.unit_tile_lo[c], plan + L.unit_cum[c], plan + L.unit_order, *maps,
@@ -1090,5 +1091,11 @@ int emlx_attn_decode(const emlx_attn_args* a, const emlx_pool* p, void* s) { ret
 int emlx_attn_prefill(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 3, 3); }
 int emlx_attn_plan_flags(int32_t kv_format, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim) {
     return emlx::prefill_supported(kv_format, num_q_heads, num_kv_heads, head_dim) ? emlx::kPlanWideUnits : 0;
+}
+int emlx_attn_row_class(int32_t kv_format, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, int32_t query_len) {
+    if (query_len <= 0 || num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % num_kv_heads) return -1;
+    const long long rows = (long long)query_len * (num_q_heads / num_kv_heads);
+    return emlx::unit_class(rows > (1 << 20) ? (1 << 20) : (int)rows,
+                            emlx::prefill_supported(kv_format, num_q_heads, num_kv_heads, head_dim));
 }
 }

@@ -136,7 +136,7 @@ class AttentionCall:
     def __init__(self, queries, key_cache, value_cache, block_tables, kv_lens, query_start_loc, *,
                  softmax_scale: float | None = None, sliding_window: int | None = None,
                  k_scale=None, v_scale=None, k_bias=None, v_bias=None, kernel: str | None = None,
-                 max_query_len: int = 0, plan=None):
+                 max_query_len: int = 0, plan=None, query_len_set: tp.Sequence[int] | None = None):
         nv.require_cuda(queries, key_cache, value_cache)
         dev = queries.device
         affine = key_cache.dtype == torch.uint8
@@ -180,6 +180,14 @@ class AttentionCall:
         a.max_blocks_per_seq, a.q_dtype = int(self.block_tables.shape[1]), nv.dtype_code(queries.dtype)
         a.sliding_window, a.softmax_scale = self.window, self.scale
         a.max_query_len = max(0, int(max_query_len))
+        a.row_class_mask = 0
+        if query_len_set:
+            # the host knows which query lengths occur: launch only the kernels of those row classes
+            lib_ = nv.lib()
+            for q_len in set(int(x) for x in query_len_set):
+                cls = lib_.emlx_attn_row_class(self.pool.kv_format, self.hq, self.pool.num_kv_heads, self.d, q_len)
+                if cls >= 0:
+                    a.row_class_mask |= 1 << cls
         a.status = self.status.data_ptr()
         self.args = a
         if self.kernel != "generic":
@@ -246,6 +254,7 @@ def paged_attention(
     kernel: str | None = None,
     max_query_len: int = 0,
     plan=None,
+    query_len_set: tp.Sequence[int] | None = None,
 ) -> torch.Tensor:
     """Ragged causal attention of packed queries over a paged KV pool.
 
@@ -254,8 +263,8 @@ def paged_attention(
     ``threadgroup_size`` and ``allow_fallback`` are accepted and ignored.  For affine pools
     ``k_scale``/``v_scale`` are per-group fp16 arrays and ``k_bias``/``v_bias`` join them.
     ``single_token_decode`` / ``max_query_len`` are host-side hints (an upper bound on the query tokens of
-    any sequence); without them the kernels for every row class are launched and the empty ones return at
-    once.  ``kernel`` (``None`` = automatic, ``"generic"``, ``"tiled"``, ``"decode"``, ``"prefill"``) selects
+    any sequence) and ``query_len_set`` (the distinct query lengths of the batch); without them the kernels for every
+    row class are launched and the empty ones return at once.  ``kernel`` (``None`` = automatic, ``"generic"``, ``"tiled"``, ``"decode"``, ``"prefill"``) selects
     an entry point explicitly; tests and benchmarks use it.
     """
     del use_metal, threadgroup_size, allow_fallback
@@ -264,7 +273,7 @@ def paged_attention(
     return AttentionCall(queries, key_cache, value_cache, block_tables, kv_lens, query_start_loc,
                          softmax_scale=softmax_scale, sliding_window=sliding_window, k_scale=k_scale, v_scale=v_scale,
                          k_bias=k_bias, v_bias=v_bias, kernel=kernel, max_query_len=max_query_len,
-                         plan=plan).plan().launch()
+                         plan=plan, query_len_set=query_len_set).plan().launch()
 
 
 @OperationRegistry.register
@@ -316,7 +325,7 @@ class UnifiedAttention(BaseOperation):
             softmax_scale=scale, sliding_window=cache_metadata.sliding_window,
             single_token_decode=cache_metadata.is_single_token_decode,
             max_query_len=int(getattr(cache_metadata, "max_query_len", 0) or 0),
-            plan=getattr(cache_metadata, "plan", None), **extra,
+            plan=getattr(cache_metadata, "plan", None), query_len_set=getattr(cache_metadata, "query_len_set", None), **extra,
         )
         return AttentionOutput(attention_outputs=outputs, cache_view=cache_view)
 

@@ -90,6 +90,8 @@ typedef struct emlx_attn_args {
     int32_t sliding_window;         /* 0 = off                                        */
     float softmax_scale;
     int32_t max_query_len;          /* host hint: upper bound of query tokens per sequence, 0 = unknown */
+    int32_t row_class_mask;         /* host hint: OR of 1 << emlx_attn_row_class(q_len) over the batch's query
+                                     * lengths; kernels of the other row classes are not launched; 0 = unknown */
     void* plan;                     /* from emlx_attn_plan (not used by emlx_attn_generic)        */
     size_t plan_bytes;
     void* workspace;                /* split-KV partials and counters; zero it once after allocating */
@@ -167,6 +169,9 @@ int emlx_attn_plan(const int32_t* query_start_loc, const int32_t* kv_lens, int32
 /* Flags a plan should be built with for this pool and head geometry: bit 0 = cut sequences with more than 32
  * query rows into 128-row units for the tcgen05 prefill kernel (fp16/bf16 pools, 128 % (Hq/Hkv) == 0). */
 int emlx_attn_plan_flags(int32_t kv_format, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim);
+/* Row class (0..3: which kernel variant serves it) of a sequence with `query_len` tokens in this step, for
+ * emlx_attn_args.row_class_mask; -1 for query_len <= 0 (such sequences produce no rows). */
+int emlx_attn_row_class(int32_t kv_format, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, int32_t query_len);
 
 /* (5) Unified ragged attention: decode rows and prefill chunks of one packed batch in one call.
  * Replaces paged_attention() (operations/kernels/unified_attention.py:1377-1512) and the Metal
