@@ -245,8 +245,10 @@ int emlx_rows_assign(int32_t* block_tables, int32_t* kv_lens, int32_t num_slots,
 int emlx_rows_update(int32_t* block_tables, int32_t* kv_lens, int32_t num_slots, int32_t max_blocks_per_seq,
                      const int32_t* ops, int32_t count, int32_t mode, int32_t* status, void* stream);
 
-/* Tracing aid: when `records` is a device buffer of 4 * 256 int64, every CTA of the tiled attention kernels
- * writes {start ns, end ns, tiles processed, 0} (GPU global timer) at index 4 * blockIdx.x; NULL turns it off. */
+/* Tracing aid: when `records` is a device buffer of at least 4 * 256 int64, every CTA of the tiled attention kernel
+ * writes {start ns, end ns, tiles processed, SM id} (GPU global timer) at index 4 * blockIdx.x; NULL turns it off.
+ * Builds with -DEMLX_TRACE_PARTS / -DEMLX_TRACE_PREFILL add per-part and per-tile records behind those (the buffer
+ * must then hold 1024 + 256 * 16 * 4 int64); see profiles/. */
 void emlx_set_trace_buffer(int64_t* records);
 
 /* Number of kernels this library has launched from the calling process (for launch accounting). */
