@@ -18,6 +18,7 @@ struct WriteParams {
     const int32_t* positions;
     const float* inv_freq;
     int Hq, rope_dims, traditional, has_pool;
+    int raw_ok;  // rows can be copied bit for bit in 16-byte pieces
     float pos_scale, mscale;
 };
 
@@ -156,12 +157,20 @@ __global__ void __launch_bounds__(256) kv_write_kernel(WriteParams w) {
     const int groups = D / kQuantGroup;
     QuantRow kq, vq;
     float kf[8], vf[8];  // float pools: head_dim <= 256, element d = lane + 32 i
+    // same 16-bit type on both sides, no rotation, 16-byte aligned rows: a row moves as 16-byte pieces, one per lane
+    const bool raw_copy = w.raw_ok && p.kv_format == EMLX_KV_FLOAT;
+    uint4 kraw = make_uint4(0u, 0u, 0u, 0u), vraw = kraw;
     if (p.kv_format == EMLX_KV_AFFINE8) {
         quantize_row<TIn, 8>(krow, groups, lane, kq);
         quantize_row<TIn, 8>(vrow, groups, lane, vq);
     } else if (p.kv_format == EMLX_KV_AFFINE4) {
         quantize_row<TIn, 4>(krow, groups, lane, kq);
         quantize_row<TIn, 4>(vrow, groups, lane, vq);
+    } else if (raw_copy) {
+        if (lane < D / 8) {
+            kraw = *(const uint4*)((const uint16_t*)krow.row + lane * 8);
+            vraw = *(const uint4*)((const uint16_t*)vrow.row + lane * 8);
+        }
     } else {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -177,7 +186,13 @@ __global__ void __launch_bounds__(256) kv_write_kernel(WriteParams w) {
         if (lane == 0) flag_error(w.status, EMLX_DEV_BAD_PAGE);
         return;
     }
-    if (p.kv_format == EMLX_KV_FLOAT) {
+    if (raw_copy) {
+        const int64_t off = (slot * Hkv + h) * D;
+        if (lane < D / 8) {
+            *(uint4*)((uint16_t*)p.key_cache + off + lane * 8) = kraw;
+            *(uint4*)((uint16_t*)p.value_cache + off + lane * 8) = vraw;
+        }
+    } else if (p.kv_format == EMLX_KV_FLOAT) {
         const int64_t off = (slot * Hkv + h) * D;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -231,6 +246,10 @@ static int launch_write(WriteParams& w, int in_dtype, cudaStream_t s) {
     if (warps == 0) return EMLX_OK;
     const int threads = 256;
     const unsigned blocks = (unsigned)((warps * 32 + threads - 1) / threads);
+    const emlx_pool& p = w.pool;
+    w.raw_ok = w.has_pool && w.rope_dims == 0 && p.kv_format == EMLX_KV_FLOAT && in_dtype == p.kv_dtype &&
+               (in_dtype == EMLX_F16 || in_dtype == EMLX_BF16) && p.head_dim % 8 == 0 &&
+               (((uintptr_t)w.keys | (uintptr_t)w.values | (uintptr_t)p.key_cache | (uintptr_t)p.value_cache) & 15) == 0;
     switch (in_dtype) {
         case EMLX_F16: EMLX_CUDA_OK(launch_pdl(kv_write_kernel<__half>, blocks, threads, 0, s, w)); break;
         case EMLX_BF16: EMLX_CUDA_OK(launch_pdl(kv_write_kernel<__nv_bfloat16>, blocks, threads, 0, s, w)); break;

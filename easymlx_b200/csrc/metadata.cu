@@ -17,7 +17,7 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
     int32_t* __restrict__ qsl, int32_t* __restrict__ bt_out, int32_t* __restrict__ kv_out,
     int64_t* __restrict__ slot_mapping, int32_t* __restrict__ token_positions, int64_t num_blocks, int32_t* status,
     int32_t* plan, PlanLayout L, int G,
-    int window, int class_lo, int class_hi, bool wide, int Hkv, int num_ctas) {
+    int window, int class_lo, int class_hi, bool wide, int Hkv, int num_ctas, bool scatter_later) {
     __shared__ int32_t scan_smem[kMetaThreads / 32 + 1];
     // batches of up to kSmemSeqs sequences keep their prefix sums and lengths in shared memory: every later phase
     // (work list, slot mapping) then reads them without an L2 round trip
@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
     for (int k = 0; k < kBatch; ++k) {
         const int64_t c = tid + (int64_t)k * kMetaThreads;
         g_val[k] = -1;
-        if (c < cells) {
+        if (c < cells && !scatter_later) {
             const int row = (int)(c / MB), col = (int)(c - (int64_t)row * MB);
             const int slot = slot_ids[row];
             if (slot >= 0 && slot < num_slots) g_val[k] = bt_all[(int64_t)slot * MB + col];
@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
         return r;
     };
     TokenProbe probe{0, 0, -1, false};
-    if (slot_mapping != nullptr && tid < T) probe = probe_token(tid);
+    if (slot_mapping != nullptr && tid < T && !scatter_later) probe = probe_token(tid);
 
     // attention work list in the same launch (lengths after the write are final here)
     if (plan != nullptr)
@@ -123,6 +123,7 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
                    small ? s_off : nullptr, s_cum, kSmemUnits);
 
     META_STAMP(3);
+    if (scatter_later) return;  // a large batch: the gather and the slot mapping run on many CTAs in a second launch
     // gathered page-table rows: the preloaded batch, then the rest
 #pragma unroll
     for (int k = 0; k < kBatch; ++k) {
@@ -164,6 +165,49 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
 
 }  // namespace emlx
 
+namespace emlx {
+
+// Second launch for large batches: page-table gather and slot mapping spread over many CTAs (the first launch does
+// them itself when they fit one pass of its single CTA).
+__global__ void __launch_bounds__(kMetaThreads) metadata_scatter_kernel(
+    const int32_t* __restrict__ slot_ids, int S, int T, const int32_t* __restrict__ bt_all, int num_slots, int MB, int bs,
+    const int32_t* __restrict__ qsl, const int32_t* __restrict__ kv_out, int32_t* __restrict__ bt_out,
+    int64_t* __restrict__ slot_mapping, int32_t* __restrict__ token_positions, int64_t num_blocks, int32_t* status) {
+    grid_dep_wait();  // query_start_loc and the lengths come from the first launch
+    grid_dep_launch();
+    const int64_t cells = (int64_t)S * MB;
+    const int64_t stride = (int64_t)gridDim.x * kMetaThreads;
+    for (int64_t c = (int64_t)blockIdx.x * kMetaThreads + threadIdx.x; c < cells; c += stride) {
+        const int row = (int)(c / MB), col = (int)(c - (int64_t)row * MB);
+        const int slot = slot_ids[row];
+        bt_out[c] = (slot >= 0 && slot < num_slots) ? bt_all[(int64_t)slot * MB + col] : -1;
+    }
+    if (slot_mapping == nullptr) return;
+    const int n_tok = min(T, qsl[S]);
+    for (int64_t t = (int64_t)blockIdx.x * kMetaThreads + threadIdx.x; t < T; t += stride) {
+        int64_t dst = -1;
+        int pos = 0;
+        if (t < n_tok) {
+            const int s = find_sequence(qsl, S, (int)t);
+            const int slot = s >= 0 ? slot_ids[s] : -1;
+            if (slot >= 0 && slot < num_slots) {
+                const int q_len = qsl[s + 1] - qsl[s];
+                pos = kv_out[s] - q_len + ((int)t - qsl[s]);
+                const int page_idx = pos / bs;
+                if (page_idx < MB) {
+                    const int page = bt_all[(int64_t)slot * MB + page_idx];
+                    if (page >= 0 && page < num_blocks) dst = (int64_t)page * bs + (pos - page_idx * bs);
+                    else flag_error(status, EMLX_DEV_BAD_PAGE);
+                }
+            }
+        }
+        slot_mapping[t] = dst;
+        if (token_positions) token_positions[t] = pos;
+    }
+}
+
+}  // namespace emlx
+
 #ifdef EMLX_TRACE_META
 extern "C" __attribute__((visibility("default"))) int emlx_debug_meta_trace(long long* out) {
     return (int)cudaMemcpyFromSymbol(out, emlx::g_meta_trace, sizeof(long long) * 32);
@@ -197,11 +241,22 @@ extern "C" int emlx_build_metadata(const int32_t* query_lens, const int32_t* slo
         G = num_q_heads / num_kv_heads;
         class_range(G, max_query_len, (plan_flags & kPlanWideUnits) != 0, class_lo, class_hi);
     }
+    // small batches: one launch does everything; large ones hand the gather and the slot mapping to a second launch
+    const int64_t cells = (int64_t)num_seqs * max_blocks_per_seq;
+    const bool scatter_later = cells > 4 * kMetaThreads || total_tokens > kMetaThreads;
     EMLX_CUDA_OK(launch_pdl(build_metadata_kernel, 1, kMetaThreads, 0, (cudaStream_t)stream,
         query_lens, slot_ids, num_seqs, total_tokens, block_tables_all, num_slots, max_blocks_per_seq, kv_lens_all,
         block_size, advance_kv_lens, query_start_loc, block_tables, kv_lens, slot_mapping, token_positions, num_blocks,
         status, (int32_t*)plan, L, G, sliding_window, class_lo, class_hi, (plan_flags & kPlanWideUnits) != 0, num_kv_heads,
-        min(num_sms(), kMaxGrid)));
+        min(num_sms(), kMaxGrid), scatter_later));
+    if (scatter_later) {
+        EMLX_LAUNCHED();
+        const int64_t work = cells > total_tokens ? cells : (int64_t)total_tokens;
+        const int grid = (int)min((int64_t)num_sms(), (work + kMetaThreads - 1) / kMetaThreads);
+        EMLX_CUDA_OK(launch_pdl(metadata_scatter_kernel, grid, kMetaThreads, 0, (cudaStream_t)stream, slot_ids, num_seqs,
+            total_tokens, block_tables_all, num_slots, max_blocks_per_seq, block_size, (const int32_t*)query_start_loc,
+            (const int32_t*)kv_lens, block_tables, slot_mapping, token_positions, num_blocks, status));
+    }
     EMLX_LAUNCHED();
     return EMLX_OK;
 }
