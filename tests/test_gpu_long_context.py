@@ -76,3 +76,29 @@ def test_mixed_lengths_with_empty_and_single_token_sequences():
     fast = _run(cache, q, qlens, kv, None)
     ref = _run(cache, q, qlens, kv, "generic")
     assert_close(fast, ref.float().cpu().numpy())
+
+
+@pytest.mark.parametrize("bits", [0, 8])
+def test_output_does_not_depend_on_where_the_pages_live(bits):
+    """Same logical K/V, pages shuffled through the pool: the rows must come out bit for bit the same (the work split
+    depends on lengths only, and the split merge runs in a fixed order)."""
+    import easymlx_b200 as emlx
+    hq, hkv, d = 8, 2, 128
+    qlens = [1, 1, 1, 9]
+    kv = [3000, 130, 777, 2000]
+    cache = _pool(hkv, d, kv, bits, seed=21)
+    q = torch.randn(sum(qlens), hq, d, device="cuda", dtype=torch.float16)
+    first = _run(cache, q, qlens, kv, None)
+    # move every page to a new place
+    nb = cache.num_blocks
+    perm = torch.randperm(nb, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(nb, device="cuda")
+    arrays = [cache.key_cache, cache.value_cache]
+    if cache.is_affine:
+        arrays += [cache.k_scales, cache.k_biases, cache.v_scales, cache.v_biases]
+    for a in arrays:
+        a.copy_(a[inv].clone())  # page p of the old pool is page perm[p] of the new one
+    cache.block_tables.copy_(perm[cache.block_tables.long()].to(torch.int32))
+    second = _run(cache, q, qlens, kv, None)
+    assert torch.equal(first, second)
