@@ -373,7 +373,7 @@ def run_ours(args):
     if rank == 0:
         traffic = None
         tpath = os.path.join(ROOT, "profiles", f"traffic_{args.config}.json")
-        if os.path.exists(tpath):
+        if os.path.exists(tpath) and not head_shard:  # captured on one GPU holding every KV head
             traffic = json.load(open(tpath)).get("dram_bytes_per_launch")
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
