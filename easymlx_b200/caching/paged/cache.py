@@ -310,7 +310,8 @@ class PageCacheView:
             raise ValueError("block_tables and kv_lens must be contiguous")
         plan = None
         hq = window = max_q = plan_bytes = flags = 0
-        if plan_for is not None and self.block_size == 128 and total_tokens > 0:
+        if plan_for is not None and total_tokens > 0 and (
+                self.block_size == 128 or (not self.is_affine and self.block_size in (16, 32, 64))):
             hq, window, max_q = plan_for
             flags = int(lib.emlx_attn_plan_flags(self.cache_bits if self.is_affine else nv.KV_FLOAT, hq,
                                                  self.num_kv_heads, self.head_dim))

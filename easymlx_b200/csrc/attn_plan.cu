@@ -35,7 +35,7 @@ int emlx_attn_plan(const int32_t* query_start_loc, const int32_t* kv_lens, int32
     using namespace emlx;
     if (num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % num_kv_heads)
         return fail(EMLX_ERR_INVALID, "num_q_heads must be divisible by num_kv_heads (GQA)");
-    if (block_size != kTile) return fail(EMLX_ERR_UNSUPPORTED, "the tiled kernels need page size %d", kTile);
+    if (!tiled_page_size_ok(block_size, 0)) return fail(EMLX_ERR_UNSUPPORTED, "the attention work list needs page size 16, 32, 64 or 128");
     if (num_seqs < 0 || total_tokens < 0) return fail(EMLX_ERR_INVALID, "num_seqs/total_tokens must be non-negative");
     if (!plan || plan_bytes < emlx_attn_plan_bytes(num_seqs, total_tokens, num_q_heads, num_kv_heads))
         return fail(EMLX_ERR_WORKSPACE, "plan buffer missing or smaller than emlx_attn_plan_bytes()");

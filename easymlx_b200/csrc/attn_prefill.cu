@@ -44,6 +44,7 @@ struct PrefillParams {
     long long* trace;  // measurement aid (only with EMLX_TRACE_PREFILL): per-tile cycle stamps of CTA 0
     long long num_blocks;
     int Hq, Hkv, G, MB, window;
+    int bs, ppt_log;  // page size in tokens and log2(pages per 128-token tile)
     float scale_log2e;
 };
 
@@ -241,53 +242,110 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 for (int h = 0; h < C::HALVES; ++h)
                     ptx::tma_load_3d(q_smem + h * (kPfRows * 128), &qmap, &bars->q_full, 64 * h, head * p.G, qs + row0 / p.G);
             }
-            // K runs two tiles ahead of V: the K slot of tile t is free as soon as QK of tile t - 3 is done, long before
-            // the V slot that PV of tile t - 3 still reads, and one warp issuing both in step would hold K back
-            auto load_pages = [&](int base) -> int {
-                const int idx = tile_lo + base + lane;
-                return (base + lane < ntiles && idx < p.MB) ? p.bt[(long long)seq * p.MB + idx] : -1;
-            };
-            int pg_cur = load_pages(0), pg_next = load_pages(32), base = 0;
-            auto page_of = [&](int i) -> int {  // tile i of the item, base <= i < base + 64; every lane takes part
-                const int a = __shfl_sync(0xffffffffu, pg_cur, (i - base) & 31), b = __shfl_sync(0xffffffffu, pg_next, (i - base) & 31);
-                return i - base < 32 ? a : b;
-            };
-            auto issue = [&](int i, bool is_k) {
-                const uint32_t t = kt + (uint32_t)i;
-                const int pg = page_of(i);
-                const bool bad = pg < 0 || pg >= p.num_blocks;
-                const int tok0 = bad ? -kTile : pg * kTile;  // out-of-range coordinates read as zeros
-                if (is_k) {
-                    if (lane == 0 && bad && (long long)(tile_lo + i) * kTile < kv_len) flag_error(p.status, EMLX_DEV_BAD_PAGE);
-                    const uint32_t ks = t % C::KST;
-                    if (t >= C::KST) ptx::mbar_wait(&bars->qk_done[(t - C::KST) & 3], ((t - C::KST) >> 2) & 1, abort_word);
-                    if (lane == 0 && !*abort_word) {
-                        ptx::mbar_arrive_expect_tx(&bars->k_full[ks], C::KBYTES);
-#pragma unroll
-                        for (int h = 0; h < C::HALVES; ++h)
-                            ptx::tma_load_3d(k_smem + (size_t)ks * C::KBYTES + h * (kTile * 128), &kmap, &bars->k_full[ks], 64 * h, head, tok0);
+            if (p.ppt_log == 0) {  // one page per tile: the common case keeps the shortest instruction stream (this warp
+                                   // shares a scheduler with a softmax warp)
+                // K runs two tiles ahead of V: the K slot of tile t is free as soon as QK of tile t - 3 is done, long before
+                // the V slot that PV of tile t - 3 still reads, and one warp issuing both in step would hold K back
+                auto load_pages = [&](int base) -> int {
+                    const int idx = tile_lo + base + lane;
+                    return (base + lane < ntiles && idx < p.MB) ? p.bt[(long long)seq * p.MB + idx] : -1;
+                };
+                int pg_cur = load_pages(0), pg_next = load_pages(32), base = 0;
+                auto page_of = [&](int i) -> int {  // tile i of the item, base <= i < base + 64; every lane takes part
+                    const int a = __shfl_sync(0xffffffffu, pg_cur, (i - base) & 31), b = __shfl_sync(0xffffffffu, pg_next, (i - base) & 31);
+                    return i - base < 32 ? a : b;
+                };
+                auto issue = [&](int i, bool is_k) {
+                    const uint32_t t = kt + (uint32_t)i;
+                    const int pg = page_of(i);
+                    const bool bad = pg < 0 || pg >= p.num_blocks;
+                    const int tok0 = bad ? -kTile : pg * kTile;  // out-of-range coordinates read as zeros
+                    if (is_k) {
+                        if (lane == 0 && bad && (long long)(tile_lo + i) * kTile < kv_len) flag_error(p.status, EMLX_DEV_BAD_PAGE);
+                        const uint32_t ks = t % C::KST;
+                        if (t >= C::KST) ptx::mbar_wait(&bars->qk_done[(t - C::KST) & 3], ((t - C::KST) >> 2) & 1, abort_word);
+                        if (lane == 0 && !*abort_word) {
+                            ptx::mbar_arrive_expect_tx(&bars->k_full[ks], C::KBYTES);
+    #pragma unroll
+                            for (int h = 0; h < C::HALVES; ++h)
+                                ptx::tma_load_3d(k_smem + (size_t)ks * C::KBYTES + h * (kTile * 128), &kmap, &bars->k_full[ks], 64 * h, head, tok0);
+                        }
+                    } else {
+                        const uint32_t vs = t % C::VST;
+                        if (t >= C::VST) ptx::mbar_wait(&bars->pv_done[(t - C::VST) & 3], ((t - C::VST) >> 2) & 1, abort_word);
+                        if (lane == 0 && !*abort_word) {
+                            ptx::mbar_arrive_expect_tx(&bars->v_full[vs], C::KBYTES);
+    #pragma unroll
+                            for (int h = 0; h < C::HALVES; ++h)
+                                ptx::tma_load_3d(v_smem + (size_t)vs * C::KBYTES + h * (kTile * 128), &vmap, &bars->v_full[vs], 64 * h, head, tok0);
+                        }
                     }
-                } else {
-                    const uint32_t vs = t % C::VST;
-                    if (t >= C::VST) ptx::mbar_wait(&bars->pv_done[(t - C::VST) & 3], ((t - C::VST) >> 2) & 1, abort_word);
-                    if (lane == 0 && !*abort_word) {
-                        ptx::mbar_arrive_expect_tx(&bars->v_full[vs], C::KBYTES);
-#pragma unroll
-                        for (int h = 0; h < C::HALVES; ++h)
-                            ptx::tma_load_3d(v_smem + (size_t)vs * C::KBYTES + h * (kTile * 128), &vmap, &bars->v_full[vs], 64 * h, head, tok0);
+                    __syncwarp();
+                };
+                issue(0, true);
+                if (ntiles > 1) issue(1, true);
+                for (int i = 0; i < ntiles; ++i) {
+                    if (i + 2 < ntiles) issue(i + 2, true);
+                    issue(i, false);
+                    if (i + 1 == base + 32) {  // tiles up to base + 34 have been looked up: the older half is done with
+                        base += 32;
+                        pg_cur = pg_next;
+                        pg_next = load_pages(base + 32);
                     }
                 }
-                __syncwarp();
-            };
-            issue(0, true);
-            if (ntiles > 1) issue(1, true);
-            for (int i = 0; i < ntiles; ++i) {
-                if (i + 2 < ntiles) issue(i + 2, true);
-                issue(i, false);
-                if (i + 1 == base + 32) {  // tiles up to base + 34 have been looked up: the older half is done with
-                    base += 32;
-                    pg_cur = pg_next;
-                    pg_next = load_pages(base + 32);
+            } else {
+                // K runs two tiles ahead of V: the K slot of tile t is free as soon as QK of tile t - 3 is done, long before
+                // the V slot that PV of tile t - 3 still reads, and one warp issuing both in step would hold K back
+                // page ids in batches of 32: lane l holds page (l mod pages-per-tile) of tile base + l / pages-per-tile, and two
+                // batches (cur, next) are kept so that K can run ahead
+                const int ppt_log = p.ppt_log, ppt = 1 << ppt_log, tiles_per_batch = 32 >> ppt_log;
+                auto load_pages = [&](int base) -> int {
+                    const int tile = base + (lane >> ppt_log);
+                    const long long pidx = ((long long)(tile_lo + tile) << ppt_log) + (lane & (ppt - 1));
+                    return (tile < ntiles && pidx < p.MB) ? p.bt[(long long)seq * p.MB + pidx] : -1;
+                };
+                int pg_cur = load_pages(0), pg_next = load_pages(tiles_per_batch), base = 0;
+                auto page_of = [&](int i, int sub) -> int {  // page `sub` of tile i, base <= i < base + 2 batches; every lane takes part
+                    const int idx = ((i - base) << ppt_log) + sub;
+                    const int a = __shfl_sync(0xffffffffu, pg_cur, idx & 31), b = __shfl_sync(0xffffffffu, pg_next, idx & 31);
+                    return idx < 32 ? a : b;
+                };
+                auto issue = [&](int i, bool is_k) {
+                    const uint32_t t = kt + (uint32_t)i;
+                    const uint32_t slot = is_k ? t % C::KST : t % C::VST;
+                    if (is_k) {
+                        if (t >= C::KST) ptx::mbar_wait(&bars->qk_done[(t - C::KST) & 3], ((t - C::KST) >> 2) & 1, abort_word);
+                    } else {
+                        if (t >= C::VST) ptx::mbar_wait(&bars->pv_done[(t - C::VST) & 3], ((t - C::VST) >> 2) & 1, abort_word);
+                    }
+                    const bool go = lane == 0 && !*abort_word;
+                    uint64_t* bar = is_k ? &bars->k_full[slot] : &bars->v_full[slot];
+                    uint8_t* tile = (is_k ? k_smem : v_smem) + (size_t)slot * C::KBYTES;
+                    if (go) ptx::mbar_arrive_expect_tx(bar, C::KBYTES);
+                    for (int sub = 0; sub < ppt; ++sub) {
+                        const int pg = page_of(i, sub);
+                        if (go) {
+                            const bool bad = pg < 0 || pg >= p.num_blocks;
+                            const int tok0 = bad ? -p.bs : pg * p.bs;  // out-of-range coordinates read as zeros
+                            if (is_k && bad && (long long)(tile_lo + i) * kTile + (long long)sub * p.bs < kv_len)
+                                flag_error(p.status, EMLX_DEV_BAD_PAGE);
+    #pragma unroll
+                            for (int h = 0; h < C::HALVES; ++h)
+                                ptx::tma_load_3d(tile + h * (kTile * 128) + (size_t)sub * p.bs * 128, is_k ? &kmap : &vmap, bar, 64 * h, head, tok0);
+                        }
+                    }
+                    __syncwarp();
+                };
+                issue(0, true);
+                if (ntiles > 1) issue(1, true);
+                for (int i = 0; i < ntiles; ++i) {
+                    if (i + 2 < ntiles) issue(i + 2, true);
+                    issue(i, false);
+                    if (i + 1 == base + tiles_per_batch) {  // the tiles of the older batch are all issued (K is at most two ahead)
+                        base += tiles_per_batch;
+                        pg_cur = pg_next;
+                        pg_next = load_pages(base + tiles_per_batch);
+                    }
                 }
             }
             kt += (uint32_t)ntiles;
@@ -577,6 +635,7 @@ int launch_prefill(const emlx_attn_args* a, const emlx_pool* pool, const int32_t
     p.hdr = plan_class_hdr; p.unit_seq = unit_seq; p.unit_row0 = unit_row0; p.unit_tile_lo = unit_tile_lo; p.unit_cum = unit_cum; p.unit_order = unit_order;
     p.status = a->status; p.num_blocks = pool->num_blocks; p.trace = trace_buffer();
     p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.MB = a->max_blocks_per_seq; p.window = a->sliding_window;
+    p.bs = pool->block_size; p.ppt_log = pages_per_tile_log2(pool->block_size);
     p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
     const bool bf16 = a->q_dtype == EMLX_BF16;
     if (D == 128) return bf16 ? launch_pf<128, true>(qmap, maps, p, stream) : launch_pf<128, false>(qmap, maps, p, stream);

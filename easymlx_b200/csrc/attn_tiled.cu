@@ -52,6 +52,7 @@ struct TiledParams {
     const __half* v_bias;
     long long num_blocks;
     int Hq, Hkv, G, MB, window;
+    int bs, ppt_log;  // page size in tokens and log2(pages per 128-token tile)
     float scale_log2e;
 };
 
@@ -222,9 +223,15 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
         const int tile_lo = p.unit_tile_lo[w.u];
         const int kv_len = p.kv_lens[seq];
         const int run = (int)min((long long)(w.ntiles - w.j), f_stop - f);
-        // page ids of the part's first tiles: requested before the descriptor is built so that both latencies overlap
-        int page_first = -1;
-        if (lane < run && tile_lo + w.j + lane < p.MB) page_first = p.bt[(long long)seq * p.MB + tile_lo + w.j + lane];
+        // page ids of the part's first tiles: requested before the descriptor is built so that both latencies overlap.
+        // A batch of 32 ids covers 32 >> ppt_log tiles: lane l holds page (l mod pages-per-tile) of tile base + l / ppt.
+        const int ppt_log = p.ppt_log, ppt = 1 << ppt_log, tiles_per_batch = 32 >> ppt_log;
+        auto load_ids = [&](int base) -> int {
+            const int tile = base + (lane >> ppt_log);
+            const long long pidx = ((long long)(tile_lo + w.j + tile) << ppt_log) + (lane & (ppt - 1));
+            return (tile < run && pidx < p.MB) ? p.bt[(long long)seq * p.MB + pidx] : -1;
+        };
+        const int page_first = load_ids(0);
         if constexpr (C::PRIVATE) {
             // descriptor + Q rows of this part, so that the consumers start it without touching global memory
             const uint32_t slot = part_idx % C::NDESC, use = part_idx / C::NDESC;
@@ -248,45 +255,94 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
             __syncwarp();
             ++part_idx;
         }
-        for (int base = 0; base < run; base += 32) {
-            const int idx = tile_lo + w.j + base + lane;
-            int page = page_first;
-            if (base > 0) {
-                page = -1;
-                if (base + lane < run && idx < p.MB) page = p.bt[(long long)seq * p.MB + idx];
+        if (ppt_log == 0) {  // one page per tile: the common case, kept as short as it can be
+            for (int base = 0; base < run; base += 32) {
+                const int idx = tile_lo + w.j + base + lane;
+                int page = page_first;
+                if (base > 0) {
+                    page = -1;
+                    if (base + lane < run && idx < p.MB) page = p.bt[(long long)seq * p.MB + idx];
+                }
+                const int cnt = min(32, run - base);
+                for (int i = 0; i < cnt; ++i) {
+                    int pg = __shfl_sync(0xffffffffu, page, i);
+                    const uint32_t stage = it % C::STAGES, use = it / C::STAGES;
+                    if (use > 0) ptx::mbar_wait(&empty[stage], (use & 1) ^ 1, abort_word);
+                    if (lane == 0 && !*abort_word) {
+                        const bool bad = pg < 0 || pg >= p.num_blocks;
+                        if (bad && (long long)(tile_lo + w.j + base + i) * kTile < kv_len) flag_error(p.status, EMLX_DEV_BAD_PAGE);
+                        uint8_t* st = stages + (size_t)stage * C::STAGE;
+                        ptx::mbar_arrive_expect_tx(&full[stage], C::STAGE);
+                        if constexpr (FMT == 0) {
+                            // a page id outside the pool gives out-of-range coordinates: the tile is zero-filled
+                            const int tok0 = bad ? -kTile : pg * kTile;
+    #pragma unroll
+                            for (int h = 0; h < D / 64; ++h) {
+                                ptx::tma_load_3d(st + h * (kTile * 128), kmap, &full[stage], 64 * h, w.head, tok0);
+                                ptx::tma_load_3d(st + C::KBYTES + h * (kTile * 128), vmap, &full[stage], 64 * h, w.head, tok0);
+                            }
+                        } else {
+                            const long long pgc = bad ? 0 : pg;  // keep every address inside the pool; such tiles are masked
+                            ptx::tma_load_3d(st, kmap, &full[stage], 0, w.head, (int)(pgc * kTile));
+                            ptx::tma_load_2d(st + C::KBYTES, vmap, &full[stage], 0, (int)((pgc * p.Hkv + w.head) * D));
+                            const long long sb = (pgc * p.Hkv + w.head) * (long long)(kTile * C::GROUPS);
+                            uint8_t* sbs = st + C::KBYTES + C::VBYTES;
+                            ptx::bulk_load(sbs + 0 * C::SB1, p.k_scale + sb, C::SB1, &full[stage]);
+                            ptx::bulk_load(sbs + 1 * C::SB1, p.k_bias + sb, C::SB1, &full[stage]);
+                            ptx::bulk_load(sbs + 2 * C::SB1, p.v_scale + sb, C::SB1, &full[stage]);
+                            ptx::bulk_load(sbs + 3 * C::SB1, p.v_bias + sb, C::SB1, &full[stage]);
+                        }
+                    }
+                    __syncwarp();
+                    ++it;
+                }
             }
-            const int cnt = min(32, run - base);
-            for (int i = 0; i < cnt; ++i) {
-                int pg = __shfl_sync(0xffffffffu, page, i);
-                const uint32_t stage = it % C::STAGES, use = it / C::STAGES;
-                if (use > 0) ptx::mbar_wait(&empty[stage], (use & 1) ^ 1, abort_word);
-                if (lane == 0 && !*abort_word) {
-                    const bool bad = pg < 0 || pg >= p.num_blocks;
-                    if (bad && (long long)(tile_lo + w.j + base + i) * kTile < kv_len) flag_error(p.status, EMLX_DEV_BAD_PAGE);
+        } else {
+            for (int base = 0; base < run; base += tiles_per_batch) {
+                const int page = base == 0 ? page_first : load_ids(base);
+                const int cnt = min(tiles_per_batch, run - base);
+                for (int i = 0; i < cnt; ++i) {
+                    const uint32_t stage = it % C::STAGES, use = it / C::STAGES;
+                    if (use > 0) ptx::mbar_wait(&empty[stage], (use & 1) ^ 1, abort_word);
+                    const bool go = lane == 0 && !*abort_word;
                     uint8_t* st = stages + (size_t)stage * C::STAGE;
-                    ptx::mbar_arrive_expect_tx(&full[stage], C::STAGE);
+                    const long long tile_tok = (long long)(tile_lo + w.j + base + i) * kTile;
+                    if (go) ptx::mbar_arrive_expect_tx(&full[stage], C::STAGE);
                     if constexpr (FMT == 0) {
-                        // a page id outside the pool gives out-of-range coordinates: the tile is zero-filled
-                        const int tok0 = bad ? -kTile : pg * kTile;
-#pragma unroll
-                        for (int h = 0; h < D / 64; ++h) {
-                            ptx::tma_load_3d(st + h * (kTile * 128), kmap, &full[stage], 64 * h, w.head, tok0);
-                            ptx::tma_load_3d(st + C::KBYTES + h * (kTile * 128), vmap, &full[stage], 64 * h, w.head, tok0);
+                        for (int sub = 0; sub < ppt; ++sub) {
+                            const int pg = __shfl_sync(0xffffffffu, page, (i << ppt_log) + sub);
+                            if (go) {
+                                const bool bad = pg < 0 || pg >= p.num_blocks;
+                                if (bad && tile_tok + (long long)sub * p.bs < kv_len) flag_error(p.status, EMLX_DEV_BAD_PAGE);
+                                // a page id outside the pool gives out-of-range coordinates: its rows are zero-filled
+                                const int tok0 = bad ? -p.bs : pg * p.bs;
+                                uint8_t* dst = st + (size_t)sub * p.bs * 128;
+    #pragma unroll
+                                for (int h = 0; h < D / 64; ++h) {
+                                    ptx::tma_load_3d(dst + h * (kTile * 128), kmap, &full[stage], 64 * h, w.head, tok0);
+                                    ptx::tma_load_3d(dst + C::KBYTES + h * (kTile * 128), vmap, &full[stage], 64 * h, w.head, tok0);
+                                }
+                            }
                         }
                     } else {
-                        const long long pgc = bad ? 0 : pg;  // keep every address inside the pool; such tiles are masked
-                        ptx::tma_load_3d(st, kmap, &full[stage], 0, w.head, (int)(pgc * kTile));
-                        ptx::tma_load_2d(st + C::KBYTES, vmap, &full[stage], 0, (int)((pgc * p.Hkv + w.head) * D));
-                        const long long sb = (pgc * p.Hkv + w.head) * (long long)(kTile * C::GROUPS);
-                        uint8_t* sbs = st + C::KBYTES + C::VBYTES;
-                        ptx::bulk_load(sbs + 0 * C::SB1, p.k_scale + sb, C::SB1, &full[stage]);
-                        ptx::bulk_load(sbs + 1 * C::SB1, p.k_bias + sb, C::SB1, &full[stage]);
-                        ptx::bulk_load(sbs + 2 * C::SB1, p.v_scale + sb, C::SB1, &full[stage]);
-                        ptx::bulk_load(sbs + 3 * C::SB1, p.v_bias + sb, C::SB1, &full[stage]);
+                        const int pg = __shfl_sync(0xffffffffu, page, i);
+                        if (go) {
+                            const bool bad = pg < 0 || pg >= p.num_blocks;
+                            if (bad && tile_tok < kv_len) flag_error(p.status, EMLX_DEV_BAD_PAGE);
+                            const long long pgc = bad ? 0 : pg;  // keep every address inside the pool; such tiles are masked
+                            ptx::tma_load_3d(st, kmap, &full[stage], 0, w.head, (int)(pgc * kTile));
+                            ptx::tma_load_2d(st + C::KBYTES, vmap, &full[stage], 0, (int)((pgc * p.Hkv + w.head) * D));
+                            const long long sb = (pgc * p.Hkv + w.head) * (long long)(kTile * C::GROUPS);
+                            uint8_t* sbs = st + C::KBYTES + C::VBYTES;
+                            ptx::bulk_load(sbs + 0 * C::SB1, p.k_scale + sb, C::SB1, &full[stage]);
+                            ptx::bulk_load(sbs + 1 * C::SB1, p.k_bias + sb, C::SB1, &full[stage]);
+                            ptx::bulk_load(sbs + 2 * C::SB1, p.v_scale + sb, C::SB1, &full[stage]);
+                            ptx::bulk_load(sbs + 3 * C::SB1, p.v_bias + sb, C::SB1, &full[stage]);
+                        }
                     }
+                    __syncwarp();
+                    ++it;
                 }
-                __syncwarp();
-                ++it;
             }
         }
         f += run;
@@ -937,9 +993,9 @@ static CUtensorMapSwizzle swizzle_of(int row_bytes) {
 // Tensor maps depend only on the pool's address and geometry; they are encoded once and cached.
 int get_maps(const emlx_pool& pool, MapPair** out) {
     static std::mutex mu;
-    static std::map<std::tuple<void*, void*, long long, int, int, int, int>, MapPair> cache;
+    static std::map<std::tuple<void*, void*, long long, int, int, int, int, int>, MapPair> cache;
     auto key = std::make_tuple(pool.key_cache, pool.value_cache, (long long)pool.num_blocks, pool.num_kv_heads,
-                               pool.head_dim, pool.kv_format, pool.kv_dtype);
+                               pool.head_dim, pool.kv_format, pool.kv_dtype, pool.block_size);
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) {
@@ -956,9 +1012,10 @@ int get_maps(const emlx_pool& pool, MapPair** out) {
     CUresult r1, r2;
     if (pool.kv_format == EMLX_KV_FLOAT) {
         const CUtensorMapDataType dt = pool.kv_dtype == EMLX_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-        const cuuint64_t dims[3] = {D, Hkv, NB * kTile};
+        const cuuint64_t bs = (cuuint64_t)pool.block_size;  // a box is one page (128 tokens, or a part of a tile)
+        const cuuint64_t dims[3] = {D, Hkv, NB * bs};
         const cuuint64_t strides[2] = {D * 2, Hkv * D * 2};
-        const cuuint32_t box[3] = {64, 1, kTile};
+        const cuuint32_t box[3] = {64, 1, (cuuint32_t)bs};
         // a tile row is D*2 contiguous bytes: do not let L2 promotion pull in the neighbouring head's row
         const CUtensorMapL2promotion promo = D * 2 >= 256 ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
         r1 = enc(&mp.k, dt, 3, pool.key_cache, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -1030,7 +1087,8 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
     if (int rc = validate_attn(a, pool, true)) return rc;
     if (a->total_tokens == 0) return EMLX_OK;
     const int D = pool->head_dim, Hq = a->num_q_heads, Hkv = pool->num_kv_heads, G = Hq / Hkv;
-    if (pool->block_size != kTile) return fail(EMLX_ERR_UNSUPPORTED, "the tiled kernels need page size %d", kTile);
+    if (!tiled_page_size_ok(pool->block_size, pool->kv_format))
+        return fail(EMLX_ERR_UNSUPPORTED, "the tiled kernels need page size 128 (16, 32 or 64 also for fp16/bf16 pools)");
     if (D != 64 && D != 128) return fail(EMLX_ERR_UNSUPPORTED, "the tiled kernels need head_dim 64 or 128");
     if (a->q_dtype == EMLX_F32) return fail(EMLX_ERR_UNSUPPORTED, "the tiled kernels need fp16 or bf16 queries");
     const bool bf16 = a->q_dtype == EMLX_BF16;
@@ -1076,6 +1134,7 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
         p.v_scale = (const __half*)pool->v_scale; p.v_bias = (const __half*)pool->v_bias;
         p.num_blocks = pool->num_blocks;
         p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.MB = a->max_blocks_per_seq; p.window = a->sliding_window;
+        p.bs = pool->block_size; p.ppt_log = pages_per_tile_log2(pool->block_size);
         p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
         if (int rc = launch_class(c, D, pool->kv_format, bf16, *maps, p, (cudaStream_t)stream)) return rc;
     }

@@ -19,6 +19,13 @@ constexpr int kTile = 128;        // tokens per KV tile = page size the tiled ke
 constexpr int kNumClasses = 4;
 constexpr int kPlanWideUnits = 1;  // plan flag: cut sequences with more than 32 rows into 128-row units (class 3)
 constexpr int kPlanHeaderWords = 16;
+// Page sizes the tiled kernels read: a 128-token tile is one page, or 2 / 4 / 8 pages of a 16/32-bit pool (affine pools
+// keep their values transposed inside a 128-token page, so they need that size).
+__host__ __device__ inline bool tiled_page_size_ok(int block_size, int kv_format) {
+    if (block_size == 128) return true;
+    return kv_format == 0 && (block_size == 64 || block_size == 32 || block_size == 16);
+}
+__host__ __device__ inline int pages_per_tile_log2(int block_size) { return block_size == 128 ? 0 : block_size == 64 ? 1 : block_size == 32 ? 2 : 3; }
 // relative cost of a tile and of a part boundary when slices are cut: measured 1 : 2.3 on the 8-row decode kernel;
 // the 128-row kernel keeps 1 : 1.5
 constexpr long long kTileCost = 4;

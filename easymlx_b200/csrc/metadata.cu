@@ -234,7 +234,7 @@ extern "C" int emlx_build_metadata(const int32_t* query_lens, const int32_t* slo
     if (plan) {
         if (num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % num_kv_heads)
             return fail(EMLX_ERR_INVALID, "num_q_heads must be divisible by num_kv_heads (GQA)");
-        if (block_size != kTile) return fail(EMLX_ERR_UNSUPPORTED, "the attention work list needs page size %d", kTile);
+        if (!tiled_page_size_ok(block_size, 0)) return fail(EMLX_ERR_UNSUPPORTED, "the attention work list needs page size 16, 32, 64 or 128");
         L = plan_layout(num_seqs, total_tokens, num_q_heads, num_kv_heads);
         if (plan_bytes < (size_t)L.words * sizeof(int32_t))
             return fail(EMLX_ERR_WORKSPACE, "plan buffer smaller than emlx_attn_plan_bytes()");

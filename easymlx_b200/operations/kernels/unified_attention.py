@@ -24,7 +24,8 @@ from ..requirements import ExecutionMode, MetadataField, RequirementsBuilder
 
 _CHECK = os.environ.get("EASYMLX_B200_CHECK", "0") not in ("", "0")
 _TILED_HEAD_DIMS = (64, 128)
-_TILED_BLOCK_SIZE = 128
+_TILED_BLOCK_SIZES_FLOAT = (16, 32, 64, 128)  # a 128-token tile is one page or 2 / 4 / 8 pages
+_TILED_BLOCK_SIZE_AFFINE = 128              # affine pools keep values transposed inside a 128-token page
 
 
 @dataclass
@@ -159,7 +160,8 @@ class AttentionCall:
         self.scales = (k_scale, v_scale, k_bias, v_bias)
         self.pool, _ = _make_pool(key_cache, value_cache, self.d, k_scale, v_scale, k_bias, v_bias)
         tiled_ok = (
-            self.pool.block_size == _TILED_BLOCK_SIZE and self.d in _TILED_HEAD_DIMS
+            (self.pool.block_size == _TILED_BLOCK_SIZE_AFFINE if affine else self.pool.block_size in _TILED_BLOCK_SIZES_FLOAT)
+            and self.d in _TILED_HEAD_DIMS
             and queries.dtype in (torch.float16, torch.bfloat16)
             and (affine or key_cache.dtype == queries.dtype)
             and (not affine or queries.dtype == torch.float16)
@@ -168,7 +170,7 @@ class AttentionCall:
             self.kernel = "tiled" if tiled_ok else "generic"
         if self.kernel != "generic" and not tiled_ok:
             raise NotImplementedError(
-                "the tiled kernels need page size 128, head_dim 64 or 128, fp16/bf16 queries and a pool of the "
+                "the tiled kernels need page size 128 (or 16/32/64 with a 16-bit pool), head_dim 64 or 128, fp16/bf16 queries and a pool of the "
                 "same dtype (or fp16 queries with an affine pool)")
         self.num_seqs = int(self.block_tables.shape[0])
         self.status = _scratch.get(dev, "status", 4, zero=True)

@@ -12,12 +12,12 @@ from gpu_util import assert_close
 pytestmark = pytest.mark.gpu
 
 
-def _pool(hkv, d, lens, bits, seed):
+def _pool(hkv, d, lens, bits, seed, block_size=128, dtype=torch.float16):
     from easymlx_b200 import PageCacheView
     g = torch.Generator(device="cuda").manual_seed(seed)
-    pages = [-(-int(n) // 128) for n in lens]
-    cache = PageCacheView.init(num_seqs=len(lens), max_seq_len=max(pages) * 128, num_kv_heads=hkv, head_dim=d,
-                               block_size=128, cache_dtype=(f"affine{bits}" if bits else None), device="cuda")
+    pages = [-(-int(n) // block_size) for n in lens]
+    cache = PageCacheView.init(num_seqs=len(lens), max_seq_len=max(pages) * block_size, num_kv_heads=hkv, head_dim=d,
+                               block_size=block_size, dtype=dtype, cache_dtype=(f"affine{bits}" if bits else None), device="cuda")
     for a in (cache.key_cache, cache.value_cache):
         if a.dtype == torch.uint8:
             a.copy_(torch.randint(0, 256, a.shape, device="cuda", generator=g, dtype=torch.uint8))
@@ -102,3 +102,27 @@ def test_output_does_not_depend_on_where_the_pages_live(bits):
     cache.block_tables.copy_(perm[cache.block_tables.long()].to(torch.int32))
     second = _run(cache, q, qlens, kv, None)
     assert torch.equal(first, second)
+
+
+@pytest.mark.parametrize("block_size", [16, 32, 64])
+@pytest.mark.parametrize("d,dtype", [(128, torch.float16), (64, torch.bfloat16)])
+def test_small_pages_take_the_fast_kernels(block_size, d, dtype):
+    """Pages of 16 / 32 / 64 tokens (the reference's default is 16): a 128-token tile is assembled from several pages.
+    Decode rows, a 3-token row and a prefill chunk; page order scrambled; fast path against the coverage kernel."""
+    import easymlx_b200 as emlx
+    hq, hkv = 8, 2
+    qlens = [1, 3, 1, 150, 1]
+    prior = [1000, 77, 0, 300, 2049]
+    kv = [a + b for a, b in zip(qlens, prior)]
+    cache = _pool(hkv, d, kv, 0, seed=block_size, block_size=block_size, dtype=dtype)
+    # scatter the pages: every row of the table is a random set of distinct pages
+    g = torch.Generator(device="cuda").manual_seed(9)
+    perm = torch.randperm(cache.num_blocks, device="cuda", generator=g).to(torch.int32)
+    cache.block_tables.copy_(perm.reshape(cache.block_tables.shape))
+    q = torch.randn(sum(qlens), hq, d, device="cuda", generator=g).to(dtype)
+    args = (q, cache.key_cache, cache.value_cache, cache.block_tables, torch.tensor(kv, dtype=torch.int32, device="cuda"),
+            emlx.build_query_start_loc(qlens, device="cuda"))
+    fast = emlx.paged_attention(*args, max_query_len=max(qlens), kernel="tiled")
+    ref = emlx.paged_attention(*args, kernel="generic")
+    assert_close(fast, ref.float().cpu().numpy(), atol=(2e-3 if dtype == torch.float16 else 8e-3), rtol=(1e-2 if dtype == torch.float16 else 2e-2))
+    assert torch.equal(fast, emlx.paged_attention(*args, max_query_len=max(qlens), query_len_set=qlens))
