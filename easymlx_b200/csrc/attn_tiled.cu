@@ -214,14 +214,28 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
         }
     }
     uint32_t it = 0;
+    // Consecutive parts are usually the KV heads of one unit: same sequence, same tiles, same pages.  What the last part
+    // read from global memory is kept, so that a head switch costs the producer no dependent loads (while it waits for
+    // them no tile is requested, and at HBM speed the ring never makes the lost time up again).
+    int c_u = -1, c_seq = 0, c_tile_lo = 0, c_kv_len = 0, c_row0 = 0, c_qs = 0, c_qlen = 0, c_cum = 0;
+    int c_pages = -1, c_pages_j = -1, c_pages_run = 0;
     for (int rg = 0; rg < 2; ++rg) {
     long long f = range_lo[rg];
     const long long f_stop = range_hi[rg];
     if (f < f_stop) w.locate_near(f, range_hint[rg], p.unit_cum, num_units, p.Hkv);
     while (f < f_stop && !*abort_word) {
-        const int seq = p.unit_seq[w.u];
-        const int tile_lo = p.unit_tile_lo[w.u];
-        const int kv_len = p.kv_lens[seq];
+        if (w.u != c_u) {
+            c_u = w.u;
+            c_seq = p.unit_seq[w.u];
+            c_tile_lo = p.unit_tile_lo[w.u];
+            c_row0 = p.unit_row0[w.u];
+            c_cum = p.unit_cum[w.u];
+            c_kv_len = p.kv_lens[c_seq];
+            c_qs = p.qsl[c_seq];
+            c_qlen = p.qsl[c_seq + 1] - c_qs;
+            c_pages_j = -1;
+        }
+        const int seq = c_seq, tile_lo = c_tile_lo, kv_len = c_kv_len;
         const int run = (int)min((long long)(w.ntiles - w.j), f_stop - f);
         // page ids of the part's first tiles: requested before the descriptor is built so that both latencies overlap.
         // A batch of 32 ids covers 32 >> ppt_log tiles: lane l holds page (l mod pages-per-tile) of tile base + l / ppt.
@@ -231,17 +245,22 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
             const long long pidx = ((long long)(tile_lo + w.j + tile) << ppt_log) + (lane & (ppt - 1));
             return (tile < run && pidx < p.MB) ? p.bt[(long long)seq * p.MB + pidx] : -1;
         };
-        const int page_first = load_ids(0);
+        if (c_pages_j != w.j || run > c_pages_run) {
+            c_pages = load_ids(0);
+            c_pages_j = w.j;
+            c_pages_run = run;
+        }
+        const int page_first = c_pages;
         if constexpr (C::PRIVATE) {
             // descriptor + Q rows of this part, so that the consumers start it without touching global memory
             const uint32_t slot = part_idx % C::NDESC, use = part_idx / C::NDESC;
             if (use > 0) ptx::mbar_wait(&dempty[slot], (use & 1) ^ 1, abort_word);
             if (lane == 0 && !*abort_word) {
                 PartDesc* d = (PartDesc*)(fixed + (size_t)slot * C::DESC_BYTES);
-                const int row0 = p.unit_row0[w.u], qs = p.qsl[seq], q_len = p.qsl[seq + 1] - qs;
+                const int row0 = c_row0, qs = c_qs, q_len = c_qlen;
                 const int R = q_len * p.G, rows_here = min(C::ROWS, R - row0);
                 d->seq = seq; d->row0 = row0; d->tile_lo = tile_lo; d->qs = qs; d->q_len = q_len; d->kv_len = kv_len;
-                d->head = w.head; d->u = w.u; d->j = w.j; d->run = run; d->ntiles = w.ntiles; d->cum_u = p.unit_cum[w.u];
+                d->head = w.head; d->u = w.u; d->j = w.j; d->run = run; d->ntiles = w.ntiles; d->cum_u = c_cum;
                 ptx::mbar_arrive_expect_tx(&dfull[slot], (uint32_t)(rows_here * D * 2));
                 uint8_t* qdst = (uint8_t*)d + 64;
                 for (int r = row0; r < row0 + rows_here;) {
