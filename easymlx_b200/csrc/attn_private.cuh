@@ -82,8 +82,15 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
 
     while (remaining > 0) {
         // ------------------------------------------------------------------ part descriptor from the producer
+#ifdef EMLX_TRACE_PARTS
+        long long trace_a = 0, trace_b = 0, trace_c = 0, trace_d = 0;
+        if (p.trace && tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(trace_a));
+#endif
         const uint32_t dslot = part_idx % C::NDESC;
         ptx::mbar_wait(&dfull[dslot], (part_idx / C::NDESC) & 1, abort_word);
+#ifdef EMLX_TRACE_PARTS
+        if (p.trace && tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(trace_b));
+#endif
         const PartDesc* desc = (const PartDesc*)(fixed + (size_t)dslot * C::DESC_BYTES);
         const int row0 = desc->row0, tile_lo = desc->tile_lo, qs = desc->qs, q_len = desc->q_len;
         const int kv_len = desc->kv_len, head = desc->head, unit = desc->u, j_first = desc->j, run = desc->run;
@@ -169,6 +176,9 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
             for (int j = 0; j < NG; ++j) bsum[j][nt][0] = bsum[j][nt][1] = 0.f;
         }
 
+#ifdef EMLX_TRACE_PARTS
+        if (p.trace && tid == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(trace_c));
+#endif
         for (int jj = 0; jj < run; ++jj, ++it) {
             const uint32_t stage = it % C::STAGES;
             uint8_t* st = stages + (size_t)stage * C::STAGE;
@@ -177,6 +187,9 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
             const int t0 = (tile_lo + j_first + jj) * kTile;
             const bool interior = (t0 + kTile <= hi_min) && (t0 >= lo_max);
             ptx::mbar_wait(&full[stage], (it / C::STAGES) & 1, abort_word);
+#ifdef EMLX_TRACE_PARTS
+            if (p.trace && tid == 0 && jj == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(trace_d));
+#endif
 #ifdef EMLX_EXPERIMENT_STREAM_ONLY  // measurement aid: consume the tiles without any arithmetic
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&empty[stage]);
@@ -496,7 +509,8 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
             long long now;
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
             long long* rec = p.trace + 1024 + ((size_t)blockIdx.x * 16 + part_idx) * 4;
-            rec[0] = trace_t0; rec[1] = now; rec[2] = run; rec[3] = complete ? 0 : 1;
+            rec[0] = trace_t0; rec[1] = now; rec[2] = run;
+            rec[3] = (complete ? 0 : 1) | ((trace_b - trace_a) << 8) | ((trace_c - trace_b) << 24) | ((trace_d - trace_c) << 40);
         }
 #endif
         remaining -= run;
