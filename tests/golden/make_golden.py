@@ -61,7 +61,7 @@ def _null_packed(cache):
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the easymlx checkout")
     args = ap.parse_args()
     mx, PageCacheView, PageMetadata, build_qsl, UnifiedAttention, paged_attention = _import_reference(args.reference)
 
