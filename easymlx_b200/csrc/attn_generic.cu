@@ -1,7 +1,8 @@
 // Reference-semantics ragged paged attention for any geometry: head_dim <= 256, any page size,
 // fp16/bf16/fp32 queries and pools, affine pools.  One warp per (packed token, q head) walks the
-// keys of its causal range with an fp32 online softmax.  This is the coverage kernel; the tiled
-// kernels in attn_tiled.cu are the fast path for page size 128 and head_dim 64/128.
+// keys of its causal range with an fp32 online softmax; small batches (decode) put WPR warps on a row, each taking
+// every WPR-th key, and fold the partial states in warp order.  This is the coverage kernel; the tiled kernels in
+// attn_tiled.cu are the fast path.
 #include "common.cuh"
 
 namespace emlx {
@@ -45,12 +46,20 @@ struct PoolView {
     }
 };
 
-template <typename TQ>
-__global__ void __launch_bounds__(128) attn_generic_kernel(emlx_attn_args a, PoolView pv) {
-    const int lane = threadIdx.x & 31;
-    const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+constexpr int kGenericThreads = 256;
+
+template <typename TQ, int WPR>  // WPR warps share one (token, q head) row; WPR divides the warps of a CTA
+__global__ void __launch_bounds__(kGenericThreads) attn_generic_kernel(emlx_attn_args a, PoolView pv) {
+    constexpr int kWarps = kGenericThreads / 32, kRows = kWarps / WPR;
+    __shared__ float part_acc[WPR > 1 ? kWarps : 1][WPR > 1 ? kMaxHeadDim : 1];
+    __shared__ float part_ml[WPR > 1 ? kWarps : 1][2];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int sub = wid % WPR;  // this warp takes keys start_k + sub, + WPR, ...
+    const int64_t row = (int64_t)blockIdx.x * kRows + wid / WPR;
     const int Hq = a.num_q_heads, D = pv.p.head_dim, Hkv = pv.p.num_kv_heads, bs = pv.p.block_size;
-    if (warp >= (int64_t)a.total_tokens * Hq) return;
+    const bool row_live = row < (int64_t)a.total_tokens * Hq;
+    if (WPR == 1 && !row_live) return;
+    const int64_t warp = row_live ? row : 0;
     const int token = (int)(warp / Hq), head = (int)(warp - (int64_t)token * Hq);
     const int kvh = head / (Hq / Hkv);
     TQ* out = (TQ*)a.out + ((int64_t)token * Hq + head) * D;
@@ -77,7 +86,7 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(emlx_attn_args a, Poo
 
     float m = -INFINITY, l = 0.f;
     const int32_t* table = a.block_tables + (int64_t)max(s, 0) * a.max_blocks_per_seq;
-    for (int k = start_k; k <= max_k; ++k) {
+    for (int k = start_k + sub; k <= max_k; k += WPR) {
         const int page_idx = k / bs, off = k - page_idx * bs;
         const int64_t page = page_idx < a.max_blocks_per_seq ? table[page_idx] : -1;
         const bool live = page >= 0 && page < pv.p.num_blocks;  // an unassigned page reads as zero rows
@@ -101,6 +110,35 @@ __global__ void __launch_bounds__(128) attn_generic_kernel(emlx_attn_args a, Poo
             acc[j] = fmaf(acc[j], corr, p * v);
         }
         m = m_new;
+    }
+    if constexpr (WPR > 1) {
+        // fold the WPR partial states of the row in warp order (the result does not depend on timing)
+        part_ml[wid][0] = m;
+        part_ml[wid][1] = l;
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j) {
+            const int d = lane + 32 * j;
+            if (d < D) part_acc[wid][d] = acc[j];
+        }
+        __syncthreads();
+        if (sub != 0 || !row_live) return;
+        float M = -INFINITY;
+        for (int w = 0; w < WPR; ++w)
+            if (part_ml[wid + w][1] > 0.f) M = fmaxf(M, part_ml[wid + w][0]);
+        l = 0.f;
+#pragma unroll
+        for (int j = 0; j < kPerLane; ++j) acc[j] = 0.f;
+        for (int w = 0; w < WPR; ++w) {
+            const float lw = part_ml[wid + w][1];
+            if (lw <= 0.f) continue;
+            const float f = expf(part_ml[wid + w][0] - M);
+            l = fmaf(f, lw, l);
+#pragma unroll
+            for (int j = 0; j < kPerLane; ++j) {
+                const int d = lane + 32 * j;
+                if (d < D) acc[j] = fmaf(f, part_acc[wid + w][d], acc[j]);
+            }
+        }
     }
     const float inv = l > 0.f ? 1.0f / l : 0.f;
 #pragma unroll
@@ -136,14 +174,24 @@ extern "C" int emlx_attn_generic(const emlx_attn_args* args, const emlx_pool* po
     if (pool->head_dim > kMaxHeadDim) return fail(EMLX_ERR_UNSUPPORTED, "head_dim %d > %d", pool->head_dim, kMaxHeadDim);
     if (args->total_tokens == 0) return EMLX_OK;
     PoolView pv{*pool};
-    const int64_t warps = (int64_t)args->total_tokens * args->num_q_heads;
-    const int threads = 128;
-    const unsigned blocks = (unsigned)((warps * 32 + threads - 1) / threads);
+    // few rows (decode batches): eight warps per row, so that the GPU has enough warps in flight; many rows: one each
+    const int64_t rows = (int64_t)args->total_tokens * args->num_q_heads;
+    const bool split = rows * 2 <= (int64_t)num_sms() * 64;
+    const int rows_per_cta = split ? 1 : kGenericThreads / 32;
+    const unsigned blocks = (unsigned)((rows + rows_per_cta - 1) / rows_per_cta);
     cudaStream_t s = (cudaStream_t)stream;
-    switch (args->q_dtype) {
-        case EMLX_F16: attn_generic_kernel<__half><<<blocks, threads, 0, s>>>(*args, pv); break;
-        case EMLX_BF16: attn_generic_kernel<__nv_bfloat16><<<blocks, threads, 0, s>>>(*args, pv); break;
-        default: attn_generic_kernel<float><<<blocks, threads, 0, s>>>(*args, pv); break;
+    if (split) {
+        switch (args->q_dtype) {
+            case EMLX_F16: attn_generic_kernel<__half, 8><<<blocks, kGenericThreads, 0, s>>>(*args, pv); break;
+            case EMLX_BF16: attn_generic_kernel<__nv_bfloat16, 8><<<blocks, kGenericThreads, 0, s>>>(*args, pv); break;
+            default: attn_generic_kernel<float, 8><<<blocks, kGenericThreads, 0, s>>>(*args, pv); break;
+        }
+    } else {
+        switch (args->q_dtype) {
+            case EMLX_F16: attn_generic_kernel<__half, 1><<<blocks, kGenericThreads, 0, s>>>(*args, pv); break;
+            case EMLX_BF16: attn_generic_kernel<__nv_bfloat16, 1><<<blocks, kGenericThreads, 0, s>>>(*args, pv); break;
+            default: attn_generic_kernel<float, 1><<<blocks, kGenericThreads, 0, s>>>(*args, pv); break;
+        }
     }
     EMLX_LAUNCHED();
     return EMLX_OK;
