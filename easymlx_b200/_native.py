@@ -76,6 +76,7 @@ SIGNATURES = {
     "emlx_page_staging_bytes": (C.c_int64, [C.POINTER(Pool)]),
     "emlx_copy_blocks": (C.c_int, [C.POINTER(Pool), _P, C.c_int32, _P, C.c_int64, _P, _P]),
     "emlx_zero_pages": (C.c_int, [C.POINTER(Pool), _P, C.c_int32, _P]),
+    "emlx_gather_kv_cache": (C.c_int, [C.POINTER(Pool), _P, C.c_int32, C.c_int32, _P, C.c_int32, C.c_int32, _P, _P, _P, _P]),
     "emlx_rows_assign": (C.c_int, [_P, _P, C.c_int32, C.c_int32, C.c_int32, _P, C.c_int32, C.c_int32, _P]),
     "emlx_rows_update": (C.c_int, [_P, _P, C.c_int32, C.c_int32, _P, C.c_int32, C.c_int32, _P, _P]),
 }

@@ -438,6 +438,45 @@ class PageCacheView:
         dev = self.key_cache.device
         nv.check(nv.lib().emlx_zero_pages(self.native_pool(), nv.ptr(ids), int(ids.numel()), nv.stream_ptr(dev)))
 
+    def gather_kv_cache(self, block_table, cu_seq_lens, *, out_dtype=None) -> tuple[torch.Tensor, torch.Tensor]:
+        """Contiguous ``[total_tokens, num_kv_heads, head_dim]`` K and V of the sequences whose pages ``block_table
+        [num_seqs, max_blocks]`` lists and whose lengths ``cu_seq_lens [num_seqs + 1]`` accumulates
+        (``caching/paged/cache.py:974-1027``).  Affine pools come back dequantised."""
+        dev = self.key_cache.device
+        bt = torch.as_tensor(block_table).to(device=dev, dtype=torch.int32).contiguous()
+        if bt.ndim != 2:
+            raise ValueError("block_table must be rank-2: [num_seqs, max_blocks_per_seq]")
+        cu_host = cu_seq_lens.tolist() if isinstance(cu_seq_lens, torch.Tensor) else list(cu_seq_lens)
+        if len(cu_host) != bt.shape[0] + 1:
+            raise ValueError("cu_seq_lens must have num_seqs + 1 entries")
+        total = int(cu_host[-1])
+        cu = torch.as_tensor(cu_host, dtype=torch.int32).to(dev)
+        if out_dtype is None:
+            out_dtype = torch.float16 if self.is_affine else self.key_cache.dtype
+        out_dtype = _resolve_dtype(out_dtype)
+        k_out = torch.empty((total, self.num_kv_heads, self.head_dim), dtype=out_dtype, device=dev)
+        v_out = torch.empty_like(k_out)
+        nv.check(nv.lib().emlx_gather_kv_cache(self.native_pool(), nv.ptr(bt), int(bt.shape[0]), int(bt.shape[1]), nv.ptr(cu),
+                                               total, nv.dtype_code(out_dtype), nv.ptr(k_out), nv.ptr(v_out),
+                                               nv.ptr(self.status), nv.stream_ptr(dev)))
+        if _CHECK:
+            self.check()
+        return k_out, v_out
+
+    def dequantize_kv_cache(self, key_cache: torch.Tensor, value_cache: torch.Tensor, *, block_tables=None,
+                            out_dtype=torch.float16) -> tuple[torch.Tensor, torch.Tensor]:
+        """Float pools are returned as they are (``cache.py:1050-1086`` does the same when the pool is not quantised); an
+        affine pool comes back as ``[num_blocks, block_size, num_kv_heads, head_dim]`` tensors of ``out_dtype``."""
+        del block_tables
+        if not self.is_affine:
+            return key_cache, value_cache
+        nb, bs = self.num_blocks, self.block_size
+        table = torch.arange(nb, dtype=torch.int32, device=self.key_cache.device).reshape(nb, 1)
+        cu = [i * bs for i in range(nb + 1)]
+        k, v = self.gather_kv_cache(table, cu, out_dtype=out_dtype)
+        shape = (nb, bs, self.num_kv_heads, self.head_dim)
+        return k.reshape(shape), v.reshape(shape)
+
     def concatenate_to_cache(self, queries: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, *,
                              cache_metadata: tp.Any, rope: tp.Any = None,
                              slot_ids: tp.Sequence[int] | None = None,

@@ -148,6 +148,35 @@ __global__ void __launch_bounds__(kGenericThreads) attn_generic_kernel(emlx_attn
     }
 }
 
+// Contiguous K/V rows of the listed sequences out of the pool, cast (float pools) or dequantised (affine pools) to TOut:
+// one warp per (output token, kv head).  Pages outside the pool leave zero rows and flag EMLX_DEV_BAD_PAGE.
+template <typename TOut>
+__global__ void __launch_bounds__(256) gather_kv_kernel(PoolView pv, const int32_t* __restrict__ block_table, int MB,
+                                                        const int32_t* __restrict__ cu_seq_lens, int S, int total,
+                                                        TOut* __restrict__ k_out, TOut* __restrict__ v_out, int32_t* status) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int Hkv = pv.p.num_kv_heads, D = pv.p.head_dim, bs = pv.p.block_size;
+    if (warp >= (int64_t)total * Hkv) return;
+    const int t = (int)(warp / Hkv), h = (int)(warp - (int64_t)t * Hkv);
+    TOut* kd = k_out + ((int64_t)t * Hkv + h) * D;
+    TOut* vd = v_out + ((int64_t)t * Hkv + h) * D;
+    const int s = find_sequence(cu_seq_lens, S, t);
+    int64_t page = -1;
+    int off = 0;
+    if (s >= 0) {
+        const int pos = t - cu_seq_lens[s], page_idx = pos / bs;
+        off = pos - page_idx * bs;
+        if (page_idx < MB) page = block_table[(int64_t)s * MB + page_idx];
+    }
+    const bool live = page >= 0 && page < pv.p.num_blocks;
+    if (!live && lane == 0) flag_error(status, EMLX_DEV_BAD_PAGE);
+    for (int d = lane; d < D; d += 32) {
+        kd[d] = from_f32<TOut>(live ? pv.key(page, off, h, d) : 0.f);
+        vd[d] = from_f32<TOut>(live ? pv.value(page, off, h, d) : 0.f);
+    }
+}
+
 int validate_attn(const emlx_attn_args* a, const emlx_pool* pool, bool need_plan) {
     if (!a) return fail(EMLX_ERR_INVALID, "attention args are NULL");
     if (int rc = validate_pool(pool)) return rc;
@@ -192,6 +221,38 @@ extern "C" int emlx_attn_generic(const emlx_attn_args* args, const emlx_pool* po
             case EMLX_BF16: attn_generic_kernel<__nv_bfloat16, 1><<<blocks, kGenericThreads, 0, s>>>(*args, pv); break;
             default: attn_generic_kernel<float, 1><<<blocks, kGenericThreads, 0, s>>>(*args, pv); break;
         }
+    }
+    EMLX_LAUNCHED();
+    return EMLX_OK;
+}
+
+extern "C" int emlx_gather_kv_cache(const emlx_pool* pool, const int32_t* block_table, int32_t num_seqs,
+                                    int32_t max_blocks_per_seq, const int32_t* cu_seq_lens, int32_t total_tokens,
+                                    int32_t out_dtype, void* k_out, void* v_out, int32_t* status, void* stream) {
+    using namespace emlx;
+    if (!pool) return fail(EMLX_ERR_INVALID, "pool is NULL");
+    if (int rc = validate_pool(pool)) return rc;
+    if (num_seqs < 0 || total_tokens < 0 || max_blocks_per_seq <= 0) return fail(EMLX_ERR_INVALID, "gather_kv_cache: bad sizes");
+    if (out_dtype < EMLX_F16 || out_dtype > EMLX_F32) return fail(EMLX_ERR_INVALID, "unknown out_dtype");
+    if (total_tokens == 0) return EMLX_OK;
+    if (!block_table || !cu_seq_lens || !k_out || !v_out) return fail(EMLX_ERR_INVALID, "gather_kv_cache: NULL pointer");
+    PoolView pv{*pool};
+    const int64_t warps = (int64_t)total_tokens * pool->num_kv_heads;
+    const unsigned blocks = (unsigned)((warps + 7) / 8);
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (out_dtype) {
+        case EMLX_F16:
+            gather_kv_kernel<__half><<<blocks, 256, 0, s>>>(pv, block_table, max_blocks_per_seq, cu_seq_lens, num_seqs,
+                                                           total_tokens, (__half*)k_out, (__half*)v_out, status);
+            break;
+        case EMLX_BF16:
+            gather_kv_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(pv, block_table, max_blocks_per_seq, cu_seq_lens, num_seqs,
+                                                                  total_tokens, (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, status);
+            break;
+        default:
+            gather_kv_kernel<float><<<blocks, 256, 0, s>>>(pv, block_table, max_blocks_per_seq, cu_seq_lens, num_seqs,
+                                                          total_tokens, (float*)k_out, (float*)v_out, status);
+            break;
     }
     EMLX_LAUNCHED();
     return EMLX_OK;

@@ -228,6 +228,15 @@ int64_t emlx_page_staging_bytes(const emlx_pool* pool);
 int emlx_copy_blocks(const emlx_pool* pool, const int32_t* block_mapping, int32_t num_pairs, void* staging,
                      int64_t staging_bytes, int32_t* status, void* stream);
 
+/* Contiguous K/V of the listed sequences: k_out / v_out [total_tokens, Hkv, D] in out_dtype, token t of sequence s read
+ * from page block_table[s, (t - cu_seq_lens[s]) / bs].  Float pools are cast, affine pools dequantised
+ * (scale * code + bias in fp32).  Replaces PageCacheView.gather_kv_cache, caching/paged/cache.py:974-1027 (whose kernel
+ * reads the packed side caches this build does not keep) and, with one row per page, the whole-pool dequantisation of
+ * dequantize_kv_cache, cache.py:1050-1086.  A page id outside [0, NB) leaves zero rows and sets EMLX_DEV_BAD_PAGE. */
+int emlx_gather_kv_cache(const emlx_pool* pool, const int32_t* block_table, int32_t num_seqs, int32_t max_blocks_per_seq,
+                         const int32_t* cu_seq_lens, int32_t total_tokens, int32_t out_dtype, void* k_out, void* v_out,
+                         int32_t* status, void* stream);
+
 /* Zero pages page_ids[0..count) (device, int32) in every array of the pool; ids outside [0, NB) are skipped, as
  * _zero_pages does (inference/esurge/runners/model_runner.py:1058-1094). */
 int emlx_zero_pages(const emlx_pool* pool, const int32_t* page_ids, int32_t count, void* stream);

@@ -191,3 +191,38 @@ def test_prepare_step_drives_write_and_attention():
     hidden = out.reshape(t, hq * d)
     last = extract_last_tokens(hidden, batch.cache_metadata)
     assert torch.equal(last, hidden[[39, 40]])
+
+
+@pytest.mark.parametrize("bits", [0, 8, 4])
+def test_gather_and_dequantize_kv_cache(bits):
+    """PageCacheView.gather_kv_cache / dequantize_kv_cache against the oracle's gather and dequantisation."""
+    from easymlx_b200 import PageCacheView
+    from oracle import kv_quant, paged_attention as opa
+    hkv, d, bs = 2, 128, 128
+    v = PageCacheView.init(num_seqs=3, max_seq_len=512, num_kv_heads=hkv, head_dim=d, block_size=bs,
+                           cache_dtype=(f"affine{bits}" if bits else None), device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(40 + bits)
+    for a in _pool_arrays(v):
+        if a.dtype == torch.uint8:
+            a.copy_(torch.randint(0, 256, a.shape, device="cuda", generator=g, dtype=torch.uint8))
+        else:
+            a.copy_(torch.randn(a.shape, device="cuda", generator=g).to(a.dtype))
+    if bits:
+        kf = kv_quant.dequantize_key_pool(v.key_cache.cpu().numpy(), v.k_scales.cpu().numpy(), v.k_biases.cpu().numpy(), bits)
+        vf = kv_quant.dequantize_value_pool(v.value_cache.cpu().numpy(), v.v_scales.cpu().numpy(), v.v_biases.cpu().numpy(), bits)
+    else:
+        kf, vf = v.key_cache.float().cpu().numpy(), v.value_cache.float().cpu().numpy()
+    table = np.asarray([[7, 2, 9, -1], [0, -1, -1, -1], [11, 3, 5, 1]], dtype=np.int32)
+    lens = [300, 0, 512]
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    k_out, v_out = v.gather_kv_cache(table, cu, out_dtype=torch.float32)
+    want_k = np.concatenate([opa.gather_sequence(kf, table[s], lens[s], bs) for s in range(3)])
+    want_v = np.concatenate([opa.gather_sequence(vf, table[s], lens[s], bs) for s in range(3)])
+    np.testing.assert_array_equal(k_out.cpu().numpy(), want_k)
+    np.testing.assert_array_equal(v_out.cpu().numpy(), want_v)
+    dk, dv = v.dequantize_kv_cache(v.key_cache, v.value_cache, out_dtype=torch.float32)
+    if bits:
+        np.testing.assert_array_equal(dk.cpu().numpy(), kf)
+        np.testing.assert_array_equal(dv.cpu().numpy(), vf)
+    else:
+        assert dk is v.key_cache and dv is v.value_cache
