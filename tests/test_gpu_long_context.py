@@ -126,3 +126,36 @@ def test_small_pages_take_the_fast_kernels(block_size, d, dtype):
     ref = emlx.paged_attention(*args, kernel="generic")
     assert_close(fast, ref.float().cpu().numpy(), atol=(2e-3 if dtype == torch.float16 else 8e-3), rtol=(1e-2 if dtype == torch.float16 else 2e-2))
     assert torch.equal(fast, emlx.paged_attention(*args, max_query_len=max(qlens), query_len_set=qlens))
+
+
+def test_step_with_more_sequences_than_the_metadata_kernel_keeps_on_chip():
+    """2 500 decode sequences in one step: the prefix sums, lengths and unit table of the metadata kernel no longer fit
+    its shared-memory staging (2 048 sequences / 4 096 units), and the scan runs in three passes of 1 024."""
+    import easymlx_b200 as emlx
+    from oracle import kv_write
+    hq, hkv, d, s = 8, 2, 64, 2500
+    rng = np.random.default_rng(12)
+    prior = rng.integers(0, 300, size=s).astype(np.int32)
+    qlens = np.ones(s, dtype=np.int64)
+    qlens[::97] = 3  # a few multi-token rows among the decode rows
+    cache = emlx.PageCacheView.init(num_seqs=s, max_seq_len=384, num_kv_heads=hkv, head_dim=d, block_size=128, device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(12)
+    cache.key_cache.copy_(torch.randn(cache.key_cache.shape, device="cuda", generator=g).half())
+    cache.value_cache.copy_(torch.randn(cache.value_cache.shape, device="cuda", generator=g).half())
+    cache.kv_lens.copy_(torch.from_numpy(prior))
+    t = int(qlens.sum())
+    q, k, v = (torch.randn(t, h, d, device="cuda", generator=g).half() for h in (hq, hkv, hkv))
+    slots = tuple(range(s))
+    meta = emlx.PageMetadata(query_start_loc=emlx.build_query_start_loc(qlens.tolist()), slot_ids=slots)
+    want_meta = kv_write.batch_metadata(qlens, np.arange(s), cache.block_tables.cpu().numpy(), prior, 128)
+    _, kc, vc, resolved = cache.concatenate_to_cache(q, k, v, cache_metadata=meta, slot_ids=slots, query_lens=qlens.tolist())
+    cache.check()
+    kv = (prior + qlens).astype(np.int32)
+    np.testing.assert_array_equal(resolved.kv_lens.cpu().numpy(), kv)
+    np.testing.assert_array_equal(resolved.query_start_loc.cpu().numpy(), np.concatenate([[0], np.cumsum(qlens)]).astype(np.int32))
+    slot_map = torch.from_numpy(want_meta["slot_mapping"]).cuda()
+    assert torch.equal(kc.reshape(-1, hkv, d)[slot_map], k) and torch.equal(vc.reshape(-1, hkv, d)[slot_map], v)
+    fast = emlx.AttentionPerformer(scale=d ** -0.5).executor.mixin_impl(
+        query=q, key=kc, value=vc, cache_metadata=resolved, cache_view=cache, scale=d ** -0.5).attention_outputs
+    ref = emlx.paged_attention(q, kc, vc, resolved.block_tables, resolved.kv_lens, resolved.query_start_loc, kernel="generic")
+    assert_close(fast, ref.float().cpu().numpy())
