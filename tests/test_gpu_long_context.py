@@ -159,3 +159,23 @@ def test_step_with_more_sequences_than_the_metadata_kernel_keeps_on_chip():
         query=q, key=kc, value=vc, cache_metadata=resolved, cache_view=cache, scale=d ** -0.5).attention_outputs
     ref = emlx.paged_attention(q, kc, vc, resolved.block_tables, resolved.kv_lens, resolved.query_start_loc, kernel="generic")
     assert_close(fast, ref.float().cpu().numpy())
+
+
+@pytest.mark.parametrize("qlens,kv", [([1, 1], [700, 300]), ([200], [600])])
+def test_unassigned_page_inside_a_live_range_reads_as_zero_rows_and_is_reported(qlens, kv):
+    """A page id of -1 below kv_len: the fp16 kernels attend zero K/V rows there (as the reference's NumPy path does) and
+    raise the bad-page flag; decode kernel and 128-row kernel alike."""
+    import easymlx_b200 as emlx
+    hq, hkv, d = 8, 2, 128
+    cache = _pool(hkv, d, kv, 0, seed=33)
+    cache.block_tables[0, 1] = -1
+    q = torch.randn(sum(qlens), hq, d, device="cuda", dtype=torch.float16)
+    args = (q, cache.key_cache, cache.value_cache, cache.block_tables, torch.tensor(kv, dtype=torch.int32, device="cuda"),
+            emlx.build_query_start_loc(qlens, device="cuda"))
+    outs = {}
+    for kernel in ("tiled", "generic"):
+        call = emlx.operations.kernels.unified_attention.AttentionCall(*args, max_query_len=max(qlens), kernel=kernel).plan()
+        with pytest.raises(RuntimeError, match="page id out of range"):  # the tests run with device-side checks reported
+            call.launch()
+        outs[kernel] = call.out
+    assert_close(outs["tiled"], outs["generic"].float().cpu().numpy())
