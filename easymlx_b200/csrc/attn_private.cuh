@@ -151,6 +151,15 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&dempty[dslot]);
         }
+        if constexpr (FMT != 0 && BF16) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    qf[ks][nt][0] = bf16x2_to_f16x2(qf[ks][nt][0]);
+                    qf[ks][nt][1] = bf16x2_to_f16x2(qf[ks][nt][1]);
+                }
+        }
         if constexpr (FMT != 0) {
             const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
 #pragma unroll

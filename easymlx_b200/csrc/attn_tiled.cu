@@ -375,6 +375,15 @@ template <bool BF16> __device__ __forceinline__ uint16_t to_bits16(float v) {
     if constexpr (BF16) return __bfloat16_as_ushort(__float2bfloat16_rn(v));
     else return __half_as_ushort(__float2half_rn(v));
 }
+// two bf16 -> two fp16, round to nearest, clamped to the fp16 range: affine pools are multiplied on the fp16 tensor
+// path (their codes are fp16 subnormals), so bf16 queries are converted once per part
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t v) {
+    const float lo = fminf(fmaxf(__uint_as_float(v << 16), -65504.f), 65504.f);
+    const float hi = fminf(fmaxf(__uint_as_float(v & 0xffff0000u), -65504.f), 65504.f);
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+}
 __device__ __forceinline__ float quad_column_max(float v) {  // over the 8 lanes that share lane%4
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
     v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
@@ -483,6 +492,15 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
                         qf[2 * jx + 1][nt][1] = ptx::prmt(v.z, v.w, 0x7632u);  // (q5, q7)
                     }
                 }
+            }
+            if constexpr (FMT != 0 && BF16) {
+#pragma unroll
+                for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) {
+                        qf[ks][nt][0] = bf16x2_to_f16x2(qf[ks][nt][0]);
+                        qf[ks][nt][1] = bf16x2_to_f16x2(qf[ks][nt][1]);
+                    }
             }
             if constexpr (FMT != 0) {
                 // column sums of Q per scale group through an all-ones A operand: c[e] = sum_d q[row 2t+e][d]
@@ -1082,8 +1100,8 @@ static int launch_one(const MapPair& maps, const TiledParams& p, cudaStream_t st
 
 template <int D, int NT>
 static int launch_fmt(int fmt, bool bf16, const MapPair& maps, const TiledParams& p, cudaStream_t stream) {
-    if (fmt == EMLX_KV_AFFINE8) return launch_one<D, NT, 8, false>(maps, p, stream);
-    if (fmt == EMLX_KV_AFFINE4) return launch_one<D, NT, 4, false>(maps, p, stream);
+    if (fmt == EMLX_KV_AFFINE8) return bf16 ? launch_one<D, NT, 8, true>(maps, p, stream) : launch_one<D, NT, 8, false>(maps, p, stream);
+    if (fmt == EMLX_KV_AFFINE4) return bf16 ? launch_one<D, NT, 4, true>(maps, p, stream) : launch_one<D, NT, 4, false>(maps, p, stream);
     return bf16 ? launch_one<D, NT, 0, true>(maps, p, stream) : launch_one<D, NT, 0, false>(maps, p, stream);
 }
 
@@ -1113,8 +1131,6 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
     const bool bf16 = a->q_dtype == EMLX_BF16;
     if (pool->kv_format == EMLX_KV_FLOAT && pool->kv_dtype != a->q_dtype)
         return fail(EMLX_ERR_UNSUPPORTED, "the tiled kernels need the pool dtype to equal the query dtype");
-    if (pool->kv_format != EMLX_KV_FLOAT && bf16)
-        return fail(EMLX_ERR_UNSUPPORTED, "affine pools are read with fp16 queries");
     const PlanLayout L = plan_layout(a->num_seqs, a->total_tokens, Hq, Hkv);
     const WorkspaceLayout W = workspace_layout(a->num_seqs, a->total_tokens, Hq, Hkv, D);
     if (a->plan_bytes < (size_t)L.words * 4 || a->workspace_bytes < W.bytes)

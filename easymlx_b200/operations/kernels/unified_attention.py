@@ -164,14 +164,13 @@ class AttentionCall:
             and self.d in _TILED_HEAD_DIMS
             and queries.dtype in (torch.float16, torch.bfloat16)
             and (affine or key_cache.dtype == queries.dtype)
-            and (not affine or queries.dtype == torch.float16)
         )
         if self.kernel is None:
             self.kernel = "tiled" if tiled_ok else "generic"
         if self.kernel != "generic" and not tiled_ok:
             raise NotImplementedError(
                 "the tiled kernels need page size 128 (or 16/32/64 with a 16-bit pool), head_dim 64 or 128, fp16/bf16 queries and a pool of the "
-                "same dtype (or fp16 queries with an affine pool)")
+                "same dtype (or an affine pool)")
         self.num_seqs = int(self.block_tables.shape[0])
         self.status = _scratch.get(dev, "status", 4, zero=True)
         a = nv.AttnArgs()

@@ -240,3 +240,25 @@ def test_bfloat16_queries_and_pool(name):
                                     sliding_window=x["window"])
     # bf16 keeps 8 significant bits: probabilities and outputs are rounded to 2^-9 relative
     assert_close(out, want, atol=4e-3, rtol=2e-2)
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+@pytest.mark.parametrize("name", ["attn_f16_decode_d128", "attn_f16_decode_d64", "attn_f16_specverify", "attn_f16_mixed_d128"])
+def test_bfloat16_queries_over_an_affine_pool(name, bits):
+    """bf16 models with a quantised cache: the queries are converted to fp16 inside the fast kernels (the codes are
+    multiplied on the fp16 tensor path), the output comes back as bf16."""
+    from easymlx_b200 import paged_attention
+
+    x = cases.attention_inputs(**cases.ATTENTION_CASES[name])
+    kcode, vcode, ks, kb, vs, vb = quantized_pool_from_float(x["key_cache"], x["value_cache"], bits)
+    kf = kv_quant.dequantize_key_pool(kcode, ks, kb, bits)
+    vf = kv_quant.dequantize_value_pool(vcode, vs, vb, bits)
+    q = torch.from_numpy(x["q"]).float().bfloat16().cuda()
+    expect = opa.paged_attention_rows(q.float().cpu().numpy(), kf, vf, x["block_tables"], x["kv_lens"], x["query_start_loc"],
+                                      softmax_scale=x["scale"], sliding_window=x["window"])
+    out = paged_attention(q, dev(kcode), dev(vcode), dev(x["block_tables"]), dev(x["kv_lens"]), dev(x["query_start_loc"]),
+                          softmax_scale=x["scale"], sliding_window=x["window"], kernel="tiled",
+                          k_scale=dev(ks), k_bias=dev(kb), v_scale=dev(vs), v_bias=dev(vb))
+    assert out.dtype == torch.bfloat16
+    # the output is rounded to bf16 (8 significant bits)
+    assert_close(out, expect, atol=4e-3, rtol=2e-2)
