@@ -243,7 +243,8 @@ extern "C" int emlx_build_metadata(const int32_t* query_lens, const int32_t* slo
     }
     // small batches: one launch does everything; large ones hand the gather and the slot mapping to a second launch
     const int64_t cells = (int64_t)num_seqs * max_blocks_per_seq;
-    const bool scatter_later = cells > 4 * kMetaThreads || total_tokens > kMetaThreads;
+    // (a second launch costs about as much as four passes of the single CTA)
+    const bool scatter_later = cells > 16 * kMetaThreads || total_tokens > 4 * kMetaThreads;
     EMLX_CUDA_OK(launch_pdl(build_metadata_kernel, 1, kMetaThreads, 0, (cudaStream_t)stream,
         query_lens, slot_ids, num_seqs, total_tokens, block_tables_all, num_slots, max_blocks_per_seq, kv_lens_all,
         block_size, advance_kv_lens, query_start_loc, block_tables, kv_lens, slot_mapping, token_positions, num_blocks,
