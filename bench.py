@@ -243,10 +243,18 @@ def run_ours(args):
         per = base.hkv // world
         w = workloads.materialize(base, dev, seed=0, kv_head_slice=slice(rank * per, (rank + 1) * per))
     else:
-        # weak scaling: the global batch is `world` draws of the configuration, partitioned by sequence;
-        # every rank owns the page pool of its own sequences
-        w = workloads.materialize(workloads.describe(args.config, seed=None if rank == 0 else 1000 * rank + 7),
-                                  dev, seed=rank)
+        # weak scaling: the global batch is `world` draws of the configuration (different lengths per draw), partitioned
+        # by sequence, longest first, so that every rank attends about the same number of KV tokens; every rank owns
+        # the page pool of its own sequences
+        if world == 1:
+            w = workloads.materialize(base, dev, seed=0)
+        else:
+            draws = [workloads.describe(args.config, seed=None if r == 0 else 1000 * r + 7) for r in range(world)]
+            whole = workloads.describe(args.config)
+            whole.qlens = np.concatenate([d.qlens for d in draws])
+            whole.prior = np.concatenate([d.prior for d in draws])
+            mine = workloads.partition_by_sequence(whole, world)[rank]
+            w = workloads.materialize(whole, dev, seed=rank, seq_subset=mine)
     if args.attn_only:
         # profiling aid: a few bare attention launches over the written pool, nothing else
         from easymlx_b200.operations.kernels.unified_attention import AttentionCall
