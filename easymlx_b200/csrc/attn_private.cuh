@@ -349,9 +349,9 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                     if constexpr (NG == 2) {
                         const float2 sv = h2_to_f2(*(const uint32_t*)(sbs + 2 * kTile * GROUPS + tok * 2));
                         const float2 bv = h2_to_f2(*(const uint32_t*)(sbs + 3 * kTile * GROUPS + tok * 2));
-                        vsc[ab][0] = sv.x; vsc[ab][1] = sv.y; vbi[ab][0] = bv.x; vbi[ab][1] = bv.y;
+                        vsc[ab][0] = weight_scale(sv.x); vsc[ab][1] = weight_scale(sv.y); vbi[ab][0] = bv.x; vbi[ab][1] = bv.y;
                     } else {
-                        vsc[ab][0] = __half2float(sbs[2 * kTile * GROUPS + tok]);
+                        vsc[ab][0] = weight_scale(__half2float(sbs[2 * kTile * GROUPS + tok]));
                         vbi[ab][0] = __half2float(sbs[3 * kTile * GROUPS + tok]);
                     }
                 }
@@ -480,8 +480,8 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                     if constexpr (FMT != 0) bias = fmaf(fw, wb[((d / 64) * kConsumerWarps + ww) * 32 + row], bias);
                 }
                 if constexpr (FMT != 0) {
-                    acc.x = fmaf(acc.x, kTwo24, bias); acc.y = fmaf(acc.y, kTwo24, bias);
-                    acc.z = fmaf(acc.z, kTwo24, bias); acc.w = fmaf(acc.w, kTwo24, bias);
+                    acc.x = fmaf(acc.x, kValueDown, bias); acc.y = fmaf(acc.y, kValueDown, bias);
+                    acc.z = fmaf(acc.z, kValueDown, bias); acc.w = fmaf(acc.w, kValueDown, bias);
                 }
                 if (complete) {
                     const int r = row0 + row;

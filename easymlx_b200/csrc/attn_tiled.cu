@@ -406,6 +406,11 @@ __device__ __forceinline__ void nibbles_to_h2(uint32_t x, uint32_t (&h)[4]) {
 }
 
 constexpr float kTwo24 = 16777216.0f;  // codes enter the MMA as fp16 subnormals c * 2^-24
+// The value-side weights p * scale become fp16 after a multiplication by 2^8: in a long row with one dominant key the
+// others have p * scale below the fp16 subnormal step (6e-8) and would be rounded away, thousands of them together
+// carrying a visible share of the output.  Scales above 255.9 saturate at the largest finite fp16.
+constexpr float kWeightUp = 256.0f, kHalfMax = 65504.0f, kValueDown = kTwo24 / kWeightUp;
+__device__ __forceinline__ float weight_scale(float v_scale) { return fminf(v_scale * kWeightUp, kHalfMax); }
 
 template <int D, int NT, int FMT, bool BF16>
 __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* stages, uint8_t* fixed, uint64_t* full,
@@ -687,8 +692,8 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
                 float vsA[NG], vsB[NG], vbA[NG], vbB[NG];
 #pragma unroll
                 for (int j = 0; j < NG; ++j) {
-                    vsA[j] = __half2float(sbs[2 * kTile * GROUPS + tokA * GROUPS + j]);
-                    vsB[j] = __half2float(sbs[2 * kTile * GROUPS + tokB * GROUPS + j]);
+                    vsA[j] = weight_scale(__half2float(sbs[2 * kTile * GROUPS + tokA * GROUPS + j]));
+                    vsB[j] = weight_scale(__half2float(sbs[2 * kTile * GROUPS + tokB * GROUPS + j]));
                     vbA[j] = __half2float(sbs[3 * kTile * GROUPS + tokA * GROUPS + j]);
                     vbB[j] = __half2float(sbs[3 * kTile * GROUPS + tokB * GROUPS + j]);
                 }
@@ -819,8 +824,8 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
                 }
                 lsum[nt][e] = v;
                 if constexpr (FMT != 0) {
-                    o[nt][e] = o[nt][e] * kTwo24 + bv;
-                    o[nt][2 + e] = o[nt][2 + e] * kTwo24 + bv;
+                    o[nt][e] = o[nt][e] * kValueDown + bv;
+                    o[nt][2 + e] = o[nt][2 + e] * kValueDown + bv;
                 }
             }
         if constexpr (C::TS > 1) {
@@ -832,7 +837,7 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             float other = ored[((warp + k * C::DSL) * NT * 4 + nt * 4 + c) * 32 + lane];
-                            if constexpr (FMT != 0) other *= kTwo24;
+                            if constexpr (FMT != 0) other *= kValueDown;
                             o[nt][c] += other;
                         }
             }

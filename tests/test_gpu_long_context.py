@@ -179,3 +179,21 @@ def test_unassigned_page_inside_a_live_range_reads_as_zero_rows_and_is_reported(
             call.launch()
         outs[kernel] = call.out
     assert_close(outs["tiled"], outs["generic"].float().cpu().numpy())
+
+
+@pytest.mark.parametrize("bits", [8, 4])
+def test_tail_of_a_long_peaked_row_over_an_affine_pool(bits):
+    """30 000 keys whose values all sit well above zero, scores spread widely: in most rows one key takes most of the
+    weight and the others share a few per cent, each with weight * scale below the fp16 subnormal step.  Rounding
+    those weights away lowers every channel of the row by the same amount; the decode rows, a 40-token chunk (32-row
+    units) and the coverage kernel must agree element by element and in the mean over each row."""
+    hq, hkv, d = 16, 2, 64
+    qlens, prior = [40, 1, 1], [30_000, 30_000, 12_345]
+    kv = [a + b for a, b in zip(qlens, prior)]
+    cache = _pool(hkv, d, kv, bits, seed=31)
+    q = torch.randn(sum(qlens), hq, d, device="cuda", dtype=torch.float16)
+    fast = _run(cache, q, qlens, kv, None)
+    ref = _run(cache, q, qlens, kv, "generic")
+    assert_close(fast, ref.float().cpu().numpy())
+    row_shift = (fast.float() - ref.float()).mean(dim=-1).abs().max().item()
+    assert row_shift <= 1e-3, f"rows shifted by up to {row_shift:.2e}"
