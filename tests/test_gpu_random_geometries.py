@@ -171,3 +171,57 @@ def test_cache_write_over_random_batches(block):
         np.testing.assert_array_equal(cache.kv_lens.cpu().numpy(), want["kv_lens_all"], err_msg=label)
         np.testing.assert_array_equal(meta.kv_lens.cpu().numpy(), want["kv_lens"], err_msg=label)
         np.testing.assert_array_equal(meta.block_tables.cpu().numpy(), want["block_tables"], err_msg=label)
+
+
+@pytest.mark.parametrize("block", range(4))
+def test_small_random_batches_against_the_oracle(block):
+    """Both routes against the oracle itself on batches small enough for it: head sizes and page sizes that only the
+    coverage kernel takes (32, 96, 256; pages of 8 or 48 tokens), fp32 and fp16 queries, 8- and 4-bit pools built by the
+    oracle's quantiser, negative page ids past the sequence end."""
+    from easymlx_b200 import paged_attention
+    from gpu_util import assert_close, quantized_pool_from_float
+    from oracle import kv_quant, paged_attention as opa
+    for case in range(block * 8, block * 8 + 8):
+        rng = np.random.default_rng(50_000 + case)
+        d = int(rng.choice([32, 64, 96, 128, 256]))
+        hkv = int(rng.choice([1, 2, 3]))
+        hq = hkv * int(rng.choice([1, 2, 4, 7]))
+        bs = int(rng.choice([8, 16, 48, 128]))
+        bits = int(rng.choice([0, 0, 8, 4])) if d % 64 == 0 else 0
+        f32 = bits == 0 and rng.random() < 0.3
+        nseq = int(rng.integers(1, 7))
+        qlens = [int(rng.choice([0, 1, 1, 2, 5, 19, 140])) for _ in range(nseq)]
+        prior = [int(rng.integers(0, 400)) for _ in range(nseq)]
+        if sum(qlens) == 0:
+            qlens[0] = 1
+        kv = np.asarray([a + b for a, b in zip(qlens, prior)], dtype=np.int32)
+        window = 0 if rng.random() < 0.6 else int(rng.choice([1, 9, 200]))
+        mb = max(1, -(-int(kv.max()) // bs)) + 1
+        nb = nseq * mb
+        bt = rng.permutation(nb).reshape(nseq, mb).astype(np.int32)
+        for s in range(nseq):                       # entries past the last page of a sequence are -1, as an engine leaves them
+            bt[s, -(-int(kv[s]) // bs):] = -1
+        np_dtype = np.float32 if f32 else np.float16
+        kc = rng.standard_normal((nb, bs, hkv, d)).astype(np_dtype)
+        vc = rng.standard_normal((nb, bs, hkv, d)).astype(np_dtype)
+        q = rng.standard_normal((sum(qlens), hq, d)).astype(np_dtype)
+        qsl = kv_write.build_query_start_loc(qlens)
+        scale = float(d) ** -0.5
+        label = f"case {case}: d={d} hq={hq} hkv={hkv} page={bs} bits={bits} f32={f32} window={window} qlens={qlens} prior={prior}"
+        extra = {}
+        if bits:
+            kcode, vcode, ks, kb, vs, vb = quantized_pool_from_float(kc, vc, bits)
+            kf = kv_quant.dequantize_key_pool(kcode, ks, kb, bits)
+            vf = kv_quant.dequantize_value_pool(vcode, vs, vb, bits)
+            pools = (dev(kcode), dev(vcode))
+            extra = dict(k_scale=dev(ks), k_bias=dev(kb), v_scale=dev(vs), v_bias=dev(vb))
+        else:
+            kf, vf, pools = kc, vc, (dev(kc), dev(vc))
+        expect = opa.paged_attention_rows(q, kf, vf, bt, kv, qsl, softmax_scale=scale, sliding_window=window)
+        for kernel in ("generic", None):
+            out = paged_attention(dev(q), *pools, dev(bt), dev(kv), dev(qsl), softmax_scale=scale,
+                                  sliding_window=(window or None), kernel=kernel, **extra)
+            try:
+                assert_close(out, expect, **(dict(atol=1e-5, rtol=1e-5) if f32 else {}))
+            except AssertionError as err:
+                raise AssertionError(f"{label} kernel={kernel}: {err}") from None
