@@ -80,3 +80,20 @@ def test_fused_rope_write_matches_oracle(traditional, bits):
     want4 = orope.rotate(x["q"][:6], 11 + np.arange(6), rope.freqs, 64, traditional=traditional, scale=0.5, mscale=1.25)
     np.testing.assert_allclose(b4.permute(0, 2, 1, 3).reshape(6, -1, d).float().cpu().numpy(), want4.astype(np.float32),
                                atol=4e-3, rtol=2e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("traditional", [False, True])
+def test_rotation_at_long_context_positions(traditional):
+    """Positions up to 131 071 with the llama3 table: the angle reaches 1e5 rad, where a fast sine would be off by
+    several per cent; the kernel and the oracle both reduce the fp32 angle exactly."""
+    from easymlx_b200.layers import get_rope
+
+    rope = get_rope(128, 500000.0, traditional, {"type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                                 "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}, 131072)
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((64, 4, 128)).astype(np.float16)
+    pos = np.concatenate([rng.integers(100_000, 131_072, size=60), [0, 1, 131_071, 65_536]]).astype(np.int32)
+    got = rope(torch.from_numpy(x).cuda(), offset=torch.from_numpy(pos).cuda())
+    want = orope.rotate(x, pos, rope.freqs, 128, traditional=traditional, scale=rope.scale, mscale=rope.mscale)
+    np.testing.assert_allclose(got.float().cpu().numpy(), want.astype(np.float32), atol=4e-3, rtol=2e-3)
