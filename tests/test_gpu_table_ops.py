@@ -226,3 +226,64 @@ def test_gather_and_dequantize_kv_cache(bits):
         np.testing.assert_array_equal(dv.cpu().numpy(), vf)
     else:
         assert dk is v.key_cache and dv is v.value_cache
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_sequences_of_row_and_page_operations(seed):
+    """Twenty random operations in a row (assign, exchange, compaction with chained moves, clear, page zeroing,
+    copy-on-write page copies with chained mappings) on one cache; table, lengths and every pool array against the oracle
+    after each of them."""
+    from easymlx_b200 import PageCacheView
+    rng = np.random.default_rng(4200 + seed)
+    bits = int(rng.choice([0, 8, 4]))
+    slots, mb, bs = int(rng.choice([3, 8, 33])), int(rng.choice([2, 5, 9])), int(rng.choice([16, 128]))
+    v = PageCacheView.init(num_seqs=slots, max_seq_len=mb * bs, num_kv_heads=int(rng.choice([1, 2])), head_dim=64,
+                           block_size=bs, cache_dtype=(f"affine{bits}" if bits else None), device="cuda")
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    for a in _pool_arrays(v):
+        if a.dtype == torch.uint8:
+            a.copy_(torch.randint(0, 256, a.shape, device="cuda", generator=g, dtype=torch.uint8))
+        else:
+            a.copy_(torch.randn(a.shape, device="cuda", generator=g).to(a.dtype))
+    nb = v.num_blocks
+    bt = rng.integers(-1, nb, size=(slots, mb)).astype(np.int32)
+    lens = rng.integers(0, mb * bs, size=slots).astype(np.int32)
+    v.block_tables.copy_(torch.from_numpy(bt)); v.kv_lens.copy_(torch.from_numpy(lens))
+    arrays = [a.cpu().numpy().copy() for a in _pool_arrays(v)]
+    r = _runner(v)
+    for step in range(20):
+        op = str(rng.choice(["assign", "swap", "compact", "clear", "zero", "copy"]))
+        if op == "assign":
+            row, pages = int(rng.integers(0, slots)), rng.integers(0, nb, size=int(rng.integers(0, mb + 3))).tolist()
+            cached = int(rng.integers(-4, mb * bs))
+            r._assign_row_mapping(row, pages, cached_tokens=cached)
+            ot.assign_row(bt, lens, row, pages, cached)
+        elif op == "swap":
+            a, b = int(rng.integers(0, slots)), int(rng.integers(0, slots))
+            r._move_cache_row(a, b)
+            ot.swap_rows(bt, lens, a, b)
+        elif op == "compact":
+            # holes are filled from the back, and a later move may read a row that an earlier one wrote
+            moves = [(int(rng.integers(0, slots)), int(rng.integers(0, slots))) for _ in range(int(rng.integers(1, 5)))]
+            r.compact_rows(moves)
+            ot.compact_rows(bt, lens, moves)
+        elif op == "clear":
+            row = int(rng.integers(0, slots))
+            r._clear_row_mapping(row)
+            ot.clear_row(bt, lens, row)
+        elif op == "zero":
+            ids = rng.integers(-2, nb + 3, size=int(rng.integers(1, 6))).tolist()
+            r._zero_pages(ids)
+            ot.zero_pages(arrays, ids)
+        else:
+            n = int(rng.integers(1, min(nb, 6) + 1))
+            dst = rng.permutation(nb)[:n]                      # one writer per destination page
+            mapping = [[int(rng.integers(0, nb)), int(d)] for d in dst]
+            v.copy_blocks(mapping if rng.random() < 0.5 else torch.tensor(mapping, dtype=torch.int32, device="cuda"))
+            ot.copy_blocks(arrays, mapping)
+        label = f"seed {seed} step {step} {op}"
+        np.testing.assert_array_equal(v.block_tables.cpu().numpy(), bt, err_msg=label)
+        np.testing.assert_array_equal(v.kv_lens.cpu().numpy(), lens, err_msg=label)
+        for a, w in zip(_pool_arrays(v), arrays):
+            np.testing.assert_array_equal(a.cpu().numpy().view(np.uint8), w.view(np.uint8), err_msg=label)
+    v.check()
