@@ -43,6 +43,7 @@ class AttnArgs(C.Structure):
         ("total_tokens", C.c_int32), ("num_seqs", C.c_int32), ("num_q_heads", C.c_int32),
         ("max_blocks_per_seq", C.c_int32), ("q_dtype", C.c_int32), ("sliding_window", C.c_int32),
         ("softmax_scale", C.c_float), ("max_query_len", C.c_int32), ("row_class_mask", C.c_int32),
+        ("plan_flags", C.c_int32),
         ("plan", C.c_void_p), ("plan_bytes", C.c_size_t), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
         ("status", C.c_void_p),
     ]
@@ -59,6 +60,8 @@ SIGNATURES = {
                                      _I32, _I32, _I32, _I32, _I32, _P, C.c_size_t, _P]),
     "emlx_kv_write": (C.c_int, [_P, _P, _I32, _I32, _P, C.POINTER(Pool), _P, _P]),
     "emlx_kv_write_rope": (C.c_int, [_P, _P, _I32, _P, _P, _I32, _I32, _P, _P, C.POINTER(Rope), C.POINTER(Pool), _P, _P]),
+    "emlx_kv_write_decode": (C.c_int, [_P, _P, _P, _P, _I32, _P, _I32, _P, _I32, _I32, _P, _I32, C.POINTER(Pool),
+                                      C.POINTER(Rope), _P, _P, _P, _I32, _I32, _I32, _P, C.c_size_t, _P, _P, _P]),
     "emlx_attn_plan_bytes": (C.c_size_t, [_I32, _I32, _I32, _I32]),
     "emlx_attn_workspace_bytes": (C.c_size_t, [_I32, _I32, _I32, _I32, _I32]),
     "emlx_attn_plan": (C.c_int, [_P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _P, C.c_size_t, _P]),
@@ -67,7 +70,6 @@ SIGNATURES = {
     "emlx_attn_decode": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
     "emlx_attn_prefill": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
     "emlx_attn_generic": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
-    "emlx_set_trace_buffer": (None, [_P]),
     "emlx_selftest_wait_timeout": (C.c_int, [_P, C.c_uint32, _P]),
     "emlx_attn_decode_static": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
     "emlx_attn_row_class": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),

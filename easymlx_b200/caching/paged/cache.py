@@ -28,6 +28,7 @@ from ... import _native as nv
 
 _CHECK = os.environ.get("EASYMLX_B200_CHECK", "0") not in ("", "0")
 QUANT_GROUP = 64
+_FUSED_DECODE_MAX_SEQS = 2048  # batch size up to which emlx_kv_write_decode serves a single-token batch
 
 _TORCH_DTYPES = {
     "float16": torch.float16, "half": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32,
@@ -108,8 +109,11 @@ class PageMetadata:
     # filled by concatenate_to_cache: the distinct query lengths of the batch when the host knows them; lets the
     # attention call skip the kernels of row classes the batch does not contain
     query_len_set: tuple[int, ...] | None = field(default=None, compare=False)
-    # attention work list built on the GPU together with the metadata: (buffer, num_q_heads, sliding_window)
+    # attention work list built on the GPU together with the metadata: (buffer, num_q_heads, sliding_window, plan_flags)
     plan: tp.Any | None = field(default=None, compare=False)
+    # optional host hint from the runner: length of the longest scheduled sequence after this step (0 = unknown);
+    # a length-dependent rotary embedding (longrope) picks its table from it without reading the device
+    max_kv_len: int = field(default=0, compare=False)
 
     def with_cache_state(self, *, block_tables, kv_lens, block_size: int) -> "PageMetadata":
         return PageMetadata(
@@ -155,6 +159,7 @@ class PageCacheView:
         self.k_scales, self.v_scales, self.k_biases, self.v_biases = k_scales, v_scales, k_biases, v_biases
         self.cache_bits = int(cache_bits)
         self._status: torch.Tensor | None = None
+        self._ticket: torch.Tensor | None = None
         self._validate_shape()
 
     # ------------------------------------------------------------------ geometry
@@ -188,6 +193,13 @@ class PageCacheView:
         if self._status is None:
             self._status = torch.zeros(1, dtype=torch.int32, device=self.key_cache.device)
         return self._status
+
+    @property
+    def ticket(self) -> torch.Tensor:
+        """Arrival counter of the fused decode step (zero between launches; the kernel resets it)."""
+        if self._ticket is None:
+            self._ticket = torch.zeros(1, dtype=torch.int32, device=self.key_cache.device)
+        return self._ticket
 
     def check(self) -> None:
         """Synchronise and raise if any kernel that used this cache flagged a bad slot / page / overflow."""
@@ -291,9 +303,11 @@ class PageCacheView:
     # ------------------------------------------------------------------ writes
     def _write_batch(self, keys: torch.Tensor, values: torch.Tensor, query_lens_dev: torch.Tensor,
                      slots_dev: torch.Tensor, total_tokens: int, plan_for: tuple | None = None,
-                     advance: bool = True, rope=None, queries: torch.Tensor | None = None):
-        """Metadata kernel + write kernel for one packed batch.  Returns ``(qsl, block_tables, kv_lens)``
-        of the scheduled rows; ``self.kv_lens`` is advanced in place."""
+                     advance: bool = True, rope=None, queries: torch.Tensor | None = None,
+                     single_token: bool = False):
+        """Metadata kernel + write kernel for one packed batch (one fused launch when every sequence brings exactly
+        one token, ``single_token``).  Returns ``(qsl, block_tables, kv_lens)`` of the scheduled rows;
+        ``self.kv_lens`` is advanced in place."""
         nv.require_cuda(keys, values, self.key_cache)
         dev = self.key_cache.device
         lib, stream = nv.lib(), nv.stream_ptr(dev)
@@ -317,11 +331,6 @@ class PageCacheView:
                                                  self.num_kv_heads, self.head_dim))
             plan_bytes = int(lib.emlx_attn_plan_bytes(s, total_tokens, hq, self.num_kv_heads))
             plan = torch.empty(plan_bytes, dtype=torch.uint8, device=dev)
-        nv.check(lib.emlx_build_metadata(
-            nv.ptr(query_lens_dev), nv.ptr(slots_dev), s, total_tokens, nv.ptr(self.block_tables), self.num_seqs,
-            self.blocks_per_seq, nv.ptr(self.kv_lens), self.block_size, 1 if advance else 0, nv.ptr(qsl), nv.ptr(bt),
-            nv.ptr(lens), nv.ptr(slot_mapping), nv.ptr(positions), self.num_blocks, nv.ptr(self.status), hq, self.num_kv_heads, window, max_q,
-            flags, nv.ptr(plan), plan_bytes, stream))
         if total_tokens > 0:
             if keys.shape != values.shape:
                 raise ValueError("key and value must have the same shape")
@@ -330,24 +339,43 @@ class PageCacheView:
             if keys.dtype != values.dtype:
                 raise ValueError("key and value must have the same dtype")
             keys, values = keys.contiguous(), values.contiguous()
-            pool = self.native_pool()
-            if rope is None:
-                nv.check(lib.emlx_kv_write(nv.ptr(keys), nv.ptr(values), nv.dtype_code(keys.dtype), total_tokens,
-                                           nv.ptr(slot_mapping), pool, nv.ptr(self.status), stream))
-            else:
+            if rope is not None:
                 if not hasattr(rope, "native"):
                     raise TypeError("rope must be an easymlx_b200.layers.rotary.RotaryEmbedding (see get_rope)")
                 if queries.dtype != keys.dtype:
                     raise ValueError("queries and keys must have the same dtype when RoPE is fused into the write")
                 queries = queries.contiguous()
                 rotated_q = torch.empty_like(queries)
+        if single_token and 0 < total_tokens == s <= _FUSED_DECODE_MAX_SEQS:
+            # decode fast path (the reference's, cache.py:1155-1206): metadata, work list and write in one launch
+            nv.check(lib.emlx_kv_write_decode(
+                nv.ptr(queries) if rope is not None else None, nv.ptr(rotated_q), nv.ptr(keys), nv.ptr(values),
+                nv.dtype_code(keys.dtype), nv.ptr(slots_dev), s, nv.ptr(self.block_tables), self.num_seqs,
+                self.blocks_per_seq, nv.ptr(self.kv_lens), 1 if advance else 0, self.native_pool(),
+                rope.native(dev) if rope is not None else None, nv.ptr(qsl), nv.ptr(bt), nv.ptr(lens),
+                hq if plan is not None else (int(queries.shape[1]) if rope is not None else 0), window, flags,
+                nv.ptr(plan), plan_bytes, nv.ptr(self.ticket), nv.ptr(self.status), stream))
+            if _CHECK:
+                self.check()
+            return qsl, bt, lens, (None if plan is None else (plan, hq, window, flags)), rotated_q
+        nv.check(lib.emlx_build_metadata(
+            nv.ptr(query_lens_dev), nv.ptr(slots_dev), s, total_tokens, nv.ptr(self.block_tables), self.num_seqs,
+            self.blocks_per_seq, nv.ptr(self.kv_lens), self.block_size, 1 if advance else 0, nv.ptr(qsl), nv.ptr(bt),
+            nv.ptr(lens), nv.ptr(slot_mapping), nv.ptr(positions), self.num_blocks, nv.ptr(self.status), hq, self.num_kv_heads, window, max_q,
+            flags, nv.ptr(plan), plan_bytes, stream))
+        if total_tokens > 0:
+            pool = self.native_pool()
+            if rope is None:
+                nv.check(lib.emlx_kv_write(nv.ptr(keys), nv.ptr(values), nv.dtype_code(keys.dtype), total_tokens,
+                                           nv.ptr(slot_mapping), pool, nv.ptr(self.status), stream))
+            else:
                 nv.check(lib.emlx_kv_write_rope(
                     nv.ptr(queries), nv.ptr(rotated_q), int(queries.shape[1]), nv.ptr(keys), nv.ptr(values),
                     nv.dtype_code(keys.dtype), total_tokens, nv.ptr(slot_mapping), nv.ptr(positions),
                     rope.native(dev), pool, nv.ptr(self.status), stream))
         if _CHECK:
             self.check()
-        return qsl, bt, lens, (None if plan is None else (plan, hq, window)), rotated_q
+        return qsl, bt, lens, (None if plan is None else (plan, hq, window, flags)), rotated_q
 
     def append(self, seq_idx: int, key: torch.Tensor, value: torch.Tensor) -> None:
         """Append ``[num_tokens, num_kv_heads, head_dim]`` rows to one slot (``cache.py:834-872``)."""
@@ -516,9 +544,16 @@ class PageCacheView:
                 single = bool(getattr(cache_metadata, "is_single_token_decode", False)) and total == len(slots)
                 max_q = 1 if single else 0
         window = int(getattr(cache_metadata, "sliding_window", None) or 0)
+        if rope is not None and hasattr(rope, "select"):
+            # longrope: one table per batch, chosen from the longest scheduled sequence after the step
+            longest = int(getattr(cache_metadata, "max_kv_len", 0) or 0)
+            if longest <= 0 and slots:
+                longest = int((self.kv_lens[_uploaded.get(slots, dev).long()] + qlens_dev[: len(slots)]).max().item())
+            rope = rope.select(longest)
         qsl, bt, lens, plan, rotated_q = self._write_batch(
             keys, values, qlens_dev, _uploaded.get(slots, dev), total,
-            plan_for=(int(queries.shape[1]), window, max_q), advance=advance, rope=rope, queries=queries)
+            plan_for=(int(queries.shape[1]), window, max_q), advance=advance, rope=rope, queries=queries,
+            single_token=single and len(slots) == total)
         if rotated_q is not None:
             queries = rotated_q
         meta = PageMetadata(

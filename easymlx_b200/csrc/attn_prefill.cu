@@ -497,8 +497,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                     l *= corr;
                 }
                 PF_STAMP(tid == 0, kt, 2);
+                // fp16 weights are stored as 2^(s - m_ref + 7): m_ref trails the true maximum by up to 2^8, so the
+                // largest stored weight is 2^15, and a key only rounds to zero below 2^-32 of the reference (the sum l
+                // carries the same factor, which cancels in O / l)
+                constexpr float kShift = BF16 ? 0.0f : 7.0f;
                 const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;
-                const float neg_m = -m_safe;
+                const float neg_m = kShift - m_safe;
                 float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
@@ -612,11 +616,8 @@ template <int D, bool BF16>
 static int launch_pf(const CUtensorMap& qmap, const MapPair& maps, const PrefillParams& p, cudaStream_t stream) {
     using C = PfCfg<D>;
     auto kernel = attn_prefill_kernel<D, BF16>;
-    static bool configured = false;
-    if (!configured) {
-        EMLX_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-        configured = true;
-    }
+    static DeviceOnce configured;
+    EMLX_CUDA_OK(allow_dynamic_smem(kernel, C::SMEM, configured));
     EMLX_CUDA_OK(launch_pdl(kernel, num_sms(), kPfThreads, C::SMEM, stream, qmap, maps.k, maps.v, p));
     EMLX_LAUNCHED();
     return EMLX_OK;

@@ -322,7 +322,8 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                     corr[nt][e] = ex2(m[nt][e] - m_safe);
                     rescale |= (m_new != m[nt][e]);
                     m[nt][e] = m_new;
-                    const float pA = ex2(s[nt][e] - m_safe), pB = ex2(s[nt][2 + e] - m_safe);
+                    constexpr float kShift = weight_shift<FMT, BF16>();  // fp16 weights are kept away from the subnormals
+                    const float pA = ex2(s[nt][e] - m_safe + kShift), pB = ex2(s[nt][2 + e] - m_safe + kShift);
                     l[nt][e] = fmaf(l[nt][e], corr[nt][e], pA + pB);
                     s[nt][e] = pA;
                     s[nt][2 + e] = pB;

@@ -11,16 +11,16 @@ namespace {
 constexpr size_t kStaticScratchBytes = 10u << 20;  // 10 MiB
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-constexpr int kMaxDevices = 64;
+constexpr int kStaticMaxDevices = 64;
 std::mutex g_mu;
-void* g_scratch_addr[kMaxDevices] = {};
+void* g_scratch_addr[kStaticMaxDevices] = {};
 
 // In host code the array's name is only a handle; the device address comes from the runtime, once per
 // device, with that device current.
 int scratch_address(void** out) {
     int dev = 0;
     EMLX_CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= kMaxDevices) return emlx::fail(EMLX_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
+    if (dev < 0 || dev >= kStaticMaxDevices) return emlx::fail(EMLX_ERR_UNSUPPORTED, "device ordinal %d not supported", dev);
     std::lock_guard<std::mutex> lock(g_mu);
     if (!g_scratch_addr[dev]) {
         void* ptr = nullptr;
@@ -59,6 +59,10 @@ extern "C" int emlx_attn_decode_static(const emlx_attn_args* args, const emlx_po
                                 args->sliding_window, args->max_query_len, 0, plan, plan_bytes, stream))
         return rc;
     emlx_attn_args local = *args;
+    // the work list above is built without 128-row units (plan_flags 0), so every row set lands in the classes the
+    // decode kernels serve; a caller's row-class hint may speak for a different kind of plan and is dropped
+    local.plan_flags = 0;
+    local.row_class_mask = 0;
     local.plan = plan;
     local.plan_bytes = plan_bytes;
     local.workspace = workspace;

@@ -405,6 +405,16 @@ __device__ __forceinline__ void nibbles_to_h2(uint32_t x, uint32_t (&h)[4]) {
     h[3] = ptx::prmt(hi, 0u, 0x4342u);
 }
 
+// Softmax weights of an fp16 pool go to the tensor cores as fp16.  A weight below 2^-25 of the row's reference
+// maximum would round to zero there, and in a row of 10^5 keys with one dominant key the thousands of such keys hold
+// a visible share of the output.  The weights are therefore computed as 2^(s - m + kShift): the row sum and the
+// accumulator carry the same factor, which cancels in O / l and in every merge of partial results (all parts use the
+// same shift).  The largest weight is then 2^kShift = 256, far inside the fp16 range.  bf16 has fp32's exponent
+// range and needs no shift.
+template <int FMT, bool BF16> __device__ __forceinline__ constexpr float weight_shift() {
+    return (FMT == 0 && !BF16) ? 8.0f : 0.0f;
+}
+
 constexpr float kTwo24 = 16777216.0f;  // codes enter the MMA as fp16 subnormals c * 2^-24
 // The value-side weights p * scale become fp16 after a multiplication by 2^8: in a long row with one dominant key the
 // others have p * scale below the fp16 subnormal step (6e-8) and would be rounded away, thousands of them together
@@ -669,7 +679,8 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
                     const float m_safe = m_new == -INFINITY ? 0.f : m_new;
                     corr[nt][e] = exp2f(m[nt][e] - m_safe);
                     m[nt][e] = m_new;
-                    const float pA = exp2f(s[nt][e] - m_safe), pB = exp2f(s[nt][2 + e] - m_safe);
+                    constexpr float kShift = weight_shift<FMT, BF16>();
+                    const float pA = exp2f(s[nt][e] - m_safe + kShift), pB = exp2f(s[nt][2 + e] - m_safe + kShift);
                     l[nt][e] = l[nt][e] * corr[nt][e] + pA + pB;
                     s[nt][e] = pA;
                     s[nt][2 + e] = pB;
@@ -960,11 +971,13 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     volatile int* abort_word = (volatile int*)(fixed + C::OFF_MISC);  // misc[0]
 
     if (threadIdx.x == 0) {
+#ifdef EMLX_TRACE
         if (p.trace) {
             long long now;
             asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
             p.trace[4 * blockIdx.x + 0] = now;
         }
+#endif
         for (int s = 0; s < C::STAGES; ++s) {
             ptx::mbar_init(&full[s], 1);
             ptx::mbar_init(&empty[s], kConsumerWarps);
@@ -1003,6 +1016,7 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             consumer_loop<D, NT, FMT, BF16>(p, smem, fixed, full, empty, abort_word, f_begin, f_end, num_units, total_flat, active);
     }
     if (*abort_word && threadIdx.x == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
+#ifdef EMLX_TRACE
     if (p.trace && threadIdx.x == 0) {
         long long now;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
@@ -1012,6 +1026,7 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         asm volatile("mov.u32 %0, %smid;" : "=r"(smid));
         p.trace[4 * blockIdx.x + 3] = smid;
     }
+#endif
 }
 
 // ------------------------------------------------------------------------------------------ host
@@ -1032,8 +1047,9 @@ static CUtensorMapSwizzle swizzle_of(int row_bytes) {
     return row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : (row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
 }
 
-// Tensor maps depend only on the pool's address and geometry; they are encoded once and cached.
-int get_maps(const emlx_pool& pool, MapPair** out) {
+// Tensor maps depend only on the pool's address and geometry; they are encoded once and cached.  The pair is
+// copied out while the lock is held, so a concurrent call that evicts the cache cannot invalidate it.
+int get_maps(const emlx_pool& pool, MapPair* out) {
     static std::mutex mu;
     static std::map<std::tuple<void*, void*, long long, int, int, int, int, int>, MapPair> cache;
     auto key = std::make_tuple(pool.key_cache, pool.value_cache, (long long)pool.num_blocks, pool.num_kv_heads,
@@ -1041,7 +1057,7 @@ int get_maps(const emlx_pool& pool, MapPair** out) {
     std::lock_guard<std::mutex> lock(mu);
     auto it = cache.find(key);
     if (it != cache.end()) {
-        *out = &it->second;
+        *out = it->second;
         return EMLX_OK;
     }
     EncodeTiledFn enc = encode_fn();
@@ -1084,7 +1100,8 @@ int get_maps(const emlx_pool& pool, MapPair** out) {
     if (r1 != CUDA_SUCCESS || r2 != CUDA_SUCCESS)
         return fail(EMLX_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d, %d)", (int)r1, (int)r2);
     if (cache.size() > 256) cache.clear();
-    *out = &(cache[key] = mp);
+    cache[key] = mp;
+    *out = mp;
     return EMLX_OK;
 }
 
@@ -1092,11 +1109,8 @@ template <int D, int NT, int FMT, bool BF16>
 static int launch_one(const MapPair& maps, const TiledParams& p, cudaStream_t stream) {
     using C = Cfg<D, NT, FMT>;
     auto kernel = attn_tiled_kernel<D, NT, FMT, BF16>;
-    static bool configured = false;
-    if (!configured) {
-        EMLX_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM));
-        configured = true;
-    }
+    static DeviceOnce configured;
+    EMLX_CUDA_OK(allow_dynamic_smem(kernel, C::SMEM, configured));
     const int grid = min(num_sms(), kMaxGrid);
     EMLX_CUDA_OK(launch_pdl(kernel, grid, kThreads, C::SMEM, stream, maps.k, maps.v, p));
     EMLX_LAUNCHED();
@@ -1121,9 +1135,15 @@ static int launch_class(int cls, int D, int fmt, bool bf16, const MapPair& maps,
     return launch_fmt<64, 4>(fmt, bf16, maps, p, s);
 }
 
+// Measurement aid, only in builds with -DEMLX_TRACE: a device buffer of at least 4 * 256 int64 into which every CTA
+// of the tiled kernel writes {start ns, end ns, tiles processed, SM id}; -DEMLX_TRACE_PARTS / -DEMLX_TRACE_PREFILL
+// add per-part and per-tile records behind those (the buffer must then hold 1024 + 256 * 16 * 4 int64).
+#ifdef EMLX_TRACE
 static long long* g_trace = nullptr;
-void set_trace(long long* buf) { g_trace = buf; }
 long long* trace_buffer() { return g_trace; }
+#else
+long long* trace_buffer() { return nullptr; }
+#endif
 
 static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* stream, int class_lo, int class_hi) {
     if (int rc = validate_attn(a, pool, true)) return rc;
@@ -1141,12 +1161,19 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
     if (a->plan_bytes < (size_t)L.words * 4 || a->workspace_bytes < W.bytes)
         return fail(EMLX_ERR_WORKSPACE, "plan/workspace smaller than emlx_attn_plan_bytes()/emlx_attn_workspace_bytes()");
     if (((uintptr_t)a->queries | (uintptr_t)a->out) & 15) return fail(EMLX_ERR_INVALID, "queries/out must be 16-byte aligned");
-    MapPair* maps = nullptr;
+    MapPair maps;
     if (int rc = get_maps(*pool, &maps)) return rc;
 
-    const bool wide = prefill_supported(pool->kv_format, Hq, Hkv, D);
+    // the row classes a plan holds depend on the flags it was built with, not on what this pool could support
+    const bool wide = (a->plan_flags & kPlanWideUnits) != 0;
+    if (wide && !prefill_supported(pool->kv_format, Hq, Hkv, D))
+        return fail(EMLX_ERR_INVALID, "plan_flags ask for 128-row units, which this pool / head geometry cannot run");
     int lo, hi;
     class_range(G, a->max_query_len, wide, lo, hi);
+    if (max(lo, class_lo) > min(hi, class_hi))
+        return fail(EMLX_ERR_UNSUPPORTED,
+                    "this plan holds row classes %d..%d and the entry point serves %d..%d: nothing to launch (build "
+                    "the plan with other plan_flags or call emlx_attn_unified)", lo, hi, class_lo, class_hi);
     lo = max(lo, class_lo);
     hi = min(hi, class_hi);
     const int32_t* plan = (const int32_t*)a->plan;
@@ -1154,7 +1181,7 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
         if (a->row_class_mask != 0 && !((a->row_class_mask >> c) & 1)) continue;  // the caller knows this class is empty
         if (c == 3) {
             if (int rc = launch_prefill(a, pool, plan + 4 * c, plan + L.unit_seq[c], plan + L.unit_row0[c],
-                                        plan + L.unit_tile_lo[c], plan + L.unit_cum[c], plan + L.unit_order, *maps,
+                                        plan + L.unit_tile_lo[c], plan + L.unit_cum[c], plan + L.unit_order, maps,
                                         (cudaStream_t)stream))
                 return rc;
             continue;
@@ -1169,22 +1196,26 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
         p.counters = (int32_t*)((uint8_t*)a->workspace + W.counter_off[c]);
         p.slots = (float*)((uint8_t*)a->workspace + W.slots_off);
         p.status = a->status;
-        p.trace = g_trace;
+        p.trace = trace_buffer();
         p.k_scale = (const __half*)pool->k_scale; p.k_bias = (const __half*)pool->k_bias;
         p.v_scale = (const __half*)pool->v_scale; p.v_bias = (const __half*)pool->v_bias;
         p.num_blocks = pool->num_blocks;
         p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.MB = a->max_blocks_per_seq; p.window = a->sliding_window;
         p.bs = pool->block_size; p.ppt_log = pages_per_tile_log2(pool->block_size);
         p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
-        if (int rc = launch_class(c, D, pool->kv_format, bf16, *maps, p, (cudaStream_t)stream)) return rc;
+        if (int rc = launch_class(c, D, pool->kv_format, bf16, maps, p, (cudaStream_t)stream)) return rc;
     }
     return EMLX_OK;
 }
 
 }  // namespace emlx
 
+#ifdef EMLX_TRACE
+extern "C" __attribute__((visibility("default"))) void emlx_set_trace_buffer(int64_t* records) {
+    emlx::g_trace = (long long*)records;
+}
+#endif
 extern "C" {
-void emlx_set_trace_buffer(int64_t* records) { emlx::set_trace((long long*)records); }
 int emlx_attn_unified(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 0, emlx::kNumClasses - 1); }
 int emlx_attn_decode(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 0, 2); }
 int emlx_attn_prefill(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 3, 3); }

@@ -33,14 +33,49 @@ extern std::atomic<int64_t> g_launches;
         EMLX_CUDA_OK(cudaGetLastError());                                                      \
     } while (0)
 
-inline int num_sms() {
-    static int cached = 0;
-    if (!cached) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
+// Per-device bookkeeping.  Attributes such as the dynamic shared-memory limit of a kernel and the SM count belong
+// to a device, not to the process: a process that drives several GPUs needs them once per device.
+constexpr int kMaxDevices = 128;
+
+inline int current_device() {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return dev;
+}
+
+// One flag per device ordinal; `needs(dev)` is true until `done(dev)` has been called for that device.  Ordinals
+// outside [0, kMaxDevices) are never remembered (the caller then repeats its set-up on every call, which is correct).
+struct DeviceOnce {
+    std::atomic<uint64_t> mask[kMaxDevices / 64] = {};
+    bool needs(int dev) const {
+        if (dev < 0 || dev >= kMaxDevices) return true;
+        return ((mask[dev >> 6].load(std::memory_order_acquire) >> (dev & 63)) & 1ull) == 0;
     }
-    return cached;
+    void done(int dev) {
+        if (dev >= 0 && dev < kMaxDevices) mask[dev >> 6].fetch_or(1ull << (dev & 63), std::memory_order_release);
+    }
+};
+
+// Sets the dynamic shared-memory limit of `kernel` once per device.
+template <typename K>
+inline cudaError_t allow_dynamic_smem(K kernel, int bytes, DeviceOnce& once) {
+    const int dev = current_device();
+    if (!once.needs(dev)) return cudaSuccess;
+    const cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess) once.done(dev);
+    return e;
+}
+
+inline int num_sms() {
+    static std::atomic<int> cached[kMaxDevices] = {};
+    const int dev = current_device();
+    const bool slot = dev >= 0 && dev < kMaxDevices;
+    int n = slot ? cached[dev].load(std::memory_order_relaxed) : 0;
+    if (!n) {
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (slot) cached[dev].store(n, std::memory_order_relaxed);
+    }
+    return n;
 }
 
 // Launch with programmatic stream serialisation: the kernel may be scheduled while its predecessor in the stream

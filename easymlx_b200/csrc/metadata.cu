@@ -25,16 +25,10 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
     __shared__ int32_t s_q[kSmemSeqs + 1], s_kv[kSmemSeqs], s_off[kSmemSeqs], s_cum[kSmemUnits];
     const int tid = threadIdx.x;
     META_STAMP(0);
-    // The first 1024 sequences' inputs are read before waiting for the predecessor: they come from the host or from
-    // launches older than it (the lengths were last written by the previous metadata launch), so their latency
-    // overlaps the predecessor's tail.
-    int pre_q = 0, pre_slot = -1, pre_base = 0;
-    if (tid < S) {
-        pre_q = max(query_lens[tid], 0);
-        pre_slot = slot_ids[tid];
-        if (pre_slot >= 0 && pre_slot < num_slots) pre_base = kv_lens_all[pre_slot];
-    }
-    grid_dep_wait();  // a preceding attention kernel may still be reading the plan buffer and the gathered lengths
+    // Nothing is read before the wait: the stored lengths were last written by the previous metadata launch, which
+    // the immediate predecessor in the stream (a write or an attention kernel that started early) does not order
+    // against this grid, and the query lengths / slot ids may come from a kernel that is still running.
+    grid_dep_wait();
     grid_dep_launch();
     META_STAMP(1);
     const bool small = S <= kSmemSeqs;
@@ -46,21 +40,23 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
         const int i = i0 + tid;
         int q_len = 0, slot = -1, base = 0;
         if (i < S) {
-            if (i0 == 0) {
-                q_len = pre_q; slot = pre_slot; base = pre_base;
-            } else {
-                q_len = max(query_lens[i], 0);
-                slot = slot_ids[i];
-                if (slot >= 0 && slot < num_slots) base = kv_lens_all[slot];
-            }
-            if (slot < 0 || slot >= num_slots) flag_error(status, EMLX_DEV_BAD_SLOT);
+            q_len = max(query_lens[i], 0);
+            slot = slot_ids[i];
+            if (slot >= 0 && slot < num_slots) base = kv_lens_all[slot];
+            else flag_error(status, EMLX_DEV_BAD_SLOT);
         }
         int chunk_total;
         const int excl = carry + block_scan_value(q_len, scan_smem, chunk_total);
         if (i < S) {
-            const bool ok = slot >= 0 && slot < num_slots;
+            bool ok = slot >= 0 && slot < num_slots;
+            // A sequence that would outgrow its page-table row is reported and left alone: its stored length
+            // stays, none of its rows is written (their slots are -1) and its gathered length is 0, so that
+            // attention gives zero rows for it instead of reading past the row.
+            if (ok && (int64_t)base + q_len > (int64_t)MB * bs) {
+                flag_error(status, EMLX_DEV_OVERFLOW);
+                ok = false;
+            }
             const int after = ok ? base + q_len : 0;
-            if (ok && after > MB * bs) flag_error(status, EMLX_DEV_OVERFLOW);
             qv[i] = excl;
             kvv[i] = after;
             if (small) {
@@ -106,6 +102,7 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
         const int slot = s >= 0 ? slot_ids[s] : -1;
         if (slot < 0 || slot >= num_slots) return r;
         const int q_len = qv[s + 1] - qv[s];
+        if (kvv[s] < q_len) return r;  // a sequence that would overflow its row: nothing of it is written
         r.pos = kvv[s] - q_len + (t - qv[s]);
         const int page_idx = r.pos / bs;
         if (page_idx >= MB) return r;
@@ -192,9 +189,10 @@ __global__ void __launch_bounds__(kMetaThreads) metadata_scatter_kernel(
             const int slot = s >= 0 ? slot_ids[s] : -1;
             if (slot >= 0 && slot < num_slots) {
                 const int q_len = qsl[s + 1] - qsl[s];
-                pos = kv_out[s] - q_len + ((int)t - qsl[s]);
+                const bool live = kv_out[s] >= q_len;  // false for a sequence that would overflow its row
+                pos = live ? kv_out[s] - q_len + ((int)t - qsl[s]) : 0;
                 const int page_idx = pos / bs;
-                if (page_idx < MB) {
+                if (live && page_idx < MB) {
                     const int page = bt_all[(int64_t)slot * MB + page_idx];
                     if (page >= 0 && page < num_blocks) dst = (int64_t)page * bs + (pos - page_idx * bs);
                     else flag_error(status, EMLX_DEV_BAD_PAGE);

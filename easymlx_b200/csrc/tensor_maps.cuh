@@ -15,7 +15,7 @@ struct MapPair {
     CUtensorMap k, v;
 };
 // Maps of the pool (cached per pool address and geometry).
-int get_maps(const emlx_pool& pool, MapPair** out);
+int get_maps(const emlx_pool& pool, MapPair* out);
 // Launches the tcgen05 prefill kernel over the plan's 128-row units.
 int launch_prefill(const emlx_attn_args* a, const emlx_pool* pool, const int32_t* plan_class_hdr, const int32_t* unit_seq,
                    const int32_t* unit_row0, const int32_t* unit_tile_lo, const int32_t* unit_cum, const int32_t* unit_order,

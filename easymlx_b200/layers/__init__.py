@@ -1,3 +1,3 @@
-from .rotary import RotaryEmbedding, get_rope
+from .rotary import LongRopeEmbedding, RotaryEmbedding, get_rope
 
-__all__ = ("RotaryEmbedding", "get_rope")
+__all__ = ("LongRopeEmbedding", "RotaryEmbedding", "get_rope")

@@ -2,7 +2,8 @@
 
 Mirrors the factory of easymlx ``layers/rotary/_rotary.py`` (``get_rope`` ``:327-415``): every variant there ends
 in ``mx.fast.rope(x, dims, traditional, base | freqs, scale, offset)``, i.e. a table of per-pair periods, a
-position scale and an optional magnitude scale.  ``RotaryEmbedding`` holds exactly that; ``PageCacheView.
+position scale and an optional magnitude scale.  ``RotaryEmbedding`` holds exactly that (``LongRopeEmbedding`` holds two
+of them and picks one by sequence length); ``PageCacheView.
 concatenate_to_cache(rope=...)`` hands it to the CUDA write kernel, which rotates K while storing it and Q in the
 same launch.  Calling the object rotates a tensor on its own (``rope(x, offset=...)``, ``x`` ``[B, H, L, D]`` or
 ``[T, H, D]``).
@@ -75,6 +76,41 @@ class RotaryEmbedding:
         return out
 
 
+class LongRopeEmbedding:
+    """Su-scaled ("longrope") rotary embedding: two period tables, one for sequences up to
+    ``original_max_position_embeddings`` tokens and one for longer ones, each with its magnitude scale
+    (easymlx ``layers/rotary/_rotary.py:36-131``).
+
+    The reference chooses per call from ``offset + length``.  Here the choice is made on the host, once per call or
+    per packed batch: ``select(total_len)`` returns the ``RotaryEmbedding`` for a sequence that is ``total_len``
+    tokens long after the step.  ``PageCacheView.concatenate_to_cache`` calls it with the longest scheduled
+    sequence (``PageMetadata.max_kv_len`` when the runner supplies it, else one device read), so a batch that mixes
+    sequences on both sides of the threshold is rotated with the long table throughout.
+    """
+
+    def __init__(self, dims: int, base: float = 10000.0, max_position_embeddings: int = 131072,
+                 original_max_position_embeddings: int = 4096, short_factor: tp.Sequence[float] | float = 1.0,
+                 long_factor: tp.Sequence[float] | float = 1.0, short_mscale: float | None = None,
+                 long_mscale: float | None = None):
+        self.dims = int(dims)
+        self.original_max_position_embeddings = int(original_max_position_embeddings)
+        freqs = np.float32(base) ** (np.arange(0, dims, 2, dtype=np.float32) / np.float32(dims))
+        factor = max_position_embeddings / original_max_position_embeddings
+        default = 1.0 if factor <= 1.0 else math.sqrt(1 + math.log(factor) / math.log(original_max_position_embeddings))
+        self.short = RotaryEmbedding(self.dims, freqs=np.asarray(short_factor, dtype=np.float32) * freqs,
+                                     mscale=short_mscale or default)
+        self.long = RotaryEmbedding(self.dims, freqs=np.asarray(long_factor, dtype=np.float32) * freqs,
+                                    mscale=long_mscale or default)
+
+    def select(self, total_len: int) -> RotaryEmbedding:
+        return self.long if int(total_len) > self.original_max_position_embeddings else self.short
+
+    def __call__(self, x: torch.Tensor, offset: int | torch.Tensor = 0) -> torch.Tensor:
+        length = int(x.shape[-2]) if x.ndim == 4 else 1
+        last = int(torch.as_tensor(offset).max().item()) if torch.is_tensor(offset) else int(offset)
+        return self.select(last + length)(x, offset=offset)
+
+
 def _llama3_freqs(dims, base, cfg) -> np.ndarray:
     factor = cfg["factor"]
     low, high = cfg.get("low_freq_factor", 1.0), cfg.get("high_freq_factor", 4.0)
@@ -124,8 +160,10 @@ def get_rope(dims: int, base: float, traditional: bool, scaling_config: dict | N
         freqs, mscale = _yarn(int(dims), base, scaling_config["factor"], **kw)
         return RotaryEmbedding(int(dims), traditional=traditional, freqs=freqs, mscale=mscale)
     if kind == "longrope":
-        raise NotImplementedError("longrope switches tables by sequence length on the host; not provided")
+        return LongRopeEmbedding(int(dims), base=base, max_position_embeddings=int(max_position_embeddings or 131072),
+                                 original_max_position_embeddings=scaling_config["original_max_position_embeddings"],
+                                 short_factor=scaling_config["short_factor"], long_factor=scaling_config["long_factor"])
     raise ValueError(f"Unsupported RoPE type {kind}")
 
 
-__all__ = ("RotaryEmbedding", "get_rope")
+__all__ = ("LongRopeEmbedding", "RotaryEmbedding", "get_rope")

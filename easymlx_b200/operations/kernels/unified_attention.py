@@ -76,17 +76,20 @@ def _as_int32(value, device) -> torch.Tensor:
 
 
 class _Scratch:
-    """Per-device plan / workspace / status buffers, grown on demand and reused across calls.
+    """Plan / workspace / status buffers per (device, stream), grown on demand and reused across calls.
 
     The workspace must start zeroed (its counters reset themselves after every merge), so it is
-    zero-filled whenever it is (re)allocated.
+    zero-filled whenever it is (re)allocated.  Calls issued on one stream run one after the other and may
+    share these buffers; calls on different streams may overlap on the GPU, so each stream gets its own
+    set.  Two ``AttentionCall`` objects built on the same stream share the work list: build, plan and launch
+    one call before constructing the next (``paged_attention`` does).
     """
 
     def __init__(self):
         self.buffers: dict = {}
 
     def get(self, device, kind: str, nbytes: int, zero: bool) -> torch.Tensor:
-        key = (str(device), kind)
+        key = (str(device), int(torch.cuda.current_stream(device).cuda_stream), kind)
         buf = self.buffers.get(key)
         if buf is None or buf.numel() < nbytes:
             size = max(256, int(nbytes))
@@ -182,13 +185,6 @@ class AttentionCall:
         a.sliding_window, a.softmax_scale = self.window, self.scale
         a.max_query_len = max(0, int(max_query_len))
         a.row_class_mask = 0
-        if query_len_set:
-            # the host knows which query lengths occur: launch only the kernels of those row classes
-            lib_ = nv.lib()
-            for q_len in set(int(x) for x in query_len_set):
-                cls = lib_.emlx_attn_row_class(self.pool.kv_format, self.hq, self.pool.num_kv_heads, self.d, q_len)
-                if cls >= 0:
-                    a.row_class_mask |= 1 << cls
         a.status = self.status.data_ptr()
         self.args = a
         if self.kernel != "generic":
@@ -197,10 +193,23 @@ class AttentionCall:
             self.plan_bytes = int(lib.emlx_attn_plan_bytes(self.num_seqs, self.total, self.hq, hkv))
             ws_bytes = int(lib.emlx_attn_workspace_bytes(self.num_seqs, self.total, self.hq, hkv, self.d))
             self.planned = False
+            # the flags decide which row classes the work list holds; the launch has to use the ones it was built with
+            # (the decode entry point serves the short-row classes only: its work list is built without 128-row units)
+            self.plan_flags = 0 if self.kernel == "decode" else \
+                int(lib.emlx_attn_plan_flags(self.pool.kv_format, self.hq, hkv, self.d))
             if plan is not None and plan[1] == self.hq and plan[2] == self.window and plan[0].numel() >= self.plan_bytes:
                 self.plan_buf, self.planned = plan[0], True   # built together with the batch metadata
+                self.plan_flags = int(plan[3])
             else:
                 self.plan_buf = _scratch.get(dev, "plan", self.plan_bytes, zero=False)
+            a.plan_flags = self.plan_flags
+            if query_len_set and self.plan_flags == int(lib.emlx_attn_plan_flags(self.pool.kv_format, self.hq, hkv, self.d)):
+                # the host knows which query lengths occur: launch only the kernels of those row classes
+                # (emlx_attn_row_class speaks for plans built with emlx_attn_plan_flags)
+                for q_len in set(int(x) for x in query_len_set):
+                    cls = lib.emlx_attn_row_class(self.pool.kv_format, self.hq, hkv, self.d, q_len)
+                    if cls >= 0:
+                        a.row_class_mask |= 1 << cls
             self.workspace = _scratch.get(dev, "workspace", ws_bytes, zero=True)
             a.plan, a.plan_bytes = self.plan_buf.data_ptr(), self.plan_bytes
             a.workspace, a.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
@@ -210,8 +219,7 @@ class AttentionCall:
             nv.check(nv.lib().emlx_attn_plan(
                 nv.ptr(self.query_start_loc), nv.ptr(self.kv_lens), self.num_seqs, self.total, self.hq,
                 self.pool.num_kv_heads, self.pool.block_size, self.window, int(self.args.max_query_len),
-                int(nv.lib().emlx_attn_plan_flags(self.pool.kv_format, self.hq, self.pool.num_kv_heads, self.d)),
-                nv.ptr(self.plan_buf), self.plan_bytes, nv.stream_ptr(self.device)))
+                self.plan_flags, nv.ptr(self.plan_buf), self.plan_bytes, nv.stream_ptr(self.device)))
             self.planned = True
         return self
 

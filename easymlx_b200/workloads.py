@@ -178,12 +178,8 @@ def materialize(w: Workload, device="cuda", seed: int = 0, kv_head_slice: slice 
 
 
 def partition_by_sequence(w: Workload, world: int) -> list[np.ndarray]:
-    """Greedy longest-first assignment of sequences to ranks, balancing attended KV tokens."""
-    order = np.argsort(-(w.kv_lens * 1.0 + 64.0 * w.qlens), kind="stable")
-    load = np.zeros(world)
-    parts: list[list[int]] = [[] for _ in range(world)]
-    for i in order:
-        r = int(np.argmin(load))
-        parts[r].append(int(i))
-        load[r] += float(w.kv_lens[i]) + 64.0 * float(w.qlens[i])
-    return [np.asarray(sorted(p), dtype=np.int64) for p in parts]
+    """The sequences of ``w`` assigned to ``world`` ranks (``distributed.partition_by_sequence``: greedy, longest
+    first, balancing attended KV tokens)."""
+    from .distributed import partition_by_sequence as _partition
+
+    return _partition(w.qlens, w.kv_lens, world)

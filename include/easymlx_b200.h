@@ -92,9 +92,12 @@ typedef struct emlx_attn_args {
     int32_t max_query_len;          /* host hint: upper bound of query tokens per sequence, 0 = unknown */
     int32_t row_class_mask;         /* host hint: OR of 1 << emlx_attn_row_class(q_len) over the batch's query
                                      * lengths; kernels of the other row classes are not launched; 0 = unknown */
+    int32_t plan_flags;             /* the plan_flags `plan` was built with (emlx_attn_plan / emlx_build_metadata):
+                                     * they decide which row classes the plan holds, so the launch must use the same */
     void* plan;                     /* from emlx_attn_plan (not used by emlx_attn_generic)        */
     size_t plan_bytes;
-    void* workspace;                /* split-KV partials and counters; zero it once after allocating */
+    void* workspace;                /* split-KV partials and counters; zero it once after allocating, and again
+                                     * after a call that reported EMLX_DEV_WAIT_TIMEOUT (counters may be left set) */
     size_t workspace_bytes;
     int32_t* status;                /* device status word, may be NULL                */
 } emlx_attn_args;
@@ -116,7 +119,11 @@ int emlx_read_status(const int32_t* status, void* stream);
  *   query_start_loc[S+1]                   out: exclusive prefix sum of query_lens
  *   block_tables[S, MB], kv_lens[S]        out: rows of the scheduled slots, lengths after the step
  *   slot_mapping[T]                        out: page*bs + offset of every new row, -1 = skip
- * A slot id must not appear twice in one batch. */
+ * A slot id must not appear twice in one batch.  A sequence that would outgrow its page-table row sets
+ * EMLX_DEV_OVERFLOW and is left alone: its stored length stays, its rows get slot_mapping -1 and kv_lens[i] = 0.
+ * Ordering: all kernels of this library are launched with programmatic stream serialisation and wait for the
+ * preceding launch of the stream before their first global load, so inputs produced by any earlier work of the
+ * same stream (a projection, a copy, a previous step) are complete when they are read. */
 int emlx_build_metadata(const int32_t* query_lens, const int32_t* slot_ids, int32_t num_seqs, int32_t total_tokens,
                         const int32_t* block_tables_all, int32_t num_slots, int32_t max_blocks_per_seq,
                         int32_t* kv_lens_all, int32_t block_size, int32_t advance_kv_lens,
@@ -156,6 +163,25 @@ int emlx_kv_write_rope(const void* queries, void* queries_out, int32_t num_q_hea
                        const int32_t* token_positions, const emlx_rope* rope, const emlx_pool* pool, int32_t* status,
                        void* stream);
 
+/* (1)+(2) for a batch in which every scheduled sequence appends exactly one token, in ONE launch.  Replaces the
+ * decode fast path of PageCacheView.concatenate_to_cache (caching/paged/cache.py:1155-1206): the row of sequence i
+ * goes to position kv_lens_all[slot_ids[i]] of its slot (page block_tables_all[slot, pos / bs], offset pos % bs), the
+ * stored length becomes pos + 1 (when advance_kv_lens != 0), and the rows of the scheduled slots are gathered:
+ *   query_start_loc[S+1] = 0..S, block_tables[S, MB], kv_lens[S] (lengths after the step), and, when plan != NULL,
+ *   the attention work list (as emlx_attn_plan with max_query_len 1).
+ * keys/values are [S, Hkv, D] in in_dtype.  With `rope` the key is rotated at its position before it is stored and,
+ * when queries_out != NULL, queries [S, Hq, D] are rotated into queries_out (caching/paged/cache.py:1161-1166).
+ * `ticket` is one int32 of device memory owned by the caller, zero before the first call; the kernel leaves it zero.
+ * A slot id must not appear twice.  A sequence whose page-table row is full sets EMLX_DEV_OVERFLOW, keeps its stored
+ * length, writes nothing and gets kv_lens[i] = 0 (attention then returns zero rows for it).  Up to 2048 sequences;
+ * larger batches return EMLX_ERR_UNSUPPORTED and go through emlx_build_metadata + emlx_kv_write. */
+int emlx_kv_write_decode(const void* queries, void* queries_out, const void* keys, const void* values, int32_t in_dtype,
+                         const int32_t* slot_ids, int32_t num_seqs, const int32_t* block_tables_all, int32_t num_slots,
+                         int32_t max_blocks_per_seq, int32_t* kv_lens_all, int32_t advance_kv_lens, const emlx_pool* pool,
+                         const emlx_rope* rope, int32_t* query_start_loc, int32_t* block_tables, int32_t* kv_lens,
+                         int32_t num_q_heads, int32_t sliding_window, int32_t plan_flags, void* plan, size_t plan_bytes,
+                         int32_t* ticket, int32_t* status, void* stream);
+
 /* Work list for the tiled attention kernels, built on the GPU from query_start_loc / kv_lens
  * (replaces the host-side classification of _is_single_token_decode,
  * operations/kernels/unified_attention.py:175-184, which forces a device->host sync). */
@@ -177,9 +203,12 @@ int emlx_attn_row_class(int32_t kv_format, int32_t num_q_heads, int32_t num_kv_h
  * Replaces paged_attention() (operations/kernels/unified_attention.py:1377-1512) and the Metal
  * kernels it launches (unified_attention.py:290-464, 467-608). */
 int emlx_attn_unified(const emlx_attn_args* args, const emlx_pool* pool, void* stream);
-/* (3) Split-KV flash-decode over the plan's short-row units only (rows with few query tokens). */
+/* (3) Split-KV flash-decode over the plan's short-row units only (row classes 0-2: up to 32 query rows per unit).
+ * EMLX_ERR_UNSUPPORTED when the plan can hold no such unit (a plan built with 128-row units and a GQA group above
+ * 16 puts even single-token rows into class 3): `out` is then left untouched. */
 int emlx_attn_decode(const emlx_attn_args* args, const emlx_pool* pool, void* stream);
-/* (4) Prefill-chunk attention over the plan's long-row units only. */
+/* (4) Prefill-chunk attention over the plan's long-row units only (row class 3, 128-row units; needs a plan built
+ * with emlx_attn_plan_flags() bit 0).  EMLX_ERR_UNSUPPORTED when the plan holds no such class. */
 int emlx_attn_prefill(const emlx_attn_args* args, const emlx_pool* pool, void* stream);
 /* Reference-semantics kernel for any geometry the tiled kernels do not cover (head_dim <= 256,
  * any page size, fp16/bf16/fp32); same arithmetic as _paged_attention_reference
@@ -254,13 +283,8 @@ int emlx_rows_assign(int32_t* block_tables, int32_t* kv_lens, int32_t num_slots,
 int emlx_rows_update(int32_t* block_tables, int32_t* kv_lens, int32_t num_slots, int32_t max_blocks_per_seq,
                      const int32_t* ops, int32_t count, int32_t mode, int32_t* status, void* stream);
 
-/* Tracing aid: when `records` is a device buffer of at least 4 * 256 int64, every CTA of the tiled attention kernel
- * writes {start ns, end ns, tiles processed, SM id} (GPU global timer) at index 4 * blockIdx.x; NULL turns it off.
- * Builds with -DEMLX_TRACE_PARTS / -DEMLX_TRACE_PREFILL add per-part and per-tile records behind those (the buffer
- * must then hold 1024 + 256 * 16 * 4 int64); see profiles/. */
-void emlx_set_trace_buffer(int64_t* records);
-
-/* Number of kernels this library has launched from the calling process (for launch accounting). */
+/* Number of kernels this library has launched from the calling process.  A benchmark that reports how many of
+ * the library's kernels ran in its timed region reads it before and after. */
 int64_t emlx_launch_count(void);
 
 #if defined(__GNUC__)

@@ -40,9 +40,10 @@ def test_binding_covers_the_header(built_lib):
 def test_struct_layouts_match_the_header():
     from easymlx_b200 import _native
 
-    # 6 pointers + int64 + 6 int32; 5 pointers + 6 int32 + float + 2 int32 (+4 padding) + 2x(pointer,size_t) + pointer
+    # 6 pointers + int64 + 6 int32; 5 pointers + 6 int32 + float + 3 int32 + 2x(pointer,size_t) + pointer
     assert ctypes.sizeof(_native.Pool) == 6 * 8 + 8 + 6 * 4
-    assert ctypes.sizeof(_native.AttnArgs) == 5 * 8 + 9 * 4 + 4 + 4 * 8 + 8
+    assert ctypes.sizeof(_native.AttnArgs) == 5 * 8 + 10 * 4 + 4 * 8 + 8
+    assert _native.AttnArgs.plan_flags.offset == 76 and _native.AttnArgs.plan.offset == 80
 
 
 def test_host_side_validation_needs_no_gpu(built_lib):

@@ -87,9 +87,21 @@ def test_step_matches_coverage_kernel_and_oracle(workload):
     assert_close(out, ref.float().cpu().numpy(), atol=ATOL, rtol=RTOL)
     assert not torch.isnan(out).any()
 
-    # ---- and the CPU oracle on a few sequences (shortest, median, one of the longest the oracle can take)
+    # ---- and the CPU oracle on the rows that are hardest to get right: the shortest, the median and a long sequence,
+    # the LONGEST decode sequence of the batch, and of every prefill chunk its first row, its last row and eight
+    # random ones (a row of a chunk costs the oracle microseconds per thousand keys, a whole chunk would cost minutes)
     order = np.argsort(w.kv_lens * np.maximum(w.qlens, 1), kind="stable")
-    picks = sorted({int(order[0]), int(order[len(order) // 2]), int(order[min(len(order) - 1, (3 * len(order)) // 4)])})
+    picks = {int(order[0]), int(order[len(order) // 2]), int(order[min(len(order) - 1, (3 * len(order)) // 4)])}
+    decode_like = np.flatnonzero(w.qlens <= 8)
+    if len(decode_like):
+        picks.add(int(decode_like[np.argmax(w.kv_lens[decode_like])]))
+    row_subset = {}
+    rng_rows = np.random.default_rng(5)
+    for s_idx in np.flatnonzero(w.qlens > 32):
+        n = int(w.qlens[s_idx])
+        picks.add(int(s_idx))
+        row_subset[int(s_idx)] = np.unique(np.concatenate([[0, n - 1], rng_rows.integers(0, n, 8)]))
+    picks = sorted(picks)
     bt = c.block_tables.cpu().numpy()
     pages = np.unique(np.concatenate([bt[s, : -(-int(w.kv_lens[s]) // 128)] for s in picks]))
     remap = -np.ones(c.num_blocks, dtype=np.int64)
@@ -105,7 +117,7 @@ def test_step_matches_coverage_kernel_and_oracle(workload):
     sub_bt = np.where(bt >= 0, remap[np.maximum(bt, 0)], -1).astype(np.int32)
     qsl = np.concatenate([[0], np.cumsum(w.qlens)]).astype(np.int32)
     want = opa.paged_attention_rows(w.q.cpu().numpy(), kf, vf, sub_bt, w.kv_lens.astype(np.int32), qsl,
-                                    softmax_scale=w.d ** -0.5, seq_subset=picks)
-    rows = np.concatenate([np.arange(qsl[s], qsl[s + 1]) for s in picks])
+                                    softmax_scale=w.d ** -0.5, seq_subset=picks, row_subset=row_subset)
+    rows = np.concatenate([qsl[s] + row_subset[s] if s in row_subset else np.arange(qsl[s], qsl[s + 1]) for s in picks])
     assert_close(out[torch.from_numpy(rows).cuda()], want[rows].astype(np.float32), atol=ATOL, rtol=RTOL)
     del performer

@@ -197,3 +197,34 @@ def test_tail_of_a_long_peaked_row_over_an_affine_pool(bits):
     assert_close(fast, ref.float().cpu().numpy())
     row_shift = (fast.float() - ref.float()).mean(dim=-1).abs().max().item()
     assert row_shift <= 1e-3, f"rows shifted by up to {row_shift:.2e}"
+
+
+def test_tail_of_a_long_peaked_row_over_an_fp16_pool():
+    """One key holds nearly all the weight of a row and 131 000 others sit 2^-25.5 below it.  As plain fp16 numbers
+    those weights would all round to zero (half the smallest subnormal is 2^-25) and the row would lose everything the
+    others contribute, 5e-3 in every channel; the kernels therefore scale the weights up before the 16-bit cast.  The
+    128-row chunk runs on the tcgen05 kernel (one thread follows a row over all of its keys, so the whole tail is at
+    stake), the decode row on the split-KV kernel.  Expected values are exact: scores are 0 except for the first
+    key, values are 2 except for the first key's 0."""
+    import easymlx_b200 as emlx
+    hq, hkv, d = 4, 1, 128
+    qlens, prior = [32, 1], [131_072, 131_072]
+    kv = [a + b for a, b in zip(qlens, prior)]
+    cache = _pool(hkv, d, kv, 0, seed=5)
+    cache.key_cache.zero_()
+    cache.value_cache.fill_(2.0)
+    for s in range(2):
+        first_page = int(cache.block_tables[s, 0])
+        cache.key_cache[first_page, 0] = 1.25
+        cache.value_cache[first_page, 0] = 0.0
+    q = torch.full((sum(qlens), hq, d), 1.25, device="cuda", dtype=torch.float16)
+    fast = _run(cache, q, qlens, kv, None)
+    ref = _run(cache, q, qlens, kv, "generic")
+    gap = 1.25 * 1.25 * d / np.sqrt(d)                      # score of the first key; every other score is 0
+    others = np.concatenate([prior[0] + np.arange(qlens[0]), [prior[1]]]).astype(np.float64)  # keys besides the first
+    tail = others * np.exp(-gap)
+    expect = 2.0 * tail / (1.0 + tail)                       # per packed row, the same in every head and channel
+    assert 4e-3 < expect.min() < 7e-3
+    got = fast.float().cpu().numpy().astype(np.float64)
+    assert np.abs(got - expect[:, None, None]).max() <= 3e-4, np.abs(got - expect[:, None, None]).max()
+    assert_close(fast, ref.float().cpu().numpy())

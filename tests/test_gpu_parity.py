@@ -193,6 +193,41 @@ def test_affine_write_is_bit_exact(name, bits):
     np.testing.assert_array_equal(cache.kv_lens.cpu().numpy(), meta["kv_lens_all"])
 
 
+def test_two_appends_in_a_row_and_strided_inputs():
+    """Launch ordering: every kernel waits for the launch before it, so a second append right behind the first sees the
+    advanced length, and rows that a copy kernel has only just made contiguous (views into a fused QKV projection)
+    are complete when the write reads them.  Bit-exact against the oracle."""
+    from easymlx_b200 import PageCacheView, PageMetadata, build_query_start_loc
+
+    rng = np.random.default_rng(5)
+    hkv, hq, d, bs = 4, 8, 64, 128
+    cache = PageCacheView.init(num_seqs=3, max_seq_len=512, num_kv_heads=hkv, head_dim=d, block_size=bs)
+    bt = rng.permutation(12).astype(np.int32).reshape(3, 4)
+    cache.block_tables.copy_(torch.from_numpy(bt))
+    kc = np.zeros((12, bs, hkv, d), np.float16)
+    vc = np.zeros_like(kc)
+    lens = np.zeros(3, np.int32)
+    for n in (100, 60, 3, 130):  # back to back on slot 1, crossing a page edge, no synchronisation in between
+        k = rng.standard_normal((n, hkv, d)).astype(np.float16)
+        v = rng.standard_normal((n, hkv, d)).astype(np.float16)
+        cache.append(1, dev(k), dev(v))
+        kv_write.append(kc, vc, bt, lens, 1, k, v, bs)
+    # a packed batch whose K and V are strided views of one [T, Hq + 2 Hkv, D] projection output
+    qlens, slots = [7, 1, 30], [2, 1, 0]
+    t = sum(qlens)
+    qkv = dev(rng.standard_normal((t, hq + 2 * hkv, d)).astype(np.float16))
+    q, k, v = qkv[:, :hq], qkv[:, hq:hq + hkv], qkv[:, hq + hkv:]
+    assert not k.is_contiguous()
+    cache.concatenate_to_cache(q, k, v, cache_metadata=PageMetadata(query_start_loc=build_query_start_loc(qlens)),
+                               slot_ids=slots, query_lens=qlens)
+    cache.check()
+    m = kv_write.batch_metadata(qlens, slots, bt, lens, bs)
+    kv_write.write_rows(kc, vc, k.cpu().numpy(), v.cpu().numpy(), m["slot_mapping"])
+    np.testing.assert_array_equal(cache.key_cache.cpu().numpy(), kc)
+    np.testing.assert_array_equal(cache.value_cache.cpu().numpy(), vc)
+    np.testing.assert_array_equal(cache.kv_lens.cpu().numpy(), m["kv_lens_all"])
+
+
 def test_bad_slot_and_overflow_are_flagged():
     from easymlx_b200 import PageCacheView, PageMetadata, build_query_start_loc
 
@@ -203,11 +238,15 @@ def test_bad_slot_and_overflow_are_flagged():
             query_start_loc=build_query_start_loc([3])), slot_ids=[5])
         cache.check()
     big = torch.zeros((300, 2, 64), dtype=torch.float16, device="cuda")
+    before = cache.key_cache.clone()
     with pytest.raises(RuntimeError, match="outgrows"):
         cache.concatenate_to_cache(big.repeat(1, 2, 1), big, big, cache_metadata=PageMetadata(
             query_start_loc=build_query_start_loc([300])), slot_ids=[1])
         cache.check()
     cache.check()  # reported once, then clear
+    # the sequence that would not fit is left alone: length unchanged, nothing written (the reference raises before
+    # it touches the cache)
+    assert cache.kv_lens.cpu().tolist() == [0, 0] and torch.equal(cache.key_cache, before)
 
 
 def test_bounded_wait_reports_a_timeout_and_leaves_the_context_usable():

@@ -36,6 +36,55 @@ def test_factory_tables_match_the_oracle_restatement():
         get_rope(64, 10000.0, False, {"type": "nope"})
 
 
+def test_longrope_picks_its_table_by_sequence_length():
+    """Su-scaled rotary embedding (layers/rotary/_rotary.py:36-131 of the reference): periods are the base periods
+    times the short or the long factors, the magnitude scale is sqrt(1 + ln(factor) / ln(original_max)), and the long
+    table applies to sequences of more than original_max tokens."""
+    import math
+
+    from easymlx_b200.layers import LongRopeEmbedding, get_rope
+
+    short, long_ = [1.0 + 0.01 * i for i in range(16)], [2.0 + 0.5 * i for i in range(16)]
+    r = get_rope(32, 10000.0, False, {"type": "longrope", "original_max_position_embeddings": 4096,
+                                      "short_factor": short, "long_factor": long_}, 131072)
+    assert isinstance(r, LongRopeEmbedding)
+    base = np.float32(10000.0) ** (np.arange(0, 32, 2, dtype=np.float32) / np.float32(32))
+    np.testing.assert_allclose(r.short.freqs, np.asarray(short, np.float32) * base, rtol=1e-6)
+    np.testing.assert_allclose(r.long.freqs, np.asarray(long_, np.float32) * base, rtol=1e-6)
+    want = math.sqrt(1 + math.log(131072 / 4096) / math.log(4096))
+    assert abs(r.short.mscale - want) < 1e-12 and abs(r.long.mscale - want) < 1e-12
+    assert r.select(4096) is r.short and r.select(4097) is r.long
+    same = get_rope(32, 10000.0, False, {"rope_type": "longrope", "original_max_position_embeddings": 4096,
+                                         "short_factor": short, "long_factor": long_}, 4096)
+    assert same.short.mscale == 1.0  # no length extension: no magnitude change
+
+
+@pytest.mark.gpu
+def test_longrope_in_the_cache_write_uses_the_long_table_past_the_threshold():
+    import easymlx_b200 as emlx
+    from easymlx_b200.layers import get_rope
+
+    long_ = [1.0 + 0.25 * i for i in range(32)]
+    rope = get_rope(64, 10000.0, False, {"type": "longrope", "original_max_position_embeddings": 256,
+                                         "short_factor": [1.0] * 32, "long_factor": long_}, 1024)
+    hkv, hq, d, bs = 2, 4, 64, 128
+    rng = np.random.default_rng(1)
+    for base_len, table in ((100, rope.short), (300, rope.long)):
+        cache = emlx.PageCacheView.init(num_seqs=1, max_seq_len=512, num_kv_heads=hkv, head_dim=d, block_size=bs)
+        cache.kv_lens.fill_(base_len)
+        q = rng.standard_normal((3, hq, d)).astype(np.float16)
+        k = rng.standard_normal((3, hkv, d)).astype(np.float16)
+        meta = emlx.PageMetadata(query_start_loc=emlx.build_query_start_loc([3]))
+        pq, kc, _, _ = cache.concatenate_to_cache(torch.from_numpy(q).cuda(), torch.from_numpy(k).cuda(),
+                                                  torch.from_numpy(k).cuda(), cache_metadata=meta, slot_ids=[0],
+                                                  query_lens=[3], rope=rope)
+        pos = base_len + np.arange(3)
+        want_q = orope.rotate(q, pos, table.freqs, 64, mscale=table.mscale)
+        np.testing.assert_allclose(pq.float().cpu().numpy(), want_q.astype(np.float32), atol=4e-3, rtol=2e-3)
+        x = torch.from_numpy(q).cuda()
+        assert torch.equal(rope(x.reshape(1, 3, hq, d).permute(0, 2, 1, 3), offset=base_len).permute(0, 2, 1, 3).reshape(3, hq, d), pq)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("traditional", [False, True])
 @pytest.mark.parametrize("bits", [0, 8])
