@@ -3,11 +3,13 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--config c2] [--impl ours|reference]
 
 A step is one pass of the hot path over one packed batch: batch metadata + paged KV write of
-the step's new rows + attention.  The default workload is c2 (Llama-3-8B-shaped decode, 64
-sequences, 8-bit affine KV); see easymlx_b200/workloads.py for the five configurations.
-Under torchrun every rank owns its own sequences and page pool (partition by sequence, no
-collective; c4 alone shards KV heads and all-gathers the output), the timed region is
-bracketed by barriers and the maximum over ranks is reported.  Prints one JSON line.
+the step's new rows + attention.  The headline workload is c2 (Llama-3-8B-shaped decode, 64
+sequences, 8-bit affine KV); the same JSON line carries all five configurations of
+easymlx_b200/workloads.py under "configs" (one GPU), and under torchrun the strong-scaling runs
+of c3 / c5 (the same global batch partitioned by sequence) and c4 sharded by KV head with its
+NCCL all-gather.  Under torchrun every rank owns its own sequences and page pool (no collective
+on the data path except c4's all-gather), every timed region is bracketed by barriers and the
+maximum over ranks is reported.  Prints one JSON line.
 """
 
 from __future__ import annotations
@@ -26,6 +28,8 @@ sys.path.insert(0, ROOT)
 
 METRIC = "attended_kv_tokens_per_s"
 UNIT = "tokens/s"
+ALL_CONFIGS = ("c1", "c2", "c3", "c4", "c5")
+BAD_CLOCK_REASONS = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown")
 
 
 def _peaks():
@@ -33,8 +37,9 @@ def _peaks():
     if os.path.exists(path):
         p = json.load(open(path))
         return dict(hbm_gbs=float(p["hbm_gbs"]), bf16_tflops=float(p.get("bf16_tflops_sustained", p["bf16_tflops"])),
-                    source="measured (MEASURED_PEAKS.json)")
-    return dict(hbm_gbs=6650.0, bf16_tflops=1400.0, source="fallback (6.65 TB/s, 1.4 PFLOP/s sustained)")
+                    bf16_tflops_burst=float(p["bf16_tflops"]), source="measured (MEASURED_PEAKS.json)")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1400.0, bf16_tflops_burst=1590.0,
+                source="fallback (6.65 TB/s, 1.4 PFLOP/s sustained)")
 
 
 class ClockSampler:
@@ -46,6 +51,7 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.proc = index, None
+        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
 
     def __enter__(self):
         try:
@@ -57,7 +63,6 @@ class ClockSampler:
         return self
 
     def __exit__(self, *exc):
-        self.summary = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.proc is None:
             return
         time.sleep(0.15)
@@ -92,20 +97,31 @@ def _dist():
     return world, rank, local
 
 
+def _kv_format(bits):
+    return {0: "fp16", 8: "affine8 group-64", 4: "affine4 group-64"}[bits]
+
+
+def headline_config(name, world, layers):
+    """The `config` object of the JSON line; both arms print the same one for the same command line."""
+    from easymlx_b200 import workloads
+
+    base = workloads.describe(name)
+    return {
+        "workload": f"{name}: {base.description}",
+        "kv_format": _kv_format(base.bits),
+        "step": (f"batch metadata + work list + paged KV write + attention; {layers} consecutive steps per CUDA "
+                 "graph, as an engine step holds one per layer"),
+        "parallelism": f"sequence partition x{world}" + (" (each rank one draw of the configuration)" if world > 1 else ""),
+        "l2": "per-step KV working set exceeds L2 (no flush needed)",
+        "sequences_per_gpu": int(len(base.qlens)), "tokens_per_gpu": int(base.total_tokens),
+        "attended_kv_tokens_per_gpu": int(base.attended_kv_tokens),
+    }
+
+
 # ----------------------------------------------------------------------------- CPU arm
 
-def _pick_sample(w, budget_tokens):
-    order = np.argsort(w.kv_lens, kind="stable")
-    picked, total = [], 0
-    for s in order[::max(1, len(order) // 8)]:
-        if total and total + w.kv_lens[s] * max(1, w.qlens[s]) > budget_tokens:
-            continue
-        picked.append(int(s)); total += int(w.kv_lens[s] * max(1, w.qlens[s]))
-    return np.asarray(sorted(picked or [int(order[0])]), dtype=np.int64)
-
-
 def _cpu_pool_for(w, seqs, seed):
-    """NumPy-built pool holding only the sampled sequences (same distributions as the GPU workload)."""
+    """NumPy-built pool holding only the listed sequences (same distributions as the GPU workload)."""
     from oracle import kv_quant
 
     rng = np.random.default_rng(seed)
@@ -117,22 +133,25 @@ def _cpu_pool_for(w, seqs, seed):
         n = -(-int(kv[s]) // 128)
         bt[s, :n] = np.arange(cursor, cursor + n)
         cursor += n
-    shape = (n_pages, 128, w.hkv, w.d)
-    kc = rng.standard_normal(shape, dtype=np.float32).astype(np.float16)
-    vc = rng.standard_normal(shape, dtype=np.float32).astype(np.float16)
     host = dict(block_tables=bt, kv_lens=kv,
                 query_start_loc=np.concatenate([[0], np.cumsum(w.qlens)]).astype(np.int32))
-    if w.bits:
-        kcodes, ks, kb = kv_quant.quantize_rows(kc, w.bits)
-        vcodes, vs, vb = kv_quant.quantize_rows(vc, w.bits)
-        host.update(key_cache=kv_quant.pack_codes(kcodes, w.bits),
-                    value_cache=kv_quant.pack_codes(np.ascontiguousarray(np.transpose(vcodes, (0, 2, 3, 1))), w.bits),
-                    k_scale=np.ascontiguousarray(np.transpose(ks, (0, 2, 1, 3))),
-                    k_bias=np.ascontiguousarray(np.transpose(kb, (0, 2, 1, 3))),
-                    v_scale=np.ascontiguousarray(np.transpose(vs, (0, 2, 1, 3))),
-                    v_bias=np.ascontiguousarray(np.transpose(vb, (0, 2, 1, 3))))
-    else:
-        host.update(key_cache=kc, value_cache=vc)
+    parts = {}
+    for p0 in range(0, n_pages, 128):  # in pieces, so that the fp32 temporaries of the quantiser stay small
+        shape = (min(128, n_pages - p0), 128, w.hkv, w.d)
+        kc = rng.standard_normal(shape, dtype=np.float32).astype(np.float16)
+        vc = rng.standard_normal(shape, dtype=np.float32).astype(np.float16)
+        if w.bits:
+            kcodes, ks, kb = kv_quant.quantize_rows(kc, w.bits)
+            vcodes, vs, vb = kv_quant.quantize_rows(vc, w.bits)
+            piece = dict(key_cache=kv_quant.pack_codes(kcodes, w.bits),
+                         value_cache=kv_quant.pack_codes(np.ascontiguousarray(np.transpose(vcodes, (0, 2, 3, 1))), w.bits),
+                         k_scale=np.transpose(ks, (0, 2, 1, 3)), k_bias=np.transpose(kb, (0, 2, 1, 3)),
+                         v_scale=np.transpose(vs, (0, 2, 1, 3)), v_bias=np.transpose(vb, (0, 2, 1, 3)))
+        else:
+            piece = dict(key_cache=kc, value_cache=vc)
+        for name, a in piece.items():
+            parts.setdefault(name, []).append(np.ascontiguousarray(a))
+    host.update({name: np.concatenate(chunks) for name, chunks in parts.items()})
     q = rng.standard_normal((w.total_tokens, w.hq, w.d), dtype=np.float32).astype(np.float16)
     return host, q
 
@@ -146,7 +165,6 @@ def _fork_worker(seq):
 
     kv = int(host["kv_lens"][seq])
     pages = host["block_tables"][seq, : -(-kv // 128)]
-    sub = dict(host)
     # one sequence: gather (and dequantise) only its pages, as the reference's per-sequence loop does
     kc, vc = host["key_cache"][pages], host["value_cache"][pages]
     if w.bits:
@@ -154,15 +172,15 @@ def _fork_worker(seq):
         vc = kv_quant.dequantize_value_pool(vc, host["v_scale"][pages], host["v_bias"][pages], w.bits)
     bt = -np.ones_like(host["block_tables"])
     bt[seq, : len(pages)] = np.arange(len(pages))
-    sub.update(key_cache=kc, value_cache=vc, block_tables=bt)
     opa.paged_attention_rows(q, kc, vc, bt, host["kv_lens"], host["query_start_loc"], softmax_scale=w.d ** -0.5,
                              seq_subset=[seq])
     return kv
 
 
 def run_reference(args):
-    """The reference's CPU algorithm for this op (its NumPy path, restated in oracle/) on the host cores.
-    The reference project itself cannot run here: it needs Apple's MLX, which has no Linux/py3.12 wheel."""
+    """The reference's CPU algorithm for this op (its NumPy path, restated in oracle/) on the host cores, over the
+    whole batch of the configuration (one draw of it when the GPU arm runs several).  The reference project itself
+    cannot run on the measurement box: it needs Apple's MLX (no Linux wheel) and its sources do not travel."""
     world, rank, _ = _dist()
     if rank != 0:
         return
@@ -173,13 +191,14 @@ def run_reference(args):
     os.environ.setdefault("OMP_NUM_THREADS", "1")
     w = workloads.describe(args.config)
     cores = len(os.sched_getaffinity(0))
-    seqs = _pick_sample(w, budget_tokens=args.cpu_budget_tokens * max(1, cores // 2))
+    # longest first, so that the pool's workers finish together
+    seqs = np.argsort(-(w.kv_lens * np.maximum(w.qlens, 1)), kind="stable")
     host, q = _cpu_pool_for(w, seqs, seed=1234)
     _FORK_STATE.update(w=w, host=host, q=q)
     ctx = mp.get_context("fork")
     times = []
     with ctx.Pool(min(cores, len(seqs))) as pool:
-        budget_s, t_start = 150.0, time.perf_counter()
+        budget_s, t_start = 240.0, time.perf_counter()
         for it in range(args.warmup + args.steps):
             t0 = time.perf_counter()
             tokens = sum(pool.map(_fork_worker, [int(s) for s in seqs], chunksize=1))
@@ -190,14 +209,16 @@ def run_reference(args):
                 break
     per_step = float(np.mean(times))
     value = tokens / per_step
-    sample = (f"{len(seqs)} of {len(w.qlens)} sequences of {args.config} ({tokens} attended KV tokens per step), "
-              f"{len(times)} timed steps, sequences spread over a fork pool")
+    layers = _layers_per_graph(args)
+    sample = (f"all {len(seqs)} sequences of one draw of {args.config} ({tokens} attended KV tokens per step), "
+              f"{len(times)} timed steps, sequences spread over a fork pool of {min(cores, len(seqs))} processes; "
+              + ("affine KV has no path in the reference: the oracle dequantises, then attends with the reference's "
+                 "NumPy algorithm" if w.bits else "fp16 KV, the reference's NumPy algorithm"))
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
         "warmup": args.warmup, "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": f"{args.config}: {w.description}", "note": "reference algorithm on host cores; "
-                   + ("affine KV has no reference path: oracle dequantise-then-attend" if w.bits else "fp16 KV")},
+        "config": headline_config(args.config, world, layers),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": min(cores, len(seqs)), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -207,7 +228,13 @@ def run_reference(args):
 
 def _cpu_baseline_single_core(w, config, budget_tokens):
     """The oracle on one core over a bounded sample of the same workload (rank 0, N=1 only)."""
-    seqs = _pick_sample(w, budget_tokens=budget_tokens)
+    order = np.argsort(w.kv_lens, kind="stable")
+    picked, total = [], 0
+    for s in order[::max(1, len(order) // 8)]:
+        if total and total + w.kv_lens[s] * max(1, w.qlens[s]) > budget_tokens:
+            continue
+        picked.append(int(s)); total += int(w.kv_lens[s] * max(1, w.qlens[s]))
+    seqs = np.asarray(sorted(picked or [int(order[0])]), dtype=np.int64)
     host, q = _cpu_pool_for(w, seqs, seed=4321)
     _FORK_STATE.update(w=w, host=host, q=q)
     _fork_worker(int(seqs[0]))  # warm-up
@@ -224,200 +251,351 @@ def _cpu_baseline_single_core(w, config, budget_tokens):
                       f"{dt:.1f} s of NumPy oracle (dequantise + attend), BLAS threads pinned to 1"}
 
 
+# ----------------------------------------------------------------------------- GPU arm
+
+def _layers_per_graph(args):
+    layers = 1 if args.no_graph else max(1, args.layers_per_graph)
+    return 1 if args.steps % layers else layers
+
+
+class Bench:
+    """Timing helpers bound to one rank."""
+
+    def __init__(self, args, dev, world, rank, local):
+        import torch
+
+        self.torch, self.args, self.dev = torch, args, dev
+        self.world, self.rank, self.local = world, rank, local
+        self.peaks = _peaks()
+
+    def barrier(self):
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def timed(self, fn, steps):
+        """Milliseconds for `steps` calls of fn: CUDA events on the launching stream, barrier + synchronise on both
+        sides, maximum over ranks."""
+        torch = self.torch
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.barrier()
+        start.record()
+        for _ in range(steps):
+            fn()
+        stop.record()
+        self.barrier()
+        ms = start.elapsed_time(stop)
+        if self.world > 1:
+            import torch.distributed as dist
+            t = torch.tensor([ms], device=self.dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    def graph_time(self, launch, reps, steps):
+        """Average milliseconds of one `launch` replayed from a CUDA graph that holds `reps` of them."""
+        torch = self.torch
+        launch()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                launch()
+        for _ in range(3):
+            g.replay()
+        n = max(1, steps // reps)
+        return self.timed(g.replay, n) / (n * reps)
+
+    def all_sum(self, x):
+        if self.world == 1:
+            return float(x)
+        import torch.distributed as dist
+        t = self.torch.tensor([float(x)], device=self.dev, dtype=self.torch.float64)
+        dist.all_reduce(t)
+        return float(t.item())
+
+    # ------------------------------------------------------------------ one workload on this rank
+    def measure(self, w, label, *, after_step=None, parts=True, e2e=True):
+        """Step time (device-resident), end-to-end step time and the attention launch alone for workload `w`.
+        `after_step(out)` runs inside every step (the KV-head shard's all-gather)."""
+        import easymlx_b200 as emlx
+        from easymlx_b200 import _native as nv
+        from easymlx_b200.operations.kernels.unified_attention import AttentionCall
+        from easymlx_b200.runtime import AttentionStep
+
+        torch, args, dev = self.torch, self.args, self.dev
+        layers = _layers_per_graph(args)
+        step = AttentionStep(w.cache, w.q, w.k, w.v, w.qlens.tolist(), w.slot_ids)
+
+        def one_step():
+            out = step.step()
+            if after_step is not None:
+                after_step(out)
+            return out
+
+        for _ in range(2):
+            step._eager()
+        torch.cuda.synchronize()
+        if not args.no_graph:
+            step.capture(warmup=2, steps_per_graph=layers)
+        for _ in range(max(3, args.warmup)):
+            one_step()
+        torch.cuda.synchronize()
+
+        ms_total, clocks = None, None
+        for attempt in range(2):  # a run that saw a thermal / hardware slowdown is taken again, once
+            with ClockSampler(self.local) as sampler:
+                ms_total = self.timed(one_step, args.steps // layers)
+                # the timed region lasts a few milliseconds, shorter than nvidia-smi's sampling period: the same step
+                # keeps replaying (untimed) for a moment so that the clock record holds samples under this load
+                t_end = time.perf_counter() + 0.35
+                while time.perf_counter() < t_end:
+                    for _ in range(20):
+                        one_step()
+                    torch.cuda.synchronize()
+            clocks = dict(sampler.summary, window="timed steps + 0.35 s of the same step replayed", attempts=attempt + 1)
+            if not any(r in BAD_CLOCK_REASONS for r in clocks["reasons"]):
+                break
+        ms_step = ms_total / args.steps
+        tokens_all = self.all_sum(w.attended_kv_tokens) if after_step is None else float(w.attended_kv_tokens)
+        result = {
+            "label": label, "kv_format": _kv_format(w.bits), "us_per_batch": ms_step * 1e3,
+            "value": tokens_all / (ms_step * 1e-3), "unit": UNIT,
+            "attended_kv_tokens": int(tokens_all), "sequences_this_rank": int(len(w.qlens)),
+            "tokens_this_rank": int(w.total_tokens), "gpu_launches_per_step": int(step.launches_per_step),
+            "clocks": clocks,
+        }
+
+        # ---- end to end: pinned host q/k/v in, host output back, every step; q, k and v travel as one packed host
+        # buffer (one copy per step instead of three) and the device side reads them through views of it
+        if e2e:
+            parts_qkv = (w.q, w.k, w.v)
+            sizes = [t.numel() for t in parts_qkv]
+            hqkv = torch.cat([t.reshape(-1).cpu() for t in parts_qkv]).pin_memory()
+            dqkv = torch.empty_like(hqkv, device=dev)
+            dqkv.copy_(hqkv)
+            dq, dk, dv = (v.view(t.shape) for v, t in zip(torch.split(dqkv, sizes), parts_qkv))
+            hout = torch.empty_like(w.q, device="cpu").pin_memory()
+            step1 = AttentionStep(w.cache, dq, dk, dv, w.qlens.tolist(), w.slot_ids).capture(warmup=2)
+
+            def e2e_step():
+                dqkv.copy_(hqkv, non_blocking=True)
+                out = step1.step()
+                if after_step is not None:
+                    after_step(out)
+                hout.copy_(out, non_blocking=True)
+
+            for _ in range(3):
+                e2e_step()
+            ms_e2e = self.timed(e2e_step, args.steps) / args.steps
+            result["e2e"] = {"value": tokens_all / (ms_e2e * 1e-3), "unit": UNIT,
+                             "h2d_bytes_per_step": int(hqkv.numel() * hqkv.element_size()),
+                             "d2h_bytes_per_step": int(hout.numel() * hout.element_size()),
+                             "us_per_batch": ms_e2e * 1e3}
+            del step1, dqkv, hqkv, hout
+
+        # ---- the attention launch alone (over the already written pool), for the roofline
+        c = w.cache
+        lens_dev = torch.from_numpy(w.kv_lens.astype(np.int32)).to(dev)
+        qsl = emlx.build_query_start_loc(w.qlens.tolist(), device=dev)
+        extra = dict(k_scale=c.k_scales, v_scale=c.v_scales, k_bias=c.k_biases, v_bias=c.v_biases) if w.bits else {}
+        lens_set = sorted(set(int(x) for x in w.qlens if x > 0))
+
+        def attention_call(len_set):
+            return AttentionCall(w.q, c.key_cache, c.value_cache, c.block_tables, lens_dev, qsl,
+                                 max_query_len=int(w.qlens.max()), query_len_set=len_set, **extra).plan()
+
+        call = attention_call(lens_set)
+        ms_attn = self.graph_time(call.launch, 10, args.steps)
+        attn_bytes = w.attention_bytes()
+        achieved = attn_bytes / (ms_attn * 1e-3) / 1e9
+        hbm = self.peaks["hbm_gbs"]
+        roof = {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                "frac_of_8TBs_nominal": achieved / 8000.0, "kernel": "attention (all launches of emlx_attn_unified)",
+                "algorithmic_bytes_per_launch": int(attn_bytes), "us_per_launch": ms_attn * 1e3,
+                "peak_source": self.peaks["source"],
+                "l2": "KV working set exceeds L2" if attn_bytes > 3 * 126e6 else
+                      "working set comparable to the 126 MB L2: the figure is L2-assisted"}
+        result["step_frac_of_hbm_peak"] = attn_bytes / (ms_step * 1e-3) / 1e9 / hbm
+        result["roofline"] = roof
+
+        # ---- mixed batches: the prefill-chunk launch (tensor-bound) and the short-row launches (HBM-bound) alone
+        lib = nv.lib()
+        fmt = w.bits if w.bits else nv.KV_FLOAT
+        cls_of = {q: int(lib.emlx_attn_row_class(fmt, w.hq, w.hkv, w.d, q)) for q in lens_set}
+        long_lens = [q for q in lens_set if cls_of[q] == 3]
+        short_lens = [q for q in lens_set if cls_of[q] != 3]
+        if parts and long_lens and self.world == 1:  # (ranks may hold different row classes: no collective timing here)
+            is_long = np.isin(w.qlens, long_lens)
+            flops = 4 * w.hq * w.d * int(sum(int(q) * int(p) + int(q) * (int(q) + 1) // 2
+                                             for q, p in zip(w.qlens[is_long], w.prior[is_long])))
+            ms_pf = self.graph_time(attention_call(long_lens).launch, 5, args.steps)
+            tf = flops / (ms_pf * 1e-3) / 1e12
+            roof["tensor"] = {"kernel": "attn_prefill_kernel (128-row units, tcgen05), timed alone", "flops": int(flops),
+                              "us_per_launch": ms_pf * 1e3, "achieved_tflops": tf,
+                              "peak_sustained_tflops": self.peaks["bf16_tflops"],
+                              "frac_of_sustained": tf / self.peaks["bf16_tflops"],
+                              "frac_of_burst": tf / self.peaks["bf16_tflops_burst"]}
+            if short_lens:
+                ms_dec = self.graph_time(attention_call(short_lens).launch, 5, args.steps)
+                kv_short = int(w.kv_lens[~is_long].sum()) * 2 * w.hkv * w.row_bytes()
+                roof["decode_part"] = {"kernel": "short-row launches timed alone", "us_per_launch": ms_dec * 1e3,
+                                       "kv_bytes": kv_short, "achieved_gbs": kv_short / (ms_dec * 1e-3) / 1e9,
+                                       "frac": kv_short / (ms_dec * 1e-3) / 1e9 / hbm}
+                roof["bound_of_the_whole_launch_us"] = max(attn_bytes / hbm / 1e3, flops / self.peaks["bf16_tflops"] / 1e6)
+        del step
+        return result
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
 
-    import easymlx_b200 as emlx
-    from easymlx_b200 import _native as nv, workloads
-    from easymlx_b200.runtime import AttentionStep
+    from easymlx_b200 import workloads
+    from easymlx_b200.distributed import all_gather_heads
 
     world, rank, local = _dist()
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    base = workloads.describe(args.config)
-    head_shard = args.config == "c4" and world > 1 and base.hkv % world == 0
-    if head_shard:
-        per = base.hkv // world
-        w = workloads.materialize(base, dev, seed=0, kv_head_slice=slice(rank * per, (rank + 1) * per))
-    else:
-        # weak scaling: the global batch is `world` draws of the configuration (different lengths per draw), partitioned
-        # by sequence, longest first, so that every rank attends about the same number of KV tokens; every rank owns
-        # the page pool of its own sequences
-        if world == 1:
-            w = workloads.materialize(base, dev, seed=0)
-        else:
-            draws = [workloads.describe(args.config, seed=None if r == 0 else 1000 * r + 7) for r in range(world)]
-            whole = workloads.describe(args.config)
-            whole.qlens = np.concatenate([d.qlens for d in draws])
-            whole.prior = np.concatenate([d.prior for d in draws])
-            mine = workloads.partition_by_sequence(whole, world)[rank]
-            w = workloads.materialize(whole, dev, seed=rank, seq_subset=mine)
+    bench = Bench(args, dev, world, rank, local)
+    layers = _layers_per_graph(args)
+    head = args.config
+
     if args.attn_only:
         # profiling aid: a few bare attention launches over the written pool, nothing else
+        import easymlx_b200 as emlx
         from easymlx_b200.operations.kernels.unified_attention import AttentionCall
 
+        w = workloads.materialize(workloads.describe(head), dev, seed=0)
         c = w.cache
         extra = dict(k_scale=c.k_scales, v_scale=c.v_scales, k_bias=c.k_biases, v_bias=c.v_biases) if w.bits else {}
         call = AttentionCall(w.q, c.key_cache, c.value_cache, c.block_tables,
                              torch.from_numpy(w.kv_lens.astype(np.int32)).to(dev),
                              emlx.build_query_start_loc(w.qlens.tolist(), device=dev),
-                             max_query_len=int(w.qlens.max()), **extra).plan()
+                             max_query_len=int(w.qlens.max()),
+                             query_len_set=sorted(set(int(x) for x in w.qlens if x > 0)), **extra).plan()
         for _ in range(args.attn_only):
             call.launch()
         torch.cuda.synchronize()
-        print(json.dumps({"attn_only": args.attn_only, "config": args.config}))
+        print(json.dumps({"attn_only": args.attn_only, "config": head}))
         return
-    step = AttentionStep(w.cache, w.q, w.k, w.v, w.qlens.tolist(), w.slot_ids)
-    gathered = None
-    if head_shard:
-        gathered = torch.empty((world,) + tuple(w.q.shape), dtype=w.q.dtype, device=dev)
 
-    def one_step():
-        out = step.step()
-        if head_shard:
-            dist.all_gather_into_tensor(gathered.view(-1, *out.shape[1:]), out)
-        return out
+    def weak_workload(name):
+        """N draws of the configuration, partitioned by sequence, longest first, so that every rank attends about
+        the same number of KV tokens; every rank owns the page pool of its own sequences."""
+        base = workloads.describe(name)
+        if world == 1:
+            return workloads.materialize(base, dev, seed=0)
+        draws = [workloads.describe(name, seed=None if r == 0 else 1000 * r + 7) for r in range(world)]
+        whole = workloads.describe(name)
+        whole.qlens = np.concatenate([d.qlens for d in draws])
+        whole.prior = np.concatenate([d.prior for d in draws])
+        mine = workloads.partition_by_sequence(whole, world)[rank]
+        return workloads.materialize(whole, dev, seed=rank, seq_subset=mine)
 
-    for _ in range(2):
-        step._eager()
-    torch.cuda.synchronize()
-    layers = 1 if args.no_graph else max(1, args.layers_per_graph)
-    if args.steps % layers:
-        layers = 1
-    if not args.no_graph:
-        step.capture(warmup=2, steps_per_graph=layers)
-    for _ in range(max(3, args.warmup)):
-        one_step()
-    torch.cuda.synchronize()
+    # ---- headline: weak scaling of the chosen configuration
+    w = weak_workload(head)
+    headline = bench.measure(w, f"{head}, {'one GPU' if world == 1 else f'weak scaling over {world} GPUs'}")
+    base = workloads.describe(head)
+    w = None
+    torch.cuda.empty_cache()
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+    # ---- one GPU: all five configurations
+    configs = None
+    if world == 1 and not args.headline_only:
+        configs = {}
+        for name in ALL_CONFIGS:
+            if name == head:
+                configs[name] = headline
+                continue
+            wl = workloads.materialize(workloads.describe(name), dev, seed=0)
+            configs[name] = bench.measure(wl, f"{name}, one GPU")
+            wl = None
+            torch.cuda.empty_cache()
 
-    def timed(fn, steps):
-        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        start.record()
-        for _ in range(steps):
-            fn()
-        stop.record()
-        barrier()
-        ms = start.elapsed_time(stop)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
+    # ---- several GPUs: the same global batch split over the ranks (strong scaling), and c4 sharded by KV head
+    strong, c4_shard = None, None
+    if world > 1 and not args.headline_only:
+        strong = {}
+        for name in ("c3", "c5"):
+            whole = workloads.describe(name)
+            mine = workloads.partition_by_sequence(whole, world)[rank]
+            wl = workloads.materialize(whole, dev, seed=0, seq_subset=mine)
+            r = bench.measure(wl, f"{name}: the one-GPU batch partitioned by sequence over {world} GPUs", parts=False, e2e=False)
+            r["scaling"] = "strong"
+            r["attended_kv_tokens_all_ranks"] = int(whole.attended_kv_tokens)
+            strong[name] = r
+            wl = None
+            torch.cuda.empty_cache()
+        whole = workloads.describe("c4")
+        if whole.hkv % world == 0:
+            per = whole.hkv // world
+            wl = workloads.materialize(whole, dev, seed=0, kv_head_slice=slice(rank * per, (rank + 1) * per))
+            gathered = torch.empty((world,) + tuple(wl.q.shape), dtype=wl.q.dtype, device=dev)
 
-    # ---- device-resident steps
-    with ClockSampler(local) as clocks:
-        ms_total = timed(one_step, args.steps // layers)
-        # the timed region lasts a few milliseconds, shorter than nvidia-smi's sampling period: the same step keeps
-        # replaying (untimed) for about half a second so that the clock record holds several samples under this load
-        t_end = time.perf_counter() + 0.5
-        while time.perf_counter() < t_end:
-            for _ in range(20):
-                one_step()
-            torch.cuda.synchronize()
-    ms_step = ms_total / args.steps
-    tokens_rank = torch.tensor([float(w.attended_kv_tokens)], device=dev)
-    if world > 1 and not head_shard:
-        dist.all_reduce(tokens_rank)
-    tokens_all = float(tokens_rank.item())
-    value = tokens_all / (ms_step * 1e-3)
+            def gather(out):
+                dist.all_gather_into_tensor(gathered.view(-1, *out.shape[1:]), out)
 
-    # ---- end to end: pinned host q/k/v in, host output back, every step
-    # q, k and v travel as one packed host buffer (one copy per step instead of three); the device side of the
-    # end-to-end step reads them through views of the packed device buffer
-    parts = (w.q, w.k, w.v)
-    sizes = [t.numel() for t in parts]
-    hqkv = torch.cat([t.reshape(-1).cpu() for t in parts]).pin_memory()
-    dqkv = torch.empty_like(hqkv, device=dev)
-    dqkv.copy_(hqkv)
-    dq, dk, dv = (v.view(t.shape) for v, t in zip(torch.split(dqkv, sizes), parts))
-    hout = torch.empty_like(w.q, device="cpu").pin_memory()
+            # parity first: the gathered heads against one rank attending all heads of the same pool
+            from easymlx_b200.runtime import AttentionStep
+            out = AttentionStep(wl.cache, wl.q, wl.k, wl.v, wl.qlens.tolist(), wl.slot_ids)._eager()
+            full = all_gather_heads(out)
+            parity = None
+            if rank == 0:
+                ref_w = workloads.materialize(whole, dev, seed=0)
+                ref = AttentionStep(ref_w.cache, ref_w.q, ref_w.k, ref_w.v, ref_w.qlens.tolist(), ref_w.slot_ids)._eager()
+                err = (full.float() - ref.float()).abs()
+                bound = 2e-3 + 1e-2 * ref.float().abs()
+                parity = {"max_abs_err": float(err.max().item()), "within_2e-3_plus_1e-2_rel": bool((err <= bound).all().item()),
+                          "shape": list(full.shape)}
+                if not parity["within_2e-3_plus_1e-2_rel"]:
+                    print(f"c4: the gathered shards differ from the unsharded output: {parity}", file=sys.stderr, flush=True)
+                ref_w = ref = None
+                torch.cuda.empty_cache()
+            r = bench.measure(wl, f"c4: KV heads sharded over {world} GPUs + NCCL all-gather of the outputs",
+                              after_step=gather, parts=False)
+            r["scaling"] = "strong"
+            r["attn_us"] = r["roofline"]["us_per_launch"]
+            dummy = wl.q.clone()
+            r["allgather_us"] = bench.graph_time(lambda: gather(dummy), 10, args.steps) * 1e3
+            r["allgather_bytes_per_rank"] = int(dummy.numel() * dummy.element_size())
+            r["parity_vs_unsharded"] = parity
+            c4_shard = r
+            wl = None
+            torch.cuda.empty_cache()
 
-    # the end-to-end loop copies inputs and output every single step: one step per graph
-    step1 = AttentionStep(w.cache, dq, dk, dv, w.qlens.tolist(), w.slot_ids).capture(warmup=2)
-
-    def e2e_step():
-        dqkv.copy_(hqkv, non_blocking=True)
-        out = step1.step()
-        if head_shard:
-            dist.all_gather_into_tensor(gathered.view(-1, *out.shape[1:]), out)
-        hout.copy_(gathered[rank] if head_shard else out, non_blocking=True)
-
-    for _ in range(3):
-        e2e_step()
-    ms_e2e = timed(e2e_step, args.steps) / args.steps
-    h2d = hqkv.numel() * hqkv.element_size()
-    d2h = hout.numel() * hout.element_size()
-
-    # ---- the dominant kernel alone (attention over the already written pool), for the roofline
-    meta_lens = torch.from_numpy(w.kv_lens.astype(np.int32)).to(dev)
-    qsl = emlx.build_query_start_loc(w.qlens.tolist(), device=dev)
-    extra = {}
-    if w.bits:
-        c = w.cache
-        extra = dict(k_scale=c.k_scales, v_scale=c.v_scales, k_bias=c.k_biases, v_bias=c.v_biases)
-    from easymlx_b200.operations.kernels.unified_attention import AttentionCall
-
-    call = AttentionCall(w.q, w.cache.key_cache, w.cache.value_cache, w.cache.block_tables, meta_lens, qsl,
-                         max_query_len=int(w.qlens.max()), query_len_set=sorted(set(int(x) for x in w.qlens if x > 0)), **extra)
-    call.plan()
-    call.launch()
-    torch.cuda.synchronize()
-    g = torch.cuda.CUDAGraph()
-    reps = 10  # launches per graph, so that the gap between graph launches does not count as kernel time
-    with torch.cuda.graph(g):
-        for _ in range(reps):
-            call.launch()
-    for _ in range(3):
-        g.replay()
-    n_replays = max(1, args.steps // reps)
-    ms_attn = timed(g.replay, n_replays) / (n_replays * reps)
-
-    peaks = _peaks()
-    attn_bytes = w.attention_bytes()
-    achieved = attn_bytes / (ms_attn * 1e-3) / 1e9
-    line = None
     if rank == 0:
-        traffic = None
-        tpath = os.path.join(ROOT, "profiles", f"traffic_{args.config}.json")
-        if os.path.exists(tpath) and not head_shard:  # captured on one GPU holding every KV head
-            traffic = json.load(open(tpath)).get("dram_bytes_per_launch")
+        roof = dict(headline["roofline"])
+        if world == 1:
+            tpath = os.path.join(ROOT, "profiles", f"traffic_{head}.json")
+            if os.path.exists(tpath):
+                roof["traffic"] = json.load(open(tpath)).get("dram_bytes_per_launch")
+                roof["traffic_source"] = f"ncu capture of this launch on one GPU (profiles/traffic_{head}.json), not measured in this run"
+            else:
+                roof["traffic"] = None
+        else:
+            roof["traffic"] = None
         line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
-            "ms_per_step": ms_step, "us_per_batch": ms_step * 1e3, "higher_is_better": True,
-            "scaling": "strong" if head_shard else "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-            "config": {
-                "workload": f"{args.config}: {base.description}",
-                "kv_format": {0: "fp16", 8: "affine8 group-64", 4: "affine4 group-64"}[w.bits],
-                "step": (f"batch metadata + work list + paged KV write + attention; {layers} consecutive steps per CUDA "
-                         "graph, as an engine step holds one per layer") if not args.no_graph
-                        else "batch metadata + work list + paged KV write + attention, eager launches",
-                "parallelism": ("kv-head shard + NCCL all-gather" if head_shard else f"sequence partition x{world}"),
-                "l2": "per-step KV working set exceeds L2 (no flush needed)" if attn_bytes > 3 * 126e6
-                      else "working set smaller than L2: numbers are L2-assisted",
-                "sequences_per_gpu": int(len(w.qlens)), "tokens_per_gpu": int(w.total_tokens),
-                "attended_kv_tokens_per_gpu": int(w.attended_kv_tokens),
-            },
-            "clocks": dict(clocks.summary, window="timed steps + 0.5 s of the same step replayed"),
-            "e2e": {"value": tokens_all / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": int(h2d),
-                    "d2h_bytes_per_step": int(d2h), "us_per_batch": ms_e2e * 1e3},
-            "gpu_launches": int(step.launches_per_step * args.steps),
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "frac_of_8TBs_nominal": achieved / 8000.0,
-                         "traffic": traffic, "kernel": "attention (all launches of emlx_attn_unified)",
-                         "algorithmic_bytes_per_launch": int(attn_bytes), "us_per_launch": ms_attn * 1e3,
-                         "peak_source": peaks["source"]},
+            "metric": METRIC, "value": headline["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(3, args.warmup), "ms_per_step": headline["us_per_batch"] / 1e3,
+            "us_per_batch": headline["us_per_batch"], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": headline_config(head, world, layers),
+            "clocks": headline["clocks"], "e2e": headline["e2e"],
+            "gpu_launches": int(headline["gpu_launches_per_step"] * args.steps),
+            "roofline": roof, "step_frac_of_hbm_peak": headline["step_frac_of_hbm_peak"],
         }
+        if configs is not None:
+            line["configs"] = configs
+        if strong is not None:
+            line["strong"] = strong
+        if c4_shard is not None:
+            line["c4_head_shard"] = c4_shard
         if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = _cpu_baseline_single_core(base, args.config, args.cpu_budget_tokens)
+            line["cpu_baseline"] = _cpu_baseline_single_core(base, head, args.cpu_budget_tokens)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -430,7 +608,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--config", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--config", default="c2", choices=list(ALL_CONFIGS), help="headline configuration")
+    ap.add_argument("--headline-only", action="store_true", help="skip the other configurations / scaling variants")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--layers-per-graph", type=int, default=10)
     ap.add_argument("--attn-only", type=int, default=0, help="run this many bare attention launches and exit (for ncu)")

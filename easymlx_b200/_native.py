@@ -70,6 +70,7 @@ SIGNATURES = {
     "emlx_attn_decode": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
     "emlx_attn_prefill": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
     "emlx_attn_generic": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
+    "emlx_selftest_device_once": (C.c_int, []),
     "emlx_selftest_wait_timeout": (C.c_int, [_P, C.c_uint32, _P]),
     "emlx_attn_decode_static": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
     "emlx_attn_row_class": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),

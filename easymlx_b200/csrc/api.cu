@@ -33,6 +33,24 @@ int emlx_abi_version(void) { return 1; }
 
 int64_t emlx_launch_count(void) { return emlx::g_launches.load(std::memory_order_relaxed); }
 
+int emlx_selftest_device_once(void) {
+    // the bookkeeping behind "once per device" set-up, driven with made-up ordinals: no CUDA call is made
+    emlx::DeviceOnce once;
+    int bad = 0;
+    for (int dev : {0, 1, 63, 64, 127}) {
+        bad += once.needs(dev) ? 0 : 1;       // nothing is configured at the start
+        once.done(dev);
+        bad += once.needs(dev) ? 1 : 0;       // ... and this device is afterwards
+    }
+    bad += once.needs(2) ? 0 : 1;             // a device nobody configured still needs it
+    bad += once.needs(65) ? 0 : 1;
+    once.done(-1);
+    once.done(emlx::kMaxDevices);             // out-of-range ordinals are never remembered
+    bad += once.needs(-1) ? 0 : 1;
+    bad += once.needs(emlx::kMaxDevices) ? 0 : 1;
+    return bad;
+}
+
 int emlx_read_status(const int32_t* status, void* stream) {
     if (!status) return emlx::fail(EMLX_ERR_INVALID, "status pointer is NULL");
     int32_t host = 0;

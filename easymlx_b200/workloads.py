@@ -156,22 +156,33 @@ def materialize(w: Workload, device="cuda", seed: int = 0, kv_head_slice: slice 
     cache.kv_lens.copy_(torch.from_numpy(prior.astype(np.int32)))
     gen = torch.Generator(device=dev)
     gen.manual_seed(seed + 1)
-    if w.bits == 0:
+    heads = kv_head_slice if kv_head_slice is not None else slice(None)
+    qheads = slice(None)
+    if kv_head_slice is not None:
+        lo, hi, _ = kv_head_slice.indices(w.hkv)
+        qheads = slice(lo * (w.hq // w.hkv), hi * (w.hq // w.hkv))
+    if w.bits == 0 and kv_head_slice is None:
         cache.key_cache.normal_(generator=gen)
         cache.value_cache.normal_(generator=gen)
     else:
+        # rows are drawn at the full head count and sliced, so that a KV-head shard holds exactly the heads it would
+        # hold in the unsharded pool (same seed on every rank)
         chunk_pages = 256
         for p0 in range(0, nb, chunk_pages):
             p1 = min(nb, p0 + chunk_pages)
             n = (p1 - p0) * PAGE
-            k = torch.randn((n, hkv, w.d), generator=gen, device=dev, dtype=torch.float32).half()
-            v = torch.randn((n, hkv, w.d), generator=gen, device=dev, dtype=torch.float32).half()
-            slots = torch.arange(p0 * PAGE, p1 * PAGE, dtype=torch.int64, device=dev)
-            fill_rows(cache, slots, k, v)
+            k = torch.randn((n, w.hkv, w.d), generator=gen, device=dev, dtype=torch.float32).half()[:, heads].contiguous()
+            v = torch.randn((n, w.hkv, w.d), generator=gen, device=dev, dtype=torch.float32).half()[:, heads].contiguous()
+            if w.bits == 0:
+                cache.key_cache[p0:p1] = k.view(p1 - p0, PAGE, hkv, w.d)
+                cache.value_cache[p0:p1] = v.view(p1 - p0, PAGE, hkv, w.d)
+            else:
+                slots = torch.arange(p0 * PAGE, p1 * PAGE, dtype=torch.int64, device=dev)
+                fill_rows(cache, slots, k, v)
     t = int(qlens.sum())
-    out.q = torch.randn((t, hq, w.d), generator=gen, device=dev, dtype=torch.float32).half()
-    out.k = torch.randn((t, hkv, w.d), generator=gen, device=dev, dtype=torch.float32).half()
-    out.v = torch.randn((t, hkv, w.d), generator=gen, device=dev, dtype=torch.float32).half()
+    out.q = torch.randn((t, w.hq, w.d), generator=gen, device=dev, dtype=torch.float32).half()[:, qheads].contiguous()
+    out.k = torch.randn((t, w.hkv, w.d), generator=gen, device=dev, dtype=torch.float32).half()[:, heads].contiguous()
+    out.v = torch.randn((t, w.hkv, w.d), generator=gen, device=dev, dtype=torch.float32).half()[:, heads].contiguous()
     out.cache = cache
     out.slot_ids = tuple(range(s))
     return out

@@ -232,6 +232,11 @@ int emlx_attn_decode_static(const emlx_attn_args* args, const emlx_pool* pool, v
  * into *status and returns normally (nothing faults, the context stays usable). */
 int emlx_selftest_wait_timeout(int32_t* status, uint32_t poll_limit, void* stream);
 
+/* Host-only self-test of the per-device set-up bookkeeping (kernel attributes such as the dynamic shared-memory limit
+ * and the SM count are kept once per device ordinal, so one process can drive several GPUs).  Makes no CUDA call;
+ * returns the number of failed checks (0 = pass). */
+int emlx_selftest_device_once(void);
+
 /* ---- batch and page-table maintenance on the device (no host synchronisation; bound by HBM or launch latency) ---- */
 
 /* out[s] = rows[query_start_loc[s+1] - 1] for s in [0, S): the last token's row of every sequence of a packed

@@ -46,6 +46,12 @@ def test_struct_layouts_match_the_header():
     assert _native.AttnArgs.plan_flags.offset == 76 and _native.AttnArgs.plan.offset == 80
 
 
+def test_per_device_setup_bookkeeping(built_lib):
+    from easymlx_b200 import _native
+
+    assert _native.lib().emlx_selftest_device_once() == 0
+
+
 def test_host_side_validation_needs_no_gpu(built_lib):
     from easymlx_b200 import _native
 
