@@ -199,6 +199,13 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
 #ifdef EMLX_TRACE_PARTS
             if (p.trace && tid == 0 && jj == 0) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(trace_d));
 #endif
+#ifdef EMLX_TRACE_TIMELINE
+            if (p.trace && tid == 0 && it == 0) {
+                long long now;
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+                p.trace[1024 + 4 * blockIdx.x + 1] = now;
+            }
+#endif
 #ifdef EMLX_EXPERIMENT_STREAM_ONLY  // measurement aid: consume the tiles without any arithmetic
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&empty[stage]);

@@ -200,6 +200,9 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
     uint64_t* dempty = full + 20;
     uint32_t part_idx = 0;
     (void)dfull; (void)dempty; (void)part_idx; (void)fixed;
+    // Units of up to 16 rows hold all rows of their sequence, so its KV tiles are read once per step: they are marked
+    // evict-first.  A sequence cut into several 32-row units reads its tiles once per unit and keeps the normal policy.
+    const uint64_t stream_once = C::PRIVATE ? ptx::l2_policy_evict_first() : ptx::l2_policy_evict_normal();
     Walk w;
     // Order of the slice's parts.  When the slice ends inside a unit, that unfinished part goes first: both parts
     // that need a merge with a neighbouring CTA are then done early and their merges run behind the other parts.
@@ -297,19 +300,19 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
                             const int tok0 = bad ? -kTile : pg * kTile;
     #pragma unroll
                             for (int h = 0; h < D / 64; ++h) {
-                                ptx::tma_load_3d(st + h * (kTile * 128), kmap, &full[stage], 64 * h, w.head, tok0);
-                                ptx::tma_load_3d(st + C::KBYTES + h * (kTile * 128), vmap, &full[stage], 64 * h, w.head, tok0);
+                                ptx::tma_load_3d(st + h * (kTile * 128), kmap, &full[stage], 64 * h, w.head, tok0, stream_once);
+                                ptx::tma_load_3d(st + C::KBYTES + h * (kTile * 128), vmap, &full[stage], 64 * h, w.head, tok0, stream_once);
                             }
                         } else {
                             const long long pgc = bad ? 0 : pg;  // keep every address inside the pool; such tiles are masked
-                            ptx::tma_load_3d(st, kmap, &full[stage], 0, w.head, (int)(pgc * kTile));
-                            ptx::tma_load_2d(st + C::KBYTES, vmap, &full[stage], 0, (int)((pgc * p.Hkv + w.head) * D));
+                            ptx::tma_load_3d(st, kmap, &full[stage], 0, w.head, (int)(pgc * kTile), stream_once);
+                            ptx::tma_load_2d(st + C::KBYTES, vmap, &full[stage], 0, (int)((pgc * p.Hkv + w.head) * D), stream_once);
                             const long long sb = (pgc * p.Hkv + w.head) * (long long)(kTile * C::GROUPS);
                             uint8_t* sbs = st + C::KBYTES + C::VBYTES;
-                            ptx::bulk_load(sbs + 0 * C::SB1, p.k_scale + sb, C::SB1, &full[stage]);
-                            ptx::bulk_load(sbs + 1 * C::SB1, p.k_bias + sb, C::SB1, &full[stage]);
-                            ptx::bulk_load(sbs + 2 * C::SB1, p.v_scale + sb, C::SB1, &full[stage]);
-                            ptx::bulk_load(sbs + 3 * C::SB1, p.v_bias + sb, C::SB1, &full[stage]);
+                            ptx::bulk_load(sbs + 0 * C::SB1, p.k_scale + sb, C::SB1, &full[stage], stream_once);
+                            ptx::bulk_load(sbs + 1 * C::SB1, p.k_bias + sb, C::SB1, &full[stage], stream_once);
+                            ptx::bulk_load(sbs + 2 * C::SB1, p.v_scale + sb, C::SB1, &full[stage], stream_once);
+                            ptx::bulk_load(sbs + 3 * C::SB1, p.v_bias + sb, C::SB1, &full[stage], stream_once);
                         }
                     }
                     __syncwarp();
@@ -338,8 +341,8 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
                                 uint8_t* dst = st + (size_t)sub * p.bs * 128;
     #pragma unroll
                                 for (int h = 0; h < D / 64; ++h) {
-                                    ptx::tma_load_3d(dst + h * (kTile * 128), kmap, &full[stage], 64 * h, w.head, tok0);
-                                    ptx::tma_load_3d(dst + C::KBYTES + h * (kTile * 128), vmap, &full[stage], 64 * h, w.head, tok0);
+                                    ptx::tma_load_3d(dst + h * (kTile * 128), kmap, &full[stage], 64 * h, w.head, tok0, stream_once);
+                                    ptx::tma_load_3d(dst + C::KBYTES + h * (kTile * 128), vmap, &full[stage], 64 * h, w.head, tok0, stream_once);
                                 }
                             }
                         }
@@ -349,14 +352,14 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* kmap, const CUt
                             const bool bad = pg < 0 || pg >= p.num_blocks;
                             if (bad && tile_tok < kv_len) flag_error(p.status, EMLX_DEV_BAD_PAGE);
                             const long long pgc = bad ? 0 : pg;  // keep every address inside the pool; such tiles are masked
-                            ptx::tma_load_3d(st, kmap, &full[stage], 0, w.head, (int)(pgc * kTile));
-                            ptx::tma_load_2d(st + C::KBYTES, vmap, &full[stage], 0, (int)((pgc * p.Hkv + w.head) * D));
+                            ptx::tma_load_3d(st, kmap, &full[stage], 0, w.head, (int)(pgc * kTile), stream_once);
+                            ptx::tma_load_2d(st + C::KBYTES, vmap, &full[stage], 0, (int)((pgc * p.Hkv + w.head) * D), stream_once);
                             const long long sb = (pgc * p.Hkv + w.head) * (long long)(kTile * C::GROUPS);
                             uint8_t* sbs = st + C::KBYTES + C::VBYTES;
-                            ptx::bulk_load(sbs + 0 * C::SB1, p.k_scale + sb, C::SB1, &full[stage]);
-                            ptx::bulk_load(sbs + 1 * C::SB1, p.k_bias + sb, C::SB1, &full[stage]);
-                            ptx::bulk_load(sbs + 2 * C::SB1, p.v_scale + sb, C::SB1, &full[stage]);
-                            ptx::bulk_load(sbs + 3 * C::SB1, p.v_bias + sb, C::SB1, &full[stage]);
+                            ptx::bulk_load(sbs + 0 * C::SB1, p.k_scale + sb, C::SB1, &full[stage], stream_once);
+                            ptx::bulk_load(sbs + 1 * C::SB1, p.k_bias + sb, C::SB1, &full[stage], stream_once);
+                            ptx::bulk_load(sbs + 2 * C::SB1, p.v_scale + sb, C::SB1, &full[stage], stream_once);
+                            ptx::bulk_load(sbs + 3 * C::SB1, p.v_bias + sb, C::SB1, &full[stage], stream_once);
                         }
                     }
                     __syncwarp();
@@ -997,6 +1000,13 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     // everything above is independent of earlier kernels; the plan, the pool and the queries are not
     grid_dep_wait();
     grid_dep_launch();
+#ifdef EMLX_TRACE_TIMELINE
+    if (p.trace && threadIdx.x == 0) {
+        long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        p.trace[1024 + 4 * blockIdx.x + 0] = now;
+    }
+#endif
     const int num_units = p.hdr[0];
     const long long total_flat = (long long)p.hdr[1] * p.Hkv;
     // every CTA takes the contiguous slice the plan cut for it; a CTA without tiles has nothing to do
@@ -1140,7 +1150,14 @@ static int launch_class(int cls, int D, int fmt, bool bf16, const MapPair& maps,
 // add per-part and per-tile records behind those (the buffer must then hold 1024 + 256 * 16 * 4 int64).
 #ifdef EMLX_TRACE
 static long long* g_trace = nullptr;
+#ifdef EMLX_TRACE_TIMELINE
+// every launch that asks gets the next of 16 regions of 8192 int64, so that the kernels of consecutive steps captured
+// into one CUDA graph leave separate records
+static int g_trace_launch = 0;
+long long* trace_buffer() { return g_trace ? g_trace + (size_t)(g_trace_launch++ % 16) * 8192 : nullptr; }
+#else
 long long* trace_buffer() { return g_trace; }
+#endif
 #else
 long long* trace_buffer() { return nullptr; }
 #endif
@@ -1213,6 +1230,9 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
 #ifdef EMLX_TRACE
 extern "C" __attribute__((visibility("default"))) void emlx_set_trace_buffer(int64_t* records) {
     emlx::g_trace = (long long*)records;
+#ifdef EMLX_TRACE_TIMELINE
+    emlx::g_trace_launch = 0;
+#endif
 }
 #endif
 extern "C" {

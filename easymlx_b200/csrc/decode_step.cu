@@ -14,8 +14,15 @@
 
 namespace emlx {
 
-constexpr int kDecodeMaxSeqs = 2048;   // lengths and the work list's scans stay in shared memory
-constexpr int kDecodeMaxUnits = 4096;
+long long* trace_buffer();  // measurement aid, NULL unless the build defines EMLX_TRACE
+
+#ifdef EMLX_TRACE_TIMELINE
+#define STEP_STAMP(slot) do { if (p.trace && threadIdx.x == 0) { long long now_; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now_)); p.trace[(blockIdx.x == 0 ? 0 : 16 + 8 * (blockIdx.x - 1)) + (slot)] = now_; } } while (0)
+#else
+#define STEP_STAMP(slot) do { } while (0)
+#endif
+
+constexpr int kDecodeMaxSeqs = 2048;   // lengths and the work list's prefix sums stay in shared memory
 
 struct DecodeStepParams {
     WriteParams w;  // keys / values / pool / rotation; slot_mapping and positions are not used
@@ -27,19 +34,23 @@ struct DecodeStepParams {
     int32_t* kv_out;
     int32_t* plan;
     int32_t* ticket;
+    long long* trace;
     PlanLayout L;
     int S, num_slots, MB, advance;
+    int warps_per_cta;  // active warps of a write CTA (the others only help with the gather)
     int G, window, class_lo, class_hi, wide, num_ctas;
 };
 
 template <typename TIn>
 __global__ void __launch_bounds__(kMetaThreads) decode_step_kernel(const DecodeStepParams p) {
     __shared__ int32_t scan_smem[kMetaThreads / 32 + 1];
-    __shared__ int32_t s_q[kDecodeMaxSeqs + 1], s_kv[kDecodeMaxSeqs], s_off[kDecodeMaxSeqs], s_cum[kDecodeMaxUnits];
+    __shared__ int32_t s_kv[kDecodeMaxSeqs], s_cum[kDecodeMaxSeqs + 1];
     __shared__ int s_last;
     // the new rows, the stored lengths and the page table may all come from the launches right before this one
+    STEP_STAMP(0);
     grid_dep_wait();
     grid_dep_launch();
+    STEP_STAMP(1);
     const int tid = threadIdx.x, lane = tid & 31;
     const emlx_pool& pool = p.w.pool;
     const int S = p.S, MB = p.MB, bs = pool.block_size, Hkv = pool.num_kv_heads;
@@ -58,26 +69,31 @@ __global__ void __launch_bounds__(kMetaThreads) decode_step_kernel(const DecodeS
                 ok = false;
             }
             const int after = ok ? base + 1 : 0;
-            s_q[i] = i;
             s_kv[i] = after;
             p.qsl[i] = i;
             p.kv_out[i] = after;
         }
-        if (tid == 0) {
-            s_q[S] = S;
-            p.qsl[S] = S;
-        }
+        if (tid == 0) p.qsl[S] = S;
         __syncthreads();
+        STEP_STAMP(2);
         if (p.plan != nullptr)
-            build_plan(s_q, s_kv, S, p.G, p.window, p.class_lo, p.class_hi, p.wide != 0, Hkv, p.num_ctas, p.plan, p.L,
-                       scan_smem, s_off, s_cum, kDecodeMaxUnits);
+            build_plan_decode(s_kv, S, p.G, p.window, p.class_lo, Hkv, p.num_ctas, p.plan, p.L, scan_smem, s_cum);
     } else {
         const int64_t kv_warps = p.w.has_pool ? (int64_t)S * Hkv : 0;
         const int64_t q_warps = p.w.q_out != nullptr ? (int64_t)S * p.w.Hq : 0;
-        const int64_t gw = (int64_t)(blockIdx.x - 1) * (kMetaThreads / 32) + (tid >> 5);
-        if (gw < kv_warps + q_warps) {
+        // A write CTA has as many threads as the work-list CTA but only its first warps_per_cta warps take a row: the
+        // byte-scattered stores of a row keep one SM's store path busy for a microsecond, so a small batch is spread
+        // over many SMs rather than packed into a few.
+        const int64_t gw = (int64_t)(blockIdx.x - 1) * p.warps_per_cta + (tid >> 5);
+        if ((tid >> 5) < p.warps_per_cta && gw < kv_warps + q_warps) {
             const bool is_kv = gw < kv_warps;
             const int t = is_kv ? (int)(gw / Hkv) : (int)((gw - kv_warps) / p.w.Hq);
+            const int h = (int)(gw - (int64_t)t * Hkv);
+            const bool rotate = p.w.rope_dims > 0;
+            // the rows do not depend on where they go: their loads are issued ahead of the slot -> length -> page
+            // chain (a rotated key needs its position first and is loaded afterwards)
+            RowRegs rows;
+            if (is_kv && !rotate) load_token_head<TIn>(p.w, t, h, lane, -1, rows);
             const int slot = p.slot_ids[t];
             if (slot >= 0 && slot < p.num_slots) {
                 const int base = p.kv_lens_all[slot];  // the new token's position in its sequence
@@ -85,11 +101,13 @@ __global__ void __launch_bounds__(kMetaThreads) decode_step_kernel(const DecodeS
                 if (page_idx < MB) {
                     if (is_kv) {
                         const int page = p.bt_all[(int64_t)slot * MB + page_idx];
+                        STEP_STAMP(4);
+                        if (rotate) load_token_head<TIn>(p.w, t, h, lane, base, rows);
                         if (page >= 0 && page < pool.num_blocks)
-                            write_token_head<TIn>(p.w, t, (int)(gw - (int64_t)t * Hkv), lane,
-                                                  (int64_t)page * bs + (base - page_idx * bs), base);
+                            store_token_head<TIn>(p.w, h, lane, (int64_t)page * bs + (base - page_idx * bs), rows);
                         else if (lane == 0)
                             flag_error(p.w.status, EMLX_DEV_BAD_PAGE);
+                        STEP_STAMP(5);
                     } else {
                         rotate_query_row<TIn>(p.w, gw - kv_warps, lane, base);
                     }
@@ -105,6 +123,7 @@ __global__ void __launch_bounds__(kMetaThreads) decode_step_kernel(const DecodeS
         }
     }
 
+    STEP_STAMP(blockIdx.x == 0 ? 3 : 2);
     // Every load of the stored lengths in this CTA is behind us.  The CTA with the last ticket knows that this holds
     // for the whole grid and advances them.
     __syncthreads();
@@ -113,7 +132,10 @@ __global__ void __launch_bounds__(kMetaThreads) decode_step_kernel(const DecodeS
         s_last = atomicAdd(p.ticket, 1) == (int)gridDim.x - 1 ? 1 : 0;
     }
     __syncthreads();
-    if (!s_last) return;
+    if (!s_last) {
+        STEP_STAMP(blockIdx.x == 0 ? 4 : 3);
+        return;
+    }
     __threadfence();
     if (p.advance) {
         for (int i = tid; i < S; i += kMetaThreads) {
@@ -124,6 +146,7 @@ __global__ void __launch_bounds__(kMetaThreads) decode_step_kernel(const DecodeS
         }
     }
     if (tid == 0) *p.ticket = 0;  // ready for the next launch
+    STEP_STAMP(blockIdx.x == 0 ? 4 : 3);
 }
 
 template <typename TIn>
@@ -166,6 +189,7 @@ extern "C" int emlx_kv_write_decode(const void* queries, void* queries_out, cons
         }
     }
     p.w.raw_ok = raw_copy_ok(p.w, in_dtype);
+    p.trace = trace_buffer();
     p.slot_ids = slot_ids; p.bt_all = block_tables_all; p.kv_lens_all = kv_lens_all;
     p.qsl = query_start_loc; p.bt_out = block_tables; p.kv_out = kv_lens; p.ticket = ticket;
     p.S = num_seqs; p.num_slots = num_slots; p.MB = max_blocks_per_seq; p.advance = advance_kv_lens;
@@ -182,7 +206,10 @@ extern "C" int emlx_kv_write_decode(const void* queries, void* queries_out, cons
         p.plan = (int32_t*)plan; p.window = sliding_window; p.num_ctas = min(num_sms(), kMaxGrid);
     }
     const int64_t warps = (int64_t)num_seqs * pool->num_kv_heads + (p.w.q_out ? (int64_t)num_seqs * num_q_heads : 0);
-    const unsigned grid = 1u + (unsigned)((warps + kMetaThreads / 32 - 1) / (kMetaThreads / 32));
+    // about two write CTAs per SM at most; at least 4 and at most 32 rows per CTA
+    const int64_t per_cta = (warps + 2 * num_sms() - 1) / (2 * num_sms());
+    p.warps_per_cta = (int)(per_cta < 4 ? 4 : (per_cta > kMetaThreads / 32 ? kMetaThreads / 32 : per_cta));
+    const unsigned grid = 1u + (unsigned)((warps + p.warps_per_cta - 1) / p.warps_per_cta);
     switch (in_dtype) {
         case EMLX_F16: return launch_decode_step<__half>(p, grid, (cudaStream_t)stream);
         case EMLX_BF16: return launch_decode_step<__nv_bfloat16>(p, grid, (cudaStream_t)stream);

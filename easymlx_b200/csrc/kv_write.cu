@@ -23,7 +23,13 @@ __global__ void __launch_bounds__(256) kv_write_kernel(WriteParams w) {
         return;
     }
     const int t = (int)(warp / Hkv), h = (int)(warp - (int64_t)t * Hkv);
-    write_token_head<TIn>(w, t, h, lane, w.slot_mapping[t], w.rope_dims > 0 ? w.positions[t] : -1);
+    // rows first, destination second: the two loads chains are independent (a rotated key needs its position)
+    RowRegs rows;
+    const bool rotate = w.rope_dims > 0;
+    if (!rotate) load_token_head<TIn>(w, t, h, lane, -1, rows);
+    const int64_t slot = w.slot_mapping[t];
+    if (rotate) load_token_head<TIn>(w, t, h, lane, w.positions[t], rows);
+    store_token_head<TIn>(w, h, lane, slot, rows);
 }
 
 int validate_pool(const emlx_pool* pool) {

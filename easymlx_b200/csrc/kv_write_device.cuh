@@ -72,26 +72,49 @@ __device__ __forceinline__ void quantize_group(float x0, float x1, int& c0, int&
 
 constexpr int kMaxGroups = 4;  // head_dim <= 256
 
-// Codes, scale and bias of one (token, head): computed before the destination is known, stored afterwards.
-struct QuantRow {
-    int c0[kMaxGroups], c1[kMaxGroups];
-    __half s[kMaxGroups], b[kMaxGroups];
+// The new K and V row of one (token, head) in registers.  The rows are loaded before the destination is known: the
+// row data and the index chain that yields the slot (slot id -> stored length -> page id) are independent, and
+// right after a kernel that has streamed hundreds of megabytes through L2 every one of these loads is a miss all
+// the way (translation included, about 3 us) - issued together they cost one such latency instead of four.
+//   affine pools : x[2g], x[2g+1] = elements 64g + 2 lane, +1 of group g
+//   float pools  : x[i] = element lane + 32 i;  raw[] = 16 bytes per lane when the row is copied bit for bit
+struct RowRegs {
+    float k[2 * kMaxGroups], v[2 * kMaxGroups];
+    uint4 kraw, vraw;
 };
 
-template <typename TIn, int BITS>
-__device__ __forceinline__ void quantize_row(const RowReader<TIn>& row, int groups, int lane, QuantRow& q) {
+template <typename TIn>
+__device__ __forceinline__ void load_token_head(const WriteParams& w, int t, int h, int lane, int pos, RowRegs& r) {
+    const emlx_pool& p = w.pool;
+    const int Hkv = p.num_kv_heads, D = p.head_dim;
+    const RowReader<TIn> krow{(const TIn*)w.keys + ((int64_t)t * Hkv + h) * D, w.rope_dims > 0 ? pos : -1, &w};
+    const RowReader<TIn> vrow{(const TIn*)w.values + ((int64_t)t * Hkv + h) * D, -1, &w};
+    if (p.kv_format != EMLX_KV_FLOAT) {
+        const int groups = D / kQuantGroup;
 #pragma unroll
-    for (int g = 0; g < kMaxGroups; ++g) {
-        if (g < groups) {
-            const int d0 = g * kQuantGroup + 2 * lane;
-            quantize_group<BITS>(row(d0), row(d0 + 1), q.c0[g], q.c1[g], q.s[g], q.b[g]);
+        for (int g = 0; g < kMaxGroups; ++g) {
+            if (g < groups) {
+                const int d0 = g * kQuantGroup + 2 * lane;
+                r.k[2 * g] = krow(d0); r.k[2 * g + 1] = krow(d0 + 1);
+                r.v[2 * g] = vrow(d0); r.v[2 * g + 1] = vrow(d0 + 1);
+            }
+        }
+    } else if (w.raw_ok) {
+        if (lane < D / 8) {
+            r.kraw = *(const uint4*)((const uint16_t*)krow.row + lane * 8);
+            r.vraw = *(const uint4*)((const uint16_t*)vrow.row + lane * 8);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2 * kMaxGroups; ++i) {
+            const int d = lane + 32 * i;
+            if (d < D) { r.k[i] = krow(d); r.v[i] = vrow(d); }
         }
     }
 }
 
 template <int BITS>
-__device__ __forceinline__ void store_affine_rows(const QuantRow& kq, const QuantRow& vq, const emlx_pool& p, int64_t page,
-                                                  int off, int h, int lane) {
+__device__ __forceinline__ void store_affine_rows(const RowRegs& r, const emlx_pool& p, int64_t page, int off, int h, int lane) {
     const int D = p.head_dim, bs = p.block_size, Hkv = p.num_kv_heads, groups = D / kQuantGroup;
     const int64_t sb_base = ((page * Hkv + h) * bs + off) * groups;
     // keys: token-major codes [NB, bs, Hkv, D*BITS/8]
@@ -102,11 +125,15 @@ __device__ __forceinline__ void store_affine_rows(const QuantRow& kq, const Quan
     for (int g = 0; g < kMaxGroups; ++g) {
         if (g >= groups) break;
         const int d0 = g * kQuantGroup + 2 * lane;
-        if (BITS == 8) *(uchar2*)(kdst + d0) = make_uchar2((unsigned char)kq.c0[g], (unsigned char)kq.c1[g]);
-        else kdst[d0 >> 1] = (uint8_t)(kq.c0[g] | (kq.c1[g] << 4));
+        int kc0, kc1, vc0, vc1;
+        __half ks, kb, vs, vb;
+        quantize_group<BITS>(r.k[2 * g], r.k[2 * g + 1], kc0, kc1, ks, kb);
+        quantize_group<BITS>(r.v[2 * g], r.v[2 * g + 1], vc0, vc1, vs, vb);
+        if (BITS == 8) *(uchar2*)(kdst + d0) = make_uchar2((unsigned char)kc0, (unsigned char)kc1);
+        else kdst[d0 >> 1] = (uint8_t)(kc0 | (kc1 << 4));
         if (BITS == 8) {
-            vdst[(int64_t)d0 * bs + off] = (uint8_t)vq.c0[g];
-            vdst[(int64_t)(d0 + 1) * bs + off] = (uint8_t)vq.c1[g];
+            vdst[(int64_t)d0 * bs + off] = (uint8_t)vc0;
+            vdst[(int64_t)(d0 + 1) * bs + off] = (uint8_t)vc1;
         } else {
             // two tokens share a byte; tokens of the same batch may land in the same 32-bit word, so the
             // nibble is replaced with word atomics (each nibble has exactly one writer per batch)
@@ -116,22 +143,21 @@ __device__ __forceinline__ void store_affine_rows(const QuantRow& kq, const Quan
                 uint8_t* byte = vdst + (int64_t)(d0 + e) * (bs / 2) + (off >> 1);
                 unsigned int* word = (unsigned int*)((uintptr_t)byte & ~(uintptr_t)3);
                 atomicAnd(word, ~(0xFu << shift));
-                atomicOr(word, (unsigned int)(e ? vq.c1[g] : vq.c0[g]) << shift);
+                atomicOr(word, (unsigned int)(e ? vc1 : vc0) << shift);
             }
         }
         if (lane == 0) {
-            ((__half*)p.k_scale)[sb_base + g] = kq.s[g];
-            ((__half*)p.k_bias)[sb_base + g] = kq.b[g];
-            ((__half*)p.v_scale)[sb_base + g] = vq.s[g];
-            ((__half*)p.v_bias)[sb_base + g] = vq.b[g];
+            ((__half*)p.k_scale)[sb_base + g] = ks;
+            ((__half*)p.k_bias)[sb_base + g] = kb;
+            ((__half*)p.v_scale)[sb_base + g] = vs;
+            ((__half*)p.v_bias)[sb_base + g] = vb;
         }
     }
 }
 
-// The K and V rows of token t, head h go to flat slot `slot` (page * block_size + offset; negative: skip).  `pos` is
-// the token's position in its sequence when the key is to be rotated, -1 otherwise.  Called by a whole warp.
+// Store the rows loaded by load_token_head at flat slot `slot` (page * block_size + offset; negative: skip).
 template <typename TIn>
-__device__ __forceinline__ void write_token_head(const WriteParams& w, int t, int h, int lane, int64_t slot, int pos) {
+__device__ __forceinline__ void store_token_head(const WriteParams& w, int h, int lane, int64_t slot, const RowRegs& r) {
     const emlx_pool& p = w.pool;
     const int Hkv = p.num_kv_heads, D = p.head_dim;
     if (slot < 0) return;
@@ -139,47 +165,34 @@ __device__ __forceinline__ void write_token_head(const WriteParams& w, int t, in
         if (lane == 0) flag_error(w.status, EMLX_DEV_BAD_PAGE);
         return;
     }
-    const RowReader<TIn> krow{(const TIn*)w.keys + ((int64_t)t * Hkv + h) * D, w.rope_dims > 0 ? pos : -1, &w};
-    const RowReader<TIn> vrow{(const TIn*)w.values + ((int64_t)t * Hkv + h) * D, -1, &w};
-    const int groups = D / kQuantGroup;
-    if (p.kv_format == EMLX_KV_AFFINE8 || p.kv_format == EMLX_KV_AFFINE4) {
-        QuantRow kq, vq;
+    if (p.kv_format != EMLX_KV_FLOAT) {
         const int64_t page = slot / p.block_size;
         const int in_page = (int)(slot - page * p.block_size);
-        if (p.kv_format == EMLX_KV_AFFINE8) {
-            quantize_row<TIn, 8>(krow, groups, lane, kq);
-            quantize_row<TIn, 8>(vrow, groups, lane, vq);
-            store_affine_rows<8>(kq, vq, p, page, in_page, h, lane);
-        } else {
-            quantize_row<TIn, 4>(krow, groups, lane, kq);
-            quantize_row<TIn, 4>(vrow, groups, lane, vq);
-            store_affine_rows<4>(kq, vq, p, page, in_page, h, lane);
-        }
+        if (p.kv_format == EMLX_KV_AFFINE8) store_affine_rows<8>(r, p, page, in_page, h, lane);
+        else store_affine_rows<4>(r, p, page, in_page, h, lane);
         return;
     }
     const int64_t off = (slot * Hkv + h) * D;
-    // same 16-bit type on both sides, no rotation, 16-byte aligned rows: a row moves as 16-byte pieces, one per lane
-    if (w.raw_ok) {
+    if (w.raw_ok) {  // same 16-bit type on both sides, no rotation, 16-byte aligned rows
         if (lane < D / 8) {
-            *(uint4*)((uint16_t*)p.key_cache + off + lane * 8) = *(const uint4*)((const uint16_t*)krow.row + lane * 8);
-            *(uint4*)((uint16_t*)p.value_cache + off + lane * 8) = *(const uint4*)((const uint16_t*)vrow.row + lane * 8);
+            *(uint4*)((uint16_t*)p.key_cache + off + lane * 8) = r.kraw;
+            *(uint4*)((uint16_t*)p.value_cache + off + lane * 8) = r.vraw;
         }
         return;
     }
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {  // head_dim <= 256, element d = lane + 32 i
+    for (int i = 0; i < 2 * kMaxGroups; ++i) {
         const int d = lane + 32 * i;
         if (d < D) {
-            const float kf = krow(d), vf = vrow(d);
             if (p.kv_dtype == EMLX_F16) {
-                ((__half*)p.key_cache)[off + d] = __float2half_rn(kf);
-                ((__half*)p.value_cache)[off + d] = __float2half_rn(vf);
+                ((__half*)p.key_cache)[off + d] = __float2half_rn(r.k[i]);
+                ((__half*)p.value_cache)[off + d] = __float2half_rn(r.v[i]);
             } else if (p.kv_dtype == EMLX_BF16) {
-                ((__nv_bfloat16*)p.key_cache)[off + d] = __float2bfloat16_rn(kf);
-                ((__nv_bfloat16*)p.value_cache)[off + d] = __float2bfloat16_rn(vf);
+                ((__nv_bfloat16*)p.key_cache)[off + d] = __float2bfloat16_rn(r.k[i]);
+                ((__nv_bfloat16*)p.value_cache)[off + d] = __float2bfloat16_rn(r.v[i]);
             } else {
-                ((float*)p.key_cache)[off + d] = kf;
-                ((float*)p.value_cache)[off + d] = vf;
+                ((float*)p.key_cache)[off + d] = r.k[i];
+                ((float*)p.value_cache)[off + d] = r.v[i];
             }
         }
     }

@@ -57,6 +57,46 @@ __device__ __forceinline__ void unit_tiles(int row0, int row1, int G, int q_len,
     }
 }
 
+// Slice boundaries of class c: CTA i of num_ctas takes the flat tiles [start[i], start[i+1]), cut at equal shares of
+// cost, kTileCost per tile + part_cost(c) per (unit, head) part (measured on the 8-row decode kernel: a part
+// boundary costs about as much as 2.3 tiles).  `cum` is the exclusive prefix sum of tiles per unit (num_units + 1).
+__device__ __forceinline__ void cut_slices(int c, const int32_t* cum, int num_units, int tile_base, int Hkv,
+                                           int num_ctas, int32_t* plan, const PlanLayout& L) {
+    const int tid = threadIdx.x;
+    {
+        for (int i = tid; i <= num_ctas; i += kMetaThreads) {
+            long long start = (long long)tile_base * Hkv;
+            int first_unit = num_units;
+            const long long kPartCost = part_cost(c);
+            if (i < num_ctas && num_units > 0) {
+                const long long total = (long long)Hkv * (kTileCost * tile_base + kPartCost * num_units);
+                // 64-bit division is a long software routine; the totals of any realistic batch fit 32 bits
+                const long long target = total * num_ctas < (1LL << 31) ? (long long)((unsigned)(total * i) / (unsigned)num_ctas)
+                                                                        : total * i / num_ctas;
+                int lo = 0, hi = num_units;  // largest u with cost_before(u) <= target
+                while (hi - lo > 1) {
+                    const int mid = (lo + hi) >> 1;
+                    if ((long long)Hkv * (kTileCost * cum[mid] + kPartCost * mid) <= target) lo = mid; else hi = mid;
+                }
+                const int u = lo, nt = cum[u + 1] - cum[u];
+                const long long rem = target - (long long)Hkv * (kTileCost * cum[u] + kPartCost * u);
+                const long long per_head = kTileCost * nt + kPartCost;
+                const int head = (int)min((long long)Hkv - 1,
+                                          rem < (1LL << 31) ? (long long)((unsigned)rem / (unsigned)per_head) : rem / per_head);
+                const long long r2 = rem - head * per_head;
+                const int j = r2 <= kPartCost ? 0 : (int)min((long long)nt, (r2 - kPartCost + kTileCost / 2) / kTileCost);
+                start = (long long)cum[u] * Hkv + (long long)head * nt + j;
+                first_unit = u;
+            } else if (num_units == 0) {
+                start = 0;
+                first_unit = 0;
+            }
+            plan[L.cta_unit[c] + i] = first_unit;
+            plan[L.cta_start[c] + i] = (int)start;
+        }
+    }
+}
+
 __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv_lens, int S, int G, int window,
                                            int class_lo, int class_hi, bool wide, int Hkv, int num_ctas,
                                            int32_t* plan, const PlanLayout& L, int32_t* scan_smem,
@@ -155,41 +195,61 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
 #ifdef EMLX_TRACE_META
         if (threadIdx.x == 0 && c == class_lo) g_meta_trace[10] = clock64();
 #endif
-        const int32_t* cum = num_units < cum_cap ? cum_smem : unit_cum;
-        // slice boundaries: equal shares of cost, kTileCost per tile + kPartCost per (unit, head) part (measured on
-        // the 8-row decode kernel: a part boundary costs about as much as 2.3 tiles)
-        for (int i = tid; i <= num_ctas; i += kMetaThreads) {
-            long long start = (long long)tile_base * Hkv;
-            int first_unit = num_units;
-            const long long kPartCost = part_cost(c);
-            if (i < num_ctas && num_units > 0) {
-                const long long total = (long long)Hkv * (kTileCost * tile_base + kPartCost * num_units);
-                // 64-bit division is a long software routine; the totals of any realistic batch fit 32 bits
-                const long long target = total * num_ctas < (1LL << 31) ? (long long)((unsigned)(total * i) / (unsigned)num_ctas)
-                                                                        : total * i / num_ctas;
-                int lo = 0, hi = num_units;  // largest u with cost_before(u) <= target
-                while (hi - lo > 1) {
-                    const int mid = (lo + hi) >> 1;
-                    if ((long long)Hkv * (kTileCost * cum[mid] + kPartCost * mid) <= target) lo = mid; else hi = mid;
-                }
-                const int u = lo, nt = cum[u + 1] - cum[u];
-                const long long rem = target - (long long)Hkv * (kTileCost * cum[u] + kPartCost * u);
-                const long long per_head = kTileCost * nt + kPartCost;
-                const int head = (int)min((long long)Hkv - 1,
-                                          rem < (1LL << 31) ? (long long)((unsigned)rem / (unsigned)per_head) : rem / per_head);
-                const long long r2 = rem - head * per_head;
-                const int j = r2 <= kPartCost ? 0 : (int)min((long long)nt, (r2 - kPartCost + kTileCost / 2) / kTileCost);
-                start = (long long)cum[u] * Hkv + (long long)head * nt + j;
-                first_unit = u;
-            } else if (num_units == 0) {
-                start = 0;
-                first_unit = 0;
-            }
-            plan[L.cta_unit[c] + i] = first_unit;
-            plan[L.cta_start[c] + i] = (int)start;
-        }
+        cut_slices(c, num_units < cum_cap ? cum_smem : unit_cum, num_units, tile_base, Hkv, num_ctas, plan, L);
         __syncthreads();
     }
+}
+
+// Work list of a batch in which every sequence has exactly one query token (G rows): unit i is sequence i, so the
+// unit counting and the owner search of build_plan fall away.  Same output as build_plan(..., max one class).
+__device__ __forceinline__ void build_plan_decode(const int32_t* kv_lens /* shared memory */, int S, int G, int window,
+                                                  int cls, int Hkv, int num_ctas, int32_t* plan, const PlanLayout& L,
+                                                  int32_t* scan_smem, int32_t* cum_smem /* [S + 1] */) {
+    const int tid = threadIdx.x;
+    for (int c = 0; c < kNumClasses; ++c) {
+        if (c == cls) continue;
+        if (tid == 0) { plan[4 * c + 0] = 0; plan[4 * c + 1] = 0; }
+        for (int i = tid; i <= num_ctas; i += kMetaThreads) { plan[L.cta_start[c] + i] = 0; plan[L.cta_unit[c] + i] = 0; }
+    }
+    int32_t* unit_seq = plan + L.unit_seq[cls];
+    int32_t* unit_row0 = plan + L.unit_row0[cls];
+    int32_t* unit_tile_lo = plan + L.unit_tile_lo[cls];
+    int32_t* unit_cum = plan + L.unit_cum[cls];
+    int tile_base = 0;
+#pragma unroll 1
+    for (int i0 = 0; i0 < S; i0 += kMetaThreads) {
+        const int idx = i0 + tid;
+        int nt = 0;
+        if (idx < S) {
+            int tile_lo;
+            unit_tiles(0, G, G, 1, kv_lens[idx], window, tile_lo, nt);
+            unit_seq[idx] = idx;
+            unit_row0[idx] = 0;
+            unit_tile_lo[idx] = tile_lo;
+        }
+        int t_total;
+        const int t_off = tile_base + block_scan_value(nt, scan_smem, t_total);
+        if (idx < S) {
+            unit_cum[idx] = t_off;
+            cum_smem[idx] = t_off;
+        }
+        tile_base += t_total;
+    }
+    if (tid == 0) {
+        unit_cum[S] = tile_base;
+        cum_smem[S] = tile_base;
+        plan[4 * cls + 0] = S;
+        plan[4 * cls + 1] = tile_base;
+        if (cls == 3) plan[L.unit_order] = 0;
+    }
+    __syncthreads();
+    if (cls == 3) {
+        // 128-row units are dealt out by decreasing length; a decode batch reaches this class only with a GQA group
+        // above 16, and its units are all alike enough for batch order
+        for (int u = tid; u < S; u += kMetaThreads) plan[L.unit_order + u] = u;
+    }
+    cut_slices(cls, cum_smem, S, tile_base, Hkv, num_ctas, plan, L);
+    __syncthreads();
 }
 
 // classes that can hold a sequence of 1..max_query_len tokens with G rows per token (0 = unknown: all of them)
