@@ -7,11 +7,13 @@ namespace emlx {
 __global__ void __launch_bounds__(kMetaThreads) attn_plan_kernel(const int32_t* __restrict__ qsl,
                                                                  const int32_t* __restrict__ kv_lens, int S, int G,
                                                                  int window, int class_lo, int class_hi, bool wide,
-                                                                 int Hkv, int num_ctas, int32_t* plan, PlanLayout L) {
+                                                                 int Hkv, int num_ctas, int32_t* plan, PlanLayout L,
+                                                                 int short_ctas) {
     __shared__ int32_t scan_smem[kMetaThreads / 32 + 1];
     grid_dep_wait();
     grid_dep_launch();
-    build_plan(qsl, kv_lens, S, G, window, class_lo, class_hi, wide, Hkv, num_ctas, plan, L, scan_smem);
+    build_plan(qsl, kv_lens, S, G, window, class_lo, class_hi, wide, Hkv, num_ctas, plan, L, scan_smem, nullptr, nullptr, 0,
+               short_ctas);
 }
 
 }  // namespace emlx
@@ -47,7 +49,7 @@ int emlx_attn_plan(const int32_t* query_start_loc, const int32_t* kv_lens, int32
     attn_plan_kernel<<<1, kMetaThreads, 0, (cudaStream_t)stream>>>(query_start_loc, kv_lens, num_seqs,
                                                                     num_q_heads / num_kv_heads, sliding_window, class_lo,
                                                                     class_hi, wide, num_kv_heads, min(num_sms(), kMaxGrid),
-                                                                    (int32_t*)plan, L);
+                                                                    (int32_t*)plan, L, (plan_flags >> kPlanShortCtasShift) & 0xff);
     EMLX_LAUNCHED();
     return EMLX_OK;
 }

@@ -40,11 +40,13 @@ struct PrefillParams {
     const int32_t* unit_tile_lo;
     const int32_t* unit_cum;
     const int32_t* unit_order;  // units by decreasing number of tiles
+    int32_t* queue;             // [0] next item to hand out, [1] CTAs that have finished; both zero between launches
     int32_t* status;
     long long* trace;  // measurement aid (only with EMLX_TRACE_PREFILL): per-tile cycle stamps of CTA 0
     long long num_blocks;
     int Hq, Hkv, G, MB, window;
     int bs, ppt_log;  // page size in tokens and log2(pages per 128-token tile)
+    int wait_late;    // the launch before this one is the short-row kernel of the same call: run beside it
     float scale_log2e;
 };
 
@@ -168,6 +170,9 @@ struct PfBarriers {
     // p_ready[t & 1]: P of tile t written over its S.
     uint64_t q_full, q_tmem, item_done, qk_done[4], p_ready[2], pv_done[4];
     uint64_t k_full[4], v_full[4];
+    // item_full[k & 3]: the index of the CTA's k-th item is in item_ring[k & 3] (-1: no more items)
+    uint64_t item_full[4];
+    int item_ring[4];
     uint32_t tmem_base;
     int abort_word;
 };
@@ -186,20 +191,20 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
     volatile int* abort_word = &bars->abort_word;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
 
-    grid_dep_wait();  // the plan, the pool and the queries come from earlier kernels
+    // The plan, the pool and the queries come from earlier kernels.  When the launch right before this one is the
+    // short-row kernel of the same attention call, that kernel has already waited for all of them, and this grid
+    // runs beside it (the two are bound by different resources: HBM there, tensor cores here); it then waits for that
+    // kernel at its END, so that whatever follows in the stream still sees both complete.
+    if (!p.wait_late) grid_dep_wait();
     grid_dep_launch();
     const int num_units = p.hdr[0];
-    const long long items = (long long)num_units * p.Hkv;
-    if ((long long)blockIdx.x >= items) return;  // uniform, before any barrier or TMEM allocation
-    // Items (unit, head) are dealt out in the order of decreasing length, back and forth over the CTAs (round k goes
-    // 0..P-1 when k is even and P-1..0 when it is odd), which keeps the CTAs' totals within about one item.
-    auto item_of = [&](uint32_t k, int& u, int& head) -> bool {
-        const long long P = gridDim.x;
-        const long long idx = (long long)k * P + ((k & 1) ? P - 1 - blockIdx.x : blockIdx.x);
-        if (idx >= items) return false;
+    const int items = num_units * p.Hkv;
+    // Items (unit, head), listed by decreasing length, are handed out through a counter in device memory: a CTA that
+    // starts late (its SM was still busy with a short-row CTA) simply takes fewer of them.  The producer warp draws
+    // the index and passes it to the other warps through a small ring in shared memory.
+    auto decode_item = [&](int idx, int& u, int& head) {
         u = p.unit_order[idx / p.Hkv];
-        head = (int)(idx % p.Hkv);
-        return true;
+        head = idx % p.Hkv;
     };
 
     if (tid == 0) {
@@ -213,6 +218,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             ptx::mbar_init(&bars->pv_done[s], 1);
             ptx::mbar_init(&bars->k_full[s], 1);
             ptx::mbar_init(&bars->v_full[s], 1);
+            ptx::mbar_init(&bars->item_full[s], 1);
         }
         bars->abort_word = 0;
         ptx::fence_barrier_init();
@@ -231,7 +237,17 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
         // ------------------------------------------------------------------ TMA producer
         uint32_t kt = 0, k = 0;
         int u, head;
-        for (; item_of(k, u, head) && !*abort_word; ++k) {
+        int next = lane == 0 ? atomicAdd(p.queue, 1) : 0;
+        for (;; ++k) {
+            int idx = __shfl_sync(0xffffffffu, next, 0);
+            if (idx >= items || *abort_word) idx = -1;
+            if (lane == 0) {
+                bars->item_ring[k & 3] = idx;
+                ptx::mbar_arrive(&bars->item_full[k & 3]);
+            }
+            if (idx < 0) break;
+            if (lane == 0) next = atomicAdd(p.queue, 1);  // the following item, drawn while this one is loaded
+            decode_item(idx, u, head);
             const int seq = p.unit_seq[u], row0 = p.unit_row0[u], tile_lo = p.unit_tile_lo[u];
             const int ntiles = p.unit_cum[u + 1] - p.unit_cum[u];
             const int qs = p.qsl[seq], kv_len = p.kv_lens[seq];
@@ -358,7 +374,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
         const uint64_t v_desc0 = smem_desc(ptx::smem_u32(v_smem), kTile * 128, 1024);
         uint32_t kt = 0, k = 0;
         int u, head;
-        for (; item_of(k, u, head) && !*abort_word; ++k) {
+        for (;; ++k) {
+            if (!ptx::mbar_wait(&bars->item_full[k & 3], (k >> 2) & 1, abort_word)) break;
+            const int idx = bars->item_ring[k & 3];
+            if (idx < 0) break;
+            decode_item(idx, u, head);
             const int ntiles = p.unit_cum[u + 1] - p.unit_cum[u];
             ptx::mbar_wait(&bars->q_tmem, k & 1, abort_word);  // the item's Q rows are in TMEM
             tc_fence_after();
@@ -415,7 +435,11 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
         const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
         uint32_t kt = 0;
         int u, head;
-        for (uint32_t k = 0; item_of(k, u, head); ++k) {
+        for (uint32_t k = 0;; ++k) {
+            if (!ptx::mbar_wait(&bars->item_full[k & 3], (k >> 2) & 1, abort_word)) break;
+            const int idx = bars->item_ring[k & 3];
+            if (idx < 0) break;
+            decode_item(idx, u, head);
             const int seq = p.unit_seq[u], row0 = p.unit_row0[u], tile_lo = p.unit_tile_lo[u];
             const int ntiles = p.unit_cum[u + 1] - p.unit_cum[u];
             const int qs = p.qsl[seq], q_len = p.qsl[seq + 1] - qs, kv_len = p.kv_lens[seq];
@@ -574,6 +598,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
     __syncthreads();
     if (warp == 5) tmem_dealloc(tmem_base, C::TMEM_COLS);
     if (*abort_word && tid == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
+    if (tid == 0) {
+        // every draw of this CTA is behind us; the last CTA to get here puts the item counter back to zero
+        __threadfence();
+        if (atomicInc((unsigned int*)&p.queue[1], gridDim.x - 1) == gridDim.x - 1) p.queue[0] = 0;
+    }
+    if (p.wait_late) grid_dep_wait();
 }
 
 // ------------------------------------------------------------------------------------------ host
@@ -618,14 +648,14 @@ static int launch_pf(const CUtensorMap& qmap, const MapPair& maps, const Prefill
     auto kernel = attn_prefill_kernel<D, BF16>;
     static DeviceOnce configured;
     EMLX_CUDA_OK(allow_dynamic_smem(kernel, C::SMEM, configured));
-    EMLX_CUDA_OK(launch_pdl(kernel, num_sms(), kPfThreads, C::SMEM, stream, qmap, maps.k, maps.v, p));
+    EMLX_CUDA_OK(launch_pdl(kernel, min(num_sms(), kMaxGrid), kPfThreads, C::SMEM, stream, qmap, maps.k, maps.v, p));
     EMLX_LAUNCHED();
     return EMLX_OK;
 }
 
 int launch_prefill(const emlx_attn_args* a, const emlx_pool* pool, const int32_t* plan_class_hdr, const int32_t* unit_seq,
                    const int32_t* unit_row0, const int32_t* unit_tile_lo, const int32_t* unit_cum, const int32_t* unit_order,
-                   const MapPair& maps, cudaStream_t stream) {
+                   int32_t* queue, bool wait_late, const MapPair& maps, cudaStream_t stream) {
     const int D = pool->head_dim, Hq = a->num_q_heads, Hkv = pool->num_kv_heads, G = Hq / Hkv;
     if (!prefill_supported(pool->kv_format, Hq, Hkv, D))
         return fail(EMLX_ERR_UNSUPPORTED, "the tcgen05 prefill kernel needs an fp16/bf16 pool, head_dim 64/128 and 128 %% (Hq/Hkv) == 0");
@@ -635,6 +665,7 @@ int launch_prefill(const emlx_attn_args* a, const emlx_pool* pool, const int32_t
     p.out = a->out; p.bt = a->block_tables; p.kv_lens = a->kv_lens; p.qsl = a->query_start_loc;
     p.hdr = plan_class_hdr; p.unit_seq = unit_seq; p.unit_row0 = unit_row0; p.unit_tile_lo = unit_tile_lo; p.unit_cum = unit_cum; p.unit_order = unit_order;
     p.status = a->status; p.num_blocks = pool->num_blocks; p.trace = trace_buffer();
+    p.queue = queue; p.wait_late = wait_late ? 1 : 0;
     p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.MB = a->max_blocks_per_seq; p.window = a->sliding_window;
     p.bs = pool->block_size; p.ppt_log = pages_per_tile_log2(pool->block_size);
     p.scale_log2e = a->softmax_scale * 1.4426950408889634f;

@@ -1194,15 +1194,19 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
     lo = max(lo, class_lo);
     hi = min(hi, class_hi);
     const int32_t* plan = (const int32_t*)a->plan;
+    bool short_rows_launched = false;
     for (int c = lo; c <= hi; ++c) {
         if (a->row_class_mask != 0 && !((a->row_class_mask >> c) & 1)) continue;  // the caller knows this class is empty
         if (c == 3) {
+            // the 128-row kernel comes last; behind a short-row kernel of this call it runs beside that kernel
             if (int rc = launch_prefill(a, pool, plan + 4 * c, plan + L.unit_seq[c], plan + L.unit_row0[c],
-                                        plan + L.unit_tile_lo[c], plan + L.unit_cum[c], plan + L.unit_order, maps,
+                                        plan + L.unit_tile_lo[c], plan + L.unit_cum[c], plan + L.unit_order,
+                                        (int32_t*)((uint8_t*)a->workspace + W.counter_off[3]), short_rows_launched, maps,
                                         (cudaStream_t)stream))
                 return rc;
             continue;
         }
+        short_rows_launched = true;
         TiledParams p;
         p.q = a->queries; p.out = a->out; p.bt = a->block_tables; p.kv_lens = a->kv_lens; p.qsl = a->query_start_loc;
         p.hdr = plan + 4 * c;

@@ -18,6 +18,7 @@ namespace emlx {
 constexpr int kTile = 128;        // tokens per KV tile = page size the tiled kernels require
 constexpr int kNumClasses = 4;
 constexpr int kPlanWideUnits = 1;  // plan flag: cut sequences with more than 32 rows into 128-row units (class 3)
+constexpr int kPlanShortCtasShift = 8;  // plan flag bits 8-15: CTAs of the short-row kernel that runs beside the 128-row one (0 = automatic)
 constexpr int kPlanHeaderWords = 16;
 // Page sizes the tiled kernels read: a 128-token tile is one page, or 2 / 4 / 8 pages of a 16/32-bit pool (affine pools
 // keep their values transposed inside a 128-token page, so they need that size).

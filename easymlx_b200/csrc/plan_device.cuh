@@ -60,19 +60,20 @@ __device__ __forceinline__ void unit_tiles(int row0, int row1, int G, int q_len,
 // Slice boundaries of class c: CTA i of num_ctas takes the flat tiles [start[i], start[i+1]), cut at equal shares of
 // cost, kTileCost per tile + part_cost(c) per (unit, head) part (measured on the 8-row decode kernel: a part
 // boundary costs about as much as 2.3 tiles).  `cum` is the exclusive prefix sum of tiles per unit (num_units + 1).
+// Only the first `used` CTAs receive work (the others get empty slices and leave at once).
 __device__ __forceinline__ void cut_slices(int c, const int32_t* cum, int num_units, int tile_base, int Hkv,
-                                           int num_ctas, int32_t* plan, const PlanLayout& L) {
+                                           int num_ctas, int32_t* plan, const PlanLayout& L, int used) {
     const int tid = threadIdx.x;
     {
         for (int i = tid; i <= num_ctas; i += kMetaThreads) {
             long long start = (long long)tile_base * Hkv;
             int first_unit = num_units;
             const long long kPartCost = part_cost(c);
-            if (i < num_ctas && num_units > 0) {
+            if (i < used && num_units > 0) {
                 const long long total = (long long)Hkv * (kTileCost * tile_base + kPartCost * num_units);
                 // 64-bit division is a long software routine; the totals of any realistic batch fit 32 bits
-                const long long target = total * num_ctas < (1LL << 31) ? (long long)((unsigned)(total * i) / (unsigned)num_ctas)
-                                                                        : total * i / num_ctas;
+                const long long target = total * used < (1LL << 31) ? (long long)((unsigned)(total * i) / (unsigned)used)
+                                                                    : total * i / used;
                 int lo = 0, hi = num_units;  // largest u with cost_before(u) <= target
                 while (hi - lo > 1) {
                     const int mid = (lo + hi) >> 1;
@@ -97,13 +98,42 @@ __device__ __forceinline__ void cut_slices(int c, const int32_t* cum, int num_un
     }
 }
 
+// How many CTAs the short-row (HBM-bound) kernel gets when the 128-row (tensor-bound) kernel runs beside it.
+// Per (head, tile) both cost about the same SM time when each has the GPU to itself (measured on the Qwen3-32B-shaped
+// mixed batch: 1.4 SM-us either way), but a short-row CTA that does not have to share HBM with 147 others streams
+// kShortRowSpeedup times faster (measured 1.9: 85-93 GB/s per SM on 24-48 SMs against 47 GB/s on all 148; with three
+// 64 KB stages in flight an SM cannot pull more).  The 128-row kernel hands its items out dynamically, so the split
+// only has to keep the short-row kernel from finishing last: it gets the share that makes both end together, plus a
+// margin, and never more CTAs than saturate HBM unless the short rows dominate the batch.
+constexpr int kShortRowSpeedupX10 = 19;
+__host__ __device__ inline int short_row_share(long long short_tiles, long long wide_tiles, int num_ctas) {
+    const long long x = short_tiles * 10 / kShortRowSpeedupX10;          // short-row work at the faster rate
+    long long balanced = (num_ctas * x + x + wide_tiles - 1) / (x + wide_tiles);
+    balanced += (balanced + 5) / 6;                                       // margin
+    const long long saturating = ((long long)num_ctas * 10 + kShortRowSpeedupX10 - 1) / kShortRowSpeedupX10;
+    long long share = balanced;
+    if (balanced > saturating) {
+        // the short rows dominate: the 128-row kernel gets the CTAs it needs to finish within the HBM-bound time of the
+        // short rows, the rest stream
+        long long wide_ctas = (wide_tiles * num_ctas + short_tiles - 1) / (short_tiles > 0 ? short_tiles : 1);
+        wide_ctas += (wide_ctas + 5) / 6;
+        share = num_ctas - wide_ctas;
+        if (share < saturating) share = saturating;
+    }
+    return (int)(share < 1 ? 1 : (share > num_ctas ? num_ctas : share));
+}
+
 __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv_lens, int S, int G, int window,
                                            int class_lo, int class_hi, bool wide, int Hkv, int num_ctas,
                                            int32_t* plan, const PlanLayout& L, int32_t* scan_smem,
                                            int32_t* seq_off_buf = nullptr, int32_t* cum_smem = nullptr,
-                                           int cum_cap = 0) {
+                                           int cum_cap = 0, int short_ctas = 0) {
     const int tid = threadIdx.x;
-    for (int c = 0; c < kNumClasses; ++c) {
+    // The 128-row class comes first: the short-row class that is launched right before the 128-row kernel runs
+    // beside it, and how many CTAs it then gets depends on how much 128-row work there is.
+    long long wide_tiles = 0;        // (unit, head, tile) triples of class 3
+    bool short_class_seen = false;   // a short-row class that is launched later than the current one has work
+    for (int c = kNumClasses - 1; c >= 0; --c) {
         if (c < class_lo || c > class_hi) {
             if (tid == 0) { plan[4 * c + 0] = 0; plan[4 * c + 1] = 0; }
             for (int i = tid; i <= num_ctas; i += kMetaThreads) { plan[L.cta_start[c] + i] = 0; plan[L.cta_unit[c] + i] = 0; }
@@ -195,7 +225,15 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
 #ifdef EMLX_TRACE_META
         if (threadIdx.x == 0 && c == class_lo) g_meta_trace[10] = clock64();
 #endif
-        cut_slices(c, num_units < cum_cap ? cum_smem : unit_cum, num_units, tile_base, Hkv, num_ctas, plan, L);
+        int used = num_ctas;
+        if (c == 3) {
+            wide_tiles = (long long)tile_base * Hkv;
+        } else if (tile_base > 0) {
+            if (wide_tiles > 0 && !short_class_seen)
+                used = short_ctas > 0 ? min(short_ctas, num_ctas) : short_row_share((long long)tile_base * Hkv, wide_tiles, num_ctas);
+            short_class_seen = true;
+        }
+        cut_slices(c, num_units < cum_cap ? cum_smem : unit_cum, num_units, tile_base, Hkv, num_ctas, plan, L, used);
         __syncthreads();
     }
 }
@@ -248,7 +286,7 @@ __device__ __forceinline__ void build_plan_decode(const int32_t* kv_lens /* shar
         // above 16, and its units are all alike enough for batch order
         for (int u = tid; u < S; u += kMetaThreads) plan[L.unit_order + u] = u;
     }
-    cut_slices(cls, cum_smem, S, tile_base, Hkv, num_ctas, plan, L);
+    cut_slices(cls, cum_smem, S, tile_base, Hkv, num_ctas, plan, L, num_ctas);
     __syncthreads();
 }
 

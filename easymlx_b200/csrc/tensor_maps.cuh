@@ -16,10 +16,12 @@ struct MapPair {
 };
 // Maps of the pool (cached per pool address and geometry).
 int get_maps(const emlx_pool& pool, MapPair* out);
-// Launches the tcgen05 prefill kernel over the plan's 128-row units.
+// Launches the tcgen05 prefill kernel over the plan's 128-row units.  `queue`: two zero-initialised ints of the
+// workspace (item counter, finished CTAs).  `wait_late`: the launch right before this one in the stream is the
+// short-row kernel of the same attention call; the prefill grid then runs beside it and waits for it at its end.
 int launch_prefill(const emlx_attn_args* a, const emlx_pool* pool, const int32_t* plan_class_hdr, const int32_t* unit_seq,
                    const int32_t* unit_row0, const int32_t* unit_tile_lo, const int32_t* unit_cum, const int32_t* unit_order,
-                   const MapPair& maps, cudaStream_t stream);
+                   int32_t* queue, bool wait_late, const MapPair& maps, cudaStream_t stream);
 long long* trace_buffer();  // the optional tracing buffer (NULL = off)
 bool prefill_supported(int kv_format, int num_q_heads, int num_kv_heads, int head_dim);
 

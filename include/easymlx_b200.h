@@ -193,7 +193,10 @@ int emlx_attn_plan(const int32_t* query_start_loc, const int32_t* kv_lens, int32
                    int32_t max_query_len /* host hint, 0 = unknown */, int32_t plan_flags /* emlx_attn_plan_flags() */,
                    void* plan, size_t plan_bytes, void* stream);
 /* Flags a plan should be built with for this pool and head geometry: bit 0 = cut sequences with more than 32
- * query rows into 128-row units for the tcgen05 prefill kernel (fp16/bf16 pools, 128 % (Hq/Hkv) == 0). */
+ * query rows into 128-row units for the tcgen05 prefill kernel (fp16/bf16 pools, 128 % (Hq/Hkv) == 0).
+ * Bits 8-15 (a tuning knob, normally 0): in a batch that holds both short rows and 128-row units the short-row
+ * kernel and the 128-row kernel run side by side, the former on a share of the SMs that the work list chooses from the
+ * two amounts of work; a non-zero value here fixes that share (in CTAs) instead. */
 int emlx_attn_plan_flags(int32_t kv_format, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim);
 /* Row class (0..3: which kernel variant serves it) of a sequence with `query_len` tokens in this step, for
  * emlx_attn_args.row_class_mask; -1 for query_len <= 0 (such sequences produce no rows). */
