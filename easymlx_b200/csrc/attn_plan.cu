@@ -13,7 +13,7 @@ __global__ void __launch_bounds__(kMetaThreads) attn_plan_kernel(const int32_t* 
     grid_dep_wait();
     grid_dep_launch();
     build_plan(qsl, kv_lens, S, G, window, class_lo, class_hi, wide, Hkv, num_ctas, plan, L, scan_smem, nullptr, nullptr, 0,
-               short_ctas);
+               short_ctas & 0xff, (short_ctas >> 8) != 0);
 }
 
 }  // namespace emlx
@@ -49,7 +49,8 @@ int emlx_attn_plan(const int32_t* query_start_loc, const int32_t* kv_lens, int32
     attn_plan_kernel<<<1, kMetaThreads, 0, (cudaStream_t)stream>>>(query_start_loc, kv_lens, num_seqs,
                                                                     num_q_heads / num_kv_heads, sliding_window, class_lo,
                                                                     class_hi, wide, num_kv_heads, min(num_sms(), kMaxGrid),
-                                                                    (int32_t*)plan, L, (plan_flags >> kPlanShortCtasShift) & 0xff);
+                                                                    (int32_t*)plan, L,
+                                                                    ((plan_flags >> kPlanShortCtasShift) & 0xff) | ((plan_flags & kPlanTwoCtas) ? 0x100 : 0));
     EMLX_LAUNCHED();
     return EMLX_OK;
 }

@@ -138,13 +138,15 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                         qf[ks][nt][1] = v.y;
                     }
                 } else {
+                    // eight queries q0..q7 face the eight nibbles of one word of key codes, which are unpacked as
+                    // (e0,e4) (e1,e5)*16 | (e2,e6) (e3,e7)*16: see unpack_nibbles
 #pragma unroll
                     for (int jx = 0; jx < KS / 2; ++jx) {
                         const uint4 v = ok ? *(const uint4*)(qrow + 64 * (jx >> 1) + 16 * t + 8 * (jx & 1)) : make_uint4(0u, 0u, 0u, 0u);
-                        qf[2 * jx][nt][0] = ptx::prmt(v.x, v.y, 0x5410u);
-                        qf[2 * jx][nt][1] = ptx::prmt(v.z, v.w, 0x5410u);
-                        qf[2 * jx + 1][nt][0] = ptx::prmt(v.x, v.y, 0x7632u);
-                        qf[2 * jx + 1][nt][1] = ptx::prmt(v.z, v.w, 0x7632u);
+                        qf[2 * jx][nt][0] = ptx::prmt(v.x, v.z, 0x5410u);      // (q0, q4)
+                        qf[2 * jx][nt][1] = ptx::prmt(v.x, v.z, 0x7632u);      // (q1, q5)
+                        qf[2 * jx + 1][nt][0] = ptx::prmt(v.y, v.w, 0x5410u);  // (q2, q6)
+                        qf[2 * jx + 1][nt][1] = ptx::prmt(v.y, v.w, 0x7632u);  // (q3, q7)
                     }
                 }
             }
@@ -160,8 +162,21 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                     qf[ks][nt][1] = bf16x2_to_f16x2(qf[ks][nt][1]);
                 }
         }
+        if constexpr (FMT == 4) {
+            // the codes in the upper nibble of a byte arrive 16 times too large: their queries are scaled down instead
+            const __half2 sixteenth = __float2half2_rn(0.0625f);
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&qf[ks][nt][1]), sixteenth);
+                    qf[ks][nt][1] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+        }
         if constexpr (FMT != 0) {
-            const uint32_t ones[4] = {0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u};
+            // column sums of Q per scale group through a constant A operand (16 where the queries were scaled down)
+            constexpr uint32_t kOne = 0x3C003C00u, kUp = FMT == 4 ? 0x4C004C00u : 0x3C003C00u;
+            const uint32_t ones[4] = {kOne, kOne, kUp, kUp};
 #pragma unroll
             for (int j = 0; j < NG; ++j)
 #pragma unroll
@@ -252,8 +267,8 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
 #pragma unroll
                         for (int x = 0; x < 2; ++x) {
                             uint32_t ha[4], hb[4];
-                            nibbles_to_h2(wa[x], ha);
-                            nibbles_to_h2(wbv[x], hb);
+                            unpack_nibbles(wa[x], ha);
+                            unpack_nibbles(wbv[x], hb);
 #pragma unroll
                             for (int y = 0; y < 2; ++y) {
                                 const uint32_t a[4] = {ha[2 * y], hb[2 * y], ha[2 * y + 1], hb[2 * y + 1]};
@@ -362,6 +377,13 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                         vsc[ab][0] = weight_scale(__half2float(sbs[2 * kTile * GROUPS + tok]));
                         vbi[ab][0] = __half2float(sbs[3 * kTile * GROUPS + tok]);
                     }
+                    if constexpr (FMT == 4) {
+                        // the second token of a pair sits in the upper nibble and is unpacked 16 times too large
+                        if (ab == 1) {
+#pragma unroll
+                            for (int j = 0; j < NG; ++j) vsc[ab][j] *= 0.0625f;
+                        }
+                    }
                 }
 #pragma unroll
                 for (int j = 0; j < NG; ++j)
@@ -406,14 +428,14 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                     a[2] = ptx::prmt(x, 0u, 0x4342u);
                     a[3] = ptx::prmt(y, 0u, 0x4342u);
                 } else {
-                    const uint32_t x = *(const uint16_t*)(st + v_off + (16 * mt) * C::VROW);
-                    const uint32_t y = *(const uint16_t*)(st + v_off + (16 * mt + 8) * C::VROW);
-                    const uint32_t z = x | (y << 16);
-                    const uint32_t lo = z & 0x0F0F0F0Fu, hi = (z >> 4) & 0x0F0F0F0Fu;
-                    a[0] = ptx::prmt(lo, 0u, 0x4140u);
-                    a[1] = ptx::prmt(lo, 0u, 0x4342u);
-                    a[2] = ptx::prmt(hi, 0u, 0x4140u);
-                    a[3] = ptx::prmt(hi, 0u, 0x4342u);
+                    // four tokens of one element per 16-bit word: bytes to half2 positions, then the even tokens by a
+                    // mask and the odd tokens (upper nibbles, 16 times too large; their weights are scaled down) by another
+                    const uint32_t x = ptx::prmt((uint32_t) * (const uint16_t*)(st + v_off + (16 * mt) * C::VROW), 0u, 0x4140u);
+                    const uint32_t y = ptx::prmt((uint32_t) * (const uint16_t*)(st + v_off + (16 * mt + 8) * C::VROW), 0u, 0x4140u);
+                    a[0] = x & 0x000F000Fu;
+                    a[1] = y & 0x000F000Fu;
+                    a[2] = x & 0x00F000F0u;
+                    a[3] = y & 0x00F000F0u;
                 }
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) ptx::mma_16816<(FMT == 0) && BF16>(o[mt][nt], a, pb[jv][nt]);

@@ -8,7 +8,7 @@
 namespace {
 
 // Every GPU on which this library runs holds this array from module load until the process exits.
-constexpr size_t kStaticScratchBytes = 10u << 20;  // 10 MiB
+constexpr size_t kStaticScratchBytes = 12u << 20;  // 12 MiB
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 constexpr int kStaticMaxDevices = 64;

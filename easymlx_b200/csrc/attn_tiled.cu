@@ -28,6 +28,7 @@ constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kThreads = kConsumerThreads + 64;  // + the producer warp and the split-merge warp
 constexpr int kPStride = kTile * 2 + 16;  // bytes per row of a P buffer (padding keeps ldmatrix conflict-free)
 constexpr int kSmemBudget = 227 * 1024 - 1024;  // dynamic shared memory minus alignment slack
+constexpr int kSmemBudgetHalf = 111 * 1024;      // the same when two CTAs share an SM (228 KB per SM, 1 KB reserved per CTA)
 
 struct TiledParams {
     const void* q;
@@ -75,13 +76,18 @@ struct Cfg {
     // Two consumer designs share the kernel: up to 16 rows every warp keeps its own softmax state and its own
     // O^T[D x rows] over its 16 tokens of each tile (no CTA barrier per tile); 32-row units split D across warps.
     static constexpr bool PRIVATE = NT <= 2;
+    // 4-bit tiles are half the bytes of 8-bit ones for the same unpacking work: an SM cannot keep up with its share of
+    // HBM on eight consumer warps, so the 8-row variant is built to fit twice on an SM (registers and shared memory;
+    // the 16-row variant would spill a kilobyte per thread under that register limit)
+    static constexpr int CTAS_PER_SM = (FMT == 4 && NT == 1) ? 2 : 1;
+    static constexpr int BUDGET = CTAS_PER_SM == 2 ? kSmemBudgetHalf : kSmemBudget;
     // private design: the producer warp also stages a descriptor and the Q rows of every upcoming part
     static constexpr int QSTRIDE = D * 2;
     static constexpr int NDESC = PRIVATE ? (NT == 1 ? 4 : 2) : 0;
     static constexpr int DESC_BYTES = PRIVATE ? 64 + ROWS * QSTRIDE : 0;
     static constexpr int SMALL = 2 * 32 * 4 + 4 * kConsumerWarps * 32 * 4 + 64 + 256 + 128;  // row stats, per-warp stats, misc, barriers, requests
     static constexpr int red_bytes(int cols) { return kConsumerWarps * ROWS * (cols + 4) * 4; }
-    static constexpr int stages_with(int fixed) { return (kSmemBudget - fixed) / STAGE > 8 ? 8 : (kSmemBudget - fixed) / STAGE; }
+    static constexpr int stages_with(int fixed) { return (BUDGET - fixed) / STAGE > 8 ? 8 : (BUDGET - fixed) / STAGE; }
     static constexpr int PRIV_BASE = NDESC * DESC_BYTES + SMALL;
     // columns of D summed across warps per pass: the widest buffer that still leaves min(4, best) stages
     static constexpr int STAGES_BEST = stages_with(PRIV_BASE + red_bytes(16));
@@ -98,7 +104,7 @@ struct Cfg {
     static constexpr int OFF_BAR = OFF_MISC + 64;                 // full[8], empty[8], dfull[4], dempty[4], mfull[2]
     static constexpr int OFF_MAIL = OFF_BAR + 256;                // two split-merge requests
     static constexpr int FIXED = OFF_MAIL + 128;
-    static constexpr int STAGES_RAW = (kSmemBudget - FIXED) / STAGE;
+    static constexpr int STAGES_RAW = (BUDGET - FIXED) / STAGE;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM = STAGES * STAGE + FIXED + 1024;
     static_assert(STAGES >= 2, "shared memory holds fewer than two stages");
@@ -416,6 +422,18 @@ __device__ __forceinline__ void nibbles_to_h2(uint32_t x, uint32_t (&h)[4]) {
 // range and needs no shift.
 template <int FMT, bool BF16> __device__ __forceinline__ constexpr float weight_shift() {
     return (FMT == 0 && !BF16) ? 8.0f : 0.0f;
+}
+
+// 8 nibbles e0..e7 of x -> four half2 registers (e0,e4) (e1,e5)*16 (e2,e6) (e3,e7)*16 as fp16 subnormal bit patterns:
+// a nibble in the low four bits of a 16-bit half is the code itself, one in bits 4-7 is the code times 16 (still
+// inside the ten mantissa bits, so still linear).  One shift and four masks; the factor 16 is taken out of the other
+// operand (queries, or softmax weights) once per part or per tile instead of once per code.
+__device__ __forceinline__ void unpack_nibbles(uint32_t x, uint32_t (&h)[4]) {
+    const uint32_t y = x >> 8;
+    h[0] = x & 0x000F000Fu;
+    h[1] = x & 0x00F000F0u;
+    h[2] = y & 0x000F000Fu;
+    h[3] = y & 0x00F000F0u;
 }
 
 constexpr float kTwo24 = 16777216.0f;  // codes enter the MMA as fp16 subnormals c * 2^-24
@@ -960,7 +978,7 @@ namespace emlx {
 // ------------------------------------------------------------------------------------------ kernel
 template <int D, int NT, int FMT, bool BF16>
 // 9 warps share four 16K-register sub-partitions: three warps on one of them caps a thread at 168 registers
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, Cfg<D, NT, FMT>::CTAS_PER_SM)
 attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const TiledParams p) {
     using C = Cfg<D, NT, FMT>;
     extern __shared__ uint8_t smem_raw[];
@@ -1116,33 +1134,32 @@ int get_maps(const emlx_pool& pool, MapPair* out) {
 }
 
 template <int D, int NT, int FMT, bool BF16>
-static int launch_one(const MapPair& maps, const TiledParams& p, cudaStream_t stream) {
+static int launch_one(const MapPair& maps, const TiledParams& p, int grid, cudaStream_t stream) {
     using C = Cfg<D, NT, FMT>;
     auto kernel = attn_tiled_kernel<D, NT, FMT, BF16>;
     static DeviceOnce configured;
     EMLX_CUDA_OK(allow_dynamic_smem(kernel, C::SMEM, configured));
-    const int grid = min(num_sms(), kMaxGrid);
     EMLX_CUDA_OK(launch_pdl(kernel, grid, kThreads, C::SMEM, stream, maps.k, maps.v, p));
     EMLX_LAUNCHED();
     return EMLX_OK;
 }
 
 template <int D, int NT>
-static int launch_fmt(int fmt, bool bf16, const MapPair& maps, const TiledParams& p, cudaStream_t stream) {
-    if (fmt == EMLX_KV_AFFINE8) return bf16 ? launch_one<D, NT, 8, true>(maps, p, stream) : launch_one<D, NT, 8, false>(maps, p, stream);
-    if (fmt == EMLX_KV_AFFINE4) return bf16 ? launch_one<D, NT, 4, true>(maps, p, stream) : launch_one<D, NT, 4, false>(maps, p, stream);
-    return bf16 ? launch_one<D, NT, 0, true>(maps, p, stream) : launch_one<D, NT, 0, false>(maps, p, stream);
+static int launch_fmt(int fmt, bool bf16, const MapPair& maps, const TiledParams& p, int grid, cudaStream_t stream) {
+    if (fmt == EMLX_KV_AFFINE8) return bf16 ? launch_one<D, NT, 8, true>(maps, p, grid, stream) : launch_one<D, NT, 8, false>(maps, p, grid, stream);
+    if (fmt == EMLX_KV_AFFINE4) return bf16 ? launch_one<D, NT, 4, true>(maps, p, grid, stream) : launch_one<D, NT, 4, false>(maps, p, grid, stream);
+    return bf16 ? launch_one<D, NT, 0, true>(maps, p, grid, stream) : launch_one<D, NT, 0, false>(maps, p, grid, stream);
 }
 
-static int launch_class(int cls, int D, int fmt, bool bf16, const MapPair& maps, const TiledParams& p, cudaStream_t s) {
+static int launch_class(int cls, int D, int fmt, bool bf16, const MapPair& maps, const TiledParams& p, int grid, cudaStream_t s) {
     if (D == 128) {
-        if (cls == 0) return launch_fmt<128, 1>(fmt, bf16, maps, p, s);
-        if (cls == 1) return launch_fmt<128, 2>(fmt, bf16, maps, p, s);
-        return launch_fmt<128, 4>(fmt, bf16, maps, p, s);
+        if (cls == 0) return launch_fmt<128, 1>(fmt, bf16, maps, p, grid, s);
+        if (cls == 1) return launch_fmt<128, 2>(fmt, bf16, maps, p, grid, s);
+        return launch_fmt<128, 4>(fmt, bf16, maps, p, grid, s);
     }
-    if (cls == 0) return launch_fmt<64, 1>(fmt, bf16, maps, p, s);
-    if (cls == 1) return launch_fmt<64, 2>(fmt, bf16, maps, p, s);
-    return launch_fmt<64, 4>(fmt, bf16, maps, p, s);
+    if (cls == 0) return launch_fmt<64, 1>(fmt, bf16, maps, p, grid, s);
+    if (cls == 1) return launch_fmt<64, 2>(fmt, bf16, maps, p, grid, s);
+    return launch_fmt<64, 4>(fmt, bf16, maps, p, grid, s);
 }
 
 // Measurement aid, only in builds with -DEMLX_TRACE: a device buffer of at least 4 * 256 int64 into which every CTA
@@ -1224,7 +1241,9 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
         p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.MB = a->max_blocks_per_seq; p.window = a->sliding_window;
         p.bs = pool->block_size; p.ppt_log = pages_per_tile_log2(pool->block_size);
         p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
-        if (int rc = launch_class(c, D, pool->kv_format, bf16, maps, p, (cudaStream_t)stream)) return rc;
+        // the grid a class is launched with is the one its slices were cut for
+        const int grid = class_ctas(c, min(num_sms(), kMaxGrid), (a->plan_flags & kPlanTwoCtas) != 0);
+        if (int rc = launch_class(c, D, pool->kv_format, bf16, maps, p, grid, (cudaStream_t)stream)) return rc;
     }
     return EMLX_OK;
 }
@@ -1244,7 +1263,8 @@ int emlx_attn_unified(const emlx_attn_args* a, const emlx_pool* p, void* s) { re
 int emlx_attn_decode(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 0, 2); }
 int emlx_attn_prefill(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 3, 3); }
 int emlx_attn_plan_flags(int32_t kv_format, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim) {
-    return emlx::prefill_supported(kv_format, num_q_heads, num_kv_heads, head_dim) ? emlx::kPlanWideUnits : 0;
+    return (emlx::prefill_supported(kv_format, num_q_heads, num_kv_heads, head_dim) ? emlx::kPlanWideUnits : 0) |
+           (kv_format == EMLX_KV_AFFINE4 ? emlx::kPlanTwoCtas : 0);
 }
 int emlx_attn_row_class(int32_t kv_format, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim, int32_t query_len) {
     if (query_len <= 0 || num_kv_heads <= 0 || num_q_heads <= 0 || num_q_heads % num_kv_heads) return -1;

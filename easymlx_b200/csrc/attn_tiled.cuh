@@ -18,6 +18,7 @@ namespace emlx {
 constexpr int kTile = 128;        // tokens per KV tile = page size the tiled kernels require
 constexpr int kNumClasses = 4;
 constexpr int kPlanWideUnits = 1;  // plan flag: cut sequences with more than 32 rows into 128-row units (class 3)
+constexpr int kPlanTwoCtas = 2;    // plan flag: the 8-row kernel runs two CTAs per SM (4-bit pools: the unpacking, not HBM, limits an SM)
 constexpr int kPlanShortCtasShift = 8;  // plan flag bits 8-15: CTAs of the short-row kernel that runs beside the 128-row one (0 = automatic)
 constexpr int kPlanHeaderWords = 16;
 // Page sizes the tiled kernels read: a 128-token tile is one page, or 2 / 4 / 8 pages of a 16/32-bit pool (affine pools
@@ -31,9 +32,14 @@ __host__ __device__ inline int pages_per_tile_log2(int block_size) { return bloc
 // the 128-row kernel keeps 1 : 1.5
 constexpr long long kTileCost = 4;
 __host__ __device__ constexpr long long part_cost(int cls) { return cls == 3 ? 6 : 9; }
-constexpr int kMaxGrid = 256;     // upper bound on CTAs per launch, sizes the partial-result slots
+constexpr int kMaxGrid = 304;     // upper bound on CTAs per launch (two per SM on 148 SMs, rounded up), sizes the partial-result slots
 constexpr int kMaxRows = 32;      // rows of the largest class
 
+// CTAs of the launch that serves class c, given the CTA count of a one-per-SM launch
+__host__ __device__ inline int class_ctas(int c, int base_ctas, bool two_per_sm) {
+    const int n = (two_per_sm && c == 0) ? 2 * base_ctas : base_ctas;
+    return n < kMaxGrid ? n : kMaxGrid;
+}
 __host__ __device__ inline int class_rows(int c) { return c < 3 ? 8 << c : 128; }
 __host__ __device__ inline int unit_class(int rows, bool wide) {
     return rows <= 8 ? 0 : (rows <= 16 ? 1 : (!wide ? 2 : 3));

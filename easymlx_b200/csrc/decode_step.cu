@@ -38,7 +38,7 @@ struct DecodeStepParams {
     PlanLayout L;
     int S, num_slots, MB, advance;
     int warps_per_cta;  // active warps of a write CTA (the others only help with the gather)
-    int G, window, class_lo, class_hi, wide, num_ctas;
+    int G, window, class_lo, class_hi, wide, num_ctas, two_per_sm;
 };
 
 template <typename TIn>
@@ -77,7 +77,8 @@ __global__ void __launch_bounds__(kMetaThreads) decode_step_kernel(const DecodeS
         __syncthreads();
         STEP_STAMP(2);
         if (p.plan != nullptr)
-            build_plan_decode(s_kv, S, p.G, p.window, p.class_lo, Hkv, p.num_ctas, p.plan, p.L, scan_smem, s_cum);
+            build_plan_decode(s_kv, S, p.G, p.window, p.class_lo, Hkv, p.num_ctas, p.plan, p.L, scan_smem, s_cum,
+                              p.two_per_sm != 0);
     } else {
         const int64_t kv_warps = p.w.has_pool ? (int64_t)S * Hkv : 0;
         const int64_t q_warps = p.w.q_out != nullptr ? (int64_t)S * p.w.Hq : 0;
@@ -202,6 +203,7 @@ extern "C" int emlx_kv_write_decode(const void* queries, void* queries_out, cons
         if (plan_bytes < (size_t)p.L.words * sizeof(int32_t)) return fail(EMLX_ERR_WORKSPACE, "plan buffer smaller than emlx_attn_plan_bytes()");
         p.G = num_q_heads / Hkv;
         p.wide = (plan_flags & kPlanWideUnits) != 0;
+        p.two_per_sm = (plan_flags & kPlanTwoCtas) != 0;
         class_range(p.G, 1, p.wide != 0, p.class_lo, p.class_hi);
         p.plan = (int32_t*)plan; p.window = sliding_window; p.num_ctas = min(num_sms(), kMaxGrid);
     }

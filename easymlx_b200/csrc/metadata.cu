@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(kMetaThreads) build_metadata_kernel(
     // attention work list in the same launch (lengths after the write are final here)
     if (plan != nullptr)
         build_plan(qv, kvv, S, G, window, class_lo, class_hi, wide, Hkv, num_ctas, plan, L, scan_smem,
-                   small ? s_off : nullptr, s_cum, kSmemUnits, short_ctas);
+                   small ? s_off : nullptr, s_cum, kSmemUnits, short_ctas & 0xff, (short_ctas >> 8) != 0);
 
     META_STAMP(3);
     if (scatter_later) return;  // a large batch: the gather and the slot mapping run on many CTAs in a second launch
@@ -247,7 +247,8 @@ extern "C" int emlx_build_metadata(const int32_t* query_lens, const int32_t* slo
         query_lens, slot_ids, num_seqs, total_tokens, block_tables_all, num_slots, max_blocks_per_seq, kv_lens_all,
         block_size, advance_kv_lens, query_start_loc, block_tables, kv_lens, slot_mapping, token_positions, num_blocks,
         status, (int32_t*)plan, L, G, sliding_window, class_lo, class_hi, (plan_flags & kPlanWideUnits) != 0, num_kv_heads,
-        min(num_sms(), kMaxGrid), scatter_later, (plan_flags >> kPlanShortCtasShift) & 0xff));
+        min(num_sms(), kMaxGrid), scatter_later,
+        ((plan_flags >> kPlanShortCtasShift) & 0xff) | ((plan_flags & kPlanTwoCtas) ? 0x100 : 0)));
     if (scatter_later) {
         EMLX_LAUNCHED();
         const int64_t work = cells > total_tokens ? cells : (int64_t)total_tokens;

@@ -127,13 +127,15 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
                                            int class_lo, int class_hi, bool wide, int Hkv, int num_ctas,
                                            int32_t* plan, const PlanLayout& L, int32_t* scan_smem,
                                            int32_t* seq_off_buf = nullptr, int32_t* cum_smem = nullptr,
-                                           int cum_cap = 0, int short_ctas = 0) {
+                                           int cum_cap = 0, int short_ctas = 0, bool two_per_sm = false) {
     const int tid = threadIdx.x;
+    const int base_ctas = num_ctas;
     // The 128-row class comes first: the short-row class that is launched right before the 128-row kernel runs
     // beside it, and how many CTAs it then gets depends on how much 128-row work there is.
     long long wide_tiles = 0;        // (unit, head, tile) triples of class 3
     bool short_class_seen = false;   // a short-row class that is launched later than the current one has work
     for (int c = kNumClasses - 1; c >= 0; --c) {
+        num_ctas = class_ctas(c, base_ctas, two_per_sm);
         if (c < class_lo || c > class_hi) {
             if (tid == 0) { plan[4 * c + 0] = 0; plan[4 * c + 1] = 0; }
             for (int i = tid; i <= num_ctas; i += kMetaThreads) { plan[L.cta_start[c] + i] = 0; plan[L.cta_unit[c] + i] = 0; }
@@ -241,14 +243,15 @@ __device__ __forceinline__ void build_plan(const int32_t* qsl, const int32_t* kv
 // Work list of a batch in which every sequence has exactly one query token (G rows): unit i is sequence i, so the
 // unit counting and the owner search of build_plan fall away.  Same output as build_plan(..., max one class).
 __device__ __forceinline__ void build_plan_decode(const int32_t* kv_lens /* shared memory */, int S, int G, int window,
-                                                  int cls, int Hkv, int num_ctas, int32_t* plan, const PlanLayout& L,
-                                                  int32_t* scan_smem, int32_t* cum_smem /* [S + 1] */) {
+                                                  int cls, int Hkv, int base_ctas, int32_t* plan, const PlanLayout& L,
+                                                  int32_t* scan_smem, int32_t* cum_smem /* [S + 1] */, bool two_per_sm) {
     const int tid = threadIdx.x;
     for (int c = 0; c < kNumClasses; ++c) {
         if (c == cls) continue;
         if (tid == 0) { plan[4 * c + 0] = 0; plan[4 * c + 1] = 0; }
-        for (int i = tid; i <= num_ctas; i += kMetaThreads) { plan[L.cta_start[c] + i] = 0; plan[L.cta_unit[c] + i] = 0; }
+        for (int i = tid; i <= class_ctas(c, base_ctas, two_per_sm); i += kMetaThreads) { plan[L.cta_start[c] + i] = 0; plan[L.cta_unit[c] + i] = 0; }
     }
+    const int num_ctas = class_ctas(cls, base_ctas, two_per_sm);
     int32_t* unit_seq = plan + L.unit_seq[cls];
     int32_t* unit_row0 = plan + L.unit_row0[cls];
     int32_t* unit_tile_lo = plan + L.unit_tile_lo[cls];

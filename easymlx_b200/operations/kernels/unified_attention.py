@@ -195,15 +195,15 @@ class AttentionCall:
             self.planned = False
             # the flags decide which row classes the work list holds; the launch has to use the ones it was built with
             # (the decode entry point serves the short-row classes only: its work list is built without 128-row units)
-            self.plan_flags = 0 if self.kernel == "decode" else \
-                int(lib.emlx_attn_plan_flags(self.pool.kv_format, self.hq, hkv, self.d))
+            recommended = int(lib.emlx_attn_plan_flags(self.pool.kv_format, self.hq, hkv, self.d))
+            self.plan_flags = recommended & ~1 if self.kernel == "decode" else recommended
             if plan is not None and plan[1] == self.hq and plan[2] == self.window and plan[0].numel() >= self.plan_bytes:
                 self.plan_buf, self.planned = plan[0], True   # built together with the batch metadata
                 self.plan_flags = int(plan[3])
             else:
                 self.plan_buf = _scratch.get(dev, "plan", self.plan_bytes, zero=False)
             a.plan_flags = self.plan_flags
-            if query_len_set and self.plan_flags == int(lib.emlx_attn_plan_flags(self.pool.kv_format, self.hq, hkv, self.d)):
+            if query_len_set and (self.plan_flags & 1) == (recommended & 1):
                 # the host knows which query lengths occur: launch only the kernels of those row classes
                 # (emlx_attn_row_class speaks for plans built with emlx_attn_plan_flags)
                 for q_len in set(int(x) for x in query_len_set):

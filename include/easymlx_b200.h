@@ -194,6 +194,8 @@ int emlx_attn_plan(const int32_t* query_start_loc, const int32_t* kv_lens, int32
                    void* plan, size_t plan_bytes, void* stream);
 /* Flags a plan should be built with for this pool and head geometry: bit 0 = cut sequences with more than 32
  * query rows into 128-row units for the tcgen05 prefill kernel (fp16/bf16 pools, 128 % (Hq/Hkv) == 0).
+ * Bit 1 = the 8-row kernel runs two CTAs per SM and its slices are cut for twice as many CTAs (4-bit pools,
+ * where unpacking the codes, not HBM, limits what one CTA's warps get through).
  * Bits 8-15 (a tuning knob, normally 0): in a batch that holds both short rows and 128-row units the short-row
  * kernel and the 128-row kernel run side by side, the former on a share of the SMs that the work list chooses from the
  * two amounts of work; a non-zero value here fixes that share (in CTAs) instead. */
@@ -223,7 +225,7 @@ int emlx_attn_generic(const emlx_attn_args* args, const emlx_pool* pool, void* s
  * already reserved all of HBM (a later cudaMalloc for the work list or the split-KV workspace could fail or
  * fragment the pool), or a step loop that must not take the device-wide synchronisation cudaMalloc/cudaFree
  * imply.  Same result as emlx_attn_plan + emlx_attn_decode; args->plan/workspace are ignored and the entry
- * point builds the work list itself.  Scratch is a 10 MiB array built into the library (held by every GPU the
+ * point builds the work list itself.  Scratch is a 12 MiB array built into the library (held by every GPU the
  * library runs on until the process exits); a batch whose plan + workspace exceed it is rejected with
  * EMLX_ERR_WORKSPACE (in practice: up to a few thousand sequences / tokens).  The first call on a device looks
  * up the array's address; make that first call outside any stream capture.  All calls share the array: two
