@@ -4,12 +4,13 @@
 // one KV head; the plan lists the KV tiles (128-token pages) the rows may attend.  Per tile
 //     S[128 rows x 128 tokens]  = Q . K^T     tcgen05.mma, both operands K-major in shared memory (TMA, 128B swizzle),
 //                                             fp32 accumulator in TMEM columns [0, 128)
-//     softmax                                  four warps, one TMEM lane (= one row) per thread: no cross-thread reduction;
+//     softmax                                  one TMEM lane (= one row) per thread and warpgroup, 64 keys each;
 //                                             P goes back to TMEM (16-bit, two per column) as the next A operand, so the
 //                                             shared-memory port only carries K and V
 //     O_tile[128 rows x D]      = P . V        tcgen05.mma with A from TMEM, V read in place as an MN-major B operand
 //     O = O * corr + O_tile                    in registers of the softmax threads
-// Warp roles: 0-3 softmax, 4 TMA producer, 5 MMA issuer (and TMEM owner).  All waits are bounded.
+// Warp roles: 0-7 softmax (two warpgroups, each half of every tile's keys), 8 TMA producer, 9 MMA issuer (and TMEM
+// owner).  All waits are bounded.
 #include "plan_device.cuh"
 #include "ptx.cuh"
 #include "tensor_maps.cuh"
@@ -26,7 +27,7 @@ namespace emlx {
 #define PF_STAMP(cond, tile, slot) do { } while (0)
 #endif
 
-constexpr int kPfThreads = 192;
+constexpr int kPfThreads = 320;  // warps 0-3 and 4-7: the two softmax warpgroups; 8: TMA producer; 9: MMA issuer
 constexpr int kPfRows = 128;
 
 struct PrefillParams {
@@ -172,10 +173,14 @@ struct PfBarriers {
     uint64_t k_full[4], v_full[4];
     // item_full[k & 3]: the index of the CTA's k-th item is in item_ring[k & 3] (-1: no more items)
     uint64_t item_full[4];
+    // x_full[t & 1]: both half-row maxima of tile t are in shared memory; l_full: both half-row sums of the item are
+    uint64_t x_full[2], l_full;
     int item_ring[4];
     uint32_t tmem_base;
     int abort_word;
 };
+
+static_assert(sizeof(PfBarriers) <= 256, "the barrier block has 256 bytes of shared memory");
 
 template <int D, bool BF16>
 __global__ void __launch_bounds__(kPfThreads, 1)
@@ -209,10 +214,13 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
 
     if (tid == 0) {
         ptx::mbar_init(&bars->q_full, 1);
-        ptx::mbar_init(&bars->q_tmem, 128);
-        ptx::mbar_init(&bars->item_done, 128);
-        ptx::mbar_init(&bars->p_ready[0], 128);
-        ptx::mbar_init(&bars->p_ready[1], 128);
+        ptx::mbar_init(&bars->q_tmem, 256);
+        ptx::mbar_init(&bars->item_done, 256);
+        ptx::mbar_init(&bars->p_ready[0], 256);
+        ptx::mbar_init(&bars->p_ready[1], 256);
+        ptx::mbar_init(&bars->x_full[0], 256);
+        ptx::mbar_init(&bars->x_full[1], 256);
+        ptx::mbar_init(&bars->l_full, 256);
         for (int s = 0; s < 4; ++s) {
             ptx::mbar_init(&bars->qk_done[s], 1);
             ptx::mbar_init(&bars->pv_done[s], 1);
@@ -226,14 +234,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
         ptx::prefetch_tensormap(&kmap);
         ptx::prefetch_tensormap(&vmap);
     }
-    if (warp == 5) tmem_alloc(&bars->tmem_base, C::TMEM_COLS);
+    if (warp == 9) tmem_alloc(&bars->tmem_base, C::TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
     const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256, tmem_Q = tmem_base + 384;
 
-    if (warp == 4) {
+    if (warp == 8) {
         // ------------------------------------------------------------------ TMA producer
         uint32_t kt = 0, k = 0;
         int u, head;
@@ -366,7 +374,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             }
             kt += (uint32_t)ntiles;
         }
-    } else if (warp == 5) {
+    } else if (warp == 9) {
         // ------------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc_qk = instr_desc(128, 128, BF16, false);
         constexpr uint32_t idesc_pv = instr_desc(128, D, BF16, true);
@@ -430,9 +438,18 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             }
         }
     } else {
-        // ------------------------------------------------------------------ softmax: one row per thread
-        const int r = tid;
-        const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+        // ------------------------------------------------------------------ softmax: two warpgroups, half a tile each
+        // Thread r of warpgroup g owns row r (= TMEM lane r) and the 64 keys [64 g, 64 g + 64) of every tile.  The two
+        // threads of a row exchange their half-row maxima (and, at the end of an item, their sums) through the Q
+        // tile's shared memory, which is idle once Q sits in TMEM; both then take the same decisions about the row's
+        // reference maximum.  A tile costs 128 x 128 exponentials and the SM makes 16 per clock: with 256 threads
+        // feeding that unit instead of 128 the time a tile spends between QK and PV, which is what the tensor pipe
+        // waits for, drops by a sixth.
+        const int wg = warp >> 2, r = tid & 127;
+        const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+        float* xmax = (float*)q_smem;          // [tile parity][warpgroup][row]
+        float* xsum = xmax + 4 * kPfRows;      // [warpgroup][row]
+        constexpr int OCH = D / 64;            // 32-column chunks of O per warpgroup
         uint32_t kt = 0;
         int u, head;
         for (uint32_t k = 0;; ++k) {
@@ -453,48 +470,55 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             const int hi_min = min(kv_len, ctx + i_first + 1);
             const int lo_max = p.window > 0 ? max(0, min(kv_len - 1, ctx + i_last) - p.window + 1) : 0;
 
-            // this row of Q: shared memory (TMA, swizzled) -> TMEM, two 16-bit elements per column, as the A operand of QK
+            // this row of Q: shared memory (TMA, swizzled) -> TMEM, two 16-bit elements per column, as the A operand of
+            // QK; warpgroup g copies the g-th 64 elements
             ptx::mbar_wait(&bars->q_full, k & 1, abort_word);
-#pragma unroll
-            for (int h = 0; h < C::HALVES; ++h) {
+            if (wg < C::HALVES) {
                 uint32_t qv[32];
 #pragma unroll
                 for (int c = 0; c < 8; ++c) {
-                    const uint4 v = *(const uint4*)(q_smem + h * (kPfRows * 128) + r * 128 + ((c ^ (r & 7)) << 4));
+                    const uint4 v = *(const uint4*)(q_smem + wg * (kPfRows * 128) + r * 128 + ((c ^ (r & 7)) << 4));
                     qv[4 * c] = v.x; qv[4 * c + 1] = v.y; qv[4 * c + 2] = v.z; qv[4 * c + 3] = v.w;
                 }
-                tmem_st32(tmem_Q + lane_addr + 32 * h, qv);
+                tmem_st32(tmem_Q + lane_addr + 32 * wg, qv);
             }
             tc_fence_before();
             ptx::mbar_arrive(&bars->q_tmem);
 
             // m_ref is the maximum the stored probabilities and O refer to; it follows the true running maximum
-            // lazily (only when that grew by more than 2^8), so O in TMEM is rarely rescaled
+            // lazily (only when that grew by more than 2^8), so O in TMEM is rarely rescaled.  Both threads of a row
+            // compute it from the same numbers, so they always agree.  l is the sum over this thread's keys only.
             float m_ref = -INFINITY, l = 0.f;
 
             for (int j = 0; j < ntiles; ++j, ++kt) {
                 const int t0 = (tile_lo + j) * kTile;
                 const bool interior = (t0 + kTile <= hi_min) && (t0 >= lo_max);
+                const uint32_t s_addr = tmem_S + (kt & 1) * 128 + lane_addr;
                 ptx::mbar_wait(&bars->qk_done[kt & 3], (kt >> 2) & 1, abort_word);
                 tc_fence_after();
                 PF_STAMP(tid == 0, kt, 0);
-                uint32_t sv[128];
-#pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) tmem_ld32_nowait(tmem_S + (kt & 1) * 128 + lane_addr + 32 * c4, sv + 32 * c4);
+                uint32_t sv[64];
+                tmem_ld32_nowait(s_addr + 64 * wg, sv);
+                tmem_ld32_nowait(s_addr + 64 * wg + 32, sv + 32);
                 tmem_wait_ld();
                 if (!interior) {
 #pragma unroll
-                    for (int i = 0; i < 128; ++i) {
-                        const int tok = t0 + i;
+                    for (int i = 0; i < 64; ++i) {
+                        const int tok = t0 + 64 * wg + i;
                         if (tok < lo || tok >= hi) sv[i] = 0xff800000u;  // -inf
                     }
                 }
-                float mx8[8];  // eight independent chains instead of one of 128 dependent maxima
+                float mx8[8];  // eight independent chains instead of one of 64 dependent maxima
 #pragma unroll
                 for (int i = 0; i < 8; ++i) mx8[i] = __uint_as_float(sv[i]);
 #pragma unroll
-                for (int i = 8; i < 128; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(sv[i]));
-                const float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+                for (int i = 8; i < 64; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(sv[i]));
+                float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+                // the other half of the row
+                xmax[((kt & 1) * 2 + wg) * kPfRows + r] = mx;
+                ptx::mbar_arrive(&bars->x_full[kt & 1]);
+                ptx::mbar_wait(&bars->x_full[kt & 1], (kt >> 1) & 1, abort_word);
+                mx = fmaxf(mx, xmax[((kt & 1) * 2 + (wg ^ 1)) * kPfRows + r]);
                 PF_STAMP(tid == 0, kt, 1);
                 const float m_new = mx * p.scale_log2e;
                 const bool grow = (j == 0) ? true : (m_new > m_ref + 8.0f);
@@ -506,11 +530,12 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 }
                 // O is only touched when the reference maximum moves (rare): every earlier PV must be complete then.
                 // P needs no such wait: it replaces this tile's own S, which nothing else uses until QK of tile kt + 2.
+                // Each warpgroup rescales its half of the row's columns.
                 if (j > 0 && __any_sync(0xffffffffu, grow)) {
                     ptx::mbar_wait(&bars->pv_done[(kt - 1) & 3], ((kt - 1) >> 2) & 1, abort_word);
                     tc_fence_after();
 #pragma unroll 1
-                    for (int c4 = 0; c4 < D / 32; ++c4) {
+                    for (int c4 = wg * OCH; c4 < (wg + 1) * OCH; ++c4) {
                         uint32_t ov[32];
                         tmem_ld32_nowait(tmem_O + lane_addr + 32 * c4, ov);
                         tmem_wait_ld();
@@ -528,35 +553,30 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;
                 const float neg_m = kShift - m_safe;
                 float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
+                uint32_t packed[32];
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    uint32_t packed[32];
-#pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        float p0, p1;
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(sv[64 * h + 2 * e]), p.scale_log2e, neg_m)));
-                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(sv[64 * h + 2 * e + 1]), p.scale_log2e, neg_m)));
-                        if (e & 1) { ls2 += p0; ls3 += p1; } else { ls0 += p0; ls1 += p1; }
-                        if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
-                        else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
-                    }
-                    // tokens [64h, 64h + 64) of this row; one wait after both stores.  (Sending a quarter of the
-                    // exponentials through an FMA-pipe polynomial, and issuing the MMAs from a one-thread loop, were both
-                    // measured and were slower on the bandwidth-bound spec-verify batch.)
-                    tmem_st32_nowait(tmem_S + (kt & 1) * 128 + lane_addr + 32 * h, packed);
+                for (int e = 0; e < 32; ++e) {
+                    float p0, p1;
+                    // (Sending a quarter of the exponentials through a cubic on the FMA pipe instead of the special-function
+                    // unit was measured twice, on the tensor-bound mixed batch and on the bandwidth-bound spec-verify
+                    // batch, and was 4-5 % slower on both: the issue slots it costs are as scarce as that unit.)
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2e, neg_m)));
+                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2e, neg_m)));
+                    if (e & 1) { ls2 += p0; ls3 += p1; } else { ls0 += p0; ls1 += p1; }
+                    if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
+                    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
                 }
-                tmem_wait_st();
-                const float lsum = (ls0 + ls1) + (ls2 + ls3);
-                l += lsum;
-                if (t0 + kTile > kv_len) {
-                    // token rows of V past the sequence end are stale memory: clear them (thread r owns token r)
+                // tokens [64 g, 64 g + 64) of this row, two per column, over the start of the tile's own S
+                tmem_st32(s_addr + 32 * wg, packed);
+                l += (ls0 + ls1) + (ls2 + ls3);
+                if (t0 + kTile > kv_len && wg < C::HALVES) {
+                    // token rows of V past the sequence end are stale memory: clear them (thread r owns token r, its
+                    // warpgroup the 64-element block of the row)
                     ptx::mbar_wait(&bars->v_full[kt % C::VST], (kt / C::VST) & 1, abort_word);
                     if (r >= max(0, kv_len - t0)) {
-                        uint8_t* vrow = v_smem + (size_t)(kt % C::VST) * C::KBYTES + r * 128;
+                        uint8_t* vrow = v_smem + (size_t)(kt % C::VST) * C::KBYTES + wg * (kTile * 128) + r * 128;
 #pragma unroll
-                        for (int h = 0; h < C::HALVES; ++h)
-#pragma unroll
-                            for (int c = 0; c < 8; ++c) *(uint4*)(vrow + h * (kTile * 128) + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+                        for (int c = 0; c < 8; ++c) *(uint4*)(vrow + c * 16) = make_uint4(0u, 0u, 0u, 0u);
                     }
                     ptx::fence_proxy_async();  // the tensor core reads V through the async proxy
                 }
@@ -564,15 +584,19 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 PF_STAMP(tid == 0, kt, 3);
                 ptx::mbar_arrive(&bars->p_ready[kt & 1]);
             }
-            // the last PV, then this row of O
+            // the last PV, then this row of O: the two sums of the row are added, each warpgroup stores half the columns
+            xsum[wg * kPfRows + r] = l;
+            ptx::mbar_arrive(&bars->l_full);
             ptx::mbar_wait(&bars->pv_done[(kt - 1) & 3], ((kt - 1) >> 2) & 1, abort_word);
             tc_fence_after();
+            ptx::mbar_wait(&bars->l_full, k & 1, abort_word);
+            l += xsum[(wg ^ 1) * kPfRows + r];
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             const bool store = row0 + r < R;
             const int oi = (row0 + r) / p.G, ohh = (row0 + r) - oi * p.G;
             uint4* dst = (uint4*)((uint16_t*)p.out + ((long long)(qs + oi) * p.Hq + head * p.G + ohh) * D);
 #pragma unroll 1
-            for (int c4 = 0; c4 < D / 32; ++c4) {
+            for (int c4 = wg * OCH; c4 < (wg + 1) * OCH; ++c4) {
                 uint32_t ov[32];
                 tmem_ld32_nowait(tmem_O + lane_addr + 32 * c4, ov);
                 tmem_wait_ld();
@@ -591,12 +615,13 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 }
             }
             tc_fence_before();
+            ptx::fence_proxy_async();  // the next item's Q arrives by TMA over the memory the exchanges above used
             ptx::mbar_arrive(&bars->item_done);
         }
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if (warp == 9) tmem_dealloc(tmem_base, C::TMEM_COLS);
     if (*abort_word && tid == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
     if (tid == 0) {
         // every draw of this CTA is behind us; the last CTA to get here puts the item counter back to zero
