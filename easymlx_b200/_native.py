@@ -60,6 +60,8 @@ SIGNATURES = {
                                      _I32, _I32, _I32, _I32, _I32, _P, C.c_size_t, _P]),
     "emlx_kv_write": (C.c_int, [_P, _P, _I32, _I32, _P, C.POINTER(Pool), _P, _P]),
     "emlx_kv_write_rope": (C.c_int, [_P, _P, _I32, _P, _P, _I32, _I32, _P, _P, C.POINTER(Rope), C.POINTER(Pool), _P, _P]),
+    "emlx_kv_write_step": (C.c_int, [_P, _P, _P, _P, _I32, _P, _P, _I32, _I32, _P, _I32, _I32, _P, _I32, C.POINTER(Pool),
+                                    C.POINTER(Rope), _P, _P, _P, _I32, _I32, _I32, _I32, _P, C.c_size_t, _P, _P, _P]),
     "emlx_kv_write_decode": (C.c_int, [_P, _P, _P, _P, _I32, _P, _I32, _P, _I32, _I32, _P, _I32, C.POINTER(Pool),
                                       C.POINTER(Rope), _P, _P, _P, _I32, _I32, _I32, _P, C.c_size_t, _P, _P, _P]),
     "emlx_attn_plan_bytes": (C.c_size_t, [_I32, _I32, _I32, _I32]),

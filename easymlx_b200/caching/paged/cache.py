@@ -28,7 +28,7 @@ from ... import _native as nv
 
 _CHECK = os.environ.get("EASYMLX_B200_CHECK", "0") not in ("", "0")
 QUANT_GROUP = 64
-_FUSED_DECODE_MAX_SEQS = 2048  # batch size up to which emlx_kv_write_decode serves a single-token batch
+_FUSED_STEP_MAX_SEQS = 2048  # batch size up to which emlx_kv_write_step serves a batch in one launch
 
 _TORCH_DTYPES = {
     "float16": torch.float16, "half": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32,
@@ -305,8 +305,9 @@ class PageCacheView:
                      slots_dev: torch.Tensor, total_tokens: int, plan_for: tuple | None = None,
                      advance: bool = True, rope=None, queries: torch.Tensor | None = None,
                      single_token: bool = False):
-        """Metadata kernel + write kernel for one packed batch (one fused launch when every sequence brings exactly
-        one token, ``single_token``).  Returns ``(qsl, block_tables, kv_lens)`` of the scheduled rows;
+        """Batch metadata, attention work list and KV write for one packed batch: one launch for up to 2048 sequences
+        (``single_token``: every sequence brings exactly one token, no prefix sum needed), else the metadata kernel
+        followed by the write kernel.  Returns ``(qsl, block_tables, kv_lens)`` of the scheduled rows;
         ``self.kv_lens`` is advanced in place."""
         nv.require_cuda(keys, values, self.key_cache)
         dev = self.key_cache.device
@@ -346,14 +347,16 @@ class PageCacheView:
                     raise ValueError("queries and keys must have the same dtype when RoPE is fused into the write")
                 queries = queries.contiguous()
                 rotated_q = torch.empty_like(queries)
-        if single_token and 0 < total_tokens == s <= _FUSED_DECODE_MAX_SEQS:
-            # decode fast path (the reference's, cache.py:1155-1206): metadata, work list and write in one launch
-            nv.check(lib.emlx_kv_write_decode(
+        if 0 < total_tokens and 0 < s <= _FUSED_STEP_MAX_SEQS:
+            # metadata, work list and write in one launch (the reference's concatenate_to_cache, cache.py:1123-1306);
+            # a batch of single tokens (its decode fast path, :1155-1206) skips the prefix sum of the query lengths
+            decode = single_token and total_tokens == s
+            nv.check(lib.emlx_kv_write_step(
                 nv.ptr(queries) if rope is not None else None, nv.ptr(rotated_q), nv.ptr(keys), nv.ptr(values),
-                nv.dtype_code(keys.dtype), nv.ptr(slots_dev), s, nv.ptr(self.block_tables), self.num_seqs,
-                self.blocks_per_seq, nv.ptr(self.kv_lens), 1 if advance else 0, self.native_pool(),
-                rope.native(dev) if rope is not None else None, nv.ptr(qsl), nv.ptr(bt), nv.ptr(lens),
-                hq if plan is not None else (int(queries.shape[1]) if rope is not None else 0), window, flags,
+                nv.dtype_code(keys.dtype), None if decode else nv.ptr(query_lens_dev), nv.ptr(slots_dev), s, total_tokens,
+                nv.ptr(self.block_tables), self.num_seqs, self.blocks_per_seq, nv.ptr(self.kv_lens), 1 if advance else 0,
+                self.native_pool(), rope.native(dev) if rope is not None else None, nv.ptr(qsl), nv.ptr(bt), nv.ptr(lens),
+                hq if plan is not None else (int(queries.shape[1]) if rope is not None else 0), window, max_q, flags,
                 nv.ptr(plan), plan_bytes, nv.ptr(self.ticket), nv.ptr(self.status), stream))
             if _CHECK:
                 self.check()

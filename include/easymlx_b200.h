@@ -163,18 +163,29 @@ int emlx_kv_write_rope(const void* queries, void* queries_out, int32_t num_q_hea
                        const int32_t* token_positions, const emlx_rope* rope, const emlx_pool* pool, int32_t* status,
                        void* stream);
 
-/* (1)+(2) for a batch in which every scheduled sequence appends exactly one token, in ONE launch.  Replaces the
- * decode fast path of PageCacheView.concatenate_to_cache (caching/paged/cache.py:1155-1206): the row of sequence i
- * goes to position kv_lens_all[slot_ids[i]] of its slot (page block_tables_all[slot, pos / bs], offset pos % bs), the
- * stored length becomes pos + 1 (when advance_kv_lens != 0), and the rows of the scheduled slots are gathered:
- *   query_start_loc[S+1] = 0..S, block_tables[S, MB], kv_lens[S] (lengths after the step), and, when plan != NULL,
- *   the attention work list (as emlx_attn_plan with max_query_len 1).
- * keys/values are [S, Hkv, D] in in_dtype.  With `rope` the key is rotated at its position before it is stored and,
- * when queries_out != NULL, queries [S, Hq, D] are rotated into queries_out (caching/paged/cache.py:1161-1166).
+/* (1)+(2) in ONE launch: batch metadata, the attention work list and the paged KV write of one step.  Replaces
+ * PageCacheView.concatenate_to_cache as a whole (caching/paged/cache.py:1123-1306: the decode fast path :1155-1206 and
+ * the ragged path :1208-1306).  Token j of sequence i goes to position kv_lens_all[slot_ids[i]] + j of its slot (page
+ * block_tables_all[slot, pos / bs], offset pos % bs); the stored length grows by the sequence's query length (when
+ * advance_kv_lens != 0); outputs as emlx_build_metadata: query_start_loc[S+1], block_tables[S, MB], kv_lens[S] (lengths
+ * after the step) and, when plan != NULL, the attention work list (as emlx_attn_plan).
+ *   query_lens[S]   device; NULL = every sequence has exactly one token (then total_tokens == num_seqs)
+ *   keys/values     [T, Hkv, D] in in_dtype
+ * With `rope` the keys are rotated at their positions before they are stored and, when queries_out != NULL, queries
+ * [T, Hq, D] are rotated into queries_out (caching/paged/cache.py:1161-1166,1225-1231).
  * `ticket` is one int32 of device memory owned by the caller, zero before the first call; the kernel leaves it zero.
- * A slot id must not appear twice.  A sequence whose page-table row is full sets EMLX_DEV_OVERFLOW, keeps its stored
- * length, writes nothing and gets kv_lens[i] = 0 (attention then returns zero rows for it).  Up to 2048 sequences;
- * larger batches return EMLX_ERR_UNSUPPORTED and go through emlx_build_metadata + emlx_kv_write. */
+ * A slot id must not appear twice.  A sequence that would outgrow its page-table row sets EMLX_DEV_OVERFLOW, keeps its
+ * stored length, writes nothing and gets kv_lens[i] = 0 (attention then returns zero rows for it).  Up to 2048
+ * sequences; larger batches return EMLX_ERR_UNSUPPORTED and go through emlx_build_metadata + emlx_kv_write. */
+int emlx_kv_write_step(const void* queries, void* queries_out, const void* keys, const void* values, int32_t in_dtype,
+                       const int32_t* query_lens, const int32_t* slot_ids, int32_t num_seqs, int32_t total_tokens,
+                       const int32_t* block_tables_all, int32_t num_slots, int32_t max_blocks_per_seq,
+                       int32_t* kv_lens_all, int32_t advance_kv_lens, const emlx_pool* pool, const emlx_rope* rope,
+                       int32_t* query_start_loc, int32_t* block_tables, int32_t* kv_lens, int32_t num_q_heads,
+                       int32_t sliding_window, int32_t max_query_len, int32_t plan_flags, void* plan, size_t plan_bytes,
+                       int32_t* ticket, int32_t* status, void* stream);
+/* The same for a batch in which every scheduled sequence appends exactly one token (query_lens == NULL above): the
+ * decode fast path of concatenate_to_cache (caching/paged/cache.py:1155-1206). */
 int emlx_kv_write_decode(const void* queries, void* queries_out, const void* keys, const void* values, int32_t in_dtype,
                          const int32_t* slot_ids, int32_t num_seqs, const int32_t* block_tables_all, int32_t num_slots,
                          int32_t max_blocks_per_seq, int32_t* kv_lens_all, int32_t advance_kv_lens, const emlx_pool* pool,

@@ -1,4 +1,5 @@
-"""The single-launch decode step (``emlx_kv_write_decode``) against the oracle and against the general two-launch path.
+"""The single-launch cache step (``emlx_kv_write_step`` / ``emlx_kv_write_decode``) against the oracle and against the
+two-launch path (``emlx_build_metadata`` + ``emlx_kv_write``).
 
 The reference has the same split: ``PageCacheView.concatenate_to_cache`` takes a fast path when every scheduled
 sequence brings exactly one token (``caching/paged/cache.py:1155-1206``) and a ragged path otherwise
@@ -75,7 +76,7 @@ def test_fused_decode_step_equals_the_two_launch_path(bits, shape, monkeypatch):
     results = []
     for fused in (True, False):
         cache, bt, q, k, v = _decode_batch(7, num_slots, max_len, hkv, hq, d, sched, lens, bits)
-        monkeypatch.setattr(cache_mod, "_FUSED_DECODE_MAX_SEQS", 2048 if fused else 0)
+        monkeypatch.setattr(cache_mod, "_FUSED_STEP_MAX_SEQS", 2048 if fused else 0)
         pq, kc, vc, meta = _step(cache, q, k, v, sched)
         cache.check()
         assert int(cache.ticket.item()) == 0
@@ -178,3 +179,65 @@ def test_decode_batch_without_host_lengths_attends_like_the_oracle():
     kv_write.write_rows(kc0, vc0, k, v, m["slot_mapping"])
     want = opa.paged_attention_rows(q, kc0, vc0, m["block_tables"], m["kv_lens"], m["query_start_loc"], softmax_scale=d ** -0.5)
     assert_close(out, want)
+
+
+@pytest.mark.parametrize("bits", [0, 8, 4])
+@pytest.mark.parametrize("name", ["write_ragged_f16", "write_specverify_f16", "write_ragged_cast", "write_decode_f16"])
+def test_ragged_single_launch_step_equals_the_two_launch_path(name, bits, monkeypatch):
+    """Ragged batches (page-edge crossings, an empty row, fp32 inputs cast on the way) through both routes: same pool,
+    same lengths, same metadata, and a work list that drives the same attention output."""
+    import easymlx_b200 as emlx
+    from easymlx_b200.caching.paged import cache as cache_mod
+
+    spec = cases.WRITE_CASES[name]
+    x = cases.write_inputs(**spec)
+    hkv, hq, d, bs = spec["hkv"], spec["hq"], spec["d"], x["block_size"]
+    if bits and (d % 64 or bs != 128):
+        pytest.skip("affine pools need head_dim % 64 == 0 and 128-token pages here")
+    results = []
+    for fused in (True, False):
+        monkeypatch.setattr(cache_mod, "_FUSED_STEP_MAX_SEQS", 2048 if fused else 0)
+        cache = emlx.PageCacheView.init(num_seqs=spec["num_seqs"], max_seq_len=spec["max_seq_len"], num_kv_heads=hkv, head_dim=d,
+                                        block_size=bs, cache_bits=bits or None, cache_dtype="affine" if bits else None)
+        rng = np.random.default_rng(11)
+        for a in (cache.key_cache, cache.value_cache):
+            if a.dtype == torch.uint8:
+                a.copy_(torch.from_numpy(rng.integers(0, 256, tuple(a.shape), dtype=np.uint8)))
+            else:
+                a.copy_(torch.from_numpy(rng.standard_normal(tuple(a.shape)).astype(np.float16)))
+        if bits:
+            for a in (cache.k_scales, cache.k_biases, cache.v_scales, cache.v_biases):
+                a.copy_(torch.from_numpy(rng.standard_normal(tuple(a.shape)).astype(np.float16)))
+        cache.block_tables.copy_(dev(x["block_tables"]))
+        cache.kv_lens.copy_(dev(x["kv_lens"]))
+        qlens = x["query_lens"].tolist()
+        meta = emlx.PageMetadata(query_start_loc=emlx.build_query_start_loc(qlens))
+        _, kc, vc, resolved = cache.concatenate_to_cache(dev(x["q"]), dev(x["k"]), dev(x["v"]), cache_metadata=meta,
+                                                         slot_ids=x["slot_ids"].tolist(), query_lens=qlens)
+        cache.check()
+        assert int(cache.ticket.item()) == 0
+        results.append((_snapshot(cache), resolved, cache))
+    (a, ma, ca), (b, mb_, _) = results
+    for u, w in zip(a, b):
+        assert torch.equal(u, w)
+    for field in ("query_start_loc", "block_tables", "kv_lens"):
+        assert torch.equal(getattr(ma, field), getattr(mb_, field)), field
+    m = kv_write.batch_metadata(x["query_lens"], x["slot_ids"], x["block_tables"], x["kv_lens"], bs)
+    np.testing.assert_array_equal(ca.kv_lens.cpu().numpy(), m["kv_lens_all"])
+    np.testing.assert_array_equal(ma.query_start_loc.cpu().numpy(), m["query_start_loc"])
+    if bs == 128 and d in (64, 128) and x["q"].dtype == np.float16:
+        extra = dict(k_scale=ca.k_scales, v_scale=ca.v_scales, k_bias=ca.k_biases, v_bias=ca.v_biases) if bits else {}
+        args = (dev(x["q"]), ca.key_cache, ca.value_cache, ma.block_tables, ma.kv_lens, ma.query_start_loc)
+        with_plan = emlx.paged_attention(*args, max_query_len=int(max(qlens)), plan=ma.plan, **extra)
+        own_plan = emlx.paged_attention(*args, max_query_len=int(max(qlens)), **extra)
+        assert torch.equal(with_plan, own_plan)
+
+
+def test_single_launch_step_reports_a_token_count_that_does_not_match():
+    import easymlx_b200 as emlx
+
+    cache = emlx.PageCacheView.init(num_seqs=2, max_seq_len=256, num_kv_heads=2, head_dim=64, block_size=128)
+    k = torch.zeros((5, 2, 64), dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="query_lens"):
+        cache.concatenate_to_cache(k.repeat(1, 2, 1), k, k, cache_metadata=emlx.PageMetadata(
+            query_start_loc=emlx.build_query_start_loc([2, 2])), slot_ids=[0, 1], query_lens=[2, 2])
