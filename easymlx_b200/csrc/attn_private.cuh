@@ -218,7 +218,7 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
             if (p.trace && tid == 0 && it == 0) {
                 long long now;
                 asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-                p.trace[1024 + 4 * blockIdx.x + 1] = now;
+                p.trace[2048 + 4 * blockIdx.x + 1] = now;
             }
 #endif
 #ifdef EMLX_EXPERIMENT_STREAM_ONLY  // measurement aid: consume the tiles without any arithmetic

@@ -1022,7 +1022,7 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
     if (p.trace && threadIdx.x == 0) {
         long long now;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
-        p.trace[1024 + 4 * blockIdx.x + 0] = now;
+        p.trace[2048 + 4 * blockIdx.x + 0] = now;
     }
 #endif
     const int num_units = p.hdr[0];

@@ -238,6 +238,9 @@ class AttentionCall:
             rc = lib.emlx_read_status(nv.ptr(self.status), nv.stream_ptr(self.device))
             if rc != nv.EMLX_OK:
                 self.status.zero_()  # report once
+                ws = getattr(self, "workspace", None)
+                if ws is not None:
+                    ws.zero_()  # a wait that gave up may have left split-KV arrival counters set
             nv.check(rc)
         return self.out
 
