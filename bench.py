@@ -316,17 +316,19 @@ class Bench:
         return float(t.item())
 
     # ------------------------------------------------------------------ one workload on this rank
-    def measure(self, w, label, *, after_step=None, parts=True, e2e=True):
+    def measure(self, w, label, *, after_step=None, gather_target=None, parts=True, e2e=True):
         """Step time (device-resident), end-to-end step time and the attention launch alone for workload `w`.
-        `after_step(out)` runs inside every step (the KV-head shard's all-gather)."""
+        `after_step(out)` runs after every step (the KV-head shard's NCCL all-gather; one step per graph then, so that
+        every step pays for its collective); `gather_target` makes the attention kernels store their heads into every
+        rank's output instead (the step's output is then the gathered one)."""
         import easymlx_b200 as emlx
         from easymlx_b200 import _native as nv
         from easymlx_b200.operations.kernels.unified_attention import AttentionCall
         from easymlx_b200.runtime import AttentionStep
 
         torch, args, dev = self.torch, self.args, self.dev
-        layers = _layers_per_graph(args)
-        step = AttentionStep(w.cache, w.q, w.k, w.v, w.qlens.tolist(), w.slot_ids)
+        layers = 1 if after_step is not None else _layers_per_graph(args)
+        step = AttentionStep(w.cache, w.q, w.k, w.v, w.qlens.tolist(), w.slot_ids, gather=gather_target)
 
         def one_step():
             out = step.step()
@@ -339,6 +341,8 @@ class Bench:
         torch.cuda.synchronize()
         if not args.no_graph:
             step.capture(warmup=2, steps_per_graph=layers)
+        if gather_target is not None:
+            self.barrier()  # ranks wait for one another inside these kernels: start the replays together
         for _ in range(max(3, args.warmup)):
             one_step()
         torch.cuda.synchronize()
@@ -349,8 +353,9 @@ class Bench:
                 ms_total = self.timed(one_step, args.steps // layers)
                 # the timed region lasts a few milliseconds, shorter than nvidia-smi's sampling period: the same step
                 # keeps replaying (untimed) for a moment so that the clock record holds samples under this load
-                t_end = time.perf_counter() + 0.35
-                while time.perf_counter() < t_end:
+                # (a count, not a deadline: `ms_total` is the maximum over ranks, so every rank replays the same number
+                # of steps, which steps that hold a collective or wait for the other ranks need)
+                for _ in range(int(min(400, max(1, 350.0 / max(ms_total, 1e-3) * (args.steps // layers) / 20)))):
                     for _ in range(20):
                         one_step()
                     torch.cuda.synchronize()
@@ -358,7 +363,8 @@ class Bench:
             if not any(r in BAD_CLOCK_REASONS for r in clocks["reasons"]):
                 break
         ms_step = ms_total / args.steps
-        tokens_all = self.all_sum(w.attended_kv_tokens) if after_step is None else float(w.attended_kv_tokens)
+        sharded = after_step is not None or gather_target is not None   # every rank works on the same batch
+        tokens_all = float(w.attended_kv_tokens) if sharded else self.all_sum(w.attended_kv_tokens)
         result = {
             "label": label, "kv_format": _kv_format(w.bits), "us_per_batch": ms_step * 1e3,
             "value": tokens_all / (ms_step * 1e-3), "unit": UNIT,
@@ -376,8 +382,10 @@ class Bench:
             dqkv = torch.empty_like(hqkv, device=dev)
             dqkv.copy_(hqkv)
             dq, dk, dv = (v.view(t.shape) for v, t in zip(torch.split(dqkv, sizes), parts_qkv))
-            hout = torch.empty_like(w.q, device="cpu").pin_memory()
-            step1 = AttentionStep(w.cache, dq, dk, dv, w.qlens.tolist(), w.slot_ids).capture(warmup=2)
+            step1 = AttentionStep(w.cache, dq, dk, dv, w.qlens.tolist(), w.slot_ids, gather=gather_target).capture(warmup=2)
+            hout = torch.empty_like(step1.out, device="cpu").pin_memory()
+            if gather_target is not None:
+                self.barrier()
 
             def e2e_step():
                 dqkv.copy_(hqkv, non_blocking=True)
@@ -555,9 +563,32 @@ def run_ours(args):
                     print(f"c4: the gathered shards differ from the unsharded output: {parity}", file=sys.stderr, flush=True)
                 ref_w = ref = None
                 torch.cuda.empty_cache()
-            r = bench.measure(wl, f"c4: KV heads sharded over {world} GPUs + NCCL all-gather of the outputs",
+            r = bench.measure(wl, f"c4: KV heads sharded over {world} GPUs + NCCL all-gather of the outputs after every step",
                               after_step=gather, parts=False)
+            # the same step with the gather done by the attention kernels: every rank's heads are stored into every
+            # rank's output through peer-mapped memory (no collective call)
+            try:
+                from easymlx_b200.distributed import PeerGather
+                peers = PeerGather(int(wl.total_tokens), whole.hq, whole.d, wl.q.dtype, dev, poll_limit=1 << 24)
+            except Exception as exc:  # the ranks fail together (see PeerGather)
+                peers, peer_store = None, {"unavailable": str(exc)[:300]}
+            if peers is not None:
+                got = AttentionStep(wl.cache, wl.q, wl.k, wl.v, wl.qlens.tolist(), wl.slot_ids, gather=peers.target)._eager()
+                torch.cuda.synchronize()
+                same = torch.tensor([int(torch.equal(got, full))], device=dev)
+                dist.all_reduce(same, op=dist.ReduceOp.MIN)
+                rp = bench.measure(wl, f"c4: KV heads sharded over {world} GPUs, heads stored into every rank's output "
+                                       "by the attention kernels (peer-mapped memory, no collective call)",
+                                   gather_target=peers.target, parts=False)
+                from easymlx_b200.operations.kernels import unified_attention as ua
+                status = max(int(t.view(torch.int32)[0].item()) for k, t in ua._scratch.buffers.items() if k[2] == "status")
+                peer_store = {"us_per_batch": rp["us_per_batch"], "value": rp["value"], "unit": UNIT,
+                              "e2e_us_per_batch": rp["e2e"]["us_per_batch"], "clocks": rp["clocks"],
+                              "gpu_launches_per_step": rp["gpu_launches_per_step"],
+                              "identical_to_all_gather_on_every_rank": bool(same.item()), "device_status": status}
+                peers.close()
             r["scaling"] = "strong"
+            r["peer_store"] = peer_store
             r["attn_us"] = r["roofline"]["us_per_launch"]
             dummy = wl.q.clone()
             r["allgather_us"] = bench.graph_time(lambda: gather(dummy), 10, args.steps) * 1e3

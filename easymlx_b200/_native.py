@@ -76,6 +76,12 @@ SIGNATURES = {
     "emlx_selftest_wait_timeout": (C.c_int, [_P, C.c_uint32, _P]),
     "emlx_attn_decode_static": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
     "emlx_attn_row_class": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32]),
+    "emlx_peer_buffer_create": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), _P]),
+    "emlx_peer_buffer_open": (C.c_int, [_P, C.POINTER(C.c_void_p)]),
+    "emlx_peer_buffer_close": (C.c_int, [_P]),
+    "emlx_peer_buffer_free": (C.c_int, [_P]),
+    "emlx_gather_init": (C.c_int, [_P, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _I32, _I32, _I32, _P]),
+    "emlx_attn_decode_gather": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P, _I32, _I32, _P]),
     "emlx_gather_last_tokens": (C.c_int, [_P, C.c_int32, C.c_int64, _P, C.c_int32, _P, _P, _P]),
     "emlx_pad_token_ids": (C.c_int, [_P, C.c_int32, _P, C.c_int32, C.c_int32, _P, _P]),
     "emlx_page_staging_bytes": (C.c_int64, [C.POINTER(Pool)]),
@@ -114,11 +120,15 @@ def lib() -> C.CDLL:
     return _lib
 
 
+def last_error() -> str:
+    return (lib().emlx_last_error() or b"unknown error").decode(errors="replace")
+
+
 def check(rc: int) -> None:
     """Turn a status code into the exception the reference would raise for the same fault."""
     if rc == EMLX_OK:
         return
-    msg = (lib().emlx_last_error() or b"").decode(errors="replace")
+    msg = last_error()
     if rc == EMLX_ERR_INVALID:
         raise ValueError(msg)
     if rc == EMLX_ERR_UNSUPPORTED:

@@ -38,7 +38,7 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
     sources = sorted(glob.glob(os.path.join(CSRC, "*.cu")))
     headers = glob.glob(os.path.join(CSRC, "*.cuh")) + glob.glob(os.path.join(INCLUDE, "*.h"))
     newest_header = max(os.path.getmtime(h) for h in headers)
-    objects, rebuilt = [], False
+    objects, jobs = [], []
     for src in sources:
         obj = os.path.join(LIB_DIR, os.path.basename(src)[:-3] + ".o")
         objects.append(obj)
@@ -48,10 +48,20 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
         cmd = [_nvcc(), *NVCC_FLAGS, *os.environ.get("EMLX_NVCC_EXTRA", "").split(), "-I", INCLUDE, "-c", src, "-o", obj]
         if ptxas_info:
             cmd += ["-Xptxas", "-v"]
+        jobs.append(cmd)
+    rebuilt = bool(jobs)
+
+    def compile_one(cmd):
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
-        rebuilt = True
+
+    # the files are independent; the largest one (the tiled attention kernels, two variants of 36 instances) sets the time
+    workers = max(1, min(len(jobs), os.cpu_count() or 1, 8))
+    if jobs:
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(workers) as pool:
+            list(pool.map(compile_one, jobs))
     if rebuilt or not os.path.exists(LIB):
         cmd = [_nvcc(), "-shared", "-o", LIB, *objects]
         if verbose:

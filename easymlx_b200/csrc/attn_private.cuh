@@ -13,6 +13,13 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t v) {
     asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
     return r;
 }
+// the final merge of a unit shared by the consumer warps (see MergeJob)
+constexpr int kHelpParts = 128;  // longest list of parts the job area holds
+constexpr int kHelpMinParts = 6; // below this the one-warp fold is as fast
+constexpr int kMiscHelpExit = 8; // misc[]: the merge warp has left, parked warps may go
+template <int D, int NT, int FMT, bool BF16, bool PEER>
+__device__ __forceinline__ void park_consumer_warp(const TiledParams& p, uint8_t* fixed, uint64_t* full,
+                                                   volatile int* abort_word);
 template <bool BF16> __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     uint32_t r;
     if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
@@ -29,7 +36,7 @@ __device__ __forceinline__ float2 h2_to_f2(uint32_t v) {
     return __half22float2(*reinterpret_cast<const __half2*>(&v));
 }
 
-template <int D, int NT, int FMT, bool BF16>
+template <int D, int NT, int FMT, bool BF16, bool PEER, bool HELP>
 __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint8_t* stages, uint8_t* fixed,
                                                       uint64_t* full, uint64_t* empty, volatile int* abort_word,
                                                       long long f_begin, long long f_end, long long total_flat,
@@ -45,6 +52,7 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
     float* wl = wm + kConsumerWarps * 32;             // [warps][32] per-warp running sum
     float* wb = wl + kConsumerWarps * 32;             // [2][warps][32] per-warp bias terms of the values
     int* misc = (int*)(fixed + C::OFF_MISC);
+    bool peer_seen = false;
     uint64_t* dfull = full + 16;
     uint64_t* dempty = full + 20;
 
@@ -79,6 +87,7 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
     long long remaining = f_end - f_begin;  // the producer decides the order of the parts; only their total is fixed
     uint32_t it = 0, part_idx = 0;
     int posted = 0;
+    bool may_help = false;  // uniform over the CTA's consumer warps
 
     while (remaining > 0) {
         // ------------------------------------------------------------------ part descriptor from the producer
@@ -521,7 +530,7 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                         uint2 packed;
                         packed.x = pack2<BF16>(acc.x * inv, acc.y * inv);
                         packed.y = pack2<BF16>(acc.z * inv, acc.w * inv);
-                        *(uint2*)((uint16_t*)p.out + ((long long)(qs + i) * p.Hq + head * p.G + hh) * D + d) = packed;
+                        store_out(p, out_offset<D>(p, qs + i, head * p.G + hh) + d, packed);
                     }
                 } else {
                     *(float4*)(slot + row * D + d) = acc;
@@ -531,6 +540,12 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
                     }
                 }
             }
+        }
+        if (PEER && complete) {  // gathering call: the rows just stored go to the other ranks as well
+            consumer_sync();
+            peer_ready(p, peer_seen, misc);
+            peer_copy_rows<D>((uint16_t*)p.out, p.peer, p.out_Hq, p.out_head0, p.G, qs, head, row0, min(row0 + ROWS, R),
+                              tid, kConsumerThreads);
         }
         if (!complete) {
             // hand the part to the merge warp: the request, then one arrival per warp after its slot stores
@@ -542,6 +557,8 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
             __syncwarp();
             if (lane == 0 && posted < 2) ptx::mbar_arrive(&mfull[posted]);
             ++posted;
+            // a unit far longer than this CTA's slice is shared by many CTAs: worth staying for its final merge
+            if (HELP && (long long)ntiles >= (kHelpMinParts - 1) * (f_end - f_begin)) may_help = true;
         }
 #ifdef EMLX_TRACE_PARTS
         if (p.trace && tid == 0 && part_idx < 16) {
@@ -561,18 +578,127 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&mfull[posted]);
     }
+    if constexpr (HELP) {
+        if (may_help) park_consumer_warp<D, NT, FMT, BF16, PEER>(p, fixed, full, abort_word);
+    }
+}
+
+// ---- the final merge of a unit, shared by the consumer warps --------------------------------------------------
+// A unit that is split over many CTAs (a few long sequences on the whole GPU) ends with one warp folding all its
+// parts: every part costs a round trip to L2 and a warp can keep only a few kilobytes in flight, so eighteen parts
+// took about 16 us at the very end of the kernel.  Consumer warps that have finished their slice therefore park
+// instead of leaving; when the merge warp finds all eight parked it computes the weights of the parts, writes them
+// and the parts' addresses to shared memory and lets every warp fold one or two rows with all its loads in flight.
+// The arithmetic (weights, order of the parts, denominators) is that of the one-warp path, so the result does not
+// depend on which path a launch happened to take.
+template <int ROWS>
+struct MergeJob {
+    int nparts, rows_here, pad0, pad1;
+    MergeRequest rq;
+    float den[16];
+    unsigned long long slot[kHelpParts];  // partial rows of part j (0: that slice holds no tiles)
+    float w[kHelpParts][ROWS];            // weight of part j for row r
+    float l[kHelpParts][ROWS];            // sum of part j for row r
+};
+
+template <int D, int NT, int FMT, bool BF16, bool PEER>
+__device__ __forceinline__ void help_merge(const TiledParams& p, const MergeJob<Cfg<D, NT, FMT>::ROWS>* job, int warp, int lane) {
+    constexpr int ROWS = Cfg<D, NT, FMT>::ROWS, V = D / 32, B = 8;
+    const int nparts = job->nparts;
+    const MergeRequest rq = job->rq;
+    for (int row = warp; row < ROWS; row += kConsumerWarps) {
+        const int r = rq.row0 + row;
+        if (r >= rq.rows) continue;
+        float acc[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) acc[k] = 0.f;
+        for (int j0 = 0; j0 < nparts; j0 += B) {
+            float wr[B], v[B][V];
+#pragma unroll
+            for (int u = 0; u < B; ++u) {
+                const int j = j0 + u;
+                const float* sl = j < nparts ? (const float*)job->slot[j] : nullptr;
+                wr[u] = sl ? job->w[j][row] : 0.f;
+                if constexpr (V == 4) {
+                    const float4 x = sl ? __ldcg((const float4*)(sl + row * D) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    v[u][0] = x.x; v[u][1] = x.y; v[u][2] = x.z; v[u][3] = x.w;
+                } else {
+                    const float2 x = sl ? __ldcg((const float2*)(sl + row * D) + lane) : make_float2(0.f, 0.f);
+                    v[u][0] = x.x; v[u][1] = x.y;
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < B; ++u)
+                if (wr[u] != 0.f) {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) acc[k] = fmaf(wr[u], v[u][k], acc[k]);
+                }
+        }
+        const float dr = job->den[row];
+        const int i = r / p.G, hh = r - i * p.G;
+        const long long dst = out_offset<D>(p, rq.qs + i, rq.head * p.G + hh) + V * lane;
+        float o[V];
+#pragma unroll
+        for (int k = 0; k < V; ++k) o[k] = dr > 0.f ? acc[k] / dr : 0.f;
+        if constexpr (V == 4) {
+            uint2 packed;
+            packed.x = pack2<BF16>(o[0], o[1]);
+            packed.y = pack2<BF16>(o[2], o[3]);
+            store_out(p, dst, packed);
+        } else {
+            store_out(p, dst, pack2<BF16>(o[0], o[1]));
+        }
+        if constexpr (PEER) {  // the merge warp has seen the other ranks' ready flags before it handed out the job
+            __syncwarp();
+            peer_copy_rows<D>((uint16_t*)p.out, p.peer, p.out_Hq, p.out_head0, p.G, rq.qs, rq.head, r, r + 1, lane, 32);
+        }
+    }
+}
+
+// Consumer warps that have finished their slice: wait for jobs of the merge warp until it says that it has left.
+template <int D, int NT, int FMT, bool BF16, bool PEER>
+__device__ __forceinline__ void park_consumer_warp(const TiledParams& p, uint8_t* fixed, uint64_t* full,
+                                                   volatile int* abort_word) {
+    using C = Cfg<D, NT, FMT>;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint64_t *parked = full + 26, *go = full + 27, *done = full + 28;
+    volatile int* misc = (volatile int*)(fixed + C::OFF_MISC);
+    if (*abort_word) return;
+    __syncwarp();
+    if (lane == 0) ptx::mbar_arrive(parked);
+    for (uint32_t job_idx = 0;; ++job_idx) {
+        int ok = 0;
+        if (lane == 0) {
+            for (uint32_t i = 0; i < (1u << 22) && !ok && !*abort_word; ++i) {
+                ok = ptx::mbar_try_wait(go, job_idx & 1) ? 1 : 0;
+                if (!ok) __nanosleep(i < 4096 ? 32 : 500);
+            }
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) {
+            if (!*abort_word) *abort_word = 1;
+            return;
+        }
+        if (misc[kMiscHelpExit]) return;
+        help_merge<D, NT, FMT, BF16, PEER>(p, (const MergeJob<C::ROWS>*)(fixed + C::PBYTES), warp, lane);
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(done);
+    }
 }
 
 // The merge warp.  For every unfinished part the consumers hand over: make the slot visible to the GPU, count the
 // arrival on the (unit, head) counter, and when this was the last of the unit's parts, fold all of them in slice
 // order (so the result does not depend on which CTA came last) and write the rows.
-template <int D, int NT, int FMT, bool BF16>
+template <int D, int NT, int FMT, bool BF16, bool PEER, bool HELP>
 __device__ __forceinline__ void merge_warp_loop(const TiledParams& p, uint8_t* fixed, uint64_t* full,
                                                 volatile int* abort_word, int active) {
     using C = Cfg<D, NT, FMT>;
     constexpr int ROWS = C::ROWS;
     const int lane = threadIdx.x & 31;
     uint64_t* mfull = full + 24;
+    bool peer_seen = false;
+    uint32_t jobs_posted = 0;  // final merges handed to the parked consumer warps
+    if constexpr (PEER) peer_ready(p, peer_seen, (const int*)(fixed + C::OFF_MISC));  // while the consumers work: off the path of the merge
     for (int e = 0; e < 2; ++e) {
         // the consumers may take their whole slice before they post: sleep between polls, give up after seconds
         int ok = 0;
@@ -602,24 +728,129 @@ __device__ __forceinline__ void merge_warp_loop(const TiledParams& p, uint8_t* f
         ticket = __shfl_sync(0xffffffffu, ticket, 0);
         if (ticket != nparts - 1) continue;
         __threadfence();
-        // Lane r < ROWS first folds the parts' (max, sum) pairs of row r, so that the loads of the partial rows
-        // below depend on nothing but addresses and all of them can be in flight together.
+#ifdef EMLX_TRACE_TIMELINE
+        if (p.trace && lane == 0) {
+            long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            p.trace[2048 + 4 * blockIdx.x + 2] = now;
+        }
+#endif
+        const int span = c_last - c_first + 1;
+        int all_parked = 0;
+        if (HELP && span >= kHelpMinParts && span <= kHelpParts) {
+            if (lane == 0) all_parked = ptx::mbar_try_wait(full + 26, 0) ? 1 : 0;
+            all_parked = __shfl_sync(0xffffffffu, all_parked, 0);
+        }
+        if (HELP && all_parked) {
+            // the consumer warps fold the rows; this warp prepares what they need (lane j looks at part base + j)
+            MergeJob<ROWS>* job = (MergeJob<ROWS>*)(fixed + C::PBYTES);
+            static_assert(sizeof(MergeJob<ROWS>) <= (size_t)C::OREDBYTES, "the job does not fit the reduction scratch");
+            float Mr[ROWS];
+#pragma unroll
+            for (int row = 0; row < ROWS; ++row) Mr[row] = -INFINITY;
+            for (int base = 0; base < span; base += 32) {
+                const int c = c_first + base + lane;
+                unsigned long long mine = 0;
+                if (c <= c_last) {
+                    const long long cb = p.cta_start[c];
+                    if (cb < p.cta_start[c + 1])
+                        mine = (unsigned long long)(p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats);
+                    job->slot[base + lane] = mine;
+                }
+                const float* sl = (const float*)mine;
+                float mp[ROWS], lp[ROWS];
+#pragma unroll
+                for (int row = 0; row < ROWS; ++row) {
+                    mp[row] = sl ? __ldcg(sl + ROWS * D + row) : -INFINITY;
+                    lp[row] = sl ? __ldcg(sl + ROWS * D + ROWS + row) : 0.f;
+                }
+#pragma unroll
+                for (int row = 0; row < ROWS; ++row) {
+                    Mr[row] = fmaxf(Mr[row], warp_max(lp[row] > 0.f ? mp[row] : -INFINITY));
+                    if (c <= c_last) {
+                        job->w[base + lane][row] = mp[row];  // the maximum for now; the weight once M is known
+                        job->l[base + lane][row] = lp[row];
+                    }
+                }
+            }
+            __syncwarp();
+            for (int j = lane; j < span; j += 32)
+#pragma unroll
+                for (int row = 0; row < ROWS; ++row) {
+                    const float lp = job->l[j][row];
+                    job->w[j][row] = lp > 0.f ? ex2(job->w[j][row] - Mr[row]) : 0.f;
+                }
+            __syncwarp();
+            if (lane < ROWS) {
+                float den = 0.f;
+                for (int j = 0; j < span; ++j)
+                    if (job->slot[j]) den = fmaf(job->w[j][lane], job->l[j][lane], den);
+                job->den[lane] = den;
+            }
+            if (lane == 0) {
+                job->nparts = span;
+                job->rows_here = min(ROWS, rq.rows - rq.row0);
+                job->rq = rq;
+            }
+            __syncwarp();
+            int ok = 0;
+            if (lane == 0) {
+                ptx::mbar_arrive(full + 27);
+                for (uint32_t i = 0; i < (1u << 22) && !ok && !*abort_word; ++i) {
+                    ok = ptx::mbar_try_wait(full + 28, jobs_posted & 1) ? 1 : 0;
+                    if (!ok) __nanosleep(i < 256 ? 50 : 2000);
+                }
+            }
+            ++jobs_posted;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) {
+                if (!*abort_word) *abort_word = 1;
+                if (lane == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
+                return;
+            }
+            if (lane == 0) *counter = 0;
+            continue;
+        }
+        // Lane r < ROWS folds the parts' (max, sum) pairs of row r; lane l folds head_dim elements [V*l, V*l + V) of
+        // every row: one vector load per row and part, one vector store per row.
         const int rows_here = min(ROWS, rq.rows - rq.row0);
         const int lrow = lane < ROWS ? lane : 0;
-        float M = -INFINITY;
-        for (int c = c_first; c <= c_last; ++c) {
-            const long long cb = p.cta_start[c];
-            if (cb >= p.cta_start[c + 1]) continue;
-            const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
-            const float mp = __ldcg(sl + ROWS * D + lrow), lp = __ldcg(sl + ROWS * D + ROWS + lrow);
-            if (lp > 0.f) M = fmaxf(M, mp);
-        }
-        float acc[ROWS][D / 32], den = 0.f;
+        constexpr int V = D / 32;
+        float acc[ROWS][V], den = 0.f, M = -INFINITY;
 #pragma unroll
         for (int row = 0; row < ROWS; ++row)
 #pragma unroll
-            for (int k = 0; k < D / 32; ++k) acc[row][k] = 0.f;
+            for (int k = 0; k < V; ++k) acc[row][k] = 0.f;
+        auto load_rows = [&](const float* sl, float (&v)[ROWS][V]) {
+#pragma unroll
+            for (int row = 0; row < ROWS; ++row) {
+                if constexpr (V == 4) {
+                    const float4 x = (sl && row < rows_here) ? __ldcg((const float4*)(sl + row * D) + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+                    v[row][0] = x.x; v[row][1] = x.y; v[row][2] = x.z; v[row][3] = x.w;
+                } else {
+                    const float2 x = (sl && row < rows_here) ? __ldcg((const float2*)(sl + row * D) + lane) : make_float2(0.f, 0.f);
+                    v[row][0] = x.x; v[row][1] = x.y;
+                }
+            }
+        };
+        auto fold = [&](float wgt, const float (&v)[ROWS][V]) {
+#pragma unroll
+            for (int row = 0; row < ROWS; ++row) {
+                const float wr = __shfl_sync(0xffffffffu, wgt, row);
+                if (wr != 0.f) {
+#pragma unroll
+                    for (int k = 0; k < V; ++k) acc[row][k] = fmaf(wr, v[row][k], acc[row][k]);
+                }
+            }
+        };
         {
+            for (int c = c_first; c <= c_last; ++c) {
+                const long long cb = p.cta_start[c];
+                if (cb >= p.cta_start[c + 1]) continue;
+                const float* sl = p.slots + ((size_t)c * 2 + (max(a_flat, cb) != cb ? 1 : 0)) * kSlotFloats;
+                const float mp = __ldcg(sl + ROWS * D + lrow), lp = __ldcg(sl + ROWS * D + ROWS + lrow);
+                if (lp > 0.f) M = fmaxf(M, mp);
+            }
 #pragma unroll 1
             for (int c = c_first; c <= c_last; ++c) {
                 const long long cb = p.cta_start[c];
@@ -628,19 +859,9 @@ __device__ __forceinline__ void merge_warp_loop(const TiledParams& p, uint8_t* f
                 const float mp = __ldcg(sl + ROWS * D + lrow), lp = __ldcg(sl + ROWS * D + ROWS + lrow);
                 const float wgt = lp > 0.f ? ex2(mp - M) : 0.f;
                 den = fmaf(wgt, lp, den);
-                float v[ROWS][D / 32];
-#pragma unroll
-                for (int row = 0; row < ROWS; ++row)
-#pragma unroll
-                    for (int k = 0; k < D / 32; ++k) v[row][k] = row < rows_here ? __ldcg(sl + row * D + 32 * k + lane) : 0.f;
-#pragma unroll
-                for (int row = 0; row < ROWS; ++row) {
-                    const float wr = __shfl_sync(0xffffffffu, wgt, row);
-                    if (wr != 0.f) {
-#pragma unroll
-                        for (int k = 0; k < D / 32; ++k) acc[row][k] = fmaf(wr, v[row][k], acc[row][k]);
-                    }
-                }
+                float v[ROWS][V];
+                load_rows(sl, v);
+                fold(wgt, v);
             }
         }
 #pragma unroll
@@ -649,12 +870,33 @@ __device__ __forceinline__ void merge_warp_loop(const TiledParams& p, uint8_t* f
             const int r = rq.row0 + row;
             if (r < rq.rows) {
                 const int i = r / p.G, hh = r - i * p.G;
-                uint16_t* dst = (uint16_t*)p.out + ((long long)(rq.qs + i) * p.Hq + rq.head * p.G + hh) * D;
+                const long long dst = out_offset<D>(p, rq.qs + i, rq.head * p.G + hh) + V * lane;
+                float o[V];
 #pragma unroll
-                for (int k = 0; k < D / 32; ++k) dst[32 * k + lane] = to_bits16<BF16>(dr > 0.f ? acc[row][k] / dr : 0.f);
+                for (int k = 0; k < V; ++k) o[k] = dr > 0.f ? acc[row][k] / dr : 0.f;
+                if constexpr (V == 4) {
+                    uint2 packed;
+                    packed.x = pack2<BF16>(o[0], o[1]);
+                    packed.y = pack2<BF16>(o[2], o[3]);
+                    store_out(p, dst, packed);
+                } else {
+                    store_out(p, dst, pack2<BF16>(o[0], o[1]));
+                }
             }
         }
+        if constexpr (PEER) {
+            __syncwarp();
+            peer_copy_rows<D>((uint16_t*)p.out, p.peer, p.out_Hq, p.out_head0, p.G, rq.qs, rq.head, rq.row0,
+                              min(rq.row0 + ROWS, rq.rows), lane, 32);
+        }
         if (lane == 0) *counter = 0;
+#ifdef EMLX_TRACE_TIMELINE
+        if (p.trace && lane == 0) {
+            long long now;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+            p.trace[2048 + 4 * blockIdx.x + 3] = now;
+        }
+#endif
     }
 }
 

@@ -11,6 +11,7 @@
 // so that one page read serves every query row of its KV head.  A slice that ends inside a
 // (unit, head) writes an un-normalised partial; the CTA that delivers the last partial merges all of
 // them in CTA order (deterministic), so no CTA ever waits for another.
+#include "peer.cuh"
 #include "plan_device.cuh"
 #include "ptx.cuh"
 #include "tensor_maps.cuh"
@@ -55,7 +56,126 @@ struct TiledParams {
     int Hq, Hkv, G, MB, window;
     int bs, ppt_log;  // page size in tokens and log2(pages per 128-token tile)
     float scale_log2e;
+    // where the rows go: `out` holds out_Hq heads per token and this call writes heads [out_head0, out_head0 + Hq).
+    // A gathering call (KV heads sharded over GPUs) also stores every row into the other ranks' buffers.
+    int out_Hq, out_head0;
+    const PeerTable* peer;  // nullptr for an ordinary call
+    int32_t* peer_flags;    // this rank's flag block
+    int peer_phase;         // kPeerFirstLaunch | kPeerLastLaunch
+    int few_units;          // host's guess that units span many CTAs (few sequences): selects the kernel build
 };
+
+// Element offset of (token, local head) in the output buffer.
+template <int D>
+__device__ __forceinline__ long long out_offset(const TiledParams& p, long long token, int head_local) {
+    return (token * p.out_Hq + p.out_head0 + head_local) * D;
+}
+
+// Stores `v` at element offset `off` of this rank's output.
+template <typename V>
+__device__ __forceinline__ void store_out(const TiledParams& p, long long off, V v) {
+    *(V*)((uint16_t*)p.out + off) = v;
+}
+
+// Gathering call: copies rows [r0, r1) of a sequence's (token, head) rows (row r = token r / G, head r % G of KV head
+// `head`) from this rank's output, where they have just been stored, into every other rank's.  Kept out of line and
+// out of the store loops: the kernels' hot paths are the same with and without a gather.  `t` of `nthreads` threads
+// share the work; the caller makes the local rows visible to them first (a barrier or __syncwarp).
+template <int D>
+__device__ __noinline__ void peer_copy_rows(uint16_t* out, const PeerTable* table, int out_Hq, int out_head0, int G,
+                                            int qs, int head, int r0, int r1, int t, int nthreads) {
+    constexpr int CH = D / 8;  // 16-byte pieces per row
+    const int n = table->num_ranks, me = table->rank;
+    for (int idx = t; idx < (r1 - r0) * CH; idx += nthreads) {
+        const int r = r0 + idx / CH, ch = idx % CH;
+        const int i = r / G, hh = r - i * G;
+        const long long off = ((long long)(qs + i) * out_Hq + out_head0 + head * G + hh) * D + ch * 8;
+        const uint4 v = __ldcg((const uint4*)(out + off));
+        for (int rank = 0; rank < n; ++rank)
+            if (rank != me) *(uint4*)((uint16_t*)table->out[rank] + off) = v;
+    }
+}
+
+// What a CTA of a gathering call keeps in shared memory (filled once after the wait on the predecessors), so that
+// the end of the kernel does not chain cold loads of the table behind its last atomic.
+struct PeerCache {
+    int32_t* flags[kMaxPeers];  // at Cfg::OFF_PEER
+};
+constexpr int kMiscExit = 2;    // misc[]: warps of the CTA that have finished
+constexpr int kMiscEpoch = 4;   // this call's epoch
+constexpr int kMiscRanks = 5, kMiscRank = 6, kMiscPoll = 7;
+
+// Before a warp's first remote store of a gathering call: every other rank has said that its output buffer may be
+// overwritten (lane r polls rank r's flag; the flags only grow, so later calls return at once).
+__device__ __forceinline__ void peer_ready(const TiledParams& p, bool& seen, const int* misc) {
+    if (!p.peer || seen) return;
+    seen = true;
+    if (!(p.peer_phase & kPeerFirstLaunch)) return;  // a later kernel of the call: the first one has waited
+    const int lane = threadIdx.x & 31;
+    bool ok = true;
+    if (lane < misc[kMiscRanks] && lane != misc[kMiscRank])
+        ok = peer_wait(p.peer_flags + kPeerReady + lane, misc[kMiscEpoch], misc[kMiscPoll]);
+    if (!ok) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
+    __syncwarp();
+}
+
+// Every warp of a gathering call passes here when it is done.  The last warp of a CTA orders the CTA's stores (remote
+// ones included) before its count at GPU scope; the last CTA of the kernel then sends the done flags with
+// system-scope release stores.  Fences are cumulative: everything that happened before the counts the last CTA
+// has observed is ordered before its flags, so one system-scope fence per kernel is enough (one per warp, thousands
+// at the end of a kernel, each waiting for the other GPUs' acknowledgements, cost tens of microseconds).
+// Out of line, like everything else of the gather: an ordinary call pays one predicate here.
+__device__ __noinline__ void peer_exit(int32_t* flags, int phase, int32_t* status, int* misc, const PeerCache* cache) {
+    __syncwarp();
+    const int lane = threadIdx.x & 31;
+    int last = 0;
+    if (lane == 0) {
+        __threadfence_block();  // this warp's stores are ordered before the count
+        if (atomicAdd_block(misc + kMiscExit, 1) == kThreads / 32 - 1) {
+            __threadfence();
+            last = atomicAdd(flags + kPeerTicket, 1) == (int)gridDim.x - 1 ? 1 : 0;
+            if (last) __threadfence();
+        }
+    }
+    last = __shfl_sync(0xffffffffu, last, 0);
+    __syncwarp();
+    if (!last) return;
+    const int n = misc[kMiscRanks], me = misc[kMiscRank], epoch = misc[kMiscEpoch];
+    if (phase & kPeerLastLaunch) {
+        bool ok = true;
+        if (lane < n && lane != me) {
+            st_release_sys(cache->flags[lane] + kPeerDone + me, epoch);
+            ok = peer_wait(flags + kPeerDone + lane, epoch, misc[kMiscPoll]);
+        }
+        if (!ok) flag_error(status, EMLX_DEV_WAIT_TIMEOUT);
+        __syncwarp();
+        if (lane == 0) flags[kPeerEpoch] = epoch;
+    }
+    if (lane == 0) flags[kPeerTicket] = 0;  // ready for the next kernel
+}
+__device__ __forceinline__ void peer_warp_exit(const TiledParams& p, int* misc, const PeerCache* cache) {
+    if (p.peer) peer_exit(p.peer_flags, p.peer_phase, p.status, misc, cache);
+}
+
+// Start of a gathering call's CTA (all its threads): the call's epoch and the table of the ranks go to shared memory,
+// and the first CTA of the call's first kernel tells the other ranks that this rank's output may be overwritten
+// (everything queued before the call on this rank's stream has finished).
+__device__ __noinline__ void peer_enter(const PeerTable* table, int32_t* flags, int phase, int* misc, PeerCache* cache) {
+    const int n = table->num_ranks, me = table->rank, epoch = flags[kPeerEpoch] + 1;
+    if ((int)threadIdx.x < n) {
+        int32_t* theirs = table->flags[threadIdx.x];
+        cache->flags[threadIdx.x] = theirs;
+        if ((phase & kPeerFirstLaunch) && blockIdx.x == 0 && (int)threadIdx.x != me)
+            st_release_sys(theirs + kPeerReady + me, epoch);
+    }
+    if (threadIdx.x == 0) {
+        misc[kMiscEpoch] = epoch;
+        misc[kMiscRanks] = n;
+        misc[kMiscRank] = me;
+        misc[kMiscPoll] = table->poll_limit;
+    }
+    __syncthreads();
+}
 
 template <int D, int NT, int FMT>
 struct Cfg {
@@ -85,7 +205,7 @@ struct Cfg {
     static constexpr int QSTRIDE = D * 2;
     static constexpr int NDESC = PRIVATE ? (NT == 1 ? 4 : 2) : 0;
     static constexpr int DESC_BYTES = PRIVATE ? 64 + ROWS * QSTRIDE : 0;
-    static constexpr int SMALL = 2 * 32 * 4 + 4 * kConsumerWarps * 32 * 4 + 64 + 256 + 128;  // row stats, per-warp stats, misc, barriers, requests
+    static constexpr int SMALL = 2 * 32 * 4 + 4 * kConsumerWarps * 32 * 4 + 64 + 256 + 128 + 64;  // row stats, per-warp stats, misc, barriers, requests, peer table
     static constexpr int red_bytes(int cols) { return kConsumerWarps * ROWS * (cols + 4) * 4; }
     static constexpr int stages_with(int fixed) { return (BUDGET - fixed) / STAGE > 8 ? 8 : (BUDGET - fixed) / STAGE; }
     static constexpr int PRIV_BASE = NDESC * DESC_BYTES + SMALL;
@@ -101,9 +221,10 @@ struct Cfg {
     static constexpr int OFF_SMALL = PBYTES + OREDBYTES;          // 64 floats of row statistics (tile max / merged max, sum)
     static constexpr int OFF_W = OFF_SMALL + 2 * 32 * 4;          // 4 x [warps][32] floats
     static constexpr int OFF_MISC = OFF_W + 4 * kConsumerWarps * 32 * 4;
-    static constexpr int OFF_BAR = OFF_MISC + 64;                 // full[8], empty[8], dfull[4], dempty[4], mfull[2]
+    static constexpr int OFF_BAR = OFF_MISC + 64;                 // full[8], empty[8], dfull[4], dempty[4], mfull[2], parked, go, done
     static constexpr int OFF_MAIL = OFF_BAR + 256;                // two split-merge requests
-    static constexpr int FIXED = OFF_MAIL + 128;
+    static constexpr int OFF_PEER = OFF_MAIL + 128;               // gathering calls: the ranks' flag blocks (8 pointers)
+    static constexpr int FIXED = OFF_PEER + 64;
     static constexpr int STAGES_RAW = (BUDGET - FIXED) / STAGE;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM = STAGES * STAGE + FIXED + 1024;
@@ -443,7 +564,7 @@ constexpr float kTwo24 = 16777216.0f;  // codes enter the MMA as fp16 subnormals
 constexpr float kWeightUp = 256.0f, kHalfMax = 65504.0f, kValueDown = kTwo24 / kWeightUp;
 __device__ __forceinline__ float weight_scale(float v_scale) { return fminf(v_scale * kWeightUp, kHalfMax); }
 
-template <int D, int NT, int FMT, bool BF16>
+template <int D, int NT, int FMT, bool BF16, bool PEER>
 __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* stages, uint8_t* fixed, uint64_t* full,
                                               uint64_t* empty, volatile int* abort_word, long long f_begin,
                                               long long f_end, int num_units, long long total_flat, long long active) {
@@ -461,6 +582,7 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
     float* wb = wl + kConsumerWarps * 32;  // [2][warps][32]
     int* misc = (int*)(fixed + C::OFF_MISC);
     const int ORD_NEG_INF = f2ord(-INFINITY);
+    bool peer_seen = false;
 
     Walk w;
     w.locate(f_begin, p.unit_cum, num_units, p.Hkv);
@@ -898,9 +1020,14 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
                 const int row = idx / CH, ch = idx - row * CH, r = row0 + row;
                 if (r < R) {
                     const int i = r / p.G, hh = r - i * p.G;
-                    uint16_t* dst = (uint16_t*)p.out + ((long long)(qs + i) * p.Hq + head * p.G + hh) * D + ch * 8;
-                    *(uint4*)dst = *(const uint4*)(Ps + row * kPStride + ch * 16);
+                    store_out(p, out_offset<D>(p, qs + i, head * p.G + hh) + ch * 8, *(const uint4*)(Ps + row * kPStride + ch * 16));
                 }
+            }
+            if constexpr (PEER) {
+                consumer_sync();
+                peer_ready(p, peer_seen, misc);
+                peer_copy_rows<D>((uint16_t*)p.out, p.peer, p.out_Hq, p.out_head0, p.G, qs, head, row0, min(row0 + ROWS, R),
+                                  tid, kConsumerThreads);
             }
         } else {
             // un-normalised partial into this CTA's slot; the CTA that delivers the last one merges
@@ -957,10 +1084,15 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
                         }
                     }
                     const int i = r / p.G, hh = r - i * p.G;
-                    ((uint16_t*)p.out)[((long long)(qs + i) * p.Hq + head * p.G + hh) * D + d] =
-                        to_bits16<BF16>(den > 0.f ? acc / den : 0.f);
+                    store_out(p, out_offset<D>(p, qs + i, head * p.G + hh) + d, to_bits16<BF16>(den > 0.f ? acc / den : 0.f));
                 }
                 if (tid == 0) *counter = 0;  // ready for the next launch
+                if constexpr (PEER) {  // uniform over the consumer warps (the ticket is shared)
+                    consumer_sync();
+                    peer_ready(p, peer_seen, misc);
+                    peer_copy_rows<D>((uint16_t*)p.out, p.peer, p.out_Hq, p.out_head0, p.G, qs, head, row0, min(row0 + ROWS, R),
+                                      tid, kConsumerThreads);
+                }
             }
         }
         consumer_sync();  // the P buffer and the reduction scratch are reused by the next part
@@ -976,7 +1108,7 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
 namespace emlx {
 
 // ------------------------------------------------------------------------------------------ kernel
-template <int D, int NT, int FMT, bool BF16>
+template <int D, int NT, int FMT, bool BF16, bool PEER, bool HELP>
 // 9 warps share four 16K-register sub-partitions: three warps on one of them caps a thread at 168 registers
 __global__ void __launch_bounds__(kThreads, Cfg<D, NT, FMT>::CTAS_PER_SM)
 attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const TiledParams p) {
@@ -1008,7 +1140,12 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
             ptx::mbar_init(&dempty[s], kConsumerWarps);
         }
         for (int s = 0; s < 2; ++s) ptx::mbar_init(&full[24 + s], kConsumerWarps);
+        ptx::mbar_init(&full[26], kConsumerWarps);  // consumer warps that have parked
+        ptx::mbar_init(&full[27], 1);               // a job (or the leave to go) from the merge warp
+        ptx::mbar_init(&full[28], kConsumerWarps);  // warps that have finished the job
+        ((int*)(fixed + C::OFF_MISC))[kMiscHelpExit] = 0;
         *abort_word = 0;
+        ((int*)(fixed + C::OFF_MISC))[kMiscExit] = 0;  // warps of this CTA that have finished (gathering calls)
         ptx::fence_barrier_init();
         ptx::prefetch_tensormap(&kmap);
         ptx::prefetch_tensormap(&vmap);
@@ -1025,25 +1162,41 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
         p.trace[2048 + 4 * blockIdx.x + 0] = now;
     }
 #endif
+    int* misc_words = (int*)(fixed + C::OFF_MISC);
+    const PeerCache* peer_cache = (const PeerCache*)(fixed + C::OFF_PEER);
+    if constexpr (PEER) peer_enter(p.peer, p.peer_flags, p.peer_phase, misc_words, (PeerCache*)(fixed + C::OFF_PEER));
     const int num_units = p.hdr[0];
     const long long total_flat = (long long)p.hdr[1] * p.Hkv;
     // every CTA takes the contiguous slice the plan cut for it; a CTA without tiles has nothing to do
     const long long f_begin = p.cta_start[blockIdx.x], f_end = p.cta_start[blockIdx.x + 1];
-    if (f_begin >= f_end) return;  // uniform for the CTA, and no thread waits on a barrier yet
+    if (f_begin >= f_end) {  // uniform for the CTA, and no thread waits on a barrier yet
+        if constexpr (PEER) peer_warp_exit(p, misc_words, peer_cache);
+        return;
+    }
     const long long active = gridDim.x;
 
     if (threadIdx.x >= kConsumerThreads + 32) {
-        if constexpr (C::PRIVATE) merge_warp_loop<D, NT, FMT, BF16>(p, fixed, full, abort_word, (int)active);
+        if constexpr (C::PRIVATE) {
+            merge_warp_loop<D, NT, FMT, BF16, PEER, HELP>(p, fixed, full, abort_word, (int)active);
+            // no further job: consumer warps that are parked, or park later, may leave
+            __syncwarp();
+            if ((threadIdx.x & 31) == 0) {
+                *(volatile int*)(misc_words + kMiscHelpExit) = 1;
+                ptx::mbar_arrive(&full[27]);
+            }
+        }
+        if constexpr (PEER) peer_warp_exit(p, misc_words, peer_cache);
         return;
     } else if (threadIdx.x >= kConsumerThreads) {
         producer_loop<D, NT, FMT>(&kmap, &vmap, p, smem, fixed, full, empty, abort_word, f_begin, f_end, num_units);
     } else {
         if constexpr (C::PRIVATE)
-            consumer_loop_private<D, NT, FMT, BF16>(p, smem, fixed, full, empty, abort_word, f_begin, f_end, total_flat, active);
+            consumer_loop_private<D, NT, FMT, BF16, PEER, HELP>(p, smem, fixed, full, empty, abort_word, f_begin, f_end, total_flat, active);
         else
-            consumer_loop<D, NT, FMT, BF16>(p, smem, fixed, full, empty, abort_word, f_begin, f_end, num_units, total_flat, active);
+            consumer_loop<D, NT, FMT, BF16, PEER>(p, smem, fixed, full, empty, abort_word, f_begin, f_end, num_units, total_flat, active);
     }
     if (*abort_word && threadIdx.x == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
+    if constexpr (PEER) peer_warp_exit(p, misc_words, peer_cache);
 #ifdef EMLX_TRACE
     if (p.trace && threadIdx.x == 0) {
         long long now;
@@ -1136,10 +1289,20 @@ int get_maps(const emlx_pool& pool, MapPair* out) {
 template <int D, int NT, int FMT, bool BF16>
 static int launch_one(const MapPair& maps, const TiledParams& p, int grid, cudaStream_t stream) {
     using C = Cfg<D, NT, FMT>;
-    auto kernel = attn_tiled_kernel<D, NT, FMT, BF16>;
-    static DeviceOnce configured;
-    EMLX_CUDA_OK(allow_dynamic_smem(kernel, C::SMEM, configured));
-    EMLX_CUDA_OK(launch_pdl(kernel, grid, kThreads, C::SMEM, stream, maps.k, maps.v, p));
+    // Three builds of the kernel.  Codes paths that an ordinary batch never takes still cost it a per cent or two
+    // when they sit in the same kernel (measured; the tile loop is the same, its scheduling is not): the final merge
+    // shared by the consumer warps is only built in for batches of few, long units, the gather only for gathering calls.
+    auto go = [&](auto kernel, DeviceOnce& configured) -> int {
+        EMLX_CUDA_OK(allow_dynamic_smem(kernel, C::SMEM, configured));
+        EMLX_CUDA_OK(launch_pdl(kernel, grid, kThreads, C::SMEM, stream, maps.k, maps.v, p));
+        return EMLX_OK;
+    };
+    static DeviceOnce once_plain, once_help, once_gather;
+    int rc;
+    if (p.peer) rc = go(attn_tiled_kernel<D, NT, FMT, BF16, true, true>, once_gather);
+    else if (p.few_units) rc = go(attn_tiled_kernel<D, NT, FMT, BF16, false, true>, once_help);
+    else rc = go(attn_tiled_kernel<D, NT, FMT, BF16, false, false>, once_plain);
+    if (rc) return rc;
     EMLX_LAUNCHED();
     return EMLX_OK;
 }
@@ -1179,7 +1342,14 @@ long long* trace_buffer() { return g_trace; }
 long long* trace_buffer() { return nullptr; }
 #endif
 
-static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* stream, int class_lo, int class_hi) {
+// A gathering call: the flag block of this rank and where its heads sit in the full output.
+struct GatherTarget {
+    void* flag_block;
+    int total_q_heads, head_offset;
+};
+
+static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* stream, int class_lo, int class_hi,
+                     const GatherTarget* gather = nullptr) {
     if (int rc = validate_attn(a, pool, true)) return rc;
     if (a->total_tokens == 0) return EMLX_OK;
     const int D = pool->head_dim, Hq = a->num_q_heads, Hkv = pool->num_kv_heads, G = Hq / Hkv;
@@ -1212,6 +1382,13 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
     hi = min(hi, class_hi);
     const int32_t* plan = (const int32_t*)a->plan;
     bool short_rows_launched = false;
+    int first_launched = -1, last_launched = -1;
+    for (int c = lo; c <= hi; ++c) {
+        if (a->row_class_mask != 0 && !((a->row_class_mask >> c) & 1)) continue;
+        if (first_launched < 0) first_launched = c;
+        last_launched = c;
+    }
+    if (first_launched < 0) return fail(EMLX_ERR_UNSUPPORTED, "row_class_mask names no row class that this call can launch");
     for (int c = lo; c <= hi; ++c) {
         if (a->row_class_mask != 0 && !((a->row_class_mask >> c) & 1)) continue;  // the caller knows this class is empty
         if (c == 3) {
@@ -1241,6 +1418,14 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
         p.Hq = Hq; p.Hkv = Hkv; p.G = G; p.MB = a->max_blocks_per_seq; p.window = a->sliding_window;
         p.bs = pool->block_size; p.ppt_log = pages_per_tile_log2(pool->block_size);
         p.scale_log2e = a->softmax_scale * 1.4426950408889634f;
+        p.out_Hq = gather ? gather->total_q_heads : Hq;
+        p.out_head0 = gather ? gather->head_offset : 0;
+        p.peer = gather ? (const PeerTable*)((const uint8_t*)gather->flag_block + kPeerTableOffset) : nullptr;
+        p.peer_flags = gather ? (int32_t*)gather->flag_block : nullptr;
+        p.peer_phase = (c == first_launched ? kPeerFirstLaunch : 0) | (c == last_launched ? kPeerLastLaunch : 0);
+        // a (sequence, KV head) unit is shared by about grid / units CTAs
+        p.few_units = (long long)a->num_seqs * Hkv * (kHelpMinParts - 1) <=
+                      class_ctas(c, min(num_sms(), kMaxGrid), (a->plan_flags & kPlanTwoCtas) != 0);
         // the grid a class is launched with is the one its slices were cut for
         const int grid = class_ctas(c, min(num_sms(), kMaxGrid), (a->plan_flags & kPlanTwoCtas) != 0);
         if (int rc = launch_class(c, D, pool->kv_format, bf16, maps, p, grid, (cudaStream_t)stream)) return rc;
@@ -1262,6 +1447,17 @@ extern "C" {
 int emlx_attn_unified(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 0, emlx::kNumClasses - 1); }
 int emlx_attn_decode(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 0, 2); }
 int emlx_attn_prefill(const emlx_attn_args* a, const emlx_pool* p, void* s) { return emlx::run_tiled(a, p, s, 3, 3); }
+int emlx_attn_decode_gather(const emlx_attn_args* a, const emlx_pool* p, void* flag_block, int32_t total_q_heads,
+                            int32_t head_offset, void* s) {
+    if (!a || !flag_block) return emlx::fail(EMLX_ERR_INVALID, "gather: null argument");
+    if (head_offset < 0 || total_q_heads < head_offset + a->num_q_heads)
+        return emlx::fail(EMLX_ERR_INVALID, "gather: heads [%d, %d) do not fit %d output heads", head_offset,
+                          head_offset + a->num_q_heads, total_q_heads);
+    if (a->plan_flags & emlx::kPlanWideUnits)
+        return emlx::fail(EMLX_ERR_UNSUPPORTED, "gather: build the work list without 128-row units (plan_flags bit 0)");
+    const emlx::GatherTarget g{flag_block, total_q_heads, head_offset};
+    return emlx::run_tiled(a, p, s, 0, 2, &g);
+}
 int emlx_attn_plan_flags(int32_t kv_format, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim) {
     return (emlx::prefill_supported(kv_format, num_q_heads, num_kv_heads, head_dim) ? emlx::kPlanWideUnits : 0) |
            (kv_format == EMLX_KV_AFFINE4 ? emlx::kPlanTwoCtas : 0);

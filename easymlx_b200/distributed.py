@@ -5,7 +5,9 @@ pages, tables and queries of its sequences and runs the single-GPU path unchange
 the data path.  Only two helpers talk to ``torch.distributed``: ``gather_packed_outputs`` (reassemble the
 packed output in the original batch order, used by parity checks and by callers that need the whole batch on
 every rank) and ``all_gather_heads`` (KV-head sharding of one long-context batch: every rank computes the
-query heads of its KV heads and the slices are all-gathered over NCCL).  The reference has no counterpart:
+query heads of its KV heads and the slices are all-gathered over NCCL).  ``PeerGather`` removes that collective:
+the attention kernels store every finished row straight into the full output buffer of every rank through
+peer-mapped memory and exchange flags (``emlx_attn_decode_gather``).  The reference has no counterpart:
 its only multi-device code is a replicated lock-step control plane
 (``inference/esurge/distributed/``) and the page-to-shard arithmetic of ``core/dp_sharding.py:51-73``.
 """
@@ -75,4 +77,131 @@ def all_gather_heads(local_out: torch.Tensor, group=None, out: torch.Tensor | No
     return buf.permute(1, 0, 2, 3).reshape(t, world * h, d)
 
 
-__all__ = ("all_gather_heads", "gather_packed_outputs", "local_token_index", "partition_by_sequence")
+PEER_FLAG_BYTES = 512      # EMLX_PEER_FLAG_BYTES
+PEER_HANDLE_BYTES = 64     # EMLX_PEER_HANDLE_BYTES
+MAX_PEERS = 8              # EMLX_MAX_PEERS
+
+
+class _DevicePointer:
+    """Lets ``torch.as_tensor`` wrap device memory that this module allocated itself."""
+
+    def __init__(self, ptr: int, shape: tuple[int, ...], typestr: str):
+        self.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (ptr, False), "version": 2}
+
+
+class GatherTarget:
+    """The buffers a gathering attention call writes: this rank's flag block and full ``[T, Hq, D]`` output, and the
+    table of every rank's buffers as mapped into this process (``emlx_gather_init``).
+
+    ``GatherTarget.local(...)`` builds it from plain device tensors that live in this process (one GPU playing
+    every rank in turn, for tests); ``PeerGather`` builds it from buffers shared between the processes of a node."""
+
+    def __init__(self, flag_block: int, out_ptrs: list[int], flag_ptrs: list[int], rank: int, total_q_heads: int,
+                 head_offset: int, out: torch.Tensor, poll_limit: int = 0, keep=()):
+        import ctypes as C
+
+        from . import _native as nv
+
+        world = len(out_ptrs)
+        self.flag_block, self.rank, self.world = int(flag_block), int(rank), world
+        self.total_q_heads, self.head_offset = int(total_q_heads), int(head_offset)
+        self.out = out                      # this rank's full output, [T_max, total_q_heads, D]
+        self._keep = keep
+        outs = (C.c_void_p * world)(*out_ptrs)
+        flags = (C.c_void_p * world)(*flag_ptrs)
+        nv.check(nv.lib().emlx_gather_init(C.c_void_p(self.flag_block), outs, flags, world, rank, int(poll_limit),
+                                           nv.stream_ptr(out.device)))
+
+    @classmethod
+    def local(cls, outs: list[torch.Tensor], flags: list[torch.Tensor], rank: int, head_offset: int,
+              poll_limit: int = 0) -> "GatherTarget":
+        return cls(flags[rank].data_ptr(), [o.data_ptr() for o in outs], [f.data_ptr() for f in flags], rank,
+                   int(outs[rank].shape[1]), head_offset, outs[rank], poll_limit, keep=(outs, flags))
+
+
+class PeerGather:
+    """KV-head sharding without the all-gather: one buffer per rank (flag block + full ``[T_max, Hq, D]`` output) in
+    memory the other ranks of the node map (``emlx_peer_buffer_create`` / ``_open``, handles exchanged with
+    ``all_gather_object``).  ``target`` is what ``AttentionCall(..., gather=...)`` takes; ``output(T)`` is the
+    gathered result of the last call.  Every rank must make the same calls; what reads ``output`` must be queued on
+    the calling stream before the next call."""
+
+    def __init__(self, max_tokens: int, total_q_heads: int, head_dim: int, dtype: torch.dtype, device, group=None,
+                 poll_limit: int = 0):
+        import ctypes as C
+
+        from . import _native as nv
+
+        lib = nv.lib()
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > MAX_PEERS:
+            raise ValueError(f"at most {MAX_PEERS} ranks")
+        if total_q_heads % self.world:
+            raise ValueError("total_q_heads must divide by the number of ranks")
+        self.device = torch.device(device)
+        item = torch.empty((), dtype=dtype).element_size()
+        out_bytes = max_tokens * total_q_heads * head_dim * item
+        self._bytes = PEER_FLAG_BYTES + out_bytes
+        self._own, self._mapped = 0, []
+        with torch.cuda.device(self.device):
+            # every step that can fail is followed by an exchange of what happened, so that the ranks fail together
+            # instead of leaving one another in a collective
+            ptr, handle = C.c_void_p(), (C.c_ubyte * PEER_HANDLE_BYTES)()
+            rc = lib.emlx_peer_buffer_create(self._bytes, C.byref(ptr), handle)
+            mine = bytes(handle) if rc == nv.EMLX_OK else nv.last_error()
+            self._own = int(ptr.value or 0) if rc == nv.EMLX_OK else 0
+            handles: list = [None] * self.world
+            dist.all_gather_object(handles, mine, group=group)
+            bases, problem = [], next((h for h in handles if isinstance(h, str)), None)
+            if problem is None:
+                for r in range(self.world):
+                    if r == self.rank:
+                        bases.append(self._own)
+                        continue
+                    p = C.c_void_p()
+                    buf = (C.c_ubyte * PEER_HANDLE_BYTES).from_buffer_copy(handles[r])
+                    if lib.emlx_peer_buffer_open(buf, C.byref(p)) != nv.EMLX_OK:
+                        problem = nv.last_error()
+                        break
+                    self._mapped.append(int(p.value))
+                    bases.append(int(p.value))
+            problems: list = [None] * self.world
+            dist.all_gather_object(problems, problem, group=group)
+            problem = next((x for x in problems if x), None)
+            if problem is not None:
+                for p in self._mapped:
+                    lib.emlx_peer_buffer_close(p)
+                if self._own:
+                    lib.emlx_peer_buffer_free(self._own)
+                self._own, self._mapped = 0, []
+                raise RuntimeError(f"peer-mapped buffers are not available: {problem}")
+            typestr = {torch.float16: "<f2", torch.bfloat16: "<u2"}[dtype]
+            full = torch.as_tensor(_DevicePointer(self._own + PEER_FLAG_BYTES, (max_tokens, total_q_heads, head_dim), typestr),
+                                   device=self.device)
+            if dtype == torch.bfloat16:
+                full = full.view(torch.bfloat16)
+            self.target = GatherTarget(self._own, [b + PEER_FLAG_BYTES for b in bases], bases, self.rank, total_q_heads,
+                                       self.rank * (total_q_heads // self.world), full, poll_limit)
+            torch.cuda.synchronize(self.device)
+        dist.barrier(group=group)   # every rank's table is in place before anyone's first call
+
+    def output(self, tokens: int) -> torch.Tensor:
+        return self.target.out[:tokens]
+
+    def close(self) -> None:
+        """Unmaps the other ranks' buffers and frees this rank's (after a barrier: nobody may still be storing)."""
+        from . import _native as nv
+
+        lib = nv.lib()
+        torch.cuda.synchronize(self.device)
+        dist.barrier()
+        for p in self._mapped:
+            lib.emlx_peer_buffer_close(p)
+        self._mapped = []
+        dist.barrier()
+        if self._own:
+            lib.emlx_peer_buffer_free(self._own)
+            self._own = 0
+
+
+__all__ = ("GatherTarget", "PeerGather", "all_gather_heads", "gather_packed_outputs", "local_token_index", "partition_by_sequence")

@@ -140,7 +140,7 @@ class AttentionCall:
     def __init__(self, queries, key_cache, value_cache, block_tables, kv_lens, query_start_loc, *,
                  softmax_scale: float | None = None, sliding_window: int | None = None,
                  k_scale=None, v_scale=None, k_bias=None, v_bias=None, kernel: str | None = None,
-                 max_query_len: int = 0, plan=None, query_len_set: tp.Sequence[int] | None = None):
+                 max_query_len: int = 0, plan=None, query_len_set: tp.Sequence[int] | None = None, gather=None):
         nv.require_cuda(queries, key_cache, value_cache)
         dev = queries.device
         affine = key_cache.dtype == torch.uint8
@@ -155,6 +155,15 @@ class AttentionCall:
         self.queries = queries.contiguous()
         self.out = None
         self.kernel = kernel
+        # KV heads sharded over GPUs (``easymlx_b200.distributed.GatherTarget``): the short-row kernels store this
+        # rank's heads into every rank's full output instead of a local [T, Hq, D] tensor
+        self.gather = gather
+        if gather is not None:
+            if kernel not in (None, "decode"):
+                raise ValueError("a gathering call runs the short-row kernels (kernel='decode')")
+            if self.total > gather.out.shape[0] or self.d != gather.out.shape[2] or queries.dtype != gather.out.dtype:
+                raise ValueError("the gather target does not fit this call's tokens / head_dim / dtype")
+            self.kernel = "decode"
         if self.total == 0:
             return
         if not (key_cache.is_contiguous() and value_cache.is_contiguous()):
@@ -197,7 +206,10 @@ class AttentionCall:
             # (the decode entry point serves the short-row classes only: its work list is built without 128-row units)
             recommended = int(lib.emlx_attn_plan_flags(self.pool.kv_format, self.hq, hkv, self.d))
             self.plan_flags = recommended & ~1 if self.kernel == "decode" else recommended
-            if plan is not None and plan[1] == self.hq and plan[2] == self.window and plan[0].numel() >= self.plan_bytes:
+            usable = plan is not None and plan[1] == self.hq and plan[2] == self.window and plan[0].numel() >= self.plan_bytes
+            if usable and self.kernel == "decode" and (int(plan[3]) & 1):
+                usable = False   # that work list holds 128-row units, which the short-row entry points do not serve
+            if usable:
                 self.plan_buf, self.planned = plan[0], True   # built together with the batch metadata
                 self.plan_flags = int(plan[3])
             else:
@@ -225,8 +237,16 @@ class AttentionCall:
 
     def launch(self) -> torch.Tensor:
         if self.total == 0:
-            return torch.zeros_like(self.queries)
+            return torch.zeros_like(self.queries) if self.gather is None else self.gather.out[:0]
         lib = nv.lib()
+        if self.gather is not None:
+            g = self.gather
+            self.out = g.out[: self.total]
+            self.args.out = g.out.data_ptr()
+            nv.check(lib.emlx_attn_decode_gather(self.args, self.pool, g.flag_block, g.total_q_heads, g.head_offset,
+                                                 nv.stream_ptr(self.device)))
+            self._report_status(lib)
+            return self.out
         self.out = torch.empty_like(self.queries)
         if _CHECK:
             self.out.fill_(float("nan"))  # a row no kernel writes shows up in the caller's checks
@@ -234,15 +254,19 @@ class AttentionCall:
         entry = {"generic": lib.emlx_attn_generic, "tiled": lib.emlx_attn_unified, "decode": lib.emlx_attn_decode,
                  "prefill": lib.emlx_attn_prefill}[self.kernel]
         nv.check(entry(self.args, self.pool, nv.stream_ptr(self.device)))
-        if _CHECK:
-            rc = lib.emlx_read_status(nv.ptr(self.status), nv.stream_ptr(self.device))
-            if rc != nv.EMLX_OK:
-                self.status.zero_()  # report once
-                ws = getattr(self, "workspace", None)
-                if ws is not None:
-                    ws.zero_()  # a wait that gave up may have left split-KV arrival counters set
-            nv.check(rc)
+        self._report_status(lib)
         return self.out
+
+    def _report_status(self, lib) -> None:
+        if not _CHECK:
+            return
+        rc = lib.emlx_read_status(nv.ptr(self.status), nv.stream_ptr(self.device))
+        if rc != nv.EMLX_OK:
+            self.status.zero_()  # report once
+            ws = getattr(self, "workspace", None)
+            if ws is not None:
+                ws.zero_()  # a wait that gave up may have left split-KV arrival counters set
+        nv.check(rc)
 
 
 def paged_attention(
@@ -267,6 +291,7 @@ def paged_attention(
     max_query_len: int = 0,
     plan=None,
     query_len_set: tp.Sequence[int] | None = None,
+    gather=None,
 ) -> torch.Tensor:
     """Ragged causal attention of packed queries over a paged KV pool.
 
@@ -277,7 +302,8 @@ def paged_attention(
     ``single_token_decode`` / ``max_query_len`` are host-side hints (an upper bound on the query tokens of
     any sequence) and ``query_len_set`` (the distinct query lengths of the batch); without them the kernels for every
     row class are launched and the empty ones return at once.  ``kernel`` (``None`` = automatic, ``"generic"``, ``"tiled"``, ``"decode"``, ``"prefill"``) selects
-    an entry point explicitly; tests and benchmarks use it.
+    an entry point explicitly; tests and benchmarks use it.  ``gather`` (a ``distributed.GatherTarget``) makes the call
+    store its heads into every rank's full output (KV heads sharded over GPUs) and return this rank's copy of it.
     """
     del use_metal, threadgroup_size, allow_fallback
     if single_token_decode and not max_query_len:
@@ -285,7 +311,7 @@ def paged_attention(
     return AttentionCall(queries, key_cache, value_cache, block_tables, kv_lens, query_start_loc,
                          softmax_scale=softmax_scale, sliding_window=sliding_window, k_scale=k_scale, v_scale=v_scale,
                          k_bias=k_bias, v_bias=v_bias, kernel=kernel, max_query_len=max_query_len,
-                         plan=plan, query_len_set=query_len_set).plan().launch()
+                         plan=plan, query_len_set=query_len_set, gather=gather).plan().launch()
 
 
 @OperationRegistry.register

@@ -24,13 +24,15 @@ class AttentionStep:
     """
 
     def __init__(self, cache: PageCacheView, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, query_lens,
-                 slot_ids, *, scale: float | None = None, sliding_window: int | None = None, rewind: bool = True):
+                 slot_ids, *, scale: float | None = None, sliding_window: int | None = None, rewind: bool = True,
+                 gather=None):
         self.cache = cache
         self.q, self.k, self.v = q, k, v
         self.query_lens = tuple(int(x) for x in query_lens)
         self.slot_ids = tuple(int(x) for x in slot_ids)
         self.performer = AttentionPerformer(scale=scale if scale is not None else float(q.shape[-1]) ** -0.5)
         self.rewind = rewind
+        self.gather = gather   # distributed.GatherTarget: KV heads sharded over GPUs, output gathered by the kernels
         self._base_lens = cache.kv_lens.clone()
         single = len(self.query_lens) == q.shape[0] and all(x == 1 for x in self.query_lens)
         self._meta = PageMetadata(query_start_loc=build_query_start_loc(self.query_lens), slot_ids=self.slot_ids,
@@ -46,6 +48,19 @@ class AttentionStep:
         _, kc, vc, meta = self.cache.concatenate_to_cache(self.q, self.k, self.v, cache_metadata=self._meta,
                                                           slot_ids=self.slot_ids, query_lens=self.query_lens,
                                                           advance=not self.rewind)
+        if self.gather is not None:
+            from .operations.kernels.unified_attention import paged_attention
+
+            extra = {}
+            if self.cache.is_affine:
+                extra = dict(k_scale=self.cache.k_scales, v_scale=self.cache.v_scales, k_bias=self.cache.k_biases,
+                             v_bias=self.cache.v_biases)
+            return paged_attention(self.q, kc, vc, meta.block_tables, meta.kv_lens, meta.query_start_loc,
+                                   softmax_scale=self.performer.scale, sliding_window=meta.sliding_window,
+                                   single_token_decode=meta.is_single_token_decode,
+                                   max_query_len=int(getattr(meta, "max_query_len", 0) or 0),
+                                   plan=getattr(meta, "plan", None), query_len_set=getattr(meta, "query_len_set", None),
+                                   gather=self.gather, **extra)
         op = self.performer.executor.mixin_impl
         return op(query=self.q, key=kc, value=vc, cache_metadata=meta, cache_view=self.cache,
                   scale=self.performer.scale).attention_outputs

@@ -243,6 +243,37 @@ int emlx_attn_generic(const emlx_attn_args* args, const emlx_pool* pool, void* s
  * calls that overlap on the GPU (different streams) race, so serialise them.  Calls no allocating routine. */
 int emlx_attn_decode_static(const emlx_attn_args* args, const emlx_pool* pool, void* stream);
 
+/* ---- KV heads sharded over GPUs: attention whose epilogue gathers the output over peer-mapped memory ----------------
+ * No counterpart in the reference (eSurge runs one device; its multi-device code is a replicated control plane,
+ * inference/esurge/distributed/).  One process per GPU; rank r holds the pages of KV heads [r*Hkv/N, (r+1)*Hkv/N) of
+ * every sequence and computes the query heads that belong to them.  Instead of an all-gather of the [T, Hq/N, D]
+ * slices afterwards, the kernels store every finished row straight into the full [T, Hq, D] output buffer of every
+ * rank (plain stores through peer-mapped pointers; no TMA, no multicast on peer memory) and exchange two flags per
+ * pair of ranks: "my output buffer may be overwritten" at the start of a call and "my rows have arrived" at its end.
+ * Both waits are bounded by `poll_limit` polls; on expiry the kernel ORs EMLX_DEV_WAIT_TIMEOUT into *status and
+ * finishes.  All ranks must make the same sequence of gathering calls (same batch, one call per step); whatever
+ * reads the output must be queued on the calling stream before the rank's next gathering call. */
+#define EMLX_MAX_PEERS 8
+#define EMLX_PEER_FLAG_BYTES 512   /* one rank's flag block; allocate it in peer-shared memory and zero it once */
+#define EMLX_PEER_HANDLE_BYTES 64
+/* Device memory that other processes on the same node can map: create (cudaMalloc + zero + IPC handle), open a
+ * handle received from another rank, close a mapping, free an own buffer.  Exchange the handles over any host
+ * channel (torch.distributed all_gather of 64 bytes). */
+int emlx_peer_buffer_create(size_t bytes, void** ptr, void* handle);
+int emlx_peer_buffer_open(const void* handle, void** ptr);
+int emlx_peer_buffer_close(void* ptr);
+int emlx_peer_buffer_free(void* ptr);
+/* Writes the table of the ranks' output buffers and flag blocks (as mapped into this process; entry `rank` is the
+ * local one) into this rank's flag block.  Call once after the handles are exchanged, before the first gathering
+ * call, with the flag block zeroed. */
+int emlx_gather_init(void* flag_block, void* const* out_ptrs, void* const* flag_ptrs, int32_t num_ranks, int32_t rank,
+                     int32_t poll_limit, void* stream);
+/* emlx_attn_decode over this rank's heads (args->num_q_heads = Hq/N, pool = this rank's KV heads; the work list must
+ * be built without 128-row units, plan_flags bit 0 clear), writing heads [head_offset, head_offset + Hq/N) of
+ * args->out = this rank's full [T, total_q_heads, D] buffer and of every other rank's. */
+int emlx_attn_decode_gather(const emlx_attn_args* args, const emlx_pool* pool, void* flag_block, int32_t total_q_heads,
+                            int32_t head_offset, void* stream);
+
 /* Failure-detection self-test: launches one warp that waits, with the kernels' bounded-wait routine and a limit of
  * `poll_limit` polls, on a barrier that is never completed; the wait gives up, the kernel ORs EMLX_DEV_WAIT_TIMEOUT
  * into *status and returns normally (nothing faults, the context stays usable). */
