@@ -355,11 +355,11 @@ class Bench:
                 # keeps replaying (untimed) for a moment so that the clock record holds samples under this load
                 # (a count, not a deadline: `ms_total` is the maximum over ranks, so every rank replays the same number
                 # of steps, which steps that hold a collective or wait for the other ranks need)
-                for _ in range(int(min(400, max(1, 350.0 / max(ms_total, 1e-3) * (args.steps // layers) / 20)))):
+                for _ in range(int(min(400, max(1, 500.0 / max(ms_total, 1e-3) * (args.steps // layers) / 20)))):
                     for _ in range(20):
                         one_step()
                     torch.cuda.synchronize()
-            clocks = dict(sampler.summary, window="timed steps + 0.35 s of the same step replayed", attempts=attempt + 1)
+            clocks = dict(sampler.summary, window="timed steps + 0.5 s of the same step replayed", attempts=attempt + 1)
             if not any(r in BAD_CLOCK_REASONS for r in clocks["reasons"]):
                 break
         ms_step = ms_total / args.steps

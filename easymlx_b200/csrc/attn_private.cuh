@@ -543,7 +543,7 @@ __device__ __forceinline__ void consumer_loop_private(const TiledParams& p, uint
         }
         if (PEER && complete) {  // gathering call: the rows just stored go to the other ranks as well
             consumer_sync();
-            peer_ready(p, peer_seen, misc);
+            peer_ready(p, peer_seen);
             peer_copy_rows<D>((uint16_t*)p.out, p.peer, p.out_Hq, p.out_head0, p.G, qs, head, row0, min(row0 + ROWS, R),
                               tid, kConsumerThreads);
         }
@@ -698,7 +698,7 @@ __device__ __forceinline__ void merge_warp_loop(const TiledParams& p, uint8_t* f
     uint64_t* mfull = full + 24;
     bool peer_seen = false;
     uint32_t jobs_posted = 0;  // final merges handed to the parked consumer warps
-    if constexpr (PEER) peer_ready(p, peer_seen, (const int*)(fixed + C::OFF_MISC));  // while the consumers work: off the path of the merge
+    if constexpr (PEER) peer_ready(p, peer_seen);  // while the consumers work: off the path of the merge
     for (int e = 0; e < 2; ++e) {
         // the consumers may take their whole slice before they post: sleep between polls, give up after seconds
         int ok = 0;

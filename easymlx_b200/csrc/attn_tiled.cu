@@ -107,14 +107,14 @@ constexpr int kMiscRanks = 5, kMiscRank = 6, kMiscPoll = 7;
 
 // Before a warp's first remote store of a gathering call: every other rank has said that its output buffer may be
 // overwritten (lane r polls rank r's flag; the flags only grow, so later calls return at once).
-__device__ __forceinline__ void peer_ready(const TiledParams& p, bool& seen, const int* misc) {
+__device__ __forceinline__ void peer_ready(const TiledParams& p, bool& seen) {
     if (!p.peer || seen) return;
     seen = true;
     if (!(p.peer_phase & kPeerFirstLaunch)) return;  // a later kernel of the call: the first one has waited
     const int lane = threadIdx.x & 31;
     bool ok = true;
-    if (lane < misc[kMiscRanks] && lane != misc[kMiscRank])
-        ok = peer_wait(p.peer_flags + kPeerReady + lane, misc[kMiscEpoch], misc[kMiscPoll]);
+    if (lane < p.peer->num_ranks && lane != p.peer->rank)
+        ok = peer_wait(p.peer_flags + kPeerReady + lane, p.peer_flags[kPeerEpoch] + 1, p.peer->poll_limit);
     if (!ok) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
     __syncwarp();
 }
@@ -157,24 +157,26 @@ __device__ __forceinline__ void peer_warp_exit(const TiledParams& p, int* misc, 
     if (p.peer) peer_exit(p.peer_flags, p.peer_phase, p.status, misc, cache);
 }
 
-// Start of a gathering call's CTA (all its threads): the call's epoch and the table of the ranks go to shared memory,
-// and the first CTA of the call's first kernel tells the other ranks that this rank's output may be overwritten
-// (everything queued before the call on this rank's stream has finished).
+// Start of a gathering call's CTA, run by its merge warp (idle at that point) so that the table's cold loads stay off
+// the path of the warps that start the tile loop: the call's epoch and the table of the ranks go to shared memory for
+// peer_exit (whichever warp leaves last has seen this warp's count, and with it these stores), and the first CTA of
+// the call's first kernel tells the other ranks that this rank's output may be overwritten (everything queued before
+// the call on this rank's stream has finished).
 __device__ __noinline__ void peer_enter(const PeerTable* table, int32_t* flags, int phase, int* misc, PeerCache* cache) {
+    const int lane = threadIdx.x & 31;
     const int n = table->num_ranks, me = table->rank, epoch = flags[kPeerEpoch] + 1;
-    if ((int)threadIdx.x < n) {
-        int32_t* theirs = table->flags[threadIdx.x];
-        cache->flags[threadIdx.x] = theirs;
-        if ((phase & kPeerFirstLaunch) && blockIdx.x == 0 && (int)threadIdx.x != me)
-            st_release_sys(theirs + kPeerReady + me, epoch);
+    if (lane < n) {
+        int32_t* theirs = table->flags[lane];
+        cache->flags[lane] = theirs;
+        if ((phase & kPeerFirstLaunch) && blockIdx.x == 0 && lane != me) st_release_sys(theirs + kPeerReady + me, epoch);
     }
-    if (threadIdx.x == 0) {
+    if (lane == 0) {
         misc[kMiscEpoch] = epoch;
         misc[kMiscRanks] = n;
         misc[kMiscRank] = me;
         misc[kMiscPoll] = table->poll_limit;
     }
-    __syncthreads();
+    __syncwarp();
 }
 
 template <int D, int NT, int FMT>
@@ -1025,7 +1027,7 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
             }
             if constexpr (PEER) {
                 consumer_sync();
-                peer_ready(p, peer_seen, misc);
+                peer_ready(p, peer_seen);
                 peer_copy_rows<D>((uint16_t*)p.out, p.peer, p.out_Hq, p.out_head0, p.G, qs, head, row0, min(row0 + ROWS, R),
                                   tid, kConsumerThreads);
             }
@@ -1089,7 +1091,7 @@ __device__ __forceinline__ void consumer_loop(const TiledParams& p, uint8_t* sta
                 if (tid == 0) *counter = 0;  // ready for the next launch
                 if constexpr (PEER) {  // uniform over the consumer warps (the ticket is shared)
                     consumer_sync();
-                    peer_ready(p, peer_seen, misc);
+                    peer_ready(p, peer_seen);
                     peer_copy_rows<D>((uint16_t*)p.out, p.peer, p.out_Hq, p.out_head0, p.G, qs, head, row0, min(row0 + ROWS, R),
                                       tid, kConsumerThreads);
                 }
@@ -1164,11 +1166,14 @@ attn_tiled_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constan
 #endif
     int* misc_words = (int*)(fixed + C::OFF_MISC);
     const PeerCache* peer_cache = (const PeerCache*)(fixed + C::OFF_PEER);
-    if constexpr (PEER) peer_enter(p.peer, p.peer_flags, p.peer_phase, misc_words, (PeerCache*)(fixed + C::OFF_PEER));
     const int num_units = p.hdr[0];
     const long long total_flat = (long long)p.hdr[1] * p.Hkv;
     // every CTA takes the contiguous slice the plan cut for it; a CTA without tiles has nothing to do
     const long long f_begin = p.cta_start[blockIdx.x], f_end = p.cta_start[blockIdx.x + 1];
+    if constexpr (PEER) {
+        if (threadIdx.x >= kConsumerThreads + 32)
+            peer_enter(p.peer, p.peer_flags, p.peer_phase, misc_words, (PeerCache*)(fixed + C::OFF_PEER));
+    }
     if (f_begin >= f_end) {  // uniform for the CTA, and no thread waits on a barrier yet
         if constexpr (PEER) peer_warp_exit(p, misc_words, peer_cache);
         return;

@@ -53,6 +53,22 @@ def test_one_decode_row_over_the_whole_grid(bits):
     assert torch.equal(fast, _run(cache, q, [1], [kv], None))
 
 
+@pytest.mark.parametrize("bits", [0, 8, 4])
+@pytest.mark.parametrize("group", [4, 8, 16])
+def test_few_long_sequences_share_their_final_merge(bits, group):
+    # 8 units of about 300 tiles on the whole grid: every unit ends in a merge of some twenty parts, which the
+    # consumer warps of the last CTA to arrive share when they are free and one warp does alone when they are not;
+    # both ways fold the parts in the same order with the same arithmetic, so repeated runs must agree bit for bit
+    hkv, d = 2, 128
+    lens = [40_000, 37_003, 39_111, 36_500]
+    cache = _pool(hkv, d, lens, bits, seed=40 + bits)
+    q = torch.randn(len(lens), hkv * group, d, device="cuda", dtype=torch.float16)
+    first = _run(cache, q, [1] * len(lens), lens, None)
+    assert_close(first, _run(cache, q, [1] * len(lens), lens, "generic").float().cpu().numpy())
+    for _ in range(6):
+        assert torch.equal(first, _run(cache, q, [1] * len(lens), lens, None))
+
+
 @pytest.mark.parametrize("window", [None, 5000])
 def test_prefill_chunk_after_a_long_context(window):
     # 256 new tokens after 20 000 cached ones: 32 x 128-row units x 2 KV heads, up to 159 KV tiles per item
