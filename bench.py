@@ -274,15 +274,17 @@ class Bench:
             dist.barrier()
         self.torch.cuda.synchronize()
 
-    def timed(self, fn, steps):
+    def timed(self, fn, steps, finish=None):
         """Milliseconds for `steps` calls of fn: CUDA events on the launching stream, barrier + synchronise on both
-        sides, maximum over ranks."""
+        sides, maximum over ranks.  `finish()` runs before the closing event (work on other streams joins there)."""
         torch = self.torch
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         self.barrier()
         start.record()
         for _ in range(steps):
             fn()
+        if finish is not None:
+            finish()
         stop.record()
         self.barrier()
         ms = start.elapsed_time(stop)
@@ -373,35 +375,26 @@ class Bench:
             "clocks": clocks,
         }
 
-        # ---- end to end: pinned host q/k/v in, host output back, every step; q, k and v travel as one packed host
-        # buffer (one copy per step instead of three) and the device side reads them through views of it
+        # ---- end to end through the public host-facing call: pinned host q/k/v in, host output back, every step (one
+        # packed upload per step); the upload of the next step and the download of the previous one run on their own
+        # streams beside the kernels (HostStepPipeline), and the closing event waits for the last download
         if e2e:
-            parts_qkv = (w.q, w.k, w.v)
-            sizes = [t.numel() for t in parts_qkv]
-            hqkv = torch.cat([t.reshape(-1).cpu() for t in parts_qkv]).pin_memory()
-            dqkv = torch.empty_like(hqkv, device=dev)
-            dqkv.copy_(hqkv)
-            dq, dk, dv = (v.view(t.shape) for v, t in zip(torch.split(dqkv, sizes), parts_qkv))
-            step1 = AttentionStep(w.cache, dq, dk, dv, w.qlens.tolist(), w.slot_ids, gather=gather_target).capture(warmup=2)
-            hout = torch.empty_like(step1.out, device="cpu").pin_memory()
+            from easymlx_b200.runtime import HostStepPipeline
+            # (a gathering call writes the one output buffer the ranks share: its steps cannot overlap their downloads)
+            pipe = HostStepPipeline(w.cache, (w.q.cpu(), w.k.cpu(), w.v.cpu()), w.qlens.tolist(), w.slot_ids,
+                                    depth=1 if gather_target is not None else 2, gather=gather_target, after_step=after_step)
             if gather_target is not None:
                 self.barrier()
-
-            def e2e_step():
-                dqkv.copy_(hqkv, non_blocking=True)
-                out = step1.step()
-                if after_step is not None:
-                    after_step(out)
-                hout.copy_(out, non_blocking=True)
-
-            for _ in range(3):
-                e2e_step()
-            ms_e2e = self.timed(e2e_step, args.steps) / args.steps
+            for _ in range(4):
+                pipe.submit()
+            pipe.drain()
+            ms_e2e = self.timed(pipe.submit, args.steps, finish=pipe.drain) / args.steps
             result["e2e"] = {"value": tokens_all / (ms_e2e * 1e-3), "unit": UNIT,
-                             "h2d_bytes_per_step": int(hqkv.numel() * hqkv.element_size()),
-                             "d2h_bytes_per_step": int(hout.numel() * hout.element_size()),
-                             "us_per_batch": ms_e2e * 1e3}
-            del step1, dqkv, hqkv, hout
+                             "h2d_bytes_per_step": pipe.h2d_bytes_per_step, "d2h_bytes_per_step": pipe.d2h_bytes_per_step,
+                             "us_per_batch": ms_e2e * 1e3,
+                             "overlap": "upload of step n+1 and download of step n-1 run beside the kernels of step n "
+                                        "(two buffer sets, one stream per direction)"}
+            del pipe
 
         # ---- the attention launch alone (over the already written pool), for the roofline
         c = w.cache

@@ -358,7 +358,7 @@ class PageCacheView:
                 self.native_pool(), rope.native(dev) if rope is not None else None, nv.ptr(qsl), nv.ptr(bt), nv.ptr(lens),
                 hq if plan is not None else (int(queries.shape[1]) if rope is not None else 0), window, max_q, flags,
                 nv.ptr(plan), plan_bytes, nv.ptr(self.ticket), nv.ptr(self.status), stream))
-            if _CHECK:
+            if _CHECK and not torch.cuda.is_current_stream_capturing():
                 self.check()
             return qsl, bt, lens, (None if plan is None else (plan, hq, window, flags)), rotated_q
         nv.check(lib.emlx_build_metadata(
@@ -376,7 +376,7 @@ class PageCacheView:
                     nv.ptr(queries), nv.ptr(rotated_q), int(queries.shape[1]), nv.ptr(keys), nv.ptr(values),
                     nv.dtype_code(keys.dtype), total_tokens, nv.ptr(slot_mapping), nv.ptr(positions),
                     rope.native(dev), pool, nv.ptr(self.status), stream))
-        if _CHECK:
+        if _CHECK and not torch.cuda.is_current_stream_capturing():
             self.check()
         return qsl, bt, lens, (None if plan is None else (plan, hq, window, flags)), rotated_q
 
@@ -457,7 +457,7 @@ class PageCacheView:
             staging = torch.empty(staging_bytes, dtype=torch.uint8, device=dev)
         nv.check(lib.emlx_copy_blocks(pool, nv.ptr(mapping), pairs, nv.ptr(staging), staging_bytes, nv.ptr(self.status),
                                       nv.stream_ptr(dev)))
-        if _CHECK:
+        if _CHECK and not torch.cuda.is_current_stream_capturing():
             self.check()
 
     def zero_pages(self, page_ids) -> None:
@@ -490,7 +490,7 @@ class PageCacheView:
         nv.check(nv.lib().emlx_gather_kv_cache(self.native_pool(), nv.ptr(bt), int(bt.shape[0]), int(bt.shape[1]), nv.ptr(cu),
                                                total, nv.dtype_code(out_dtype), nv.ptr(k_out), nv.ptr(v_out),
                                                nv.ptr(self.status), nv.stream_ptr(dev)))
-        if _CHECK:
+        if _CHECK and not torch.cuda.is_current_stream_capturing():
             self.check()
         return k_out, v_out
 

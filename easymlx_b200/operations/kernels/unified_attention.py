@@ -258,7 +258,8 @@ class AttentionCall:
         return self.out
 
     def _report_status(self, lib) -> None:
-        if not _CHECK:
+        # (reading the status synchronises the stream, which a stream capture does not allow)
+        if not _CHECK or torch.cuda.is_current_stream_capturing():
             return
         rc = lib.emlx_read_status(nv.ptr(self.status), nv.stream_ptr(self.device))
         if rc != nv.EMLX_OK:

@@ -97,4 +97,83 @@ class AttentionStep:
         return self.out
 
 
-__all__ = ("AttentionStep",)
+class HostStepPipeline:
+    """Steps whose q / k / v arrive in pinned host memory and whose output goes back to pinned host memory.
+
+    A step's upload, its kernels and its download depend on one another, but the upload of step n+1 and the download
+    of step n-1 do not depend on the kernels of step n: with ``depth`` buffer sets (device inputs, a captured
+    ``AttentionStep`` over them, a pinned host output) and one stream per direction, the three overlap and a step costs
+    the slowest of them instead of their sum.  q, k and v travel as one packed buffer (one copy per step).
+
+    ``submit()`` enqueues one step and returns the index of the buffer set it used; ``result(i)`` is that set's host
+    output (wait for ``downloaded[i]`` before reading it); ``drain()`` makes the calling stream wait for every download,
+    so that an event recorded after it covers all submitted work.
+    """
+
+    def __init__(self, cache: PageCacheView, host_qkv, query_lens, slot_ids, *, depth: int = 2, gather=None,
+                 after_step=None, scale: float | None = None, sliding_window: int | None = None):
+        hq, hk, hv = host_qkv
+        dev = cache.key_cache.device
+        self.device, self.depth, self.after_step = dev, max(1, int(depth)), after_step
+        parts = (hq, hk, hv)
+        sizes = [t.numel() for t in parts]
+        self.host_in = torch.cat([t.reshape(-1) for t in parts]).pin_memory()
+        self.dev_in, self.steps, self.host_out = [], [], []
+        for _ in range(self.depth):
+            packed = torch.empty_like(self.host_in, device=dev)
+            packed.copy_(self.host_in)
+            dq, dk, dv = (v.view(t.shape) for v, t in zip(torch.split(packed, sizes), parts))
+            step = AttentionStep(cache, dq, dk, dv, query_lens, slot_ids, scale=scale, sliding_window=sliding_window,
+                                 gather=gather).capture(warmup=2)
+            self.dev_in.append(packed)
+            self.steps.append(step)
+            self.host_out.append(torch.empty_like(step.out, device="cpu").pin_memory())
+        self.up, self.down = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        make = lambda: [torch.cuda.Event() for _ in range(self.depth)]
+        self.uploaded, self.computed, self.downloaded = make(), make(), make()
+        self.submitted = 0
+        torch.cuda.synchronize(dev)
+
+    @property
+    def h2d_bytes_per_step(self) -> int:
+        return int(self.host_in.numel() * self.host_in.element_size())
+
+    @property
+    def d2h_bytes_per_step(self) -> int:
+        return int(self.host_out[0].numel() * self.host_out[0].element_size())
+
+    def submit(self) -> int:
+        i = self.submitted % self.depth
+        reused = self.submitted >= self.depth
+        cur = torch.cuda.current_stream(self.device)
+        with torch.cuda.stream(self.up):
+            if reused:
+                self.up.wait_event(self.computed[i])       # the kernels that read this input buffer have finished
+            else:
+                self.up.wait_stream(cur)
+            self.dev_in[i].copy_(self.host_in, non_blocking=True)
+            self.uploaded[i].record(self.up)
+        cur.wait_event(self.uploaded[i])
+        if reused:
+            cur.wait_event(self.downloaded[i])             # the previous result of this set has left the device
+        out = self.steps[i].step()
+        if self.after_step is not None:
+            self.after_step(out)
+        self.computed[i].record(cur)
+        with torch.cuda.stream(self.down):
+            self.down.wait_event(self.computed[i])
+            self.host_out[i].copy_(out, non_blocking=True)
+            self.downloaded[i].record(self.down)
+        self.submitted += 1
+        return i
+
+    def result(self, i: int) -> torch.Tensor:
+        return self.host_out[i]
+
+    def drain(self) -> None:
+        cur = torch.cuda.current_stream(self.device)
+        for i in range(min(self.depth, self.submitted)):
+            cur.wait_event(self.downloaded[i])
+
+
+__all__ = ("AttentionStep", "HostStepPipeline")
