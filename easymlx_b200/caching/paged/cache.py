@@ -30,6 +30,14 @@ _CHECK = os.environ.get("EASYMLX_B200_CHECK", "0") not in ("", "0")
 QUANT_GROUP = 64
 _FUSED_STEP_MAX_SEQS = 2048  # batch size up to which emlx_kv_write_step serves a batch in one launch
 
+def wide_units_geometry(num_q_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    """Head geometry the 128-row (tcgen05) kernel can run: a GQA group that divides 128 and head_dim 64 or 128."""
+    if num_kv_heads <= 0 or num_q_heads % num_kv_heads:
+        return False
+    group = num_q_heads // num_kv_heads
+    return head_dim in (64, 128) and group <= 128 and 128 % group == 0
+
+
 _TORCH_DTYPES = {
     "float16": torch.float16, "half": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32,
     "torch.float16": torch.float16, "torch.bfloat16": torch.bfloat16, "torch.float32": torch.float32,
@@ -109,6 +117,9 @@ class PageMetadata:
     # filled by concatenate_to_cache: the distinct query lengths of the batch when the host knows them; lets the
     # attention call skip the kernels of row classes the batch does not contain
     query_len_set: tuple[int, ...] | None = field(default=None, compare=False)
+    # filled by concatenate_to_cache: sequences of the batch with more than 16 query rows (tokens x GQA group), when the
+    # host knows the lengths; over an affine pool those rows then go to the tcgen05 kernel through expanded pages
+    long_seqs: int = field(default=0, compare=False)
     # attention work list built on the GPU together with the metadata: (buffer, num_q_heads, sliding_window, plan_flags)
     plan: tp.Any | None = field(default=None, compare=False)
     # optional host hint from the runner: length of the longest scheduled sequence after this step (0 = unknown);
@@ -121,6 +132,7 @@ class PageMetadata:
             block_size=int(block_size), sliding_window=self.sliding_window,
             is_single_token_decode=self.is_single_token_decode, slot_ids=self.slot_ids,
             max_query_len=self.max_query_len, plan=self.plan, query_len_set=self.query_len_set,
+            long_seqs=self.long_seqs,
         )
 
     def with_sliding_window(self, sliding_window: int | None) -> "PageMetadata":
@@ -128,7 +140,7 @@ class PageMetadata:
             query_start_loc=self.query_start_loc, block_tables=self.block_tables, kv_lens=self.kv_lens,
             block_size=self.block_size, sliding_window=sliding_window,
             is_single_token_decode=self.is_single_token_decode, slot_ids=self.slot_ids,
-            max_query_len=self.max_query_len, query_len_set=self.query_len_set,
+            max_query_len=self.max_query_len, query_len_set=self.query_len_set, long_seqs=self.long_seqs,
         )
 
 
@@ -327,9 +339,11 @@ class PageCacheView:
         hq = window = max_q = plan_bytes = flags = 0
         if plan_for is not None and total_tokens > 0 and (
                 self.block_size == 128 or (not self.is_affine and self.block_size in (16, 32, 64))):
-            hq, window, max_q = plan_for
+            hq, window, max_q = plan_for[:3]
             flags = int(lib.emlx_attn_plan_flags(self.cache_bits if self.is_affine else nv.KV_FLOAT, hq,
                                                  self.num_kv_heads, self.head_dim))
+            if self.is_affine and len(plan_for) > 3 and plan_for[3] > 0 and wide_units_geometry(hq, self.num_kv_heads, self.head_dim):
+                flags |= 1  # long rows in 128-row units: the attention call expands their pages for the tcgen05 kernel
             plan_bytes = int(lib.emlx_attn_plan_bytes(s, total_tokens, hq, self.num_kv_heads))
             plan = torch.empty(plan_bytes, dtype=torch.uint8, device=dev)
         if total_tokens > 0:
@@ -553,9 +567,11 @@ class PageCacheView:
             if longest <= 0 and slots:
                 longest = int((self.kv_lens[_uploaded.get(slots, dev).long()] + qlens_dev[: len(slots)]).max().item())
             rope = rope.select(longest)
+        group = max(1, int(queries.shape[1]) // self.num_kv_heads)
+        long_seqs = 0 if qlens is None else sum(1 for q in qlens if q * group > 16)
         qsl, bt, lens, plan, rotated_q = self._write_batch(
             keys, values, qlens_dev, _uploaded.get(slots, dev), total,
-            plan_for=(int(queries.shape[1]), window, max_q), advance=advance, rope=rope, queries=queries,
+            plan_for=(int(queries.shape[1]), window, max_q, long_seqs), advance=advance, rope=rope, queries=queries,
             single_token=single and len(slots) == total)
         if rotated_q is not None:
             queries = rotated_q
@@ -564,6 +580,7 @@ class PageCacheView:
             is_single_token_decode=bool(getattr(cache_metadata, "is_single_token_decode", False)) or single,
             slot_ids=getattr(cache_metadata, "slot_ids", None) or slots, max_query_len=max_q, plan=plan,
             query_len_set=None if qlens is None else tuple(sorted(set(q for q in qlens if q > 0))),
+            long_seqs=long_seqs,
         ).with_cache_state(block_tables=bt, kv_lens=lens, block_size=self.block_size)
         return queries, self.key_cache, self.value_cache, meta
 

@@ -632,10 +632,13 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
 }
 
 // ------------------------------------------------------------------------------------------ host
-bool prefill_supported(int kv_format, int num_q_heads, int num_kv_heads, int head_dim) {
-    if (kv_format != EMLX_KV_FLOAT || num_kv_heads <= 0 || num_q_heads % num_kv_heads) return false;
+bool prefill_geometry_ok(int num_q_heads, int num_kv_heads, int head_dim) {
+    if (num_kv_heads <= 0 || num_q_heads % num_kv_heads) return false;
     const int G = num_q_heads / num_kv_heads;
     return (head_dim == 64 || head_dim == 128) && G <= kPfRows && kPfRows % G == 0;
+}
+bool prefill_supported(int kv_format, int num_q_heads, int num_kv_heads, int head_dim) {
+    return kv_format == EMLX_KV_FLOAT && prefill_geometry_ok(num_q_heads, num_kv_heads, head_dim);
 }
 
 // Q is [T, Hq, D]; a box of {64 columns, G heads, 128/G tokens} lands in shared memory as 128 rows in the

@@ -1375,8 +1375,20 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
 
     // the row classes a plan holds depend on the flags it was built with, not on what this pool could support
     const bool wide = (a->plan_flags & kPlanWideUnits) != 0;
-    if (wide && !prefill_supported(pool->kv_format, Hq, Hkv, D))
+    // 128-row units over an affine pool: the pages of the sequences that own them are expanded into scratch memory that
+    // the caller appended to the workspace (emlx_attn_dequant_bytes), and the 128-row kernel reads that
+    const bool expand = wide && pool->kv_format != EMLX_KV_FLOAT;
+    DequantScratch scratch{};
+    if (expand) {
+        if (!prefill_geometry_ok(Hq, Hkv, D))
+            return fail(EMLX_ERR_INVALID, "plan_flags ask for 128-row units, which this head geometry cannot run");
+        if (!dequant_scratch_layout(pool, a->num_seqs, a->max_blocks_per_seq, (uint8_t*)a->workspace + W.bytes,
+                                    a->workspace_bytes - W.bytes, &scratch))
+            return fail(EMLX_ERR_WORKSPACE, "128-row units over an affine pool need emlx_attn_dequant_bytes() of memory "
+                                            "behind the workspace");
+    } else if (wide && !prefill_supported(pool->kv_format, Hq, Hkv, D)) {
         return fail(EMLX_ERR_INVALID, "plan_flags ask for 128-row units, which this pool / head geometry cannot run");
+    }
     int lo, hi;
     class_range(G, a->max_query_len, wide, lo, hi);
     if (max(lo, class_lo) > min(hi, class_hi))
@@ -1394,13 +1406,29 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
         last_launched = c;
     }
     if (first_launched < 0) return fail(EMLX_ERR_UNSUPPORTED, "row_class_mask names no row class that this call can launch");
+    const bool class3 = hi == 3 && (a->row_class_mask == 0 || ((a->row_class_mask >> 3) & 1));
+    // the expansion comes first: the short-row kernels wait for it at their start, and the 128-row kernel, which may
+    // run beside them, starts only after all their CTAs have passed that wait
+    if (expand && class3)
+        if (int rc = launch_dequant_pages(a, pool, scratch, (cudaStream_t)stream)) return rc;
     for (int c = lo; c <= hi; ++c) {
         if (a->row_class_mask != 0 && !((a->row_class_mask >> c) & 1)) continue;  // the caller knows this class is empty
         if (c == 3) {
             // the 128-row kernel comes last; behind a short-row kernel of this call it runs beside that kernel
-            if (int rc = launch_prefill(a, pool, plan + 4 * c, plan + L.unit_seq[c], plan + L.unit_row0[c],
+            emlx_attn_args a3 = *a;
+            emlx_pool pool3 = *pool;
+            MapPair maps3 = maps;
+            if (expand) {  // the scratch pool stands in for the pool: 16-bit rows in the query dtype, its own page table
+                pool3.key_cache = scratch.k; pool3.value_cache = scratch.v;
+                pool3.k_scale = pool3.k_bias = pool3.v_scale = pool3.v_bias = nullptr;
+                pool3.num_blocks = scratch.cap; pool3.block_size = kTile;
+                pool3.kv_format = EMLX_KV_FLOAT; pool3.kv_dtype = a->q_dtype;
+                a3.block_tables = scratch.sbt;
+                if (int rc = get_maps(pool3, &maps3)) return rc;
+            }
+            if (int rc = launch_prefill(&a3, &pool3, plan + 4 * c, plan + L.unit_seq[c], plan + L.unit_row0[c],
                                         plan + L.unit_tile_lo[c], plan + L.unit_cum[c], plan + L.unit_order,
-                                        (int32_t*)((uint8_t*)a->workspace + W.counter_off[3]), short_rows_launched, maps,
+                                        (int32_t*)((uint8_t*)a->workspace + W.counter_off[3]), short_rows_launched, maps3,
                                         (cudaStream_t)stream))
                 return rc;
             continue;

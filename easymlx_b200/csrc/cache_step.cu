@@ -163,6 +163,8 @@ __global__ void __launch_bounds__(kMetaThreads) cache_step_kernel(const StepPara
     }
 
     STEP_STAMP(blockIdx.x == 0 ? 3 : 2);
+    // A step that leaves the stored lengths alone (every layer but one of an engine step) is finished here.
+    if (!p.advance) return;
     // Every load of the stored lengths in this CTA is behind us.  The CTA with the last ticket knows that this holds
     // for the whole grid and advances them.
     __syncthreads();
@@ -176,14 +178,12 @@ __global__ void __launch_bounds__(kMetaThreads) cache_step_kernel(const StepPara
         return;
     }
     __threadfence();
-    if (p.advance) {
-        for (int i = tid; i < S; i += kMetaThreads) {
-            const int slot = p.slot_ids[i];
-            if (slot < 0 || slot >= p.num_slots) continue;
-            const int q_len = q_start(i + 1) - q_start(i);
-            const int base = p.kv_lens_all[slot];
-            if ((int64_t)base + q_len <= capacity) p.kv_lens_all[slot] = base + q_len;
-        }
+    for (int i = tid; i < S; i += kMetaThreads) {
+        const int slot = p.slot_ids[i];
+        if (slot < 0 || slot >= p.num_slots) continue;
+        const int q_len = q_start(i + 1) - q_start(i);
+        const int base = p.kv_lens_all[slot];
+        if ((int64_t)base + q_len <= capacity) p.kv_lens_all[slot] = base + q_len;
     }
     if (tid == 0) *p.ticket = 0;  // ready for the next launch
     STEP_STAMP(blockIdx.x == 0 ? 4 : 3);

@@ -24,5 +24,18 @@ int launch_prefill(const emlx_attn_args* a, const emlx_pool* pool, const int32_t
                    int32_t* queue, bool wait_late, const MapPair& maps, cudaStream_t stream);
 long long* trace_buffer();  // the optional tracing buffer (NULL = off)
 bool prefill_supported(int kv_format, int num_q_heads, int num_kv_heads, int head_dim);
+// The same without the pool format: head geometry the 128-row kernel can run.
+bool prefill_geometry_ok(int num_q_heads, int num_kv_heads, int head_dim);
+
+// 128-row units over an affine pool: scratch behind the attention workspace into which the pages of the sequences
+// that own such units are expanded to 16-bit rows (csrc/dequant_pages.cu).
+struct DequantScratch {
+    int32_t* sbt;      // [S, MB] scratch page table
+    uint8_t* k;        // [cap, 128, Hkv, D] 16-bit
+    uint8_t* v;
+    int cap;           // pages: max_blocks_per_seq for each sequence the scratch was sized for
+};
+bool dequant_scratch_layout(const emlx_pool* pool, int S, int MB, uint8_t* base, size_t bytes, DequantScratch* out);
+int launch_dequant_pages(const emlx_attn_args* a, const emlx_pool* pool, const DequantScratch& sc, cudaStream_t stream);
 
 }  // namespace emlx

@@ -87,6 +87,7 @@ class _Scratch:
 
     def __init__(self):
         self.buffers: dict = {}
+        self.marks: dict = {}
 
     def get(self, device, kind: str, nbytes: int, zero: bool) -> torch.Tensor:
         key = (str(device), int(torch.cuda.current_stream(device).cuda_stream), kind)
@@ -140,7 +141,8 @@ class AttentionCall:
     def __init__(self, queries, key_cache, value_cache, block_tables, kv_lens, query_start_loc, *,
                  softmax_scale: float | None = None, sliding_window: int | None = None,
                  k_scale=None, v_scale=None, k_bias=None, v_bias=None, kernel: str | None = None,
-                 max_query_len: int = 0, plan=None, query_len_set: tp.Sequence[int] | None = None, gather=None):
+                 max_query_len: int = 0, plan=None, query_len_set: tp.Sequence[int] | None = None, gather=None,
+                 long_seqs: int = 0):
         nv.require_cuda(queries, key_cache, value_cache)
         dev = queries.device
         affine = key_cache.dtype == torch.uint8
@@ -205,24 +207,47 @@ class AttentionCall:
             # the flags decide which row classes the work list holds; the launch has to use the ones it was built with
             # (the decode entry point serves the short-row classes only: its work list is built without 128-row units)
             recommended = int(lib.emlx_attn_plan_flags(self.pool.kv_format, self.hq, hkv, self.d))
+            # An affine pool serves rows of more than 16 (prefill chunks) on the tcgen05 kernel when the caller says how
+            # many sequences have such rows: their pages are expanded to 16-bit rows in scratch memory behind the
+            # workspace, sized from that count (``long_seqs``, a host-side hint like ``query_len_set``).
+            from ...caching.paged.cache import wide_units_geometry
+            expandable = affine and self.kernel == "tiled" and int(long_seqs) > 0 and wide_units_geometry(self.hq, hkv, self.d)
+            if expandable:
+                recommended |= 1
             self.plan_flags = recommended & ~1 if self.kernel == "decode" else recommended
             usable = plan is not None and plan[1] == self.hq and plan[2] == self.window and plan[0].numel() >= self.plan_bytes
             if usable and self.kernel == "decode" and (int(plan[3]) & 1):
                 usable = False   # that work list holds 128-row units, which the short-row entry points do not serve
+            if usable and affine and (int(plan[3]) & 1) and not expandable:
+                usable = False   # 128-row units over an affine pool need the scratch, and the scratch needs the count
             if usable:
                 self.plan_buf, self.planned = plan[0], True   # built together with the batch metadata
                 self.plan_flags = int(plan[3])
             else:
                 self.plan_buf = _scratch.get(dev, "plan", self.plan_bytes, zero=False)
             a.plan_flags = self.plan_flags
-            if query_len_set and (self.plan_flags & 1) == (recommended & 1):
+            wide = bool(self.plan_flags & 1)
+            if query_len_set:
                 # the host knows which query lengths occur: launch only the kernels of those row classes
-                # (emlx_attn_row_class speaks for plans built with emlx_attn_plan_flags)
+                group = self.hq // hkv
                 for q_len in set(int(x) for x in query_len_set):
-                    cls = lib.emlx_attn_row_class(self.pool.kv_format, self.hq, hkv, self.d, q_len)
-                    if cls >= 0:
-                        a.row_class_mask |= 1 << cls
-            self.workspace = _scratch.get(dev, "workspace", ws_bytes, zero=True)
+                    rows = q_len * group
+                    if rows > 0:
+                        a.row_class_mask |= 1 << (0 if rows <= 8 else 1 if rows <= 16 else (3 if wide else 2))
+            if affine and wide:
+                # The expanded pages sit behind the workspace proper.  Where that ends depends on the batch, so this
+                # buffer is kept apart from the one ordinary calls share (whose counters must stay zero), and its own
+                # workspace part is zeroed again whenever a call of another geometry takes it over.
+                base_bytes = ws_bytes
+                ws_bytes += int(lib.emlx_attn_dequant_bytes(self.pool, self.num_seqs, int(self.block_tables.shape[1]),
+                                                            int(long_seqs)))
+                self.workspace = _scratch.get(dev, "workspace+pages", ws_bytes, zero=True)
+                key = (str(dev), int(torch.cuda.current_stream(dev).cuda_stream), "workspace+pages")
+                if _scratch.marks.get(key) not in (None, base_bytes):
+                    self.workspace[: max(base_bytes, _scratch.marks[key])].zero_()
+                _scratch.marks[key] = base_bytes
+            else:
+                self.workspace = _scratch.get(dev, "workspace", ws_bytes, zero=True)
             a.plan, a.plan_bytes = self.plan_buf.data_ptr(), self.plan_bytes
             a.workspace, a.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
 
@@ -293,6 +318,7 @@ def paged_attention(
     plan=None,
     query_len_set: tp.Sequence[int] | None = None,
     gather=None,
+    long_seqs: int = 0,
 ) -> torch.Tensor:
     """Ragged causal attention of packed queries over a paged KV pool.
 
@@ -303,7 +329,8 @@ def paged_attention(
     ``single_token_decode`` / ``max_query_len`` are host-side hints (an upper bound on the query tokens of
     any sequence) and ``query_len_set`` (the distinct query lengths of the batch); without them the kernels for every
     row class are launched and the empty ones return at once.  ``kernel`` (``None`` = automatic, ``"generic"``, ``"tiled"``, ``"decode"``, ``"prefill"``) selects
-    an entry point explicitly; tests and benchmarks use it.  ``gather`` (a ``distributed.GatherTarget``) makes the call
+    an entry point explicitly; tests and benchmarks use it.  ``long_seqs`` (the number of sequences with more than 16
+    query rows, another host hint) lets an affine pool serve those rows on the tcgen05 kernel.  ``gather`` (a ``distributed.GatherTarget``) makes the call
     store its heads into every rank's full output (KV heads sharded over GPUs) and return this rank's copy of it.
     """
     del use_metal, threadgroup_size, allow_fallback
@@ -312,7 +339,7 @@ def paged_attention(
     return AttentionCall(queries, key_cache, value_cache, block_tables, kv_lens, query_start_loc,
                          softmax_scale=softmax_scale, sliding_window=sliding_window, k_scale=k_scale, v_scale=v_scale,
                          k_bias=k_bias, v_bias=v_bias, kernel=kernel, max_query_len=max_query_len,
-                         plan=plan, query_len_set=query_len_set, gather=gather).plan().launch()
+                         plan=plan, query_len_set=query_len_set, gather=gather, long_seqs=long_seqs).plan().launch()
 
 
 @OperationRegistry.register
@@ -364,7 +391,8 @@ class UnifiedAttention(BaseOperation):
             softmax_scale=scale, sliding_window=cache_metadata.sliding_window,
             single_token_decode=cache_metadata.is_single_token_decode,
             max_query_len=int(getattr(cache_metadata, "max_query_len", 0) or 0),
-            plan=getattr(cache_metadata, "plan", None), query_len_set=getattr(cache_metadata, "query_len_set", None), **extra,
+            plan=getattr(cache_metadata, "plan", None), query_len_set=getattr(cache_metadata, "query_len_set", None),
+            long_seqs=int(getattr(cache_metadata, "long_seqs", 0) or 0), **extra,
         )
         return AttentionOutput(attention_outputs=outputs, cache_view=cache_view)
 
