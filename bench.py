@@ -403,9 +403,11 @@ class Bench:
         extra = dict(k_scale=c.k_scales, v_scale=c.v_scales, k_bias=c.k_biases, v_bias=c.v_biases) if w.bits else {}
         lens_set = sorted(set(int(x) for x in w.qlens if x > 0))
 
+        long_seqs = int((w.qlens * (w.hq // w.hkv) > 16).sum()) if w.bits else 0  # affine pools: rows for the tcgen05 route
+
         def attention_call(len_set):
             return AttentionCall(w.q, c.key_cache, c.value_cache, c.block_tables, lens_dev, qsl,
-                                 max_query_len=int(w.qlens.max()), query_len_set=len_set, **extra).plan()
+                                 max_query_len=int(w.qlens.max()), query_len_set=len_set, long_seqs=long_seqs, **extra).plan()
 
         call = attention_call(lens_set)
         ms_attn = self.graph_time(call.launch, 10, args.steps)
@@ -516,6 +518,14 @@ def run_ours(args):
             configs[name] = bench.measure(wl, f"{name}, one GPU")
             wl = None
             torch.cuda.empty_cache()
+        # beside BASELINE.json's five: the mixed batch of c3 over an 8-bit pool (prefill chunks on the tcgen05 kernel through
+        # expanded pages, decode rows on the fused-dequant kernel)
+        import dataclasses
+        wl = workloads.materialize(dataclasses.replace(workloads.describe("c3"), bits=8), dev, seed=0)
+        configs["c3_shape_affine8"] = bench.measure(wl, "c3's batch over an 8-bit affine pool (not a BASELINE.json configuration), one GPU",
+                                                    parts=False, e2e=False)
+        wl = None
+        torch.cuda.empty_cache()
 
     # ---- several GPUs: the same global batch split over the ranks (strong scaling), and c4 sharded by KV head
     strong, c4_shard = None, None
