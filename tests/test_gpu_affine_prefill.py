@@ -69,6 +69,13 @@ def test_expansion_scratch_too_small_is_reported():
     assert_close(good, ref.float().cpu().numpy())
 
 
+def test_short_verify_rows_keep_the_32_row_route():
+    # 5 tokens x 8 heads = 40 rows per sequence: expanding every page would cost more than it saves
+    w = _batch(8, qlens=(5, 5, 5, 5), prior=(3000, 500, 129, 0))
+    q, kc, vc, meta, extra = _after_write(w)
+    assert meta.long_seqs == 0 and not int(meta.plan[3]) & 1
+
+
 def test_performer_path_uses_the_hint():
     from easymlx_b200.runtime import AttentionStep
 
