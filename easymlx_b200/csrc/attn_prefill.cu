@@ -27,7 +27,13 @@ namespace emlx {
 #define PF_STAMP(cond, tile, slot) do { } while (0)
 #endif
 
-constexpr int kPfThreads = 320;  // warps 0-3 and 4-7: the two softmax warpgroups; 8: TMA producer; 9: MMA issuer
+constexpr int kPfWGs = 2;                       // softmax warpgroups: each takes kTile / kPfWGs keys of every tile
+constexpr int kPfKeys = kTile / kPfWGs;
+constexpr int kPfSoftThreads = 128 * kPfWGs;
+constexpr int kPfProducerWarp = 4 * kPfWGs;     // TMA producer
+constexpr int kPfMmaWarp = kPfProducerWarp + 1; // MMA issuer, owner of the TMEM allocation
+constexpr int kPfThreads = kPfSoftThreads + 64;
+static_assert(kPfKeys == 32 || kPfKeys == 64, "a warpgroup's keys are one or two 32-column TMEM loads");
 constexpr int kPfRows = 128;
 
 struct PrefillParams {
@@ -146,6 +152,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory matrix descriptor: 128-byte swizzle, 8-row groups 1024 bytes apart (stride offset); the leading
 // offset is the distance between 64-element blocks along the contiguous dimension of an MN-major operand.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
@@ -214,13 +229,13 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
 
     if (tid == 0) {
         ptx::mbar_init(&bars->q_full, 1);
-        ptx::mbar_init(&bars->q_tmem, 256);
-        ptx::mbar_init(&bars->item_done, 256);
-        ptx::mbar_init(&bars->p_ready[0], 256);
-        ptx::mbar_init(&bars->p_ready[1], 256);
-        ptx::mbar_init(&bars->x_full[0], 256);
-        ptx::mbar_init(&bars->x_full[1], 256);
-        ptx::mbar_init(&bars->l_full, 256);
+        ptx::mbar_init(&bars->q_tmem, kPfSoftThreads);
+        ptx::mbar_init(&bars->item_done, kPfSoftThreads);
+        ptx::mbar_init(&bars->p_ready[0], kPfSoftThreads);
+        ptx::mbar_init(&bars->p_ready[1], kPfSoftThreads);
+        ptx::mbar_init(&bars->x_full[0], kPfSoftThreads);
+        ptx::mbar_init(&bars->x_full[1], kPfSoftThreads);
+        ptx::mbar_init(&bars->l_full, kPfSoftThreads);
         for (int s = 0; s < 4; ++s) {
             ptx::mbar_init(&bars->qk_done[s], 1);
             ptx::mbar_init(&bars->pv_done[s], 1);
@@ -234,14 +249,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
         ptx::prefetch_tensormap(&kmap);
         ptx::prefetch_tensormap(&vmap);
     }
-    if (warp == 9) tmem_alloc(&bars->tmem_base, C::TMEM_COLS);
+    if (warp == kPfMmaWarp) tmem_alloc(&bars->tmem_base, C::TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = bars->tmem_base;
     const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256, tmem_Q = tmem_base + 384;
 
-    if (warp == 8) {
+    if (warp == kPfProducerWarp) {
         // ------------------------------------------------------------------ TMA producer
         uint32_t kt = 0, k = 0;
         int u, head;
@@ -374,7 +389,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             }
             kt += (uint32_t)ntiles;
         }
-    } else if (warp == 9) {
+    } else if (warp == kPfMmaWarp) {
         // ------------------------------------------------------------------ MMA issuer
         constexpr uint32_t idesc_qk = instr_desc(128, 128, BF16, false);
         constexpr uint32_t idesc_pv = instr_desc(128, D, BF16, true);
@@ -447,9 +462,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
         // waits for, drops by a sixth.
         const int wg = warp >> 2, r = tid & 127;
         const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-        float* xmax = (float*)q_smem;          // [tile parity][warpgroup][row]
-        float* xsum = xmax + 4 * kPfRows;      // [warpgroup][row]
-        constexpr int OCH = D / 64;            // 32-column chunks of O per warpgroup
+        float* xmax = (float*)q_smem;                      // [tile parity][warpgroup][row]
+        float* xsum = xmax + 2 * kPfWGs * kPfRows;         // [warpgroup][row]
+        constexpr int OCHUNKS = D / 32;                    // 32-column chunks of O, dealt over the warpgroups
         uint32_t kt = 0;
         int u, head;
         for (uint32_t k = 0;; ++k) {
@@ -497,14 +512,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 ptx::mbar_wait(&bars->qk_done[kt & 3], (kt >> 2) & 1, abort_word);
                 tc_fence_after();
                 PF_STAMP(tid == 0, kt, 0);
-                uint32_t sv[64];
-                tmem_ld32_nowait(s_addr + 64 * wg, sv);
-                tmem_ld32_nowait(s_addr + 64 * wg + 32, sv + 32);
+                uint32_t sv[kPfKeys];
+#pragma unroll
+                for (int c = 0; c < kPfKeys / 32; ++c) tmem_ld32_nowait(s_addr + kPfKeys * wg + 32 * c, sv + 32 * c);
                 tmem_wait_ld();
                 if (!interior) {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i) {
-                        const int tok = t0 + 64 * wg + i;
+                    for (int i = 0; i < kPfKeys; ++i) {
+                        const int tok = t0 + kPfKeys * wg + i;
                         if (tok < lo || tok >= hi) sv[i] = 0xff800000u;  // -inf
                     }
                 }
@@ -512,13 +527,14 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
 #pragma unroll
                 for (int i = 0; i < 8; ++i) mx8[i] = __uint_as_float(sv[i]);
 #pragma unroll
-                for (int i = 8; i < 64; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(sv[i]));
+                for (int i = 8; i < kPfKeys; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(sv[i]));
                 float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-                // the other half of the row
-                xmax[((kt & 1) * 2 + wg) * kPfRows + r] = mx;
+                // the other parts of the row
+                xmax[((kt & 1) * kPfWGs + wg) * kPfRows + r] = mx;
                 ptx::mbar_arrive(&bars->x_full[kt & 1]);
                 ptx::mbar_wait(&bars->x_full[kt & 1], (kt >> 1) & 1, abort_word);
-                mx = fmaxf(mx, xmax[((kt & 1) * 2 + (wg ^ 1)) * kPfRows + r]);
+#pragma unroll
+                for (int g = 0; g < kPfWGs; ++g) mx = fmaxf(mx, xmax[((kt & 1) * kPfWGs + g) * kPfRows + r]);
                 PF_STAMP(tid == 0, kt, 1);
                 const float m_new = mx * p.scale_log2e;
                 const bool grow = (j == 0) ? true : (m_new > m_ref + 8.0f);
@@ -535,7 +551,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                     ptx::mbar_wait(&bars->pv_done[(kt - 1) & 3], ((kt - 1) >> 2) & 1, abort_word);
                     tc_fence_after();
 #pragma unroll 1
-                    for (int c4 = wg * OCH; c4 < (wg + 1) * OCH; ++c4) {
+                    for (int c4 = wg; c4 < OCHUNKS; c4 += kPfWGs) {
                         uint32_t ov[32];
                         tmem_ld32_nowait(tmem_O + lane_addr + 32 * c4, ov);
                         tmem_wait_ld();
@@ -553,9 +569,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;
                 const float neg_m = kShift - m_safe;
                 float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
-                uint32_t packed[32];
+                uint32_t packed[kPfKeys / 2];
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
+                for (int e = 0; e < kPfKeys / 2; ++e) {
                     float p0, p1;
                     // (Sending a quarter of the exponentials through a cubic on the FMA pipe instead of the special-function
                     // unit was measured twice, on the tensor-bound mixed batch and on the bandwidth-bound spec-verify
@@ -566,8 +582,9 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                     if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
                     else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
                 }
-                // tokens [64 g, 64 g + 64) of this row, two per column, over the start of the tile's own S
-                tmem_st32(s_addr + 32 * wg, packed);
+                // this warpgroup's keys of the row, two per column, over the start of the tile's own S
+                if constexpr (kPfKeys == 64) tmem_st32(s_addr + 32 * wg, packed);
+                else tmem_st16(s_addr + 16 * wg, packed);
                 l += (ls0 + ls1) + (ls2 + ls3);
                 if (t0 + kTile > kv_len && wg < C::HALVES) {
                     // token rows of V past the sequence end are stale memory: clear them (thread r owns token r, its
@@ -590,13 +607,15 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             ptx::mbar_wait(&bars->pv_done[(kt - 1) & 3], ((kt - 1) >> 2) & 1, abort_word);
             tc_fence_after();
             ptx::mbar_wait(&bars->l_full, k & 1, abort_word);
-            l += xsum[(wg ^ 1) * kPfRows + r];
+            l = 0.f;  // every warpgroup adds the parts in the same order and gets the same sum
+#pragma unroll
+            for (int g = 0; g < kPfWGs; ++g) l += xsum[g * kPfRows + r];
             const float inv = l > 0.f ? 1.0f / l : 0.f;
             const bool store = row0 + r < R;
             const int oi = (row0 + r) / p.G, ohh = (row0 + r) - oi * p.G;
             uint4* dst = (uint4*)((uint16_t*)p.out + ((long long)(qs + oi) * p.Hq + head * p.G + ohh) * D);
 #pragma unroll 1
-            for (int c4 = wg * OCH; c4 < (wg + 1) * OCH; ++c4) {
+            for (int c4 = wg; c4 < OCHUNKS; c4 += kPfWGs) {
                 uint32_t ov[32];
                 tmem_ld32_nowait(tmem_O + lane_addr + 32 * c4, ov);
                 tmem_wait_ld();
@@ -621,7 +640,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
     }
     tc_fence_before();
     __syncthreads();
-    if (warp == 9) tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if (warp == kPfMmaWarp) tmem_dealloc(tmem_base, C::TMEM_COLS);
     if (*abort_word && tid == 0) flag_error(p.status, EMLX_DEV_WAIT_TIMEOUT);
     if (tid == 0) {
         // every draw of this CTA is behind us; the last CTA to get here puts the item counter back to zero
