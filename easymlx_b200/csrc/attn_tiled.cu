@@ -1380,6 +1380,10 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
     const bool expand = wide && pool->kv_format != EMLX_KV_FLOAT;
     DequantScratch scratch{};
     if (expand) {
+        // fp16 queries only: the expanded rows are fp16 (bf16 rows would add 2^-9 of rounding to every key), and the
+        // tensor core takes both operands of a product in one 16-bit type
+        if (a->q_dtype != EMLX_F16)
+            return fail(EMLX_ERR_UNSUPPORTED, "128-row units over an affine pool need fp16 queries");
         if (!prefill_geometry_ok(Hq, Hkv, D))
             return fail(EMLX_ERR_INVALID, "plan_flags ask for 128-row units, which this head geometry cannot run");
         if (!dequant_scratch_layout(pool, a->num_seqs, a->max_blocks_per_seq, (uint8_t*)a->workspace + W.bytes,
@@ -1418,11 +1422,11 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
             emlx_attn_args a3 = *a;
             emlx_pool pool3 = *pool;
             MapPair maps3 = maps;
-            if (expand) {  // the scratch pool stands in for the pool: 16-bit rows in the query dtype, its own page table
+            if (expand) {  // the scratch pool stands in for the pool: fp16 rows (also under bf16 queries), its own page table
                 pool3.key_cache = scratch.k; pool3.value_cache = scratch.v;
                 pool3.k_scale = pool3.k_bias = pool3.v_scale = pool3.v_bias = nullptr;
                 pool3.num_blocks = scratch.cap; pool3.block_size = kTile;
-                pool3.kv_format = EMLX_KV_FLOAT; pool3.kv_dtype = a->q_dtype;
+                pool3.kv_format = EMLX_KV_FLOAT; pool3.kv_dtype = EMLX_F16;
                 a3.block_tables = scratch.sbt;
                 if (int rc = get_maps(pool3, &maps3)) return rc;
             }

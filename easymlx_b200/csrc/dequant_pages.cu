@@ -1,5 +1,5 @@
 // Prefill chunks over an affine (8/4-bit) pool on the tcgen05 kernel: the pages of the sequences that own 128-row
-// units are first expanded to 16-bit rows in a scratch pool laid out like a float pool ([pages, 128, Hkv, D]), and the
+// units are first expanded to fp16 rows in a scratch pool laid out like a float pool ([pages, 128, Hkv, D]), and the
 // 128-row kernel then reads that pool through its usual tensor maps and a scratch page table.  A chunk re-reads its
 // context once per 128-row unit (hundreds of times, from L2), the expansion touches every page once: on a mixed batch
 // shaped like c3 with an 8-bit pool the long rows took 6.0 ms on the 32-row mma.sync kernel.
@@ -13,7 +13,7 @@ constexpr int kDqPageSlots = 32;   // pages of a sequence are dealt over this ma
 
 struct DequantParams {
     emlx_pool pool;        // the affine pool
-    void* k_out;           // scratch rows [cap, 128, Hkv, D], 16-bit
+    void* k_out;           // scratch rows [cap, 128, Hkv, D], fp16 whatever the query type
     void* v_out;
     const int32_t* bt;     // [S, MB] pages of the scheduled sequences
     const int32_t* kv_lens;
@@ -23,10 +23,9 @@ struct DequantParams {
     int S, MB, G, cap;     // cap: scratch pages (MB for each sequence the scratch was sized for)
 };
 
-template <bool BF16> __device__ __forceinline__ uint32_t pack16(float lo, float hi) {
+__device__ __forceinline__ uint32_t pack16(float lo, float hi) {
     uint32_t r;
-    if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
-    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
     return r;
 }
 
@@ -34,7 +33,7 @@ template <bool BF16> __device__ __forceinline__ uint32_t pack16(float lo, float 
 // their number, from the scratch size); blockIdx.x = (page slot, KV head): pages slot, slot + kDqPageSlots, ... of that
 // sequence, one KV head of each.  Many small CTAs: the expansion is a chain of dependent loads per item and stands
 // in front of the whole attention call.
-template <int BITS, bool BF16>
+template <int BITS>
 __global__ void __launch_bounds__(kDqThreads) dequant_pages_kernel(const DequantParams p) {
     __shared__ int s_seq;
     grid_dep_wait();   // the pool's newest rows come from the step's write, the lengths from its metadata
@@ -112,8 +111,8 @@ __global__ void __launch_bounds__(kDqThreads) dequant_pages_kernel(const Dequant
                 for (int e = 0; e < 8; ++e) x[e] = fmaf((float)((c >> (4 * e)) & 0xf), sc, bi);
             }
             uint4 o;
-            o.x = pack16<BF16>(x[0], x[1]); o.y = pack16<BF16>(x[2], x[3]);
-            o.z = pack16<BF16>(x[4], x[5]); o.w = pack16<BF16>(x[6], x[7]);
+            o.x = pack16(x[0], x[1]); o.y = pack16(x[2], x[3]);
+            o.z = pack16(x[4], x[5]); o.w = pack16(x[6], x[7]);
             *(uint4*)(kdst + ((long long)tok * Hkv + h) * D + d0) = o;
         }
         // values: codes [head][d][tok * BITS / 8] (tokens of one element contiguous); consecutive threads take
@@ -133,8 +132,8 @@ __global__ void __launch_bounds__(kDqThreads) dequant_pages_kernel(const Dequant
                 x[e] = fmaf((float)code, sc, bi);
             }
             uint4 o;
-            o.x = pack16<BF16>(x[0], x[1]); o.y = pack16<BF16>(x[2], x[3]);
-            o.z = pack16<BF16>(x[4], x[5]); o.w = pack16<BF16>(x[6], x[7]);
+            o.x = pack16(x[0], x[1]); o.y = pack16(x[2], x[3]);
+            o.z = pack16(x[4], x[5]); o.w = pack16(x[6], x[7]);
             *(uint4*)(vdst + ((long long)tok * Hkv + h) * D + d0) = o;
         }
     }
@@ -167,14 +166,8 @@ int launch_dequant_pages(const emlx_attn_args* a, const emlx_pool* pool, const D
     const int rows = sc.cap / a->max_blocks_per_seq;
     if (rows < 1) return fail(EMLX_ERR_WORKSPACE, "the scratch behind the workspace holds less than one sequence's pages");
     const dim3 grid((unsigned)(min(kDqPageSlots, a->max_blocks_per_seq) * pool->num_kv_heads), (unsigned)min(rows, 65535));
-    const bool bf16 = a->q_dtype == EMLX_BF16, four = pool->kv_format == EMLX_KV_AFFINE4;
-    if (four) {
-        if (bf16) EMLX_CUDA_OK(launch_pdl(dequant_pages_kernel<4, true>, grid, kDqThreads, 0, stream, p));
-        else EMLX_CUDA_OK(launch_pdl(dequant_pages_kernel<4, false>, grid, kDqThreads, 0, stream, p));
-    } else {
-        if (bf16) EMLX_CUDA_OK(launch_pdl(dequant_pages_kernel<8, true>, grid, kDqThreads, 0, stream, p));
-        else EMLX_CUDA_OK(launch_pdl(dequant_pages_kernel<8, false>, grid, kDqThreads, 0, stream, p));
-    }
+    if (pool->kv_format == EMLX_KV_AFFINE4) EMLX_CUDA_OK(launch_pdl(dequant_pages_kernel<4>, grid, kDqThreads, 0, stream, p));
+    else EMLX_CUDA_OK(launch_pdl(dequant_pages_kernel<8>, grid, kDqThreads, 0, stream, p));
     EMLX_LAUNCHED();
     return EMLX_OK;
 }

@@ -51,20 +51,28 @@ def test_long_rows_over_an_affine_pool_take_the_128_row_kernel(bits, hq, hkv):
 
 
 @pytest.mark.parametrize("bits", [8, 4])
-def test_long_rows_with_a_sliding_window_and_bfloat16_queries(bits):
-    # the expansion writes rows in the query dtype (bf16 here); the 128-row kernel applies the window itself
+def test_long_rows_with_a_sliding_window(bits):
+    # the 128-row kernel applies the window itself; the expansion covers every live page
     w = _batch(bits)
     q, kc, vc, meta, extra = _after_write(w)
-    qb = q.bfloat16()
-    ref = emlx.paged_attention(qb, kc, vc, meta.block_tables, meta.kv_lens, meta.query_start_loc, kernel="generic",
+    ref = emlx.paged_attention(q, kc, vc, meta.block_tables, meta.kv_lens, meta.query_start_loc, kernel="generic",
                                sliding_window=700, **extra)
-    out = emlx.paged_attention(qb, kc, vc, meta.block_tables, meta.kv_lens, meta.query_start_loc, sliding_window=700,
-                               max_query_len=meta.max_query_len, query_len_set=meta.query_len_set, long_seqs=meta.long_seqs,
-                               **extra)
-    assert out.dtype == torch.bfloat16
-    # keys and values are rounded to bf16 as well here (8 significant bits), on top of weights and output: the two
-    # bf16 results may differ by one unit in the last place (2^-6 for values in [2, 4))
-    assert_close(out, ref.float().cpu().numpy(), atol=1.6e-2, rtol=2e-2)
+    call = AttentionCall(q, kc, vc, meta.block_tables, meta.kv_lens, meta.query_start_loc, sliding_window=700,
+                         max_query_len=meta.max_query_len, query_len_set=meta.query_len_set, long_seqs=meta.long_seqs, **extra)
+    assert call.plan_flags & 1
+    assert_close(call.plan().launch(), ref.float().cpu().numpy())
+
+
+def test_bfloat16_queries_keep_the_32_row_route():
+    # the expanded rows are fp16: bf16 queries stay on the kernels that read the codes
+    w = _batch(8)
+    q, kc, vc, meta, extra = _after_write(w)
+    qb = q.bfloat16()
+    call = AttentionCall(qb, kc, vc, meta.block_tables, meta.kv_lens, meta.query_start_loc, max_query_len=meta.max_query_len,
+                         query_len_set=meta.query_len_set, long_seqs=meta.long_seqs, **extra)
+    assert not call.plan_flags & 1
+    ref = emlx.paged_attention(qb, kc, vc, meta.block_tables, meta.kv_lens, meta.query_start_loc, kernel="generic", **extra)
+    assert_close(call.plan().launch(), ref.float().cpu().numpy(), atol=8e-3, rtol=2e-2)
 
 
 def test_expansion_scratch_too_small_is_reported():

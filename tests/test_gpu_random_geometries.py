@@ -67,6 +67,10 @@ def _attend(cache, q, qlens, kv, kernel, window, hints):
         if cache.is_affine else {}
     if hints and kernel is None:
         extra.update(max_query_len=max(qlens), query_len_set=sorted(set(qlens)))
+        # with the count of sequences of more than 16 rows an affine pool serves them on the tcgen05 kernel through
+        # expanded pages (when the head geometry allows); without it they stay on the 32-row units
+        group = q.shape[1] // cache.num_kv_heads
+        extra.update(long_seqs=sum(1 for n in qlens if n * group > 16))
     return emlx.paged_attention(q, cache.key_cache, cache.value_cache, cache.block_tables,
                                 torch.tensor(kv, dtype=torch.int32, device="cuda"),
                                 emlx.build_query_start_loc(qlens, device="cuda"), sliding_window=window, kernel=kernel, **extra)
