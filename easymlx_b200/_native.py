@@ -68,7 +68,7 @@ SIGNATURES = {
     "emlx_attn_workspace_bytes": (C.c_size_t, [_I32, _I32, _I32, _I32, _I32]),
     "emlx_attn_plan": (C.c_int, [_P, _P, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _I32, _P, C.c_size_t, _P]),
     "emlx_attn_plan_flags": (C.c_int, [_I32, _I32, _I32, _I32]),
-    "emlx_attn_dequant_bytes": (C.c_size_t, [C.POINTER(Pool), _I32, _I32, _I32]),
+    "emlx_attn_dequant_bytes": (C.c_size_t, [C.POINTER(Pool), _I32, _I32, _I32, _I32, _I32, _I32]),
     "emlx_attn_unified": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
     "emlx_attn_decode": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),
     "emlx_attn_prefill": (C.c_int, [C.POINTER(AttnArgs), C.POINTER(Pool), _P]),

@@ -575,8 +575,6 @@ class PageCacheView:
         # hint is only given when those sequences average at least 64 rows.
         long_rows = [] if qlens is None else [q * group for q in qlens if q * group > 16]
         long_seqs = len(long_rows) if long_rows and sum(long_rows) >= 64 * len(long_rows) else 0
-        if queries.dtype != torch.float16:
-            long_seqs = 0  # the expanded rows are fp16 and the tensor core wants both operands in one type
         qsl, bt, lens, plan, rotated_q = self._write_batch(
             keys, values, qlens_dev, _uploaded.get(slots, dev), total,
             plan_for=(int(queries.shape[1]), window, max_q, long_seqs), advance=advance, rope=rope, queries=queries,

@@ -1380,14 +1380,9 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
     const bool expand = wide && pool->kv_format != EMLX_KV_FLOAT;
     DequantScratch scratch{};
     if (expand) {
-        // fp16 queries only: the expanded rows are fp16 (bf16 rows would add 2^-9 of rounding to every key), and the
-        // tensor core takes both operands of a product in one 16-bit type
-        if (a->q_dtype != EMLX_F16)
-            return fail(EMLX_ERR_UNSUPPORTED, "128-row units over an affine pool need fp16 queries");
         if (!prefill_geometry_ok(Hq, Hkv, D))
             return fail(EMLX_ERR_INVALID, "plan_flags ask for 128-row units, which this head geometry cannot run");
-        if (!dequant_scratch_layout(pool, a->num_seqs, a->max_blocks_per_seq, (uint8_t*)a->workspace + W.bytes,
-                                    a->workspace_bytes - W.bytes, &scratch))
+        if (!dequant_scratch_layout(pool, a, (uint8_t*)a->workspace + W.bytes, a->workspace_bytes - W.bytes, &scratch))
             return fail(EMLX_ERR_WORKSPACE, "128-row units over an affine pool need emlx_attn_dequant_bytes() of memory "
                                             "behind the workspace");
     } else if (wide && !prefill_supported(pool->kv_format, Hq, Hkv, D)) {
@@ -1428,6 +1423,11 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
                 pool3.num_blocks = scratch.cap; pool3.block_size = kTile;
                 pool3.kv_format = EMLX_KV_FLOAT; pool3.kv_dtype = EMLX_F16;
                 a3.block_tables = scratch.sbt;
+                if (a->q_dtype == EMLX_BF16) {
+                    // the tensor core takes both operands of a product in one type: fp16 copies of these sequences'
+                    // queries (made by the expansion kernel) go in, fp16 rows come out and are converted below
+                    a3.queries = scratch.q16; a3.out = scratch.out16; a3.q_dtype = EMLX_F16;
+                }
                 if (int rc = get_maps(pool3, &maps3)) return rc;
             }
             if (int rc = launch_prefill(&a3, &pool3, plan + 4 * c, plan + L.unit_seq[c], plan + L.unit_row0[c],
@@ -1435,6 +1435,8 @@ static int run_tiled(const emlx_attn_args* a, const emlx_pool* pool, void* strea
                                         (int32_t*)((uint8_t*)a->workspace + W.counter_off[3]), short_rows_launched, maps3,
                                         (cudaStream_t)stream))
                 return rc;
+            if (expand && a->q_dtype == EMLX_BF16)
+                if (int rc = launch_convert_out_rows(a, pool, scratch, (cudaStream_t)stream)) return rc;
             continue;
         }
         short_rows_launched = true;

@@ -31,11 +31,14 @@ bool prefill_geometry_ok(int num_q_heads, int num_kv_heads, int head_dim);
 // that own such units are expanded to 16-bit rows (csrc/dequant_pages.cu).
 struct DequantScratch {
     int32_t* sbt;      // [S, MB] scratch page table
+    uint8_t* q16;      // bf16 queries: fp16 copy of the queries [T, Hq, D] (rows of the sequences served), else nullptr
+    uint8_t* out16;    // and the fp16 output rows of the 128-row kernel before they are converted back
     uint8_t* k;        // [cap, 128, Hkv, D] 16-bit
     uint8_t* v;
     int cap;           // pages: max_blocks_per_seq for each sequence the scratch was sized for
 };
-bool dequant_scratch_layout(const emlx_pool* pool, int S, int MB, uint8_t* base, size_t bytes, DequantScratch* out);
+bool dequant_scratch_layout(const emlx_pool* pool, const emlx_attn_args* a, uint8_t* base, size_t bytes, DequantScratch* out);
 int launch_dequant_pages(const emlx_attn_args* a, const emlx_pool* pool, const DequantScratch& sc, cudaStream_t stream);
+int launch_convert_out_rows(const emlx_attn_args* a, const emlx_pool* pool, const DequantScratch& sc, cudaStream_t stream);
 
 }  // namespace emlx

@@ -209,11 +209,9 @@ class AttentionCall:
             recommended = int(lib.emlx_attn_plan_flags(self.pool.kv_format, self.hq, hkv, self.d))
             # An affine pool serves rows of more than 16 (prefill chunks) on the tcgen05 kernel when the caller says how
             # many sequences have such rows: their pages are expanded to 16-bit rows in scratch memory behind the
-            # workspace, sized from that count (``long_seqs``, a host-side hint like ``query_len_set``).  fp16 queries
-            # only: the expanded rows are fp16, and bf16 rows would cost accuracy (2^-9 of rounding on every key).
+            # workspace, sized from that count (``long_seqs``, a host-side hint like ``query_len_set``).
             from ...caching.paged.cache import wide_units_geometry
-            expandable = (affine and self.kernel == "tiled" and int(long_seqs) > 0 and queries.dtype == torch.float16
-                          and wide_units_geometry(self.hq, hkv, self.d))
+            expandable = affine and self.kernel == "tiled" and int(long_seqs) > 0 and wide_units_geometry(self.hq, hkv, self.d)
             if expandable:
                 recommended |= 1
             self.plan_flags = recommended & ~1 if self.kernel == "decode" else recommended
@@ -242,7 +240,7 @@ class AttentionCall:
                 # workspace part is zeroed again whenever a call of another geometry takes it over.
                 base_bytes = ws_bytes
                 ws_bytes += int(lib.emlx_attn_dequant_bytes(self.pool, self.num_seqs, int(self.block_tables.shape[1]),
-                                                            int(long_seqs)))
+                                                            int(long_seqs), self.total, self.hq, nv.dtype_code(queries.dtype)))
                 self.workspace = _scratch.get(dev, "workspace+pages", ws_bytes, zero=True)
                 key = (str(dev), int(torch.cuda.current_stream(dev).cuda_stream), "workspace+pages")
                 if _scratch.marks.get(key) not in (None, base_bytes):

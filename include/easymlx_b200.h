@@ -235,13 +235,16 @@ int emlx_attn_generic(const emlx_attn_args* args, const emlx_pool* pool, void* s
  * (128 % (Hq/Hkv) == 0, head_dim 64/128), emlx_attn_unified first expands the pages of the sequences that own 128-row
  * units (more than 16 rows) to 16-bit rows in scratch memory and runs the 128-row kernel over those; the other rows
  * read the codes as before.  The scratch sits directly behind the workspace: pass a workspace of
- * emlx_attn_workspace_bytes(...) + emlx_attn_dequant_bytes(pool, num_seqs, max_blocks_per_seq, n) bytes (zeroed once,
- * like the workspace), n = an upper bound on the sequences with more than 16 rows in the batch.  A batch that holds
+ * emlx_attn_workspace_bytes(...) + emlx_attn_dequant_bytes(pool, num_seqs, max_blocks_per_seq, n, total_tokens,
+ * num_q_heads, q_dtype) bytes (zeroed once, like the workspace), n = an upper bound on the sequences with more than
+ * 16 rows in the batch.  The expanded rows are fp16; for bf16 queries the scratch also holds fp16 copies of those
+ * sequences' queries and output rows (the tensor core multiplies operands of one type), converted on the way in and out.  A batch that holds
  * more such sequences sets EMLX_DEV_OVERFLOW in *status (their rows come out as zeros).  The expanded pages are not
  * cleaned up: a caller that reuses the buffer for a call of another geometry (whose workspace part ends elsewhere)
  * zeroes the first emlx_attn_workspace_bytes() bytes again before that call.  The reference serves a quantised cache through the
  * same route for every row kind (operations/kernels/unified_attention.py:1633-1656). */
-size_t emlx_attn_dequant_bytes(const emlx_pool* pool, int32_t num_seqs, int32_t max_blocks_per_seq, int32_t num_long_seqs);
+size_t emlx_attn_dequant_bytes(const emlx_pool* pool, int32_t num_seqs, int32_t max_blocks_per_seq, int32_t num_long_seqs,
+                               int32_t total_tokens, int32_t num_q_heads, int32_t q_dtype);
 
 /* Decode attention without caller-provided scratch.  No counterpart in the reference.
  * For embedders that cannot allocate device memory around this call: a serving process whose allocator has

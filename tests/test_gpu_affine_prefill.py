@@ -63,16 +63,22 @@ def test_long_rows_with_a_sliding_window(bits):
     assert_close(call.plan().launch(), ref.float().cpu().numpy())
 
 
-def test_bfloat16_queries_keep_the_32_row_route():
-    # the expanded rows are fp16: bf16 queries stay on the kernels that read the codes
-    w = _batch(8)
+@pytest.mark.parametrize("bits", [8, 4])
+def test_bfloat16_queries_go_through_fp16_copies(bits):
+    # the expanded rows are fp16 and the tensor core multiplies operands of one type: the queries of the sequences
+    # served by the 128-row kernel are converted to fp16 on the way in, their output rows back to bf16 on the way out
+    w = _batch(bits)
     q, kc, vc, meta, extra = _after_write(w)
     qb = q.bfloat16()
     call = AttentionCall(qb, kc, vc, meta.block_tables, meta.kv_lens, meta.query_start_loc, max_query_len=meta.max_query_len,
-                         query_len_set=meta.query_len_set, long_seqs=meta.long_seqs, **extra)
-    assert not call.plan_flags & 1
-    ref = emlx.paged_attention(qb, kc, vc, meta.block_tables, meta.kv_lens, meta.query_start_loc, kernel="generic", **extra)
-    assert_close(call.plan().launch(), ref.float().cpu().numpy(), atol=8e-3, rtol=2e-2)
+                         query_len_set=meta.query_len_set, long_seqs=meta.long_seqs, sliding_window=900, **extra)
+    assert call.plan_flags & 1
+    out = call.plan().launch()
+    assert out.dtype == torch.bfloat16
+    ref = emlx.paged_attention(qb, kc, vc, meta.block_tables, meta.kv_lens, meta.query_start_loc, kernel="generic",
+                               sliding_window=900, **extra)
+    assert_close(out, ref.float().cpu().numpy(), atol=8e-3, rtol=2e-2)
+    assert torch.equal(out, call.launch())
 
 
 def test_expansion_scratch_too_small_is_reported():
@@ -84,7 +90,8 @@ def test_expansion_scratch_too_small_is_reported():
     from easymlx_b200 import _native as nv
     lib = nv.lib()
     call.args.workspace_bytes = int(lib.emlx_attn_workspace_bytes(call.num_seqs, call.total, call.hq, call.pool.num_kv_heads, call.d)) + \
-        int(lib.emlx_attn_dequant_bytes(call.pool, call.num_seqs, int(meta.block_tables.shape[1]), 1))
+        int(lib.emlx_attn_dequant_bytes(call.pool, call.num_seqs, int(meta.block_tables.shape[1]), 1, call.total, call.hq,
+                                        nv.dtype_code(q.dtype)))
     with pytest.raises(RuntimeError, match="overflow|outgrow|capacity|status"):
         call.launch()
     torch.cuda.synchronize()
