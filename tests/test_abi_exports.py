@@ -91,3 +91,47 @@ def test_cpu_tensors_are_refused():
     with pytest.raises(RuntimeError, match="no CPU path"):
         emlx.paged_attention(q, kc, kc, torch.zeros((1, 1), dtype=torch.int32), torch.ones(1, dtype=torch.int32),
                              torch.tensor([0, 1], dtype=torch.int32))
+
+
+def test_expanded_page_scratch_size_is_host_arithmetic(built_lib):
+    """emlx_attn_dequant_bytes: scratch page table + two pools of MB pages per long sequence (+ fp16 copies of the
+    queries and the output for bf16 queries); zero when the pool is not affine or nothing is long."""
+    from easymlx_b200 import _native
+
+    lib = _native.lib()
+    pool = _native.Pool()
+    pool.num_kv_heads, pool.head_dim, pool.block_size, pool.kv_format = 8, 128, 128, 8
+    s, mb, n, t, hq = 244, 160, 4, 4096, 64
+    page = 128 * 8 * 128 * 2
+    header = -(-s * mb * 4 // 256) * 256
+    assert lib.emlx_attn_dequant_bytes(pool, s, mb, n, t, hq, _native.F16) == header + 2 * page * n * mb
+    rows = -(-t * hq * 128 * 2 // 256) * 256
+    assert lib.emlx_attn_dequant_bytes(pool, s, mb, n, t, hq, _native.BF16) == header + 2 * rows + 2 * page * n * mb
+    assert lib.emlx_attn_dequant_bytes(pool, s, mb, 0, t, hq, _native.F16) == 0
+    pool.kv_format = _native.KV_FLOAT
+    assert lib.emlx_attn_dequant_bytes(pool, s, mb, n, t, hq, _native.F16) == 0
+
+
+def test_gather_arguments_are_checked_on_the_host(built_lib):
+    from easymlx_b200 import _native
+
+    lib = _native.lib()
+    block = ctypes.create_string_buffer(512)
+    outs = (ctypes.c_void_p * 2)(ctypes.addressof(block), ctypes.addressof(block))
+    flags = (ctypes.c_void_p * 2)(ctypes.addressof(block), ctypes.addressof(block))
+    assert lib.emlx_gather_init(None, outs, flags, 2, 0, 0, None) == _native.EMLX_ERR_INVALID
+    assert lib.emlx_gather_init(ctypes.addressof(block), outs, flags, 9, 0, 0, None) == _native.EMLX_ERR_INVALID
+    assert lib.emlx_gather_init(ctypes.addressof(block), outs, flags, 2, 2, 0, None) == _native.EMLX_ERR_INVALID
+    other = ctypes.create_string_buffer(512)
+    wrong = (ctypes.c_void_p * 2)(ctypes.addressof(other), ctypes.addressof(block))
+    assert lib.emlx_gather_init(ctypes.addressof(block), outs, wrong, 2, 0, 0, None) == _native.EMLX_ERR_INVALID  # flags[rank] != own block
+    assert lib.emlx_attn_decode_gather(None, None, None, 64, 0, None) == _native.EMLX_ERR_INVALID
+
+
+def test_wide_unit_geometry_rule():
+    from easymlx_b200.caching.paged.cache import wide_units_geometry
+
+    assert wide_units_geometry(32, 8, 128) and wide_units_geometry(64, 8, 64) and wide_units_geometry(8, 8, 128)
+    assert not wide_units_geometry(24, 8, 128)      # group of 3 does not divide 128
+    assert not wide_units_geometry(32, 8, 256)      # head_dim outside {64, 128}
+    assert not wide_units_geometry(30, 8, 128)      # not a whole group
