@@ -191,6 +191,16 @@ __global__ void __launch_bounds__(kMetaThreads) cache_step_kernel(const StepPara
 
 template <typename TIn>
 static int launch_step(const StepParams& p, unsigned grid, cudaStream_t stream) {
+    // The attention kernels that follow take nearly all of an SM's shared memory.  With the same split between L1 and
+    // shared memory here, their CTAs can move in beside this kernel's last ones instead of waiting for the SM to drain
+    // and switch its configuration.
+    static DeviceOnce configured;
+    const int dev = current_device();
+    if (configured.needs(dev)) {
+        EMLX_CUDA_OK(cudaFuncSetAttribute(cache_step_kernel<TIn>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                          (int)cudaSharedmemCarveoutMaxShared));
+        configured.done(dev);
+    }
     EMLX_CUDA_OK(launch_pdl(cache_step_kernel<TIn>, grid, kMetaThreads, 0, stream, p));
     EMLX_LAUNCHED();
     return EMLX_OK;
