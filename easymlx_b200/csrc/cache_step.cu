@@ -120,8 +120,11 @@ __global__ void __launch_bounds__(kMetaThreads) cache_step_kernel(const StepPara
         const int n_tok = min(p.T, total);
         const int64_t kv_warps = p.w.has_pool ? (int64_t)n_tok * Hkv : 0;
         const int64_t q_warps = p.w.q_out != nullptr ? (int64_t)n_tok * p.w.Hq : 0;
-        const int64_t gw = (int64_t)(blockIdx.x - 1) * p.warps_per_cta + (tid >> 5);
-        if ((tid >> 5) < p.warps_per_cta && gw < kv_warps + q_warps) {
+        // a large batch has more rows than the grid has active warps: every warp then takes several (a CTA per handful
+        // of rows would repeat the scan of the query lengths a thousand times over, in several waves)
+        const int64_t all_warps = (int64_t)(gridDim.x - 1) * p.warps_per_cta;
+        for (int64_t gw = (int64_t)(blockIdx.x - 1) * p.warps_per_cta + (tid >> 5);
+             (tid >> 5) < p.warps_per_cta && gw < kv_warps + q_warps; gw += all_warps) {
             const bool is_kv = gw < kv_warps;
             const int t = is_kv ? (int)(gw / Hkv) : (int)((gw - kv_warps) / p.w.Hq);
             const int h = (int)(gw - (int64_t)t * Hkv);
@@ -265,8 +268,8 @@ extern "C" int emlx_kv_write_step(const void* queries, void* queries_out, const 
     // about two write CTAs per SM at most; at least 4 and at most 32 rows per CTA
     const int64_t per_cta = (warps + 2 * num_sms() - 1) / (2 * num_sms());
     p.warps_per_cta = (int)(per_cta < 4 ? 4 : (per_cta > kMetaThreads / 32 ? kMetaThreads / 32 : per_cta));
-    const int64_t write_ctas = (warps + p.warps_per_cta - 1) / p.warps_per_cta;
-    if (write_ctas > (1 << 20)) return fail(EMLX_ERR_UNSUPPORTED, "batch too large for the single-launch step");
+    int64_t write_ctas = (warps + p.warps_per_cta - 1) / p.warps_per_cta;
+    if (write_ctas > 2 * num_sms()) write_ctas = 2 * num_sms();  // one wave: the warps loop over the remaining rows
     const unsigned grid = 1u + (unsigned)(write_ctas > 0 ? write_ctas : 1);
     switch (in_dtype) {
         case EMLX_F16: return launch_step<__half>(p, grid, (cudaStream_t)stream);
