@@ -249,7 +249,8 @@ class AttentionCall:
             else:
                 self.workspace = _scratch.get(dev, "workspace", ws_bytes, zero=True)
             a.plan, a.plan_bytes = self.plan_buf.data_ptr(), self.plan_bytes
-            a.workspace, a.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
+            # (the size this call asked for, not the shared buffer's: the library sizes the expansion's grid from it)
+            a.workspace, a.workspace_bytes = self.workspace.data_ptr(), ws_bytes
 
     def plan(self) -> "AttentionCall":
         if self.total and self.kernel != "generic" and not self.planned:
