@@ -133,6 +133,7 @@ class PeerGather:
         from . import _native as nv
 
         lib = nv.lib()
+        self.group = group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         if self.world > MAX_PEERS:
             raise ValueError(f"at most {MAX_PEERS} ranks")
@@ -194,11 +195,11 @@ class PeerGather:
 
         lib = nv.lib()
         torch.cuda.synchronize(self.device)
-        dist.barrier()
+        dist.barrier(group=self.group)
         for p in self._mapped:
             lib.emlx_peer_buffer_close(p)
         self._mapped = []
-        dist.barrier()
+        dist.barrier(group=self.group)
         if self._own:
             lib.emlx_peer_buffer_free(self._own)
             self._own = 0
