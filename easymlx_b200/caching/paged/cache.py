@@ -144,6 +144,21 @@ class PageMetadata:
         )
 
 
+def expanded_page_hint(query_lens, group: int) -> int:
+    """Number of sequences with more than 16 query rows, or 0 when expanding their pages does not pay.
+
+    The hint sizes the scratch of the expanded-page route of an affine pool.  The route pays off for prefill chunks
+    (hundreds of rows re-read their context once per 32-row unit otherwise); for rows of a few dozen (speculative-
+    decoding verification) expanding every page costs more than it saves (measured on a spec-verify batch over an
+    8-bit pool: 1.15 ms on the 32-row units, 1.48 ms through expanded pages), so the hint is only given when those
+    sequences average at least 64 rows.  ``query_lens`` unknown on the host (``None``) gives 0.
+    """
+    if query_lens is None:
+        return 0
+    long_rows = [q * group for q in query_lens if q * group > 16]
+    return len(long_rows) if long_rows and sum(long_rows) >= 64 * len(long_rows) else 0
+
+
 class PageCacheView:
     """Block-table based KV cache backed by CUDA tensors.
 
@@ -568,13 +583,7 @@ class PageCacheView:
                 longest = int((self.kv_lens[_uploaded.get(slots, dev).long()] + qlens_dev[: len(slots)]).max().item())
             rope = rope.select(longest)
         group = max(1, int(queries.shape[1]) // self.num_kv_heads)
-        # Sequences with more than 16 query rows, for the expanded-page route of an affine pool.  The route pays off for
-        # prefill chunks (hundreds of rows re-read their context once per 32-row unit otherwise); for rows of a few
-        # dozen (speculative-decoding verification) expanding every page costs more than it saves (measured on a
-        # c5-shaped batch over an 8-bit pool: 1.15 ms on the 32-row units, 1.48 ms through expanded pages), so the
-        # hint is only given when those sequences average at least 64 rows.
-        long_rows = [] if qlens is None else [q * group for q in qlens if q * group > 16]
-        long_seqs = len(long_rows) if long_rows and sum(long_rows) >= 64 * len(long_rows) else 0
+        long_seqs = expanded_page_hint(qlens, group)
         qsl, bt, lens, plan, rotated_q = self._write_batch(
             keys, values, qlens_dev, _uploaded.get(slots, dev), total,
             plan_for=(int(queries.shape[1]), window, max_q, long_seqs), advance=advance, rope=rope, queries=queries,

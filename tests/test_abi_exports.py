@@ -135,3 +135,15 @@ def test_wide_unit_geometry_rule():
     assert not wide_units_geometry(24, 8, 128)      # group of 3 does not divide 128
     assert not wide_units_geometry(32, 8, 256)      # head_dim outside {64, 128}
     assert not wide_units_geometry(30, 8, 128)      # not a whole group
+
+
+def test_expanded_page_hint():
+    from easymlx_b200.caching.paged.cache import expanded_page_hint
+
+    assert expanded_page_hint(None, 4) == 0                     # lengths not known on the host
+    assert expanded_page_hint((1,) * 128, 8) == 0               # decode rows only
+    assert expanded_page_hint((1, 1, 512, 2030), 4) == 2        # prefill chunks beside decode rows
+    assert expanded_page_hint((5,) * 64, 4) == 0                # spec-verify: 20 rows each, expansion does not pay
+    assert expanded_page_hint((5,) * 64 + (2048,), 4) == 65     # one long chunk lifts the average above 64 rows
+    assert expanded_page_hint((4,), 4) == 0                     # 16 rows fit the short-row classes
+    assert expanded_page_hint((16,), 4) == 1                    # 64 rows
