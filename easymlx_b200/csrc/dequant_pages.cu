@@ -27,6 +27,7 @@ struct DequantParams {
     int32_t* sbt;          // [S, MB] scratch page of (sequence, page index), written for the pages expanded here
     int32_t* status;
     int S, MB, G, cap;     // cap: scratch pages (MB for each sequence the scratch was sized for)
+    int window;            // sliding window of the call (0 = off): pages wholly before every row's window are skipped
     // bf16 queries: the rows of the sequences served here are converted to fp16 for the tensor core (which wants both
     // operands of a product in one type); nullptr for fp16 queries
     const void* q_in;
@@ -107,7 +108,11 @@ __global__ void __launch_bounds__(kDqThreads) dequant_pages_kernel(const Dequant
     const int Hkv = pool.num_kv_heads, D = pool.head_dim, groups = D / 64;
     constexpr int bs = kTile;
     const int h = blockIdx.x % Hkv, slot = blockIdx.x / Hkv, slots = gridDim.x / Hkv;
-    for (int i = slot; i < p.MB && (long long)i * bs < kv_len; i += slots) {
+    // with a sliding window no row of the sequence looks before the window of its first query token (the same bound
+    // as the first tile of the work list's units), so the pages before it are neither expanded nor given an id
+    const int q_len = p.qsl[s + 1] - p.qsl[s];
+    const int first_page = p.window > 0 ? max(0, kv_len - q_len - p.window + 1) / bs : 0;
+    for (int i = first_page + slot; i < p.MB && (long long)i * bs < kv_len; i += slots) {
         const int page = p.bt[(long long)s * p.MB + i];
         // the CTA of head 0 hands out the scratch page; the CTAs of the other heads of this (sequence, page) cannot
         // wait for it, so every head takes the page's id from the same rule instead: pages are numbered per sequence
@@ -230,6 +235,7 @@ int launch_dequant_pages(const emlx_attn_args* a, const emlx_pool* pool, const D
     p.sbt = sc.sbt; p.status = a->status;
     p.S = a->num_seqs; p.MB = a->max_blocks_per_seq; p.G = a->num_q_heads / pool->num_kv_heads; p.cap = sc.cap;
     p.q_in = a->queries; p.q16 = sc.q16; p.Hq = a->num_q_heads;
+    p.window = a->sliding_window;
     // one grid row per sequence the scratch can hold (the caller sized it for an upper bound of the sequences with
     // more than 16 rows); rows beyond the batch's own count find no sequence and leave
     const int rows = dequant_grid_rows(a, sc);

@@ -52,7 +52,8 @@ def test_long_rows_over_an_affine_pool_take_the_128_row_kernel(bits, hq, hkv):
 
 @pytest.mark.parametrize("bits", [8, 4])
 def test_long_rows_with_a_sliding_window(bits):
-    # the 128-row kernel applies the window itself; the expansion covers every live page
+    # the 128-row kernel applies the window itself; the expansion leaves out the pages before the window of the
+    # sequence's first query token (17 of the 3200-key sequence's 25 pages here)
     w = _batch(bits)
     q, kc, vc, meta, extra = _after_write(w)
     ref = emlx.paged_attention(q, kc, vc, meta.block_tables, meta.kv_lens, meta.query_start_loc, kernel="generic",
