@@ -477,6 +477,10 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             const int qs = p.qsl[seq], q_len = p.qsl[seq + 1] - qs, kv_len = p.kv_lens[seq];
             const int R = q_len * p.G, ctx = kv_len - q_len;
             const int rows_here = min(kPfRows, R - row0);
+            // A warp whose 32 rows all lie past the unit's last row (spec-verify units hold 20 rows) keeps every
+            // barrier appointment but leaves the row work out: its lanes of S, P and O hold garbage that no one
+            // reads (rows of an MMA do not mix, and rows past the unit are never stored).
+            const bool dead = (warp & 3) * 32 >= rows_here;
             const int rr = min(row0 + r, R - 1), ti = rr / p.G;
             int hi = min(kv_len, ctx + ti + 1);
             int lo = p.window > 0 ? max(0, min(kv_len - 1, ctx + ti) - p.window + 1) : 0;
@@ -512,80 +516,85 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
                 ptx::mbar_wait(&bars->qk_done[kt & 3], (kt >> 2) & 1, abort_word);
                 tc_fence_after();
                 PF_STAMP(tid == 0, kt, 0);
-                uint32_t sv[kPfKeys];
+                if (dead) {
+                    ptx::mbar_arrive(&bars->x_full[kt & 1]);
+                    ptx::mbar_wait(&bars->x_full[kt & 1], (kt >> 1) & 1, abort_word);
+                } else {
+                    uint32_t sv[kPfKeys];
 #pragma unroll
-                for (int c = 0; c < kPfKeys / 32; ++c) tmem_ld32_nowait(s_addr + kPfKeys * wg + 32 * c, sv + 32 * c);
-                tmem_wait_ld();
-                if (!interior) {
+                    for (int c = 0; c < kPfKeys / 32; ++c) tmem_ld32_nowait(s_addr + kPfKeys * wg + 32 * c, sv + 32 * c);
+                    tmem_wait_ld();
+                    if (!interior) {
 #pragma unroll
-                    for (int i = 0; i < kPfKeys; ++i) {
-                        const int tok = t0 + kPfKeys * wg + i;
-                        if (tok < lo || tok >= hi) sv[i] = 0xff800000u;  // -inf
+                        for (int i = 0; i < kPfKeys; ++i) {
+                            const int tok = t0 + kPfKeys * wg + i;
+                            if (tok < lo || tok >= hi) sv[i] = 0xff800000u;  // -inf
+                        }
                     }
-                }
-                float mx8[8];  // eight independent chains instead of one of 64 dependent maxima
+                    float mx8[8];  // eight independent chains instead of one of 64 dependent maxima
 #pragma unroll
-                for (int i = 0; i < 8; ++i) mx8[i] = __uint_as_float(sv[i]);
+                    for (int i = 0; i < 8; ++i) mx8[i] = __uint_as_float(sv[i]);
 #pragma unroll
-                for (int i = 8; i < kPfKeys; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(sv[i]));
-                float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
-                // the other parts of the row
-                xmax[((kt & 1) * kPfWGs + wg) * kPfRows + r] = mx;
-                ptx::mbar_arrive(&bars->x_full[kt & 1]);
-                ptx::mbar_wait(&bars->x_full[kt & 1], (kt >> 1) & 1, abort_word);
+                    for (int i = 8; i < kPfKeys; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(sv[i]));
+                    float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+                    // the other parts of the row
+                    xmax[((kt & 1) * kPfWGs + wg) * kPfRows + r] = mx;
+                    ptx::mbar_arrive(&bars->x_full[kt & 1]);
+                    ptx::mbar_wait(&bars->x_full[kt & 1], (kt >> 1) & 1, abort_word);
 #pragma unroll
-                for (int g = 0; g < kPfWGs; ++g) mx = fmaxf(mx, xmax[((kt & 1) * kPfWGs + g) * kPfRows + r]);
-                PF_STAMP(tid == 0, kt, 1);
-                const float m_new = mx * p.scale_log2e;
-                const bool grow = (j == 0) ? true : (m_new > m_ref + 8.0f);
-                float corr = 1.0f;
-                if (grow) {
-                    const float m_tgt = fmaxf(m_ref, m_new);
-                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(corr) : "f"(m_ref - (m_tgt == -INFINITY ? 0.f : m_tgt)));
-                    m_ref = m_tgt;
-                }
-                // O is only touched when the reference maximum moves (rare): every earlier PV must be complete then.
-                // P needs no such wait: it replaces this tile's own S, which nothing else uses until QK of tile kt + 2.
-                // Each warpgroup rescales its half of the row's columns.
-                if (j > 0 && __any_sync(0xffffffffu, grow)) {
-                    ptx::mbar_wait(&bars->pv_done[(kt - 1) & 3], ((kt - 1) >> 2) & 1, abort_word);
-                    tc_fence_after();
+                    for (int g = 0; g < kPfWGs; ++g) mx = fmaxf(mx, xmax[((kt & 1) * kPfWGs + g) * kPfRows + r]);
+                    PF_STAMP(tid == 0, kt, 1);
+                    const float m_new = mx * p.scale_log2e;
+                    const bool grow = (j == 0) ? true : (m_new > m_ref + 8.0f);
+                    float corr = 1.0f;
+                    if (grow) {
+                        const float m_tgt = fmaxf(m_ref, m_new);
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(corr) : "f"(m_ref - (m_tgt == -INFINITY ? 0.f : m_tgt)));
+                        m_ref = m_tgt;
+                    }
+                    // O is only touched when the reference maximum moves (rare): every earlier PV must be complete then.
+                    // P needs no such wait: it replaces this tile's own S, which nothing else uses until QK of tile kt + 2.
+                    // Each warpgroup rescales its half of the row's columns.
+                    if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                        ptx::mbar_wait(&bars->pv_done[(kt - 1) & 3], ((kt - 1) >> 2) & 1, abort_word);
+                        tc_fence_after();
 #pragma unroll 1
-                    for (int c4 = wg; c4 < OCHUNKS; c4 += kPfWGs) {
-                        uint32_t ov[32];
-                        tmem_ld32_nowait(tmem_O + lane_addr + 32 * c4, ov);
-                        tmem_wait_ld();
+                        for (int c4 = wg; c4 < OCHUNKS; c4 += kPfWGs) {
+                            uint32_t ov[32];
+                            tmem_ld32_nowait(tmem_O + lane_addr + 32 * c4, ov);
+                            tmem_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
-                        tmem_st32(tmem_O + lane_addr + 32 * c4, ov);
+                            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * corr);
+                            tmem_st32(tmem_O + lane_addr + 32 * c4, ov);
+                        }
+                        l *= corr;
                     }
-                    l *= corr;
-                }
-                PF_STAMP(tid == 0, kt, 2);
-                // fp16 weights are stored as 2^(s - m_ref + 7): m_ref trails the true maximum by up to 2^8, so the
-                // largest stored weight is 2^15, and a key only rounds to zero below 2^-32 of the reference (the sum l
-                // carries the same factor, which cancels in O / l)
-                constexpr float kShift = BF16 ? 0.0f : 7.0f;
-                const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;
-                const float neg_m = kShift - m_safe;
-                float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
-                uint32_t packed[kPfKeys / 2];
+                    PF_STAMP(tid == 0, kt, 2);
+                    // fp16 weights are stored as 2^(s - m_ref + 7): m_ref trails the true maximum by up to 2^8, so the
+                    // largest stored weight is 2^15, and a key only rounds to zero below 2^-32 of the reference (the sum l
+                    // carries the same factor, which cancels in O / l)
+                    constexpr float kShift = BF16 ? 0.0f : 7.0f;
+                    const float m_safe = m_ref == -INFINITY ? 0.f : m_ref;
+                    const float neg_m = kShift - m_safe;
+                    float ls0 = 0.f, ls1 = 0.f, ls2 = 0.f, ls3 = 0.f;
+                    uint32_t packed[kPfKeys / 2];
 #pragma unroll
-                for (int e = 0; e < kPfKeys / 2; ++e) {
-                    float p0, p1;
-                    // (Sending a quarter of the exponentials through a cubic on the FMA pipe instead of the special-function
-                    // unit was measured twice, on the tensor-bound mixed batch and on the bandwidth-bound spec-verify
-                    // batch, and was 4-5 % slower on both: the issue slots it costs are as scarce as that unit.)
-                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2e, neg_m)));
-                    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2e, neg_m)));
-                    if (e & 1) { ls2 += p0; ls3 += p1; } else { ls0 += p0; ls1 += p1; }
-                    if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
-                    else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
+                    for (int e = 0; e < kPfKeys / 2; ++e) {
+                        float p0, p1;
+                        // (Sending a quarter of the exponentials through a cubic on the FMA pipe instead of the special-function
+                        // unit was measured twice, on the tensor-bound mixed batch and on the bandwidth-bound spec-verify
+                        // batch, and was 4-5 % slower on both: the issue slots it costs are as scarce as that unit.)
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p0) : "f"(fmaf(__uint_as_float(sv[2 * e]), p.scale_log2e, neg_m)));
+                        asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(p1) : "f"(fmaf(__uint_as_float(sv[2 * e + 1]), p.scale_log2e, neg_m)));
+                        if (e & 1) { ls2 += p0; ls3 += p1; } else { ls0 += p0; ls1 += p1; }
+                        if constexpr (BF16) asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
+                        else asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(packed[e]) : "f"(p1), "f"(p0));
+                    }
+                    // this warpgroup's keys of the row, two per column, over the start of the tile's own S
+                    if constexpr (kPfKeys == 64) tmem_st32(s_addr + 32 * wg, packed);
+                    else tmem_st16(s_addr + 16 * wg, packed);
+                    l += (ls0 + ls1) + (ls2 + ls3);
                 }
-                // this warpgroup's keys of the row, two per column, over the start of the tile's own S
-                if constexpr (kPfKeys == 64) tmem_st32(s_addr + 32 * wg, packed);
-                else tmem_st16(s_addr + 16 * wg, packed);
-                l += (ls0 + ls1) + (ls2 + ls3);
                 if (t0 + kTile > kv_len && wg < C::HALVES) {
                     // token rows of V past the sequence end are stale memory: clear them (thread r owns token r, its
                     // warpgroup the 64-element block of the row)
@@ -615,7 +624,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap qmap, const __grid_const
             const int oi = (row0 + r) / p.G, ohh = (row0 + r) - oi * p.G;
             uint4* dst = (uint4*)((uint16_t*)p.out + ((long long)(qs + oi) * p.Hq + head * p.G + ohh) * D);
 #pragma unroll 1
-            for (int c4 = wg; c4 < OCHUNKS; c4 += kPfWGs) {
+            for (int c4 = wg; c4 < OCHUNKS && !dead; c4 += kPfWGs) {
                 uint32_t ov[32];
                 tmem_ld32_nowait(tmem_O + lane_addr + 32 * c4, ov);
                 tmem_wait_ld();
